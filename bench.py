@@ -1,0 +1,309 @@
+#!/usr/bin/env python
+"""Benchmark of the qwen35moe MoE feed-forward layer on B200.
+
+One "step" is one pass of the layer over one batch of synthetic rows.  The
+workload at any N is the decode configuration (64 single-token sequences,
+Q4_K experts, skewed routing): inputs are generated from a seed, there is no
+dataset.  Prints ONE JSON line (rank 0).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME]
+  python bench.py --impl reference ...   # the CPU restatement of the reference's kernels
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+from biv_b200 import workloads as W  # noqa: E402
+
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+WEIGHT_COPIES = 4   # the timed loop rotates over this many resident copies of the layer
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return d["hbm_gbs"], d.get("bf16_tflops"), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def make_workload(name, args):
+    if name == "decode_q4k":
+        return W.decode_q4k(n=args.tokens or 64)
+    if name == "parity_q8_0":
+        return W.parity_q8_0(n=args.tokens or 16)
+    if name == "prefill_q8_0":
+        return W.prefill_q8_0(n=args.tokens or 4096)
+    if name == "ep_bf16":
+        return W.ep_bf16(n=args.tokens or 16384)
+    raise SystemExit(f"unknown workload {name}")
+
+
+def algorithmic_bytes(layer, n, experts_hit):
+    """Bytes one pass must move at least: every selected expert's weights once,
+    the shared expert, the router and gate vector, the rows in and out."""
+    return layer.weight_bytes(experts_hit) + 2 * n * layer.n_embd * 4
+
+
+def gateup_bytes(layer, n, experts_hit):
+    """The dominant kernel (gate+up with SwiGLU): gate and up matrices of every
+    selected expert and of the shared expert once, the Q8 rows of h once per
+    (token, expert) pair, the f32 mid rows written."""
+    k, e, ff = layer.n_expert_used, layer.n_embd, layer.n_ff_exp
+    w = experts_hit * (layer.gate.matrix_bytes + layer.up.matrix_bytes)
+    pairs = n * k
+    if layer.has_shared:
+        w += layer.sh_gate.matrix_bytes + layer.sh_up.matrix_bytes
+        pairs += n
+    quant = layer.gate.ty not in (W.F32, W.BF16)
+    act = n * (e + e // 32 * 8) if quant else n * e * 4
+    return w + act + pairs * ff * 4
+
+
+class ClockSampler(threading.Thread):
+    """Reads (never sets) SM clocks and throttle reasons through NVML while the
+    timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.stop_flag, self.samples, self.reasons = index, False, [], set()
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if not self.nv:
+            return
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40,
+                 "sw_thermal_slowdown": 0x20, "hw_power_brake": 0x80}
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def time_cpu(wl, budget_s=12.0, min_passes=2):
+    """The oracle (the C restatement of the reference's CPU kernels) on this
+    host's cores, same inputs; returns tokens/s and what was timed."""
+    import oracle
+    threads = oracle.max_threads()
+    level = oracle.host_level()
+    oracle.moe_forward(wl.layer, wl.h[: min(4, wl.n)], level=level, threads=threads)   # warm-up
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < min_passes or (time.perf_counter() < t_end and len(times) < 50):
+        t0 = time.perf_counter()
+        oracle.moe_forward(wl.layer, wl.h, level=level, threads=threads)
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return {"value": wl.n / med, "unit": UNIT, "cores": threads, "kind": "port",
+            "kernels": oracle.LEVEL_NAMES[level],
+            "sample": f"{len(times)} passes of the full workload ({wl.n} tokens), median; "
+                      f"best {wl.n / min(times):.1f} {UNIT}"}, med
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl = make_workload(args.workload, args)
+    import oracle
+    threads, level = oracle.max_threads(), oracle.host_level()
+    for _ in range(max(1, min(args.warmup, 2))):
+        oracle.moe_forward(wl.layer, wl.h, level=level, threads=threads)
+    steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.moe_forward(wl.layer, wl.h, level=level, threads=threads)
+    dt = (time.perf_counter() - t0) / steps
+    val = wl.n / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int8 -> int32 block dots, f32 scales",
+        "data": "synthetic",
+        "config": config_of(wl, args, 1),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
+                         "kernels": oracle.LEVEL_NAMES[level],
+                         "sample": f"{steps} passes of the full workload ({wl.n} tokens) on the "
+                                   "host cores; C restatement of biv's CPU kernels (the Rust "
+                                   "reference cannot be built here)"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def config_of(wl, args, world):
+    l = wl.layer
+    return {"workload": f"{wl.name}: {wl.n} tokens per GPU, hidden {l.n_embd}, {l.n_expert} experts "
+                        f"top-{l.n_expert_used} + shared expert, ff {l.n_ff_exp}, "
+                        f"gate/up {W.TYPE_NAMES[l.gate.ty]} down {W.TYPE_NAMES[l.down.ty]}, seed {wl.seed}",
+            "tokens_per_gpu": wl.n, "parallelism": "replicas" if world > 1 else "single",
+            "l2": f"steps rotate over {WEIGHT_COPIES} resident copies of the layer's weights "
+                  "(working set > 126 MB L2), no flush"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="decode_q4k")
+    ap.add_argument("--tokens", type=int, default=0)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from biv_b200 import capi
+    from biv_b200.moe import Moe, launch_count
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    warmup = max(args.warmup, 3)
+
+    wl = make_workload(args.workload, args)
+    layer, n = wl.layer, wl.n
+    copies = [Moe(layer, n, device=local) for _ in range(WEIGHT_COPIES)]
+    h = torch.from_numpy(wl.h).cuda()
+    out = torch.empty_like(h)
+    h_pin = torch.from_numpy(wl.h).pin_memory()
+    out_pin = torch.empty_like(h_pin).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(i):
+        copies[i % WEIGHT_COPIES].moe_(h, out, accumulate=False)
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    experts_hit = int((copies[0].tap(capi.TAP_COUNTS) > 0).sum())
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    # ---- timed region: exactly K steps between events on the launching stream
+    barrier()
+    l0 = launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    launches = launch_count() - l0
+    ms = e0.elapsed_time(e1)
+    # ---- end to end: host rows in, host delta out, through the host-buffer call
+    for i in range(3):
+        copies[i % WEIGHT_COPIES].moe_host(h_pin, out_pin)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        copies[i % WEIGHT_COPIES].moe_host(h_pin, out_pin)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    # ---- the dominant kernel alone, events around each launch (separate loop so
+    #      the events do not perturb the number above)
+    k_ms, stage_ms = [], []
+    for i in range(min(args.steps, 100)):
+        prof = copies[i % WEIGHT_COPIES].profile(h, out)
+        k_ms.append(prof["gateup"])
+        stage_ms.append(prof)
+    # keep the clocks sampler fed for long enough to see the load
+    t_end = time.perf_counter() + 0.5
+    i = 0
+    while time.perf_counter() < t_end:
+        step(i)
+        i += 1
+        if i % 64 == 0:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    sampler.stop_flag = True
+    sampler.join()
+
+    t = torch.tensor([ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    hbm_peak, _, peak_kind = load_peaks()
+    ms_step = ms / args.steps
+    value = world * n * args.steps / (ms * 1e-3)
+    kbytes = gateup_bytes(layer, n, experts_hit)
+    k_med = statistics.median(k_ms) if k_ms else None
+    achieved = kbytes / (k_med * 1e-3) / 1e9 if k_med else None
+    lbytes = algorithmic_bytes(layer, n, experts_hit)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 x int8 -> int32 block dots, f32 scales",
+        "data": "synthetic", "config": config_of(wl, args, world),
+        "roofline": {"bound": "hbm", "kernel": "experts_kernel<gate+up>", "achieved": achieved,
+                     "peak": hbm_peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+                     "frac": achieved / hbm_peak if achieved else None, "traffic": None,
+                     "bytes_per_launch": kbytes, "kernel_ms": k_med, "experts_hit": experts_hit,
+                     "stage_ms": {k: statistics.median(p[k] for p in stage_ms)
+                                  for k in stage_ms[0]} if stage_ms else None,
+                     "layer_bytes": lbytes,
+                     "layer_frac": lbytes / (ms_step * 1e-3) / 1e9 / hbm_peak},
+        "e2e": {"value": world * n * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": n * layer.n_embd * 4, "d2h_bytes_per_step": n * layer.n_embd * 4},
+        "gpu_launches": launches,
+        "clocks": sampler.summary(),
+    }
+    if not args.no_cpu:
+        cpu, _ = time_cpu(wl)
+        line["cpu_baseline"] = cpu
+    for m in copies:
+        m.close()
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

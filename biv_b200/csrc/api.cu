@@ -1,0 +1,502 @@
+// The C ABI of include/bivmoe.h: layer objects, weight upload and repack,
+// workspace, the forward sequence and the parity taps.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <atomic>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace bivmoe {
+
+static std::atomic<uint64_t> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+static thread_local std::string g_error;
+
+static int set_err(std::string* dst, int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    (dst ? *dst : g_error) = buf;
+    return code;
+}
+
+struct Arena {   // carves 256-byte aligned pieces out of one allocation
+    size_t off = 0;
+    uint8_t* base = nullptr;
+    template <class T> T* take(size_t count) {
+        size_t bytes = (count * sizeof(T) + 255) & ~(size_t)255;
+        T* p = base ? (T*)(base + off) : nullptr;
+        off += bytes;
+        return p;
+    }
+};
+
+}  // namespace bivmoe
+
+using namespace bivmoe;
+
+struct bivmoe_layer {
+    int device = 0, sm_count = 0;
+    int e = 0, n_expert = 0, k = 0, ff = 0, ff_sh = 0, max_tokens = 0;
+    bool has_shared = false;
+    DevStack gate, up, down, sh_gate, sh_up, sh_down;
+    float* router = nullptr;      // [n_expert + 1][e]; the last row is the shared-gate vector
+    float* post_norm = nullptr;   // [e]
+    float norm_eps = 0.0f;
+    uint8_t* ws_mem = nullptr;
+    size_t ws_bytes = 0, weight_bytes = 0;
+    Workspace ws{};
+    cudaStream_t own_stream = nullptr;   // bivmoe_forward_host
+    float* host_in = nullptr;            // device staging of forward_host
+    float* host_out = nullptr;
+    int last_n = 0;
+    std::string error, device_name;
+    std::vector<void*> allocs;
+};
+
+static void layout_workspace(bivmoe_layer* L, Arena& a) {
+    const size_t N = (size_t)L->max_tokens, P = N * L->k, ne = L->n_expert, e = L->e;
+    const size_t mid = std::max(L->ff, L->ff_sh);
+    Workspace& w = L->ws;
+    w.logits = a.take<float>(N * (ne + 1));
+    w.ids = a.take<int32_t>(P);
+    w.weights = a.take<float>(P);
+    w.counts = a.take<int32_t>(ne);
+    w.offsets = a.take<int32_t>(ne + 1);
+    w.order = a.take<int32_t>(P);
+    w.pos_of = a.take<int32_t>(P);
+    w.blk_counts = a.take<int32_t>(((N + 255) / 256) * ne);
+    w.grp_expert = a.take<int32_t>(ne + 1);
+    w.grp_start = a.take<int32_t>(ne + 1);
+    w.grp_count = a.take<int32_t>(ne + 1);
+    w.n_groups = a.take<int32_t>(1);
+    w.work_ctr = a.take<uint32_t>(4);
+    w.status = a.take<int32_t>(4);
+    w.act_q = a.take<int8_t>(N * e);
+    w.act_d = a.take<float>(N * e / 32);
+    w.act_s = a.take<float>(N * e / 32);
+    w.mid = a.take<float>((P + N) * mid);
+    w.pair_out = a.take<float>((P + N) * e);
+    w.h_norm = a.take<float>(N * e);
+}
+
+#define CU(call)                                                                          \
+    do {                                                                                  \
+        cudaError_t e_ = (call);                                                          \
+        if (e_ != cudaSuccess)                                                            \
+            return set_err(errp, e_ == cudaErrorMemoryAllocation ? BIVMOE_ERR_OOM         \
+                                                                 : BIVMOE_ERR_CUDA,       \
+                           "%s: %s", #call, cudaGetErrorString(e_));                      \
+    } while (0)
+
+static int check_stack(std::string* errp, const char* name, const bivmoe_experts& s, int64_t cols,
+                       int64_t rows, int64_t n, bool is_down) {
+    if (!s.data) return set_err(errp, BIVMOE_ERR_ARGUMENT, "%s: null data", name);
+    if (s.cols != cols || s.rows != rows || s.n != n)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT,
+                       "%s: shape [%lld x %lld] x %lld, expected [%lld x %lld] x %lld", name,
+                       (long long)s.rows, (long long)s.cols, (long long)s.n, (long long)rows,
+                       (long long)cols, (long long)n);
+    if (!experts_supported(s.ggml_type, (int)cols, (int)rows, is_down))
+        return set_err(errp, BIVMOE_ERR_UNSUPPORTED,
+                       "%s: no kernel for ggml type %d with %lld columns, %lld rows", name,
+                       s.ggml_type, (long long)cols, (long long)rows);
+    return BIVMOE_OK;
+}
+
+// copies one stack to the device in the device row layout
+static int upload_stack(bivmoe_layer* L, std::string* errp, const bivmoe_experts& s, DevStack* out) {
+    const int64_t grb = gguf_row_bytes(s.ggml_type, s.cols), drb = dev_row_bytes(s.ggml_type, s.cols);
+    const int64_t mat = s.rows * grb;
+    const int64_t stride = s.stride_bytes ? s.stride_bytes : mat;
+    out->ty = s.ggml_type;
+    out->cols = (int)s.cols; out->rows = (int)s.rows; out->n = (int)s.n;
+    out->row_bytes = drb;
+    out->expert_bytes = s.rows * drb;
+    const size_t dev_bytes = (size_t)(s.n * out->expert_bytes);
+    void* p = nullptr;
+    CU(cudaMalloc(&p, dev_bytes));
+    L->allocs.push_back(p);
+    L->weight_bytes += dev_bytes;
+    out->data = (uint8_t*)p;
+    const uint8_t* src = (const uint8_t*)s.data + s.offset_bytes;
+    const bool repack = s.ggml_type == BIVMOE_Q8_0 || s.ggml_type == BIVMOE_Q6_K;
+    if (!repack) {
+        CU(cudaMemcpy2D(p, (size_t)mat, src, (size_t)stride, (size_t)mat, (size_t)s.n,
+                        cudaMemcpyHostToDevice));
+        return BIVMOE_OK;
+    }
+    void* staging = nullptr;
+    CU(cudaMalloc(&staging, (size_t)(s.n * mat)));
+    cudaError_t e1 = cudaMemcpy2D(staging, (size_t)mat, src, (size_t)stride, (size_t)mat,
+                                  (size_t)s.n, cudaMemcpyHostToDevice);
+    if (e1 == cudaSuccess)
+        e1 = launch_repack(s.ggml_type, (const uint8_t*)staging, out->data, s.n * s.rows, s.cols, 0);
+    if (e1 == cudaSuccess) e1 = cudaDeviceSynchronize();
+    cudaFree(staging);
+    CU(e1);
+    return BIVMOE_OK;
+}
+
+extern "C" {
+
+const char* bivmoe_global_error(void) { return g_error.c_str(); }
+const char* bivmoe_last_error(const bivmoe_layer* layer) {
+    return layer ? layer->error.c_str() : g_error.c_str();
+}
+uint64_t bivmoe_launch_count(void) { return g_launches.load(); }
+
+void bivmoe_destroy(bivmoe_layer* L) {
+    if (!L) return;
+    cudaSetDevice(L->device);
+    for (void* p : L->allocs) cudaFree(p);
+    if (L->own_stream) cudaStreamDestroy(L->own_stream);
+    delete L;
+}
+
+int bivmoe_create(const bivmoe_desc* d, bivmoe_layer** out) {
+    std::string* errp = nullptr;
+    if (out) *out = nullptr;
+    if (!d || !out) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null descriptor or output");
+    if (d->n_embd <= 0 || d->n_expert <= 0 || d->n_ff_exp <= 0 || d->max_tokens <= 0 || !d->router)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "non-positive dimension or null router");
+    // model.rs:108-112: 1 <= n_expert_used <= n_expert
+    if (d->n_expert_used < 1 || d->n_expert_used > d->n_expert || d->n_expert_used > 32)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "n_expert_used %d outside 1..min(%d, 32)",
+                       d->n_expert_used, d->n_expert);
+    if (d->n_expert > 1024)
+        return set_err(errp, BIVMOE_ERR_UNSUPPORTED, "more than 1024 experts");
+    if (d->n_embd % 256)
+        return set_err(errp, BIVMOE_ERR_UNSUPPORTED, "n_embd %d is not a multiple of 256", d->n_embd);
+    int rc;
+    if ((rc = check_stack(errp, "ffn_gate_exps", d->gate, d->n_embd, d->n_ff_exp, d->n_expert, false)) ||
+        (rc = check_stack(errp, "ffn_up_exps", d->up, d->n_embd, d->n_ff_exp, d->n_expert, false)) ||
+        (rc = check_stack(errp, "ffn_down_exps", d->down, d->n_ff_exp, d->n_embd, d->n_expert, true)))
+        return rc;
+    if (d->gate.ggml_type != d->up.ggml_type)
+        return set_err(errp, BIVMOE_ERR_UNSUPPORTED, "gate and up of different types");
+    const bool shared = d->n_ff_shexp > 0;
+    if (shared) {
+        if (!d->sh_gate_inp) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null ffn_gate_inp_shexp");
+        if ((rc = check_stack(errp, "ffn_gate_shexp", d->sh_gate, d->n_embd, d->n_ff_shexp, 1, false)) ||
+            (rc = check_stack(errp, "ffn_up_shexp", d->sh_up, d->n_embd, d->n_ff_shexp, 1, false)) ||
+            (rc = check_stack(errp, "ffn_down_shexp", d->sh_down, d->n_ff_shexp, d->n_embd, 1, true)))
+            return rc;
+        if (d->sh_gate.ggml_type != d->sh_up.ggml_type)
+            return set_err(errp, BIVMOE_ERR_UNSUPPORTED, "shared gate and up of different types");
+    }
+    CU(cudaSetDevice(d->device));
+    cudaDeviceProp prop;
+    CU(cudaGetDeviceProperties(&prop, d->device));
+    if (prop.major != 10)
+        return set_err(errp, BIVMOE_ERR_UNSUPPORTED,
+                       "device %d is sm_%d%d; this library is built for sm_100a only", d->device,
+                       prop.major, prop.minor);
+    bivmoe_layer* L = new (std::nothrow) bivmoe_layer();
+    if (!L) return set_err(errp, BIVMOE_ERR_OOM, "host allocation failed");
+    L->device = d->device;
+    L->sm_count = prop.multiProcessorCount;
+    L->device_name = prop.name;
+    L->e = d->n_embd; L->n_expert = d->n_expert; L->k = d->n_expert_used;
+    L->ff = d->n_ff_exp; L->ff_sh = d->n_ff_shexp; L->max_tokens = d->max_tokens;
+    L->has_shared = shared;
+    auto fail = [&](int code) { g_error = g_error.empty() ? L->error : g_error; bivmoe_destroy(L); return code; };
+    if ((rc = upload_stack(L, errp, d->gate, &L->gate)) || (rc = upload_stack(L, errp, d->up, &L->up)) ||
+        (rc = upload_stack(L, errp, d->down, &L->down)))
+        return fail(rc);
+    if (shared && ((rc = upload_stack(L, errp, d->sh_gate, &L->sh_gate)) ||
+                   (rc = upload_stack(L, errp, d->sh_up, &L->sh_up)) ||
+                   (rc = upload_stack(L, errp, d->sh_down, &L->sh_down))))
+        return fail(rc);
+    auto cu_fail = [&](cudaError_t e, const char* what) {
+        set_err(errp, e == cudaErrorMemoryAllocation ? BIVMOE_ERR_OOM : BIVMOE_ERR_CUDA, "%s: %s",
+                what, cudaGetErrorString(e));
+        return fail(e == cudaErrorMemoryAllocation ? BIVMOE_ERR_OOM : BIVMOE_ERR_CUDA);
+    };
+    cudaError_t ce;
+    const size_t rbytes = (size_t)(L->n_expert + 1) * L->e * sizeof(float);
+    if ((ce = cudaMalloc((void**)&L->router, rbytes)) != cudaSuccess) return cu_fail(ce, "router");
+    L->allocs.push_back(L->router);
+    L->weight_bytes += rbytes;
+    if ((ce = cudaMemset(L->router, 0, rbytes)) != cudaSuccess) return cu_fail(ce, "router");
+    if ((ce = cudaMemcpy(L->router, d->router, (size_t)L->n_expert * L->e * 4,
+                         cudaMemcpyHostToDevice)) != cudaSuccess)
+        return cu_fail(ce, "router upload");
+    if (shared && (ce = cudaMemcpy(L->router + (size_t)L->n_expert * L->e, d->sh_gate_inp,
+                                   (size_t)L->e * 4, cudaMemcpyHostToDevice)) != cudaSuccess)
+        return cu_fail(ce, "shared gate upload");
+    Arena probe;
+    layout_workspace(L, probe);
+    L->ws_bytes = probe.off;
+    if ((ce = cudaMalloc((void**)&L->ws_mem, L->ws_bytes)) != cudaSuccess) {
+        set_err(errp, BIVMOE_ERR_OOM, "workspace of %zu bytes: %s", L->ws_bytes, cudaGetErrorString(ce));
+        return fail(BIVMOE_ERR_OOM);
+    }
+    L->allocs.push_back(L->ws_mem);
+    Arena real;
+    real.base = L->ws_mem;
+    layout_workspace(L, real);
+    if ((ce = cudaMemset(L->ws.status, 0, 16)) != cudaSuccess) return cu_fail(ce, "status");
+    if ((ce = cudaStreamCreateWithFlags(&L->own_stream, cudaStreamNonBlocking)) != cudaSuccess)
+        return cu_fail(ce, "stream");
+    if ((ce = cudaDeviceSynchronize()) != cudaSuccess) return cu_fail(ce, "upload");
+    *out = L;
+    return BIVMOE_OK;
+}
+
+int bivmoe_set_post_norm(bivmoe_layer* L, const float* w, float eps) {
+    if (!L || !w) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or weights");
+    std::string* errp = &L->error;
+    CU(cudaSetDevice(L->device));
+    if (!L->post_norm) {
+        CU(cudaMalloc((void**)&L->post_norm, (size_t)L->e * 4));
+        L->allocs.push_back(L->post_norm);
+        L->weight_bytes += (size_t)L->e * 4;
+    }
+    CU(cudaMemcpy(L->post_norm, w, (size_t)L->e * 4, cudaMemcpyHostToDevice));
+    L->norm_eps = eps;
+    return BIVMOE_OK;
+}
+
+static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int accumulate,
+                        cudaStream_t stream, cudaEvent_t* ev = nullptr) {
+    std::string* errp = &L->error;
+    if (!h || !out) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null activation pointer");
+    if (n < 0 || n > L->max_tokens)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens = %d", n, L->max_tokens);
+    L->last_n = n;
+    if (n == 0) return BIVMOE_OK;
+    LaunchCfg c{stream, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh, L->has_shared ? 1 : 0, L->sm_count};
+    c.ev = ev;
+    mark(c, EV_START);
+    CU(launch_router(c, L->router, h, L->ws));
+    mark(c, EV_ROUTER);
+    CU(launch_route_topk(c, L->ws));
+    mark(c, EV_TOPK);
+    CU(launch_sort(c, L->ws));
+    mark(c, EV_SORT);
+    if (!type_uses_f32_act(L->gate.ty) || (L->has_shared && !type_uses_f32_act(L->sh_gate.ty)))
+        CU(launch_quantize_rows(c, h, n, L->e, L->ws.act_q, L->ws.act_d, L->ws.act_s));
+    mark(c, EV_QUANT);
+    CU(launch_experts(c, h, L->gate, L->up, L->down, L->sh_gate, L->sh_up, L->sh_down, L->ws));
+    mark(c, EV_DOWN);
+    CU(launch_combine(c, L->ws, out, accumulate));
+    mark(c, EV_COMBINE);
+    return BIVMOE_OK;
+}
+
+int bivmoe_forward(bivmoe_layer* L, const float* h_dev, float* out_dev, int32_t n,
+                   int32_t accumulate, void* stream) {
+    if (!L) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer");
+    return forward_impl(L, h_dev, out_dev, n, accumulate, (cudaStream_t)stream);
+}
+
+int bivmoe_forward_profile(bivmoe_layer* L, const float* h_dev, float* out_dev, int32_t n,
+                           void* stream, float* ms) {
+    if (!L || !ms) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or buffer");
+    std::string* errp = &L->error;
+    cudaEvent_t ev[EV_COUNT];
+    for (int i = 0; i < EV_COUNT; i++) CU(cudaEventCreate(&ev[i]));
+    int rc = forward_impl(L, h_dev, out_dev, n, 0, (cudaStream_t)stream, ev);
+    cudaError_t ce = cudaEventSynchronize(ev[EV_COMBINE]);
+    for (int i = 1; i < EV_COUNT && ce == cudaSuccess && !rc; i++)
+        ce = cudaEventElapsedTime(&ms[i - 1], ev[i - 1], ev[i]);
+    for (int i = 0; i < EV_COUNT; i++) cudaEventDestroy(ev[i]);
+    if (rc) return rc;
+    CU(ce);
+    return BIVMOE_OK;
+}
+
+static int read_status(bivmoe_layer* L, cudaStream_t stream) {
+    std::string* errp = &L->error;
+    int32_t st[4] = {0, 0, 0, 0};
+    CU(cudaMemcpyAsync(st, L->ws.status, sizeof st, cudaMemcpyDeviceToHost, stream));
+    CU(cudaStreamSynchronize(stream));
+    if (st[0]) {
+        cudaMemsetAsync(L->ws.status, 0, 16, stream);
+        return set_err(errp, st[0], "a device-side bounded wait gave up (status %d)", st[0]);
+    }
+    return BIVMOE_OK;
+}
+
+int bivmoe_forward_host(bivmoe_layer* L, const float* h_host, float* out_host, int32_t n) {
+    if (!L) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer");
+    std::string* errp = &L->error;
+    if (!h_host || !out_host) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null host pointer");
+    if (n < 0 || n > L->max_tokens)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens = %d", n, L->max_tokens);
+    CU(cudaSetDevice(L->device));
+    if (!L->host_in) {
+        const size_t bytes = (size_t)L->max_tokens * L->e * 4;
+        CU(cudaMalloc((void**)&L->host_in, bytes));
+        L->allocs.push_back(L->host_in);
+        CU(cudaMalloc((void**)&L->host_out, bytes));
+        L->allocs.push_back(L->host_out);
+        L->ws_bytes += 2 * bytes;
+    }
+    const size_t bytes = (size_t)n * L->e * 4;
+    cudaStream_t s = L->own_stream;
+    CU(cudaMemcpyAsync(L->host_in, h_host, bytes, cudaMemcpyHostToDevice, s));
+    int rc = forward_impl(L, L->host_in, L->host_out, n, 0, s);
+    if (rc) return rc;
+    CU(cudaMemcpyAsync(out_host, L->host_out, bytes, cudaMemcpyDeviceToHost, s));
+    return read_status(L, s);
+}
+
+int bivmoe_forward_stack(bivmoe_layer* const* layers, int32_t n_layers, float* x_dev, int32_t n,
+                         void* stream) {
+    if (!layers || n_layers <= 0 || !layers[0])
+        return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "no layers");
+    for (int l = 0; l < n_layers; l++) {
+        bivmoe_layer* L = layers[l];
+        std::string* errp = L ? &L->error : nullptr;
+        if (!L || !L->post_norm)
+            return set_err(errp, BIVMOE_ERR_ARGUMENT, "layer %d has no post_norm weights", l);
+        if (n < 0 || n > L->max_tokens)
+            return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens", n);
+        if (n == 0) continue;
+        LaunchCfg c{(cudaStream_t)stream, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh,
+                    L->has_shared ? 1 : 0, L->sm_count};
+        CU(launch_rms_norm(c, x_dev, L->post_norm, L->norm_eps, L->ws.h_norm));
+        int rc = forward_impl(L, L->ws.h_norm, x_dev, n, 1, (cudaStream_t)stream);
+        if (rc) return rc;
+    }
+    return BIVMOE_OK;
+}
+
+// ---------------------------------------------------------------------------
+// taps
+
+static int copy_out(bivmoe_layer* L, void* dst, const void* src, size_t want, size_t have) {
+    std::string* errp = &L->error;
+    if (want != have)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "tap buffer of %zu bytes, expected %zu", want, have);
+    CU(cudaMemcpy(dst, src, have, cudaMemcpyDeviceToHost));
+    return BIVMOE_OK;
+}
+
+int bivmoe_tap(bivmoe_layer* L, int32_t which, void* dst, size_t bytes) {
+    if (!L || !dst) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or buffer");
+    std::string* errp = &L->error;
+    CU(cudaSetDevice(L->device));
+    CU(cudaDeviceSynchronize());
+    const size_t n = (size_t)L->last_n, k = L->k, ne = L->n_expert, e = L->e, P = n * k;
+    const size_t mid = std::max(L->ff, L->ff_sh);
+    const Workspace& w = L->ws;
+    switch (which) {
+        case BIVMOE_TAP_LOGITS:
+        case BIVMOE_TAP_SHARED_GATE: {
+            std::vector<float> tmp(n * (ne + 1));
+            CU(cudaMemcpy(tmp.data(), w.logits, tmp.size() * 4, cudaMemcpyDeviceToHost));
+            const bool lg = which == BIVMOE_TAP_LOGITS;
+            if (bytes != (lg ? n * ne : n) * 4)
+                return set_err(errp, BIVMOE_ERR_ARGUMENT, "tap buffer size mismatch");
+            float* o = (float*)dst;
+            for (size_t t = 0; t < n; t++) {
+                if (lg) memcpy(o + t * ne, tmp.data() + t * (ne + 1), ne * 4);
+                else o[t] = tmp[t * (ne + 1) + ne];
+            }
+            return BIVMOE_OK;
+        }
+        case BIVMOE_TAP_IDS: return copy_out(L, dst, w.ids, bytes, P * 4);
+        case BIVMOE_TAP_WEIGHTS: return copy_out(L, dst, w.weights, bytes, P * 4);
+        case BIVMOE_TAP_COUNTS: return copy_out(L, dst, w.counts, bytes, ne * 4);
+        case BIVMOE_TAP_ORDER: return copy_out(L, dst, w.order, bytes, P * 4);
+        case BIVMOE_TAP_ACT_Q: return copy_out(L, dst, w.act_q, bytes, n * e);
+        case BIVMOE_TAP_ACT_D: return copy_out(L, dst, w.act_d, bytes, n * e / 32 * 4);
+        case BIVMOE_TAP_ACT_S: return copy_out(L, dst, w.act_s, bytes, n * e / 32 * 4);
+        case BIVMOE_TAP_MID:
+        case BIVMOE_TAP_PAIR_OUT: {
+            const bool m = which == BIVMOE_TAP_MID;
+            const size_t width = m ? (size_t)L->ff : e, stride = m ? mid : e;
+            if (bytes != P * width * 4)
+                return set_err(errp, BIVMOE_ERR_ARGUMENT, "tap buffer size mismatch");
+            std::vector<float> tmp(P * stride);
+            std::vector<int32_t> pos(P);
+            CU(cudaMemcpy(tmp.data(), m ? w.mid : w.pair_out, tmp.size() * 4, cudaMemcpyDeviceToHost));
+            CU(cudaMemcpy(pos.data(), w.pos_of, P * 4, cudaMemcpyDeviceToHost));
+            for (size_t p = 0; p < P; p++)
+                memcpy((float*)dst + p * width, tmp.data() + (size_t)pos[p] * stride, width * 4);
+            return BIVMOE_OK;
+        }
+        case BIVMOE_TAP_SHARED_OUT:
+            if (!L->has_shared) return set_err(errp, BIVMOE_ERR_ARGUMENT, "no shared expert");
+            return copy_out(L, dst, w.pair_out + P * e, bytes, n * e * 4);
+        default: return set_err(errp, BIVMOE_ERR_ARGUMENT, "unknown tap %d", which);
+    }
+}
+
+int bivmoe_tap_block_dots(bivmoe_layer* L, int32_t matrix, int32_t expert, int32_t row,
+                          int32_t act_row, int32_t* out) {
+    if (!L || !out) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or buffer");
+    std::string* errp = &L->error;
+    CU(cudaSetDevice(L->device));
+    CU(cudaDeviceSynchronize());
+    const DevStack* stacks[6] = {&L->gate, &L->up, &L->down, &L->sh_gate, &L->sh_up, &L->sh_down};
+    if (matrix < 0 || matrix > 5 || (matrix >= 3 && !L->has_shared))
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "matrix %d", matrix);
+    const DevStack& m = *stacks[matrix];
+    const bool shared = matrix >= 3, is_down = matrix % 3 == 2;
+    const int n = L->last_n, P = n * L->k;
+    if (expert < 0 || expert >= m.n || row < 0 || row >= m.rows || act_row < 0 ||
+        act_row >= (is_down && !shared ? P : n))
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "index out of range");
+    if (type_uses_f32_act(m.ty))
+        return set_err(errp, BIVMOE_ERR_UNSUPPORTED, "type %d has no integer block dots", m.ty);
+    const int nb = m.cols / 32;
+    int8_t* xq = nullptr;
+    int32_t* dots = nullptr;
+    float* ds = nullptr;
+    CU(cudaMalloc((void**)&xq, m.cols));
+    CU(cudaMalloc((void**)&dots, (size_t)nb * 4));
+    CU(cudaMalloc((void**)&ds, (size_t)nb * 8));
+    cudaError_t ce = cudaSuccess;
+    const int8_t* act = nullptr;
+    if (!is_down) {
+        act = L->ws.act_q + (size_t)act_row * L->e;
+    } else {
+        // the Q8 row of the mid vector the down product consumed
+        int32_t pos = P + act_row;
+        if (!shared)
+            ce = cudaMemcpy(&pos, L->ws.pos_of + act_row, 4, cudaMemcpyDeviceToHost);
+        LaunchCfg c{0, 1, L->k, L->e, L->n_expert, L->ff, L->ff_sh, 0, L->sm_count};
+        if (ce == cudaSuccess)
+            ce = launch_quantize_rows(c, L->ws.mid + (size_t)pos * std::max(L->ff, L->ff_sh), 1,
+                                      m.cols, xq, ds, ds + nb);
+        act = xq;
+    }
+    if (ce == cudaSuccess)
+        ce = launch_block_dots(m.ty, m.data + (size_t)expert * m.expert_bytes + (size_t)row * m.row_bytes,
+                               m.cols, act, dots, 0);
+    if (ce == cudaSuccess) ce = cudaMemcpy(out, dots, (size_t)nb * 4, cudaMemcpyDeviceToHost);
+    cudaFree(xq); cudaFree(dots); cudaFree(ds);
+    CU(ce);
+    return BIVMOE_OK;
+}
+
+int bivmoe_numerics(const bivmoe_layer* L, char* buf, size_t len) {
+    if (!L || !buf || !len) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or buffer");
+    snprintf(buf, len,
+             "kind=cuda device=%s sms=%d repack=v%d experts=dp4a-lane-per-row/bulk-copy-staged "
+             "router=f32-avx2-order combine=ordered-fma types=%d/%d/%d",
+             L->device_name.c_str(), L->sm_count, kRepackVersion, L->gate.ty, L->up.ty, L->down.ty);
+    return BIVMOE_OK;
+}
+
+int bivmoe_memory(const bivmoe_layer* L, uint64_t* weight_bytes, uint64_t* workspace_bytes) {
+    if (!L) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer");
+    if (weight_bytes) *weight_bytes = L->weight_bytes;
+    if (workspace_bytes) *workspace_bytes = L->ws_bytes;
+    return BIVMOE_OK;
+}
+
+}  // extern "C"

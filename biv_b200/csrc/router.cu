@@ -1,0 +1,249 @@
+// Router product, softmax / top-k / renormalisation, and the stable
+// token-to-expert sort.  Reference: engine/src/model.rs:259-268 (route),
+// 864-873 (logits and per-expert lists), engine/src/ops.rs:192-201 (softmax),
+// engine/src/quant.rs:1177-1206 (the AVX2 f32 dot whose summation order the
+// logits kernel reproduces bit for bit).
+#include "common.cuh"
+
+namespace bivmoe {
+
+// ---------------------------------------------------------------------------
+// logits[t][r] = dot(W[r], h[t]) for the n_expert router rows plus, as row
+// n_expert, the shared expert's gate vector.
+//
+// The reference's x86 dot keeps 4 accumulators of 8 lanes: element i goes to
+// lane (i mod 32) of a 32-wide accumulator set, with one fused multiply-add per
+// element in ascending i, and the 32 lanes are then summed as
+// (k0+k1)+(k2+k3) per lane j (lane = 8k+j), then j with j+4, j+2, j+1.  A warp
+// lane per accumulator lane and the butterfly 8,16,4,2,1 give the same bits.
+constexpr int RT_ROWS = 4, RT_TOKS = 4, RT_WARPS = 4;
+
+__global__ void __launch_bounds__(RT_WARPS * 32)
+router_logits_kernel(const float* __restrict__ W, const float* __restrict__ h,
+                     float* __restrict__ logits, int n, int e, int n_rows) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r0 = blockIdx.x * RT_ROWS;
+    const int t0 = (blockIdx.y * RT_WARPS + warp) * RT_TOKS;
+    if (t0 >= n) return;
+    const float* wp[RT_ROWS];
+    const float* xp[RT_TOKS];
+#pragma unroll
+    for (int r = 0; r < RT_ROWS; r++) wp[r] = W + (size_t)min(r0 + r, n_rows - 1) * e + lane;
+#pragma unroll
+    for (int t = 0; t < RT_TOKS; t++) xp[t] = h + (size_t)min(t0 + t, n - 1) * e + lane;
+    float acc[RT_ROWS][RT_TOKS] = {};
+    for (int i = 0; i < e; i += 32) {
+        float w[RT_ROWS], x[RT_TOKS];
+#pragma unroll
+        for (int r = 0; r < RT_ROWS; r++) w[r] = __ldg(wp[r] + i);
+#pragma unroll
+        for (int t = 0; t < RT_TOKS; t++) x[t] = __ldg(xp[t] + i);
+#pragma unroll
+        for (int r = 0; r < RT_ROWS; r++)
+#pragma unroll
+            for (int t = 0; t < RT_TOKS; t++) acc[r][t] = fmaf(w[r], x[t], acc[r][t]);
+    }
+#pragma unroll
+    for (int r = 0; r < RT_ROWS; r++)
+#pragma unroll
+        for (int t = 0; t < RT_TOKS; t++) {
+            float v = acc[r][t];
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 8));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 16));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+            if (lane == 0 && r0 + r < n_rows && t0 + t < n)
+                logits[(size_t)(t0 + t) * n_rows + r0 + r] = v;
+        }
+}
+
+cudaError_t launch_router(const LaunchCfg& c, const float* router_dev, const float* h,
+                          const Workspace& ws) {
+    int n_rows = c.n_expert + 1;
+    dim3 grid((n_rows + RT_ROWS - 1) / RT_ROWS, (c.n + RT_WARPS * RT_TOKS - 1) / (RT_WARPS * RT_TOKS));
+    router_logits_kernel<<<grid, RT_WARPS * 32, 0, c.stream>>>(router_dev, h, ws.logits, c.n, c.e,
+                                                               n_rows);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// One warp per token: softmax in the reference's order (max, exp, sequential
+// sum, multiply by 1/sum), the k best by (probability descending, expert id
+// ascending), weights p / max(sum of the k in rank order, 2^-14).
+constexpr int TK_WARPS = 4, TK_MAX_EXPERTS = 1024, TK_MAX_K = 32;
+
+__global__ void __launch_bounds__(TK_WARPS * 32)
+route_topk_kernel(const float* __restrict__ logits, int32_t* __restrict__ ids,
+                  float* __restrict__ weights, int n, int n_expert, int k) {
+    extern __shared__ float tk_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * TK_WARPS + warp;
+    if (t >= n) return;
+    float* p = tk_smem + (size_t)warp * n_expert;
+    const float* l = logits + (size_t)t * (n_expert + 1);
+    float mx = -INFINITY;
+    for (int i = lane; i < n_expert; i += 32) mx = fmaxf(mx, l[i]);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    for (int i = lane; i < n_expert; i += 32) p[i] = expf(__fsub_rn(l[i], mx));
+    __syncwarp();
+    float sum = 0.0f;
+    if (lane == 0)
+        for (int i = 0; i < n_expert; i++) sum = __fadd_rn(sum, p[i]);
+    sum = __shfl_sync(0xffffffffu, sum, 0);
+    const float inv = __fdiv_rn(1.0f, sum);
+    for (int i = lane; i < n_expert; i += 32) p[i] = __fmul_rn(p[i], inv);
+    __syncwarp();
+    float sel_p = 0.0f;   // lane j keeps the j-th selection
+    int sel_id = 0;
+    for (int j = 0; j < k; j++) {
+        float bp = -1.0f;
+        int bi = 0x7fffffff;
+        for (int i = lane; i < n_expert; i += 32) {
+            float v = p[i];
+            if (v > bp) { bp = v; bi = i; }   // ascending i: the lower id wins ties
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            float op = __shfl_xor_sync(0xffffffffu, bp, o);
+            int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (op > bp || (op == bp && oi < bi)) { bp = op; bi = oi; }
+        }
+        if (lane == j) { sel_p = bp; sel_id = bi; }
+        if (lane == 0) p[bi] = -2.0f;         // taken
+        __syncwarp();
+    }
+    float tot = 0.0f;
+    for (int j = 0; j < k; j++) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, sel_p, j));
+    tot = fmaxf(tot, 1.0f / 16384.0f);
+    if (lane < k) {
+        ids[(size_t)t * k + lane] = sel_id;
+        weights[(size_t)t * k + lane] = __fdiv_rn(sel_p, tot);
+    }
+}
+
+cudaError_t launch_route_topk(const LaunchCfg& c, const Workspace& ws) {
+    if (c.n_expert > TK_MAX_EXPERTS || c.k > TK_MAX_K) return cudaErrorInvalidValue;
+    size_t smem = (size_t)TK_WARPS * c.n_expert * sizeof(float);
+    route_topk_kernel<<<(c.n + TK_WARPS - 1) / TK_WARPS, TK_WARPS * 32, smem, c.stream>>>(
+        ws.logits, ws.ids, ws.weights, c.n, c.n_expert, c.k);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Stable grouping of the n*k (token, expert) pairs by expert: inside an expert
+// pairs keep ascending pair index t*k+j, which is the order the reference
+// pushes them in (model.rs:867-873; Metal moe_sort, kernels.metal:1723-1729).
+// A block owns SORT_TOKENS consecutive tokens.  Phase 1 counts per (block,
+// expert); phase 2 turns the counts into bases (exclusive over blocks, then
+// over experts) and builds the list of non-empty groups; phase 3 lets one
+// thread per expert walk its block's pairs in order.  With one block the three
+// phases run in a single launch.
+constexpr int SORT_TOKENS = 256, SORT_THREADS = 256;
+
+__device__ void sort_load_ids(const int32_t* ids, int pair0, int npairs, uint16_t* s_ids) {
+    for (int i = threadIdx.x; i < npairs; i += blockDim.x) s_ids[i] = (uint16_t)ids[pair0 + i];
+}
+__device__ void sort_hist(const uint16_t* s_ids, int npairs, int n_expert, int* s_cnt) {
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) s_cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < npairs; i += blockDim.x) atomicAdd(&s_cnt[s_ids[i]], 1);
+    __syncthreads();
+}
+// one block: bases over blocks and experts, the group list, counters reset
+__device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, int k,
+                          int has_shared) {
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+        int run = 0;
+        for (int b = 0; b < nblk; b++) {
+            int c = ws.blk_counts[(size_t)b * n_expert + e];
+            ws.blk_counts[(size_t)b * n_expert + e] = run;
+            run += c;
+        }
+        ws.counts[e] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0, g = 0;
+        if (has_shared) {   // the heaviest group first
+            ws.grp_expert[g] = n_expert;
+            ws.grp_start[g] = n * k;
+            ws.grp_count[g] = n;
+            g++;
+        }
+        for (int e = 0; e < n_expert; e++) {
+            int c = ws.counts[e];
+            ws.offsets[e] = off;
+            if (c) {
+                ws.grp_expert[g] = e;
+                ws.grp_start[g] = off;
+                ws.grp_count[g] = c;
+                g++;
+            }
+            off += c;
+        }
+        ws.offsets[n_expert] = off;
+        *ws.n_groups = g;
+        for (int i = 0; i < 4; i++) ws.work_ctr[i] = 0;
+    }
+    __syncthreads();
+}
+__device__ void sort_scatter(const Workspace& ws, const uint16_t* s_ids, int pair0, int npairs,
+                             int n_expert, int blk) {
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+        int pos = ws.offsets[e] + ws.blk_counts[(size_t)blk * n_expert + e];
+        for (int i = 0; i < npairs; i++)
+            if (s_ids[i] == e) {
+                ws.order[pos] = pair0 + i;
+                ws.pos_of[pair0 + i] = pos;
+                pos++;
+            }
+    }
+}
+
+__global__ void __launch_bounds__(SORT_THREADS)
+sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int phase) {
+    extern __shared__ uint8_t sort_smem[];
+    uint16_t* s_ids = (uint16_t*)sort_smem;
+    int* s_cnt = (int*)(sort_smem + (((size_t)SORT_TOKENS * k * 2 + 15) & ~(size_t)15));
+    const int nblk = (n + SORT_TOKENS - 1) / SORT_TOKENS;
+    const int blk = blockIdx.x;
+    const int tok0 = blk * SORT_TOKENS, ntok = min(SORT_TOKENS, n - tok0);
+    const int pair0 = tok0 * k, npairs = ntok * k;
+    if (phase == 0 || phase == 1) {
+        sort_load_ids(ws.ids, pair0, npairs, s_ids);
+        __syncthreads();
+        sort_hist(s_ids, npairs, n_expert, s_cnt);
+        for (int e = threadIdx.x; e < n_expert; e += blockDim.x)
+            ws.blk_counts[(size_t)blk * n_expert + e] = s_cnt[e];
+        __syncthreads();
+    }
+    if (phase == 0 || phase == 2) sort_scan(ws, n_expert, nblk, n, k, has_shared);
+    if (phase == 0 || phase == 3) {
+        if (phase == 3) {
+            sort_load_ids(ws.ids, pair0, npairs, s_ids);
+            __syncthreads();
+        }
+        sort_scatter(ws, s_ids, pair0, npairs, n_expert, blk);
+    }
+}
+
+cudaError_t launch_sort(const LaunchCfg& c, const Workspace& ws) {
+    const int nblk = (c.n + SORT_TOKENS - 1) / SORT_TOKENS;
+    size_t smem = (((size_t)SORT_TOKENS * c.k * 2 + 15) & ~(size_t)15) + (size_t)c.n_expert * 4;
+    if (nblk == 1) {
+        sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, 0);
+        count_launch();
+    } else {
+        sort_kernel<<<nblk, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, 1);
+        sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, 2);
+        sort_kernel<<<nblk, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, 3);
+        count_launch(3);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace bivmoe

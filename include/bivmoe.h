@@ -1,0 +1,181 @@
+/*
+ * bivmoe: the qwen35moe mixture-of-experts feed-forward layer of the biv
+ * inference engine as hand-written CUDA for NVIDIA B200 (sm_100a), behind a C ABI.
+ *
+ * The reference engine (vincenthz/biv) has no per-operator plugin point: its
+ * only backend seam is the whole-model trait set `Engine` / `Session` / `Batch`
+ * (engine/src/engine.rs:15-60, 120-170, 282-323), implemented by the CPU
+ * graph (`Model`) and by `MetalEngine`.  A CUDA backend is a third
+ * implementation of those traits whose feed-forward step - the point where
+ * the CPU backend calls `Model::moe` (engine/src/model.rs:788-790, 861-898)
+ * and the Metal backend calls `encode_moe` (engine/src/metal/mod.rs:2095-2109,
+ * 2140-2266) - calls this library once per layer.  Every entry point below
+ * names the reference interface it stands in for.
+ *
+ * Conventions: every function returns a status (0 = ok); nothing aborts,
+ * throws across the boundary or traps the device.  A layer handle is not
+ * thread-safe; distinct handles may be driven from distinct host threads.
+ * Host pointers passed to `bivmoe_create` stay owned by the caller and may be
+ * freed after it returns (the engine's GGUF mmap, src/lib.rs:74-84).
+ */
+#ifndef BIVMOE_H
+#define BIVMOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define BIVMOE_API __attribute__((visibility("default")))
+#else
+#define BIVMOE_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  The Rust side maps them onto the reference's error enum
+ * (engine/src/error.rs:36-40 NoKernel, 53-56 OutOfMemory, 67-68 Backend). */
+enum {
+    BIVMOE_OK = 0,
+    BIVMOE_ERR_ARGUMENT = 1,    /* null pointer, size mismatch, n > max_tokens: Error::Backend */
+    BIVMOE_ERR_UNSUPPORTED = 2, /* a ggml type or shape without a kernel: Error::NoKernel */
+    BIVMOE_ERR_OOM = 3,         /* device allocation failed: Error::OutOfMemory{bytes} */
+    BIVMOE_ERR_CUDA = 4,        /* a CUDA runtime call failed: Error::Backend */
+    BIVMOE_ERR_NCCL = 5,        /* a collective failed or NCCL is not loadable: Error::Backend */
+    BIVMOE_ERR_TIMEOUT = 6,     /* a bounded device-side wait gave up: Error::Backend */
+};
+
+/* ggml type ids as stored in GGUF files (engine/src/quant.rs:30-48). */
+enum {
+    BIVMOE_F32 = 0,
+    BIVMOE_Q8_0 = 8,
+    BIVMOE_Q4_K = 12,
+    BIVMOE_Q5_K = 13,
+    BIVMOE_Q6_K = 14,
+    BIVMOE_BF16 = 30,
+};
+
+/* A stack of same-shaped weight matrices, one per expert, inside one GGUF
+ * tensor.  Field for field the reference's `Experts` (engine/src/model.rs:
+ * 190-204): expert `i` starts at `data + i*stride_bytes + offset_bytes`
+ * (model.rs:212-216), so the up half of a fused `ffn_gate_up_exps` tensor
+ * (model.rs:389-399) is addressed without a copy.  `stride_bytes` 0 means
+ * tightly packed (`rows * row_size(cols)`). */
+typedef struct bivmoe_experts {
+    int32_t ggml_type;
+    int32_t reserved;
+    int64_t cols;         /* elements per row (the product's inner dimension) */
+    int64_t rows;         /* rows per expert */
+    int64_t n;            /* experts in the stack (1 for the shared expert) */
+    const void* data;     /* host memory, GGUF block layout */
+    int64_t stride_bytes;
+    int64_t offset_bytes;
+} bivmoe_experts;
+
+/* Everything `Loader::ffn` hands to the CPU and Metal backends for one layer
+ * (engine/src/model.rs:377-421; `Moe` 230-237, `SharedExpert` 221-227,
+ * `MoeConfig` 57-66; Metal's `gpu_layer`, engine/src/metal/mod.rs:584-605). */
+typedef struct bivmoe_desc {
+    int32_t n_embd;
+    int32_t n_expert;
+    int32_t n_expert_used;
+    int32_t n_ff_exp;
+    int32_t n_ff_shexp;   /* 0: no shared expert */
+    int32_t max_tokens;   /* the largest n any forward call will pass */
+    int32_t device;       /* CUDA device ordinal */
+    int32_t reserved;
+    const float* router;  /* host f32 [n_expert][n_embd], `ffn_gate_inp` */
+    bivmoe_experts gate, up, down;
+    bivmoe_experts sh_gate, sh_up, sh_down; /* ignored when n_ff_shexp == 0 */
+    const float* sh_gate_inp;               /* host f32 [n_embd], `ffn_gate_inp_shexp` */
+} bivmoe_desc;
+
+typedef struct bivmoe_layer bivmoe_layer;
+
+/* Upload one layer's tensors (repacked where a GGUF block is not 16-byte
+ * sized) and allocate its workspace.  Stands in for `Loader::ffn` +
+ * `gpu_layer` (model.rs:377-421; metal/mod.rs:584-605).  On failure *out is
+ * NULL and `bivmoe_global_error` describes why. */
+BIVMOE_API int bivmoe_create(const bivmoe_desc* desc, bivmoe_layer** out);
+BIVMOE_API void bivmoe_destroy(bivmoe_layer* layer);
+
+/* The layer on device rows: out[n][n_embd] = (accumulate ? out : 0) + moe(h).
+ * `accumulate` 0 is `Model::moe`'s return value (model.rs:861-898);
+ * 1 is Metal's `moe_combine`, which adds into the residual
+ * (metal/kernels.metal:1885-1908), i.e. `moe` followed by the `add_inplace`
+ * of model.rs:790.  Asynchronous on `stream` (a cudaStream_t); no host sync. */
+BIVMOE_API int bivmoe_forward(bivmoe_layer* layer, const float* h_dev, float* out_dev, int32_t n,
+                   int32_t accumulate, void* stream);
+
+/* The same call for an engine that keeps activations on the host (the CPU
+ * backend's calling convention, `fn moe(&self, m, h: &[f32], n) -> Vec<f32>`,
+ * model.rs:861): copies h in, runs the layer, copies the delta out and
+ * waits for it.  Pinned host buffers make the copies asynchronous. */
+BIVMOE_API int bivmoe_forward_host(bivmoe_layer* layer, const float* h_host, float* out_host, int32_t n);
+
+/* `bivmoe_forward` (accumulate 0) with CUDA events between its stages, for
+ * benchmarks: waits for the pass and writes the device time of each stage in
+ * milliseconds to ms[7] = {router product, softmax/top-k, sort, activation
+ * quantiser, gate+up experts, down experts, combine}.  The reference times
+ * this path only with wall clocks (examples/bench.rs:22-35). */
+BIVMOE_API int bivmoe_forward_profile(bivmoe_layer* layer, const float* h_dev, float* out_dev,
+                                      int32_t n, void* stream, float* ms);
+
+/* The norm that precedes the layer in the graph (`post_norm`, model.rs:788;
+ * ops.rs:136-149), needed by `bivmoe_forward_stack`.  `w` is host f32 [n_embd]. */
+BIVMOE_API int bivmoe_set_post_norm(bivmoe_layer* layer, const float* w, float eps);
+
+/* A run of layers with the residual carried on the device, FFN half of
+ * `Model::layer` only (model.rs:788-790): per layer h = rms_norm(x, post_norm),
+ * x += moe(h).  `x_dev` [n][n_embd] is updated in place. */
+BIVMOE_API int bivmoe_forward_stack(bivmoe_layer* const* layers, int32_t n_layers, float* x_dev, int32_t n,
+                         void* stream);
+
+/* Intermediates of the last forward call, copied to host memory after a
+ * stream sync: test-only, not on the timed path.  The reference has no such
+ * hook; the oracle exposes the same quantities. */
+enum {
+    BIVMOE_TAP_LOGITS = 0,     /* f32 [n][n_expert] router logits */
+    BIVMOE_TAP_IDS = 1,        /* i32 [n][k] experts in order of probability (model.rs:259-268) */
+    BIVMOE_TAP_WEIGHTS = 2,    /* f32 [n][k] */
+    BIVMOE_TAP_COUNTS = 3,     /* i32 [n_expert] pairs per expert */
+    BIVMOE_TAP_ORDER = 4,      /* i32 [n*k] pair indices t*k+j grouped by expert, ascending */
+    BIVMOE_TAP_ACT_Q = 5,      /* i8  [n][n_embd] Q8 rows of h (quant.rs:368-394) */
+    BIVMOE_TAP_ACT_D = 6,      /* f32 [n][n_embd/32] */
+    BIVMOE_TAP_ACT_S = 7,      /* f32 [n][n_embd/32] */
+    BIVMOE_TAP_MID = 8,        /* f32 [n*k][n_ff_exp] silu(gate)*up by pair index */
+    BIVMOE_TAP_PAIR_OUT = 9,   /* f32 [n*k][n_embd] expert outputs by pair index */
+    BIVMOE_TAP_SHARED_OUT = 10,/* f32 [n][n_embd] */
+    BIVMOE_TAP_SHARED_GATE = 11/* f32 [n] logit before the sigmoid */
+};
+BIVMOE_API int bivmoe_tap(bivmoe_layer* layer, int32_t which, void* host_dst, size_t bytes);
+
+/* The int32 dot of every 32-element block of one weight row against one
+ * quantised activation row of the last forward call - the integers the
+ * reference's kernels produce before scaling (quant.rs:599-686; for Q6_K the
+ * value includes the int8 sub-block scales).  matrix: 0 gate, 1 up, 2 down,
+ * 3..5 the shared expert's; gate/up rows meet token `act_row`'s Q8 row of h,
+ * down rows meet the Q8 row of pair `act_row`'s mid vector (pair index
+ * t*k+j; for the shared expert, token t).  `out` is host i32 [cols/32]. */
+BIVMOE_API int bivmoe_tap_block_dots(bivmoe_layer* layer, int32_t matrix, int32_t expert, int32_t row,
+                          int32_t act_row, int32_t* out);
+
+/* What decides the numbers besides code and weights, as `Engine::numerics`
+ * reports (engine.rs:42-46): device, kernel variants, repack version. */
+BIVMOE_API int bivmoe_numerics(const bivmoe_layer* layer, char* buf, size_t len);
+
+/* Bytes held on the device by this layer: weights and workspace
+ * (`Engine::model_memory`, engine.rs:30; memory.rs:189-194). */
+BIVMOE_API int bivmoe_memory(const bivmoe_layer* layer, uint64_t* weight_bytes, uint64_t* workspace_bytes);
+
+/* Kernels this library launched since load, for benchmark accounting. */
+BIVMOE_API uint64_t bivmoe_launch_count(void);
+
+BIVMOE_API const char* bivmoe_last_error(const bivmoe_layer* layer);
+BIVMOE_API const char* bivmoe_global_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BIVMOE_H */
