@@ -79,12 +79,17 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
     w.grp_start = a.take<int32_t>(ne + 1);
     w.grp_count = a.take<int32_t>(ne + 1);
     w.n_groups = a.take<int32_t>(1);
+    const size_t tiles = P / 8 + N / 8 + ne + 2;
+    w.tile_group = a.take<int32_t>(tiles);
+    w.tile_t0 = a.take<int32_t>(tiles);
+    w.n_tiles = a.take<int32_t>(2);
     w.work_ctr = a.take<uint32_t>(4);
     w.status = a.take<int32_t>(4);
     w.act_q = a.take<int8_t>(N * e);
-    w.act_d = a.take<float>(N * e / 32);
-    w.act_s = a.take<float>(N * e / 32);
+    w.act_ds = a.take<float2>(N * e / 32);
     w.mid = a.take<float>((P + N) * mid);
+    w.mid_q = a.take<int8_t>((P + N) * mid);
+    w.mid_ds = a.take<float2>((P + N) * mid / 32);
     w.pair_out = a.take<float>((P + N) * e);
     w.h_norm = a.take<float>(N * e);
 }
@@ -285,7 +290,7 @@ static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int 
     CU(launch_sort(c, L->ws));
     mark(c, EV_SORT);
     if (!type_uses_f32_act(L->gate.ty) || (L->has_shared && !type_uses_f32_act(L->sh_gate.ty)))
-        CU(launch_quantize_rows(c, h, n, L->e, L->ws.act_q, L->ws.act_d, L->ws.act_s));
+        CU(launch_quantize_rows(c, h, n, L->e, L->ws.act_q, L->ws.act_ds));
     mark(c, EV_QUANT);
     CU(launch_experts(c, h, L->gate, L->up, L->down, L->sh_gate, L->sh_up, L->sh_down, L->ws));
     mark(c, EV_DOWN);
@@ -412,8 +417,16 @@ int bivmoe_tap(bivmoe_layer* L, int32_t which, void* dst, size_t bytes) {
         case BIVMOE_TAP_COUNTS: return copy_out(L, dst, w.counts, bytes, ne * 4);
         case BIVMOE_TAP_ORDER: return copy_out(L, dst, w.order, bytes, P * 4);
         case BIVMOE_TAP_ACT_Q: return copy_out(L, dst, w.act_q, bytes, n * e);
-        case BIVMOE_TAP_ACT_D: return copy_out(L, dst, w.act_d, bytes, n * e / 32 * 4);
-        case BIVMOE_TAP_ACT_S: return copy_out(L, dst, w.act_s, bytes, n * e / 32 * 4);
+        case BIVMOE_TAP_ACT_D:
+        case BIVMOE_TAP_ACT_S: {
+            const size_t nb = n * e / 32;
+            if (bytes != nb * 4) return set_err(errp, BIVMOE_ERR_ARGUMENT, "tap buffer size mismatch");
+            std::vector<float> tmp(nb * 2);
+            CU(cudaMemcpy(tmp.data(), w.act_ds, nb * 8, cudaMemcpyDeviceToHost));
+            for (size_t i = 0; i < nb; i++)
+                ((float*)dst)[i] = tmp[2 * i + (which == BIVMOE_TAP_ACT_S ? 1 : 0)];
+            return BIVMOE_OK;
+        }
         case BIVMOE_TAP_MID:
         case BIVMOE_TAP_PAIR_OUT: {
             const bool m = which == BIVMOE_TAP_MID;
@@ -453,12 +466,8 @@ int bivmoe_tap_block_dots(bivmoe_layer* L, int32_t matrix, int32_t expert, int32
     if (type_uses_f32_act(m.ty))
         return set_err(errp, BIVMOE_ERR_UNSUPPORTED, "type %d has no integer block dots", m.ty);
     const int nb = m.cols / 32;
-    int8_t* xq = nullptr;
     int32_t* dots = nullptr;
-    float* ds = nullptr;
-    CU(cudaMalloc((void**)&xq, m.cols));
     CU(cudaMalloc((void**)&dots, (size_t)nb * 4));
-    CU(cudaMalloc((void**)&ds, (size_t)nb * 8));
     cudaError_t ce = cudaSuccess;
     const int8_t* act = nullptr;
     if (!is_down) {
@@ -466,19 +475,14 @@ int bivmoe_tap_block_dots(bivmoe_layer* L, int32_t matrix, int32_t expert, int32
     } else {
         // the Q8 row of the mid vector the down product consumed
         int32_t pos = P + act_row;
-        if (!shared)
-            ce = cudaMemcpy(&pos, L->ws.pos_of + act_row, 4, cudaMemcpyDeviceToHost);
-        LaunchCfg c{0, 1, L->k, L->e, L->n_expert, L->ff, L->ff_sh, 0, L->sm_count};
-        if (ce == cudaSuccess)
-            ce = launch_quantize_rows(c, L->ws.mid + (size_t)pos * std::max(L->ff, L->ff_sh), 1,
-                                      m.cols, xq, ds, ds + nb);
-        act = xq;
+        if (!shared) ce = cudaMemcpy(&pos, L->ws.pos_of + act_row, 4, cudaMemcpyDeviceToHost);
+        act = L->ws.mid_q + (size_t)pos * std::max(L->ff, L->ff_sh);
     }
     if (ce == cudaSuccess)
         ce = launch_block_dots(m.ty, m.data + (size_t)expert * m.expert_bytes + (size_t)row * m.row_bytes,
                                m.cols, act, dots, 0);
     if (ce == cudaSuccess) ce = cudaMemcpy(out, dots, (size_t)nb * 4, cudaMemcpyDeviceToHost);
-    cudaFree(xq); cudaFree(dots); cudaFree(ds);
+    cudaFree(dots);
     CU(ce);
     return BIVMOE_OK;
 }
@@ -486,7 +490,7 @@ int bivmoe_tap_block_dots(bivmoe_layer* L, int32_t matrix, int32_t expert, int32
 int bivmoe_numerics(const bivmoe_layer* L, char* buf, size_t len) {
     if (!L || !buf || !len) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or buffer");
     snprintf(buf, len,
-             "kind=cuda device=%s sms=%d repack=v%d experts=dp4a-lane-per-row/bulk-copy-staged "
+             "kind=cuda device=%s sms=%d repack=v%d experts=dp4a-two-rows-per-lane/warp-ring-bulk-copy "
              "router=f32-avx2-order combine=ordered-fma types=%d/%d/%d",
              L->device_name.c_str(), L->sm_count, kRepackVersion, L->gate.ty, L->up.ty, L->down.ty);
     return BIVMOE_OK;

@@ -71,12 +71,16 @@ struct Workspace {
     int32_t* grp_start;  // [n_expert + 1] first position
     int32_t* grp_count;  // [n_expert + 1]
     int32_t* n_groups;   // [1]
+    int32_t* tile_group; // [tiles] tile -> group; a tile is <= 8 consecutive positions of a group
+    int32_t* tile_t0;    // [tiles] first token of the tile inside its group
+    int32_t* n_tiles;    // [2] all tiles; the shared group's tiles (they come first)
     uint32_t* work_ctr;  // [4] dynamic work counters, zeroed by the sort
     int32_t* status;     // [4] device-side error flags (0 = ok)
     int8_t* act_q;       // [n][e]
-    float* act_d;        // [n][e/32]
-    float* act_s;        // [n][e/32]
+    float2* act_ds;      // [n][e/32] (d, s) per block
     float* mid;          // [P + n][ff] silu(gate)*up, by position
+    int8_t* mid_q;       // [P + n][ff] its Q8 rows (quantised down types)
+    float2* mid_ds;      // [P + n][ff/32]
     float* pair_out;     // [P + n][e], by position
     float* h_norm;       // [n][e] rms-normed rows (forward_stack)
 };
@@ -98,7 +102,7 @@ cudaError_t launch_router(const LaunchCfg& c, const float* router_dev /*[n_exper
 cudaError_t launch_route_topk(const LaunchCfg& c, const Workspace& ws);
 cudaError_t launch_sort(const LaunchCfg& c, const Workspace& ws);
 cudaError_t launch_quantize_rows(const LaunchCfg& c, const float* x, int rows, int cols,
-                                 int8_t* q, float* d, float* s);
+                                 int8_t* q, float2* ds);
 cudaError_t launch_experts(const LaunchCfg& c, const float* h, const DevStack& gate,
                            const DevStack& up, const DevStack& down, const DevStack& sh_gate,
                            const DevStack& sh_up, const DevStack& sh_down, const Workspace& ws);

@@ -1,22 +1,24 @@
-// Grouped expert products for decode-sized groups: gate+up with the SwiGLU
-// fused, and down with the Q8 re-quantisation of its input fused.
+// Grouped expert products for decode-sized groups: gate+up with the SwiGLU and
+// the Q8 re-quantisation of its output fused, then down.
 // Reference: dense_ffn (engine/src/model.rs:1119-1126) over matmul
 // (engine/src/ops.rs:84-127) and the per-type dots (engine/src/quant.rs:
 // 599-686 scalar, 1369-1533 AVX2), for each expert's token list
 // (model.rs:875-889) and for the shared expert (model.rs:890-896).
 //
-// Design.  A work item is (group, slab of weight rows); persistent blocks pull
-// items from a counter.  The slab's rows are streamed from HBM exactly once
-// with per-row bulk copies (cp.async.bulk + mbarrier) into padded shared-memory
-// rows, double-buffered against the previous item's arithmetic.  A lane owns
-// one weight row, a warp owns a 256-column slice of it; the group's
-// activations are staged in shared memory eight tokens at a time and read as
-// warp-wide broadcasts, so each weight word is unpacked once and meets every
-// token from registers.  Each lane forms whole 32-element block dots with
-// __dp4a (the same int32 values as the reference) and applies the block
-// scales in f32.  Slices are summed across warps through shared memory in a
-// fixed order: no atomics, results are run-to-run identical.
-#include <cuda_bf16.h>
+// Design.  The kernel is a grid of independent warps, one block per SM.  A
+// warp pulls work items (tile of <= 8 tokens of one group, chunk of weight
+// rows) from a counter and streams the chunk's rows from HBM through its own
+// two-slot ring in shared memory: per stage one K-slice of 64 rows (and the
+// matching K-slice of the tile's activation rows) arrives by bulk copies
+// (cp.async.bulk) on the warp's own mbarrier, so warps never synchronise with
+// each other and the copies of one stage overlap the arithmetic of the other,
+// across item boundaries too.  A lane owns two weight rows (gate row r and up
+// row r; or down rows r and r+32) and reads the activations as warp-wide
+// broadcasts, so each weight word is unpacked once and meets every token from
+// registers, and both rows share one activation load.  Each lane forms whole
+// 32-element block dots with __dp4a (the reference's int32 values) and applies
+// the block scales in f32.  No atomics on data: results are run-to-run identical.
+#include <cuda_fp16.h>
 
 #include <algorithm>
 
@@ -25,34 +27,35 @@
 
 namespace bivmoe {
 
-constexpr int EX_THREADS = 256;   // 8 warps
-constexpr int EX_TT = 8;          // tokens per activation tile
+constexpr int EX_TT = 8;                       // tokens per tile
+constexpr int EX_ROWS = 64;                    // weight rows per stage (two per lane)
 constexpr uint32_t EX_WAIT_LIMIT = 1u << 20;   // bounded mbarrier spin
 
 enum { MODE_GATEUP = 0, MODE_DOWN = 1 };
 
 struct ExpertArgs {
-    DevStack w0, w1;     // routed stacks: gate, up (MODE_GATEUP) or down (MODE_DOWN)
-    DevStack s0, s1;     // the shared expert's
-    const float* x_f32;  // GATEUP: h [n][K]; DOWN: mid [P+n][mid_stride]
-    const int8_t* act_q; // GATEUP, quantised types: Q8 rows of h by token
-    const float* act_d;
-    const float* act_s;
-    float* out;          // GATEUP: mid [P+n][mid_stride]; DOWN: pair_out [P+n][e]
+    DevStack w0, w1;       // routed stacks: gate, up (MODE_GATEUP) or down, - (MODE_DOWN)
+    DevStack s0, s1;       // the shared expert's
+    const float* x_f32;    // float-activation types: h [n][K] (GATEUP) or mid [P+n][mid_stride] (DOWN)
+    const int8_t* x_q;     // quantised types: Q8 rows, by token (GATEUP) or by position (DOWN)
+    const float2* x_ds;    // their (d, s) per block
+    int x_stride;          // elements per activation row
+    float* out;            // GATEUP: mid [P+n][mid_stride]; DOWN: pair_out [P+n][rows]
+    int8_t* out_q;         // GATEUP with a quantised down type: Q8 rows of mid
+    float2* out_ds;
     const int32_t* order;
     const int32_t* grp_expert;
     const int32_t* grp_start;
     const int32_t* grp_count;
-    const int32_t* n_groups;
+    const int32_t* tile_group;
+    const int32_t* tile_t0;
+    const int32_t* n_tiles;   // [0] all tiles, [1] tiles of the shared group (they come first)
     uint32_t* work_ctr;
     int32_t* status;
     int n, k, n_expert;
     int mid_stride;
-    int g_lo;            // first group this launch serves
-    int g_only_one;      // serve exactly one group (the shared expert's)
-    int slabs;           // row slabs per group
-    int row_stride;      // shared-memory bytes per staged weight row
-    int k_max;           // largest inner dimension among the stacks served
+    int tiles_mode;        // 0: every tile, 1: skip the shared group's, 2: only the shared group's
+    int chunks;            // row chunks per group
 };
 
 // ---------------------------------------------------------------------------
@@ -97,20 +100,15 @@ __device__ __forceinline__ void fence_proxy_async() {
 }
 
 // ---------------------------------------------------------------------------
-// The activation tile in shared memory.
-struct ActTile {
-    const int8_t* qs;   // [EX_TT][K] (quantised types)
-    const float2* ds;   // [EX_TT][K/32] (d, s) per block
-    const float* xf;    // [EX_TT][K] (float-activation types)
-    int K;
-};
-
-// acc[t] += dot(row, activation t) over super-block `sb` (256 columns) for the
-// first `cnt` tokens of the tile.  `wrow` is this lane's weight row in shared memory.
-template <int TY>
-__device__ __forceinline__ void accum_sb(const uint8_t* wrow, int sb, const ActTile& a, int cnt,
-                                         float (&acc)[EX_TT]);
-
+// Per-type geometry of a stage and the arithmetic of one staged K-slice.
+//   ELEMS   columns per stage
+//   STRIDE  shared-memory bytes per weight row per stage; an odd number of
+//           16-byte units, so lanes that own consecutive rows hit distinct
+//           bank groups on 128-bit loads
+//   ROW_TX  bytes the bulk copies of one row deliver
+//   WARPS   warps per block that fit two stages each in 227 KB
+//   Side    per-row words too small for a bulk copy; the lane fetches them
+//           with a plain load when it issues the stage
 #define LO4(v) ((int)((v) & 0x0F0F0F0Fu))
 #define HI4(v) ((int)(((v) >> 4) & 0x0F0F0F0Fu))
 
@@ -125,408 +123,445 @@ __device__ __forceinline__ int dot8(const int (&w)[8], const int4& a0, const int
     s = dp4a_s8(w[7], a1.w, s);
     return s;
 }
+__device__ __forceinline__ void load8(const uint8_t* p, uint32_t (&v)[8]) {
+    const uint4 a = *(const uint4*)p, b = *(const uint4*)(p + 16);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
 
-// Q8_0 (quant.rs:599-607): term = d_w * d_x * sum(q_w * q_x)
-template <>
-__device__ __forceinline__ void accum_sb<BIVMOE_Q8_0>(const uint8_t* wrow, int sb, const ActTile& a,
-                                                      int cnt, float (&acc)[EX_TT]) {
-    const int K = a.K;
+struct NoSide {};
+
+template <int TY> struct Fmt;
+
+// ---- Q8_0 (quant.rs:599-607): term = d_w * d_x * sum(q_w * q_x) ------------
+template <> struct Fmt<BIVMOE_Q8_0> {
+    static constexpr int ELEMS = 256, STRIDE = 272, WARPS = 5, ROW_TX = 272;
+    static constexpr bool F32ACT = false;
+    using Side = NoSide;
+    __device__ static Side side(const uint8_t*, int, int) { return {}; }
+    __device__ static void issue_row(uint8_t* dst, const uint8_t* row, int K, int s, uint64_t* bar) {
+        bulk_g2s(dst, row + 256 * (size_t)s, 256, bar);             // quants
+        bulk_g2s(dst + 256, row + K + 16 * (size_t)s, 16, bar);     // the 8 f16 scales
+    }
+    __device__ static void accum2(const uint8_t* wa, const uint8_t* wb, Side, Side,
+                                  const int8_t* xq, const float2* xds, int cnt,
+                                  float (&accA)[EX_TT], float (&accB)[EX_TT]) {
 #pragma unroll 2
-    for (int bb = 0; bb < 8; bb++) {
-        const int b = sb * 8 + bb;
-        const uint4 q0 = *(const uint4*)(wrow + 32 * b), q1 = *(const uint4*)(wrow + 32 * b + 16);
-        const int w[8] = {(int)q0.x, (int)q0.y, (int)q0.z, (int)q0.w,
-                          (int)q1.x, (int)q1.y, (int)q1.z, (int)q1.w};
-        const float dw = __half2float(*(const __half*)(wrow + K + 2 * b));
+        for (int b = 0; b < 8; b++) {
+            uint32_t ua[8], ub[8];
+            load8(wa + 32 * b, ua);
+            load8(wb + 32 * b, ub);
+            int qa[8], qb[8];
 #pragma unroll
-        for (int t = 0; t < EX_TT; t++) {
-            if (t < cnt) {
-                const int4* ap = (const int4*)(a.qs + (size_t)t * K + 32 * b);
-                const int i0 = dot8(w, ap[0], ap[1]);
-                const float dx = a.ds[t * (K / 32) + b].x;
-                acc[t] += (dw * dx) * (float)i0;
+            for (int i = 0; i < 8; i++) { qa[i] = (int)ua[i]; qb[i] = (int)ub[i]; }
+            const float da = __half2float(*(const __half*)(wa + 256 + 2 * b));
+            const float db = __half2float(*(const __half*)(wb + 256 + 2 * b));
+#pragma unroll
+            for (int t = 0; t < EX_TT; t++) {
+                if (t < cnt) {
+                    const int4* ap = (const int4*)(xq + t * ELEMS + 32 * b);
+                    const int4 a0 = ap[0], a1 = ap[1];
+                    const float dx = xds[t * (ELEMS / 32) + b].x;
+                    accA[t] += (da * dx) * (float)dot8(qa, a0, a1);
+                    accB[t] += (db * dx) * (float)dot8(qb, a0, a1);
+                }
             }
         }
     }
-}
+};
 
-// Q4_K / Q5_K (quant.rs:609-649): per sub-block
-//   d*sc*d_x*sum(q*q_x) - dmin*m*s_x ; Q5_K adds bit sb of qh[l] as value bit 4
-template <int TY>
-__device__ __forceinline__ void accum_k45(const uint8_t* wrow, int sb, const ActTile& a, int cnt,
-                                          float (&acc)[EX_TT]) {
-    constexpr int BS = TY == BIVMOE_Q4_K ? 144 : 176;
-    constexpr int QOFF = TY == BIVMOE_Q4_K ? 16 : 48;
-    const int K = a.K;
-    const uint8_t* blk = wrow + (size_t)sb * BS;
-    const uint4 hdr = *(const uint4*)blk;
-    const __half2 dd = *(const __half2*)&hdr.x;
-    const float d = __low2float(dd), dmin = __high2float(dd);
-    const K4Scales sc = unpack_k4_scales(hdr.y, hdr.z, hdr.w);
-    uint32_t qh[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (TY == BIVMOE_Q5_K) {
-        const uint4 h0 = *(const uint4*)(blk + 16), h1 = *(const uint4*)(blk + 32);
-        qh[0] = h0.x; qh[1] = h0.y; qh[2] = h0.z; qh[3] = h0.w;
-        qh[4] = h1.x; qh[5] = h1.y; qh[6] = h1.z; qh[7] = h1.w;
+// ---- Q4_K / Q5_K (quant.rs:609-649): per sub-block
+//      d*sc*d_x*sum(q*q_x) - dmin*m*s_x ; Q5_K adds bit sb of qh[l] as value bit 4
+template <int TY> struct FmtK45 {
+    static constexpr int BS = TY == BIVMOE_Q4_K ? 144 : 176;
+    static constexpr int QOFF = TY == BIVMOE_Q4_K ? 16 : 48;
+    static constexpr int ELEMS = 256, STRIDE = BS, WARPS = 8, ROW_TX = BS;
+    static constexpr bool F32ACT = false;
+    using Side = NoSide;
+    __device__ static Side side(const uint8_t*, int, int) { return {}; }
+    __device__ static void issue_row(uint8_t* dst, const uint8_t* row, int, int s, uint64_t* bar) {
+        bulk_g2s(dst, row + (size_t)BS * s, BS, bar);
     }
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const uint4 qa = *(const uint4*)(blk + QOFF + 32 * j);
-        const uint4 qb = *(const uint4*)(blk + QOFF + 32 * j + 16);
-        const uint32_t qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-        int lo[8], hi[8];
+    struct Hdr { float d, dmin; K4Scales sc; uint32_t qh[8]; };
+    __device__ static Hdr header(const uint8_t* blk) {
+        Hdr h;
+        const uint4 v = *(const uint4*)blk;
+        const __half2 dd = *(const __half2*)&v.x;
+        h.d = __low2float(dd);
+        h.dmin = __high2float(dd);
+        h.sc = unpack_k4_scales(v.y, v.z, v.w);
+        if (TY == BIVMOE_Q5_K) load8(blk + 16, h.qh);
+        return h;
+    }
+    __device__ static void unpack(const uint8_t* blk, const Hdr& h, int j, int (&lo)[8], int (&hi)[8]) {
+        uint32_t qv[8];
+        load8(blk + QOFF + 32 * j, qv);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             lo[i] = LO4(qv[i]);
             hi[i] = HI4(qv[i]);
             if (TY == BIVMOE_Q5_K) {
-                lo[i] |= (int)(((qh[i] >> (2 * j)) & 0x01010101u) << 4);
-                hi[i] |= (int)(((qh[i] >> (2 * j + 1)) & 0x01010101u) << 4);
-            }
-        }
-        const float dsc0 = d * (float)k4_scale(sc, 2 * j), dm0 = dmin * (float)k4_min(sc, 2 * j);
-        const float dsc1 = d * (float)k4_scale(sc, 2 * j + 1),
-                    dm1 = dmin * (float)k4_min(sc, 2 * j + 1);
-        const int xb = sb * 8 + 2 * j;
-#pragma unroll
-        for (int t = 0; t < EX_TT; t++) {
-            if (t < cnt) {
-                const int4* ap = (const int4*)(a.qs + (size_t)t * K + 32 * xb);
-                const int i0 = dot8(lo, ap[0], ap[1]);
-                const int i1 = dot8(hi, ap[2], ap[3]);
-                const float4 dx = *(const float4*)(a.ds + t * (K / 32) + xb);  // d0 s0 d1 s1
-                acc[t] += (dsc0 * dx.x) * (float)i0 - dm0 * dx.y;
-                acc[t] += (dsc1 * dx.z) * (float)i1 - dm1 * dx.w;
+                lo[i] |= (int)(((h.qh[i] >> (2 * j)) & 0x01010101u) << 4);
+                hi[i] |= (int)(((h.qh[i] >> (2 * j + 1)) & 0x01010101u) << 4);
             }
         }
     }
-}
-template <>
-__device__ __forceinline__ void accum_sb<BIVMOE_Q4_K>(const uint8_t* wrow, int sb, const ActTile& a,
-                                                      int cnt, float (&acc)[EX_TT]) {
-    accum_k45<BIVMOE_Q4_K>(wrow, sb, a, cnt, acc);
-}
-template <>
-__device__ __forceinline__ void accum_sb<BIVMOE_Q5_K>(const uint8_t* wrow, int sb, const ActTile& a,
-                                                      int cnt, float (&acc)[EX_TT]) {
-    accum_k45<BIVMOE_Q5_K>(wrow, sb, a, cnt, acc);
-}
-
-// Q6_K (quant.rs:651-686), device row planes [ql][qh][scales][d]: per 32-block
-//   d * d_x * (sc[2g]*sum16 + sc[2g+1]*sum16), 6-bit values minus 32
-template <>
-__device__ __forceinline__ void accum_sb<BIVMOE_Q6_K>(const uint8_t* wrow, int sb, const ActTile& a,
-                                                      int cnt, float (&acc)[EX_TT]) {
-    const int K = a.K, nb = K / 256;
-    const uint8_t* ql = wrow + (size_t)sb * 128;
-    const uint8_t* qhp = wrow + (size_t)nb * 128 + (size_t)sb * 64;
-    const int8_t* scp = (const int8_t*)wrow + (size_t)nb * 192 + (size_t)sb * 16;
-    const float d = __half2float(*(const __half*)(wrow + (size_t)nb * 208 + 2 * sb));
+    __device__ static void accum2(const uint8_t* wa, const uint8_t* wb, Side, Side,
+                                  const int8_t* xq, const float2* xds, int cnt,
+                                  float (&accA)[EX_TT], float (&accB)[EX_TT]) {
+        const Hdr ha = header(wa), hb = header(wb);
 #pragma unroll
-    for (int n = 0; n < 2; n++) {
-        uint32_t l0[8], l1[8], hh[8];
-        {
-            const uint4 a0 = *(const uint4*)(ql + 64 * n), a1 = *(const uint4*)(ql + 64 * n + 16);
-            const uint4 b0 = *(const uint4*)(ql + 64 * n + 32), b1 = *(const uint4*)(ql + 64 * n + 48);
-            const uint4 h0 = *(const uint4*)(qhp + 32 * n), h1 = *(const uint4*)(qhp + 32 * n + 16);
-            l0[0] = a0.x; l0[1] = a0.y; l0[2] = a0.z; l0[3] = a0.w;
-            l0[4] = a1.x; l0[5] = a1.y; l0[6] = a1.z; l0[7] = a1.w;
-            l1[0] = b0.x; l1[1] = b0.y; l1[2] = b0.z; l1[3] = b0.w;
-            l1[4] = b1.x; l1[5] = b1.y; l1[6] = b1.z; l1[7] = b1.w;
-            hh[0] = h0.x; hh[1] = h0.y; hh[2] = h0.z; hh[3] = h0.w;
-            hh[4] = h1.x; hh[5] = h1.y; hh[6] = h1.z; hh[7] = h1.w;
-        }
-        const uint2 scw = *(const uint2*)(scp + 8 * n);
-#pragma unroll
-        for (int kq = 0; kq < 4; kq++) {
-            int q[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const uint32_t base = (kq & 1) ? l1[i] : l0[i];
-                const uint32_t nib = (kq >= 2 ? base >> 4 : base) & 0x0F0F0F0Fu;
-                const uint32_t hb = ((hh[i] >> (2 * kq)) & 0x03030303u) << 4;
-                q[i] = (int)__vsub4(nib | hb, 0x20202020u);
-            }
-            const uint32_t sw = kq < 2 ? scw.x : scw.y;
-            const int sca = (int)(int8_t)((sw >> (16 * (kq & 1))) & 0xFF);
-            const int scb = (int)(int8_t)((sw >> (16 * (kq & 1) + 8)) & 0xFF);
-            const int xb = sb * 8 + 4 * n + kq;
+        for (int j = 0; j < 4; j++) {
+            int alo[8], ahi[8], blo[8], bhi[8];
+            unpack(wa, ha, j, alo, ahi);
+            unpack(wb, hb, j, blo, bhi);
+            const float a_s0 = ha.d * (float)k4_scale(ha.sc, 2 * j);
+            const float a_m0 = ha.dmin * (float)k4_min(ha.sc, 2 * j);
+            const float a_s1 = ha.d * (float)k4_scale(ha.sc, 2 * j + 1);
+            const float a_m1 = ha.dmin * (float)k4_min(ha.sc, 2 * j + 1);
+            const float b_s0 = hb.d * (float)k4_scale(hb.sc, 2 * j);
+            const float b_m0 = hb.dmin * (float)k4_min(hb.sc, 2 * j);
+            const float b_s1 = hb.d * (float)k4_scale(hb.sc, 2 * j + 1);
+            const float b_m1 = hb.dmin * (float)k4_min(hb.sc, 2 * j + 1);
 #pragma unroll
             for (int t = 0; t < EX_TT; t++) {
                 if (t < cnt) {
-                    const int4* ap = (const int4*)(a.qs + (size_t)t * K + 32 * xb);
-                    const int4 a0 = ap[0], a1 = ap[1];
-                    int ia = dp4a_s8(q[0], a0.x, 0);
-                    ia = dp4a_s8(q[1], a0.y, ia);
-                    ia = dp4a_s8(q[2], a0.z, ia);
-                    ia = dp4a_s8(q[3], a0.w, ia);
-                    int ib = dp4a_s8(q[4], a1.x, 0);
-                    ib = dp4a_s8(q[5], a1.y, ib);
-                    ib = dp4a_s8(q[6], a1.z, ib);
-                    ib = dp4a_s8(q[7], a1.w, ib);
-                    const int isum = sca * ia + scb * ib;
-                    const float dx = a.ds[t * (K / 32) + xb].x;
-                    acc[t] += (d * dx) * (float)isum;
+                    const int4* ap = (const int4*)(xq + t * ELEMS + 64 * j);
+                    const int4 x0 = ap[0], x1 = ap[1], x2 = ap[2], x3 = ap[3];
+                    const float4 dx = *(const float4*)(xds + t * (ELEMS / 32) + 2 * j);  // d0 s0 d1 s1
+                    accA[t] += (a_s0 * dx.x) * (float)dot8(alo, x0, x1) - a_m0 * dx.y;
+                    accA[t] += (a_s1 * dx.z) * (float)dot8(ahi, x2, x3) - a_m1 * dx.w;
+                    accB[t] += (b_s0 * dx.x) * (float)dot8(blo, x0, x1) - b_m0 * dx.y;
+                    accB[t] += (b_s1 * dx.z) * (float)dot8(bhi, x2, x3) - b_m1 * dx.w;
                 }
             }
         }
     }
-}
+};
+template <> struct Fmt<BIVMOE_Q4_K> : FmtK45<BIVMOE_Q4_K> {};
+template <> struct Fmt<BIVMOE_Q5_K> : FmtK45<BIVMOE_Q5_K> {};
 
-// BF16 weights meet f32 activations (quant.rs:509-521, 1229-1256)
-template <>
-__device__ __forceinline__ void accum_sb<BIVMOE_BF16>(const uint8_t* wrow, int sb, const ActTile& a,
-                                                      int cnt, float (&acc)[EX_TT]) {
-    const int K = a.K;
-#pragma unroll 4
-    for (int u = 0; u < 32; u++) {
-        const uint4 wv = *(const uint4*)(wrow + (size_t)sb * 512 + 16 * u);
-        const float w[8] = {__uint_as_float(wv.x << 16), __uint_as_float(wv.x & 0xFFFF0000u),
-                            __uint_as_float(wv.y << 16), __uint_as_float(wv.y & 0xFFFF0000u),
-                            __uint_as_float(wv.z << 16), __uint_as_float(wv.z & 0xFFFF0000u),
-                            __uint_as_float(wv.w << 16), __uint_as_float(wv.w & 0xFFFF0000u)};
+// ---- Q6_K (quant.rs:651-686), device row planes [ql][qh][scales][d]: per
+//      32-block d * d_x * (sc[2g]*sum16 + sc[2g+1]*sum16), 6-bit values minus 32
+template <> struct Fmt<BIVMOE_Q6_K> {
+    static constexpr int ELEMS = 256, STRIDE = 208, WARPS = 7, ROW_TX = 208;
+    static constexpr bool F32ACT = false;
+    struct Side { float d; };     // the super-block's f16 scale
+    __device__ static Side side(const uint8_t* row, int K, int s) {
+        return {__half2float(*(const __half*)(row + (size_t)(K / 256) * 208 + 2 * s))};
+    }
+    __device__ static void issue_row(uint8_t* dst, const uint8_t* row, int K, int s, uint64_t* bar) {
+        const size_t nb = K / 256;
+        bulk_g2s(dst, row + 128 * (size_t)s, 128, bar);                     // ql
+        bulk_g2s(dst + 128, row + nb * 128 + 64 * (size_t)s, 64, bar);      // qh
+        bulk_g2s(dst + 192, row + nb * 192 + 16 * (size_t)s, 16, bar);      // int8 scales
+    }
+    __device__ static void unpack(const uint32_t (&l0)[8], const uint32_t (&l1)[8],
+                                  const uint32_t (&hh)[8], int kq, int (&q)[8]) {
 #pragma unroll
-        for (int t = 0; t < EX_TT; t++) {
-            if (t < cnt) {
-                const float4* xp = (const float4*)(a.xf + (size_t)t * K + sb * 256 + 8 * u);
-                const float4 x0 = xp[0], x1 = xp[1];
-                float s = acc[t];
-                s = fmaf(w[0], x0.x, s); s = fmaf(w[1], x0.y, s);
-                s = fmaf(w[2], x0.z, s); s = fmaf(w[3], x0.w, s);
-                s = fmaf(w[4], x1.x, s); s = fmaf(w[5], x1.y, s);
-                s = fmaf(w[6], x1.z, s); s = fmaf(w[7], x1.w, s);
-                acc[t] = s;
+        for (int i = 0; i < 8; i++) {
+            const uint32_t base = (kq & 1) ? l1[i] : l0[i];
+            const uint32_t nib = (kq >= 2 ? base >> 4 : base) & 0x0F0F0F0Fu;
+            const uint32_t hb = ((hh[i] >> (2 * kq)) & 0x03030303u) << 4;
+            q[i] = (int)__vsub4(nib | hb, 0x20202020u);
+        }
+    }
+    __device__ static int isum(const int (&q)[8], const int4& a0, const int4& a1, uint32_t sw, int kq) {
+        const int sca = (int)(int8_t)((sw >> (16 * (kq & 1))) & 0xFF);
+        const int scb = (int)(int8_t)((sw >> (16 * (kq & 1) + 8)) & 0xFF);
+        int ia = dp4a_s8(q[0], a0.x, 0);
+        ia = dp4a_s8(q[1], a0.y, ia);
+        ia = dp4a_s8(q[2], a0.z, ia);
+        ia = dp4a_s8(q[3], a0.w, ia);
+        int ib = dp4a_s8(q[4], a1.x, 0);
+        ib = dp4a_s8(q[5], a1.y, ib);
+        ib = dp4a_s8(q[6], a1.z, ib);
+        ib = dp4a_s8(q[7], a1.w, ib);
+        return sca * ia + scb * ib;
+    }
+    __device__ static void accum2(const uint8_t* wa, const uint8_t* wb, Side sa, Side sb,
+                                  const int8_t* xq, const float2* xds, int cnt,
+                                  float (&accA)[EX_TT], float (&accB)[EX_TT]) {
+#pragma unroll
+        for (int n = 0; n < 2; n++) {
+            uint32_t al0[8], al1[8], ah[8], bl0[8], bl1[8], bh[8];
+            load8(wa + 64 * n, al0); load8(wa + 64 * n + 32, al1); load8(wa + 128 + 32 * n, ah);
+            load8(wb + 64 * n, bl0); load8(wb + 64 * n + 32, bl1); load8(wb + 128 + 32 * n, bh);
+            const uint2 asc = *(const uint2*)(wa + 192 + 8 * n), bsc = *(const uint2*)(wb + 192 + 8 * n);
+#pragma unroll
+            for (int kq = 0; kq < 4; kq++) {
+                int qa[8], qb[8];
+                unpack(al0, al1, ah, kq, qa);
+                unpack(bl0, bl1, bh, kq, qb);
+                const uint32_t aw = kq < 2 ? asc.x : asc.y, bw = kq < 2 ? bsc.x : bsc.y;
+                const int xb = 4 * n + kq;
+#pragma unroll
+                for (int t = 0; t < EX_TT; t++) {
+                    if (t < cnt) {
+                        const int4* ap = (const int4*)(xq + t * ELEMS + 32 * xb);
+                        const int4 a0 = ap[0], a1 = ap[1];
+                        const float dx = xds[t * (ELEMS / 32) + xb].x;
+                        accA[t] += (sa.d * dx) * (float)isum(qa, a0, a1, aw, kq);
+                        accB[t] += (sb.d * dx) * (float)isum(qb, a0, a1, bw, kq);
+                    }
+                }
             }
         }
     }
-}
+};
+
+// ---- BF16 weights meet f32 activations (quant.rs:509-521, 1229-1256) -------
+template <> struct Fmt<BIVMOE_BF16> {
+    static constexpr int ELEMS = 64, STRIDE = 144, WARPS = 8, ROW_TX = 128;
+    static constexpr bool F32ACT = true;
+    using Side = NoSide;
+    __device__ static Side side(const uint8_t*, int, int) { return {}; }
+    __device__ static void issue_row(uint8_t* dst, const uint8_t* row, int, int s, uint64_t* bar) {
+        bulk_g2s(dst, row + 128 * (size_t)s, 128, bar);
+    }
+    __device__ static void widen(const uint4& v, float (&w)[8]) {
+        w[0] = __uint_as_float(v.x << 16); w[1] = __uint_as_float(v.x & 0xFFFF0000u);
+        w[2] = __uint_as_float(v.y << 16); w[3] = __uint_as_float(v.y & 0xFFFF0000u);
+        w[4] = __uint_as_float(v.z << 16); w[5] = __uint_as_float(v.z & 0xFFFF0000u);
+        w[6] = __uint_as_float(v.w << 16); w[7] = __uint_as_float(v.w & 0xFFFF0000u);
+    }
+    __device__ static float fma8(const float (&w)[8], const float4& x0, const float4& x1, float s) {
+        s = fmaf(w[0], x0.x, s); s = fmaf(w[1], x0.y, s); s = fmaf(w[2], x0.z, s);
+        s = fmaf(w[3], x0.w, s); s = fmaf(w[4], x1.x, s); s = fmaf(w[5], x1.y, s);
+        s = fmaf(w[6], x1.z, s); s = fmaf(w[7], x1.w, s);
+        return s;
+    }
+    __device__ static void accum2f(const uint8_t* wa, const uint8_t* wb, const float* xf, int cnt,
+                                   float (&accA)[EX_TT], float (&accB)[EX_TT]) {
+#pragma unroll 2
+        for (int u = 0; u < 8; u++) {
+            float fa[8], fb[8];
+            widen(*(const uint4*)(wa + 16 * u), fa);
+            widen(*(const uint4*)(wb + 16 * u), fb);
+#pragma unroll
+            for (int t = 0; t < EX_TT; t++) {
+                if (t < cnt) {
+                    const float4* xp = (const float4*)(xf + t * ELEMS + 8 * u);
+                    const float4 x0 = xp[0], x1 = xp[1];
+                    accA[t] = fma8(fa, x0, x1, accA[t]);
+                    accB[t] = fma8(fb, x0, x1, accB[t]);
+                }
+            }
+        }
+    }
+};
 
 // ---------------------------------------------------------------------------
-template <int MODE> struct Shape;
-template <> struct Shape<MODE_GATEUP> {   // 16 gate rows + the 16 matching up rows
-    static constexpr int WARPS_ROW = 1, WARPS_K = 8, ROWS = 32, OUT_ROWS = 16;
-};
-template <> struct Shape<MODE_DOWN> {
-    static constexpr int WARPS_ROW = 4, WARPS_K = 2, ROWS = 128, OUT_ROWS = 128;
-};
-
-template <int TY> struct TypeCfg { static constexpr int NSTAGE = 2; };
-template <> struct TypeCfg<BIVMOE_BF16> { static constexpr int NSTAGE = 1; };
-
-__host__ __device__ inline int padded_row_stride(int64_t row_bytes) {
-    // an odd number of 16-byte units: lanes that own consecutive rows then hit
-    // distinct bank groups on 128-bit loads
-    int units = (int)(row_bytes / 16);
-    return (units | 1) * 16;
+template <int TY>
+__host__ __device__ constexpr int act_stage_bytes() {
+    return Fmt<TY>::F32ACT ? EX_TT * Fmt<TY>::ELEMS * 4
+                           : EX_TT * Fmt<TY>::ELEMS + EX_TT * (Fmt<TY>::ELEMS / 32) * 8;
+}
+template <int TY>
+__host__ __device__ constexpr int stage_bytes() {
+    return EX_ROWS * Fmt<TY>::STRIDE + act_stage_bytes<TY>();
+}
+template <int TY>
+__host__ __device__ constexpr int smem_bytes() {
+    return 128 + Fmt<TY>::WARPS * 2 * stage_bytes<TY>();
 }
 
-struct SmemPlan {
-    int stage_off, act_off, ds_off, part_off, total;
+struct Item {           // a decoded work item (warp-uniform except src_row)
+    int valid;
+    int shared;         // the shared expert's group
+    int expert;
+    int pos0;           // first position of the tile
+    int tc;             // tokens in the tile
+    int r0;             // first output row of the chunk
+    int K;              // inner dimension
+    int src_row;        // lane t < tc: activation row of token t (token or position)
+    const uint8_t* pa;  // this lane's two weight rows
+    const uint8_t* pb;
 };
-template <int TY, int MODE>
-__host__ __device__ inline SmemPlan smem_plan(int row_stride, int k_max) {
-    using S = Shape<MODE>;
-    SmemPlan p;
-    p.stage_off = 64;
-    int off = p.stage_off + TypeCfg<TY>::NSTAGE * S::ROWS * row_stride;
-    p.act_off = off;
-    if (type_uses_f32_act(TY)) {
-        off += EX_TT * k_max * 4;
-        p.ds_off = off;
-    } else {
-        off += EX_TT * k_max;
-        p.ds_off = off;
-        off += EX_TT * (k_max / 32) * 8;
-    }
-    p.part_off = off;
-    off += S::WARPS_K * S::ROWS * EX_TT * 4;
-    p.total = off;
-    return p;
-}
 
 template <int TY, int MODE>
-__global__ void __launch_bounds__(EX_THREADS)
+__global__ void __launch_bounds__(Fmt<TY>::WARPS * 32, 1)
 experts_kernel(const ExpertArgs A) {
-    using S = Shape<MODE>;
-    constexpr int NSTAGE = TypeCfg<TY>::NSTAGE;
-    constexpr bool F32ACT = TY == BIVMOE_BF16 || TY == BIVMOE_F32;
+    using F = Fmt<TY>;
+    using Side = typename F::Side;
+    constexpr int SB = stage_bytes<TY>();
+    constexpr int CH = MODE == MODE_GATEUP ? 32 : 64;   // output rows per chunk
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t* mbar = (uint64_t*)smem;            // [NSTAGE]
-    int* s_item = (int*)(smem + 32);
-    const SmemPlan plan = smem_plan<TY, MODE>(A.row_stride, A.k_max);
-    uint8_t* stage_base = smem + plan.stage_off;
-    int8_t* s_qs = (int8_t*)(smem + plan.act_off);
-    float* s_xf = (float*)(smem + plan.act_off);
-    float2* s_ds = (float2*)(smem + plan.ds_off);
-    float* s_part = (float*)(smem + plan.part_off);
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int wr = warp % S::WARPS_ROW, wk = warp / S::WARPS_ROW;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint64_t* mbar = (uint64_t*)smem + 2 * warp;                 // this warp's two barriers
+    uint8_t* ring = smem + 128 + (size_t)warp * 2 * SB;
     const int P = A.n * A.k;
-    const int n_groups = A.g_only_one ? 1 : *A.n_groups - A.g_lo;
-    const int total = n_groups * A.slabs;
 
-    if (tid == 0) {
-        for (int s = 0; s < NSTAGE; s++) mbar_init(&mbar[s], 1);
+    if (lane == 0) {
+        mbar_init(&mbar[0], 1);
+        mbar_init(&mbar[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __syncthreads();
+    __syncwarp();
 
-    // streams the rows of one item into a stage (warp 0)
-    auto issue = [&](int item, int stage) {
-        const int g = A.g_lo + item / A.slabs, slab = item % A.slabs;
-        const int ex = A.grp_expert[g];
-        const bool shared = ex == A.n_expert;
-        const DevStack& m0 = shared ? A.s0 : A.w0;
-        const DevStack& m1 = shared ? A.s1 : A.w1;
-        const int e_idx = shared ? 0 : ex;
-        const int r0 = slab * S::OUT_ROWS;
-        const int valid = max(0, min(S::OUT_ROWS, m0.rows - r0));
-        uint8_t* dst = stage_base + (size_t)stage * S::ROWS * A.row_stride;
-        const uint32_t rb = (uint32_t)m0.row_bytes;
-        // the stage was last read through the generic proxy (before a block barrier)
-        fence_proxy_async();
-        if (lane == 0) mbar_expect_tx(&mbar[stage], rb * valid * (MODE == MODE_GATEUP ? 2 : 1));
-        __syncwarp();
-        const uint8_t* src0 = m0.data + (size_t)e_idx * m0.expert_bytes + (size_t)r0 * rb;
-        for (int r = lane; r < valid; r += 32)
-            bulk_g2s(dst + (size_t)r * A.row_stride, src0 + (size_t)r * rb, rb, &mbar[stage]);
-        if (MODE == MODE_GATEUP) {
-            const uint8_t* src1 = m1.data + (size_t)e_idx * m1.expert_bytes + (size_t)r0 * rb;
-            for (int r = lane; r < valid; r += 32)
-                bulk_g2s(dst + (size_t)(S::OUT_ROWS + r) * A.row_stride, src1 + (size_t)r * rb, rb,
-                         &mbar[stage]);
+    const int tiles_all = A.n_tiles[0], tiles_sh = A.n_tiles[1];
+    const int tile_lo = A.tiles_mode == 1 ? tiles_sh : 0;
+    const int tile_hi = A.tiles_mode == 2 ? tiles_sh : tiles_all;
+    const int total = (tile_hi - tile_lo) * A.chunks;
+
+    // pulls the next item off the counter and decodes it
+    auto fetch = [&]() -> Item {
+        Item it;
+        int idx = 0;
+        if (lane == 0) idx = (int)atomicAdd(A.work_ctr, 1u);
+        idx = __shfl_sync(0xffffffffu, idx, 0);
+        it.valid = idx < total;
+        if (!it.valid) return it;
+        const int tile = tile_lo + idx / A.chunks, chunk = idx % A.chunks;
+        const int g = A.tile_group[tile], t0 = A.tile_t0[tile];
+        it.expert = A.grp_expert[g];
+        it.shared = it.expert == A.n_expert;
+        const int start = A.grp_start[g], cnt = A.grp_count[g];
+        it.pos0 = start + t0;
+        it.tc = min(EX_TT, cnt - t0);
+        it.r0 = chunk * CH;
+        it.src_row = 0;
+        if (lane < it.tc) {
+            const int pos = it.pos0 + lane;
+            if (MODE == MODE_GATEUP) it.src_row = it.shared ? pos - P : A.order[pos] / A.k;
+            else it.src_row = pos;
         }
-    };
-    auto fetch = [&]() -> int {
-        if (tid == 0) *s_item = (int)atomicAdd(A.work_ctr, 1u);
-        __syncthreads();
-        const int it = *s_item;
-        __syncthreads();
+        const DevStack& m0 = it.shared ? A.s0 : A.w0;
+        const DevStack& m1 = MODE == MODE_GATEUP ? (it.shared ? A.s1 : A.w1) : m0;
+        const size_t e = it.shared ? 0 : it.expert;
+        const int ra = min(it.r0 + lane, m0.rows - 1);
+        const int rb = MODE == MODE_GATEUP ? ra : min(it.r0 + 32 + lane, m0.rows - 1);
+        it.pa = m0.data + e * m0.expert_bytes + (size_t)ra * m0.row_bytes;
+        it.pb = m1.data + e * m1.expert_bytes + (size_t)rb * m1.row_bytes;
+        it.K = m0.cols;
         return it;
     };
+    // issues stage `s` of an item into ring slot `slot`
+    auto issue = [&](const Item& it, int s, int slot) {
+        uint8_t* dst = ring + (size_t)slot * SB;
+        fence_proxy_async();   // the slot was last read through the generic proxy
+        __syncwarp();
+        if (lane == 0)
+            mbar_expect_tx(&mbar[slot],
+                           EX_ROWS * F::ROW_TX +
+                               it.tc * (F::F32ACT ? F::ELEMS * 4 : F::ELEMS + F::ELEMS / 4));
+        __syncwarp();
+        F::issue_row(dst + (size_t)lane * F::STRIDE, it.pa, it.K, s, &mbar[slot]);
+        F::issue_row(dst + (size_t)(32 + lane) * F::STRIDE, it.pb, it.K, s, &mbar[slot]);
+        if (lane < it.tc) {
+            uint8_t* adst = dst + EX_ROWS * F::STRIDE;
+            if (F::F32ACT) {
+                bulk_g2s(adst + (size_t)lane * F::ELEMS * 4,
+                         A.x_f32 + (size_t)it.src_row * A.x_stride + (size_t)s * F::ELEMS, F::ELEMS * 4,
+                         &mbar[slot]);
+            } else {
+                bulk_g2s(adst + (size_t)lane * F::ELEMS,
+                         A.x_q + (size_t)it.src_row * A.x_stride + (size_t)s * F::ELEMS, F::ELEMS,
+                         &mbar[slot]);
+                bulk_g2s(adst + EX_TT * F::ELEMS + (size_t)lane * (F::ELEMS / 32) * 8,
+                         A.x_ds + (size_t)it.src_row * (A.x_stride / 32) + (size_t)s * (F::ELEMS / 32),
+                         (F::ELEMS / 32) * 8, &mbar[slot]);
+            }
+        }
+    };
 
-    int item = fetch();
-    if (item >= total) return;
-    if (warp == 0) issue(item, 0);
-    uint32_t phase[2] = {0, 0};
-    int stage = 0;
+    Item cur = fetch();
+    if (!cur.valid) return;
+    Item nxt;
+    nxt.valid = 0;
+    // The stages of successive items form one stream; stream stage q lives in
+    // slot q & 1.  `issued` runs at most two ahead of `consumed`; the producer
+    // cursor (p_in_next, p_stage) names the next stage to issue.
+    int issued = 0, consumed = 0, p_in_next = 0, p_stage = 0;
+    Side sideA0{}, sideA1{}, sideB0{}, sideB1{};
+    auto pump = [&]() {
+        while (issued < consumed + 2) {
+            if (!p_in_next && p_stage >= cur.K / F::ELEMS) {
+                p_in_next = 1;
+                p_stage = 0;
+            }
+            if (p_in_next && (!nxt.valid || p_stage >= nxt.K / F::ELEMS)) break;
+            const Item& it = p_in_next ? nxt : cur;
+            const int slot = issued & 1;
+            const Side sa = F::side(it.pa, it.K, p_stage), sb = F::side(it.pb, it.K, p_stage);
+            if (slot) { sideA1 = sa; sideB1 = sb; } else { sideA0 = sa; sideB0 = sb; }
+            issue(it, p_stage, slot);
+            p_stage++;
+            issued++;
+        }
+    };
+    pump();
+    nxt = fetch();
+    pump();
 
     while (true) {
-        const int next = fetch();
-        if (NSTAGE == 2 && next < total && warp == 0) issue(next, stage ^ 1);
-        if (!mbar_wait_bounded(&mbar[stage], phase[stage])) {
-            // every thread waits on the same barrier, so all give up together; the
-            // copies already issued for the next item get the same bounded wait
-            if (tid == 0) atomicExch(A.status, BIVMOE_ERR_TIMEOUT);
-            if (NSTAGE == 2 && next < total) mbar_wait_bounded(&mbar[stage ^ 1], phase[stage ^ 1]);
-            return;
-        }
-        phase[stage] ^= 1;
-
-        const int g = A.g_lo + item / A.slabs, slab = item % A.slabs;
-        const int ex = A.grp_expert[g], start = A.grp_start[g], cnt = A.grp_count[g];
-        const bool shared = ex == A.n_expert;
-        const DevStack& m0 = shared ? A.s0 : A.w0;
-        const int K = m0.cols, nsb = K / 256;
-        const int r0 = slab * S::OUT_ROWS;
-        const uint8_t* wrow =
-            stage_base + ((size_t)stage * S::ROWS + wr * 32 + lane) * A.row_stride;
-        ActTile at;
-        at.qs = s_qs; at.ds = s_ds; at.xf = s_xf; at.K = K;
-
-        for (int t0 = 0; t0 < cnt; t0 += EX_TT) {
-            const int tc = min(EX_TT, cnt - t0);
-            // ---- stage the activations of tokens t0..t0+tc
-            if (MODE == MODE_GATEUP) {
-                if (F32ACT) {
-                    for (int i = tid; i < tc * (K / 4); i += EX_THREADS) {
-                        const int t = i / (K / 4), c = i % (K / 4);
-                        const int pos = start + t0 + t;
-                        const int tok = shared ? pos - P : A.order[pos] / A.k;
-                        ((float4*)s_xf)[t * (K / 4) + c] =
-                            ((const float4*)(A.x_f32 + (size_t)tok * K))[c];
-                    }
-                } else {
-                    for (int i = tid; i < tc * (K / 16); i += EX_THREADS) {
-                        const int t = i / (K / 16), c = i % (K / 16);
-                        const int pos = start + t0 + t;
-                        const int tok = shared ? pos - P : A.order[pos] / A.k;
-                        ((int4*)s_qs)[t * (K / 16) + c] =
-                            ((const int4*)(A.act_q + (size_t)tok * K))[c];
-                    }
-                    for (int i = tid; i < tc * (K / 32); i += EX_THREADS) {
-                        const int t = i / (K / 32), b = i % (K / 32);
-                        const int pos = start + t0 + t;
-                        const int tok = shared ? pos - P : A.order[pos] / A.k;
-                        s_ds[t * (K / 32) + b] = make_float2(A.act_d[(size_t)tok * (K / 32) + b],
-                                                             A.act_s[(size_t)tok * (K / 32) + b]);
-                    }
-                }
+        float accA[EX_TT], accB[EX_TT];
+#pragma unroll
+        for (int t = 0; t < EX_TT; t++) accA[t] = accB[t] = 0.0f;
+        const int nst = cur.K / F::ELEMS;
+        for (int s = 0; s < nst; s++) {
+            const int slot = consumed & 1;
+            if (!mbar_wait_bounded(&mbar[slot], (consumed >> 1) & 1)) {
+                // give up: flag it, give the other slot's copies the same bounded wait, leave
+                if (lane == 0) atomicExch(A.status, BIVMOE_ERR_TIMEOUT);
+                if (issued > consumed + 1)
+                    mbar_wait_bounded(&mbar[slot ^ 1], ((consumed + 1) >> 1) & 1);
+                return;
+            }
+            const uint8_t* st = ring + (size_t)slot * SB;
+            const uint8_t* wa = st + (size_t)lane * F::STRIDE;
+            const uint8_t* wb = st + (size_t)(32 + lane) * F::STRIDE;
+            const uint8_t* act = st + EX_ROWS * F::STRIDE;
+            if constexpr (F::F32ACT) {
+                F::accum2f(wa, wb, (const float*)act, cur.tc, accA, accB);
             } else {
-                if (F32ACT) {
-                    for (int i = tid; i < tc * (K / 4); i += EX_THREADS) {
-                        const int t = i / (K / 4), c = i % (K / 4);
-                        ((float4*)s_xf)[t * (K / 4) + c] =
-                            ((const float4*)(A.x_f32 + (size_t)(start + t0 + t) * A.mid_stride))[c];
-                    }
-                } else {
-                    // Q8Act of the mid rows, quantised here (quant.rs:368-394)
-                    for (int i = warp; i < tc * (K / 32); i += EX_THREADS / 32) {
-                        const int t = i / (K / 32), b = i % (K / 32);
-                        const float v =
-                            A.x_f32[(size_t)(start + t0 + t) * A.mid_stride + 32 * b + lane];
+                F::accum2(wa, wb, slot ? sideA1 : sideA0, slot ? sideB1 : sideB0, (const int8_t*)act,
+                          (const float2*)(act + EX_TT * F::ELEMS), cur.tc, accA, accB);
+            }
+            __syncwarp();
+            consumed++;
+            pump();
+        }
+        // ---- epilogue
+        const int rows = (cur.shared ? A.s0 : A.w0).rows;
+        if (MODE == MODE_GATEUP) {
+            const bool row_ok = cur.r0 + lane < rows;
+#pragma unroll
+            for (int t = 0; t < EX_TT; t++) {
+                if (t < cur.tc) {
+                    // ops.rs:160-167: silu(x) = x * (1 / (1 + exp(-x)))
+                    const float g = accA[t], u = accB[t];
+                    const float sg = __fdiv_rn(1.0f, 1.0f + expf(-g));
+                    const float v = row_ok ? (g * sg) * u : 0.0f;
+                    const size_t o = (size_t)(cur.pos0 + t) * A.mid_stride + cur.r0 + lane;
+                    if (row_ok) A.out[o] = v;
+                    if (A.out_q) {   // Q8Act of the mid row (quant.rs:368-394): this chunk is one block
                         float dd, ss;
                         const int q = q8_quantize_lane(v, dd, ss);
-                        s_qs[(size_t)t * K + 32 * b + lane] = (int8_t)q;
-                        if (lane == 0) s_ds[t * (K / 32) + b] = make_float2(dd, ss);
+                        if (row_ok) A.out_q[o] = (int8_t)q;
+                        if (lane == 0)
+                            A.out_ds[(size_t)(cur.pos0 + t) * (A.mid_stride / 32) + cur.r0 / 32] =
+                                make_float2(dd, ss);
                     }
                 }
             }
-            __syncthreads();
-            // ---- this warp's slice of the dots
-            float acc[EX_TT];
+        } else {
 #pragma unroll
-            for (int t = 0; t < EX_TT; t++) acc[t] = 0.0f;
-            for (int sb = wk; sb < nsb; sb += S::WARPS_K) accum_sb<TY>(wrow, sb, at, tc, acc);
-#pragma unroll
-            for (int t = 0; t < EX_TT; t++)
-                s_part[(wk * S::ROWS + wr * 32 + lane) * EX_TT + t] = acc[t];
-            __syncthreads();
-            // ---- sum the slices in a fixed order, epilogue
-            if (MODE == MODE_GATEUP) {
-                if (tid < S::OUT_ROWS * EX_TT) {
-                    const int r = tid % S::OUT_ROWS, t = tid / S::OUT_ROWS;
-                    float gsum = 0.0f, usum = 0.0f;
-#pragma unroll
-                    for (int w = 0; w < S::WARPS_K; w++) {
-                        gsum += s_part[(w * S::ROWS + r) * EX_TT + t];
-                        usum += s_part[(w * S::ROWS + S::OUT_ROWS + r) * EX_TT + t];
-                    }
-                    if (t < tc && r0 + r < m0.rows) {
-                        // ops.rs:160-167: silu(x) = x * (1 / (1 + exp(-x)))
-                        const float sg = __fdiv_rn(1.0f, 1.0f + expf(-gsum));
-                        A.out[(size_t)(start + t0 + t) * A.mid_stride + r0 + r] = (gsum * sg) * usum;
-                    }
-                }
-            } else {
-                for (int i = tid; i < S::OUT_ROWS * EX_TT; i += EX_THREADS) {
-                    const int r = i % S::OUT_ROWS, t = i / S::OUT_ROWS;
-                    float sum = 0.0f;
-#pragma unroll
-                    for (int w = 0; w < S::WARPS_K; w++) sum += s_part[(w * S::ROWS + r) * EX_TT + t];
-                    if (t < tc && r0 + r < m0.rows)
-                        A.out[(size_t)(start + t0 + t) * m0.rows + r0 + r] = sum;
+            for (int t = 0; t < EX_TT; t++) {
+                if (t < cur.tc) {
+                    float* o = A.out + (size_t)(cur.pos0 + t) * rows + cur.r0;
+                    if (cur.r0 + lane < rows) o[lane] = accA[t];
+                    if (cur.r0 + 32 + lane < rows) o[32 + lane] = accB[t];
                 }
             }
-            // the next tile's staging overwrites the activations only after every
-            // warp passed the barrier above; s_part is rewritten after the next one
         }
-        __syncthreads();
-        if (next >= total) break;
-        if (NSTAGE == 1 && warp == 0) issue(next, 0);
-        item = next;
-        if (NSTAGE == 2) stage ^= 1;
+        if (!nxt.valid) break;
+        // the stream may already run inside `nxt`: it becomes the current item
+        cur = nxt;
+        if (p_in_next) p_in_next = 0;
+        else p_stage = 0;   // (not reached: a finished item has all its stages issued)
+        nxt = fetch();
+        pump();
     }
 }
 
@@ -538,48 +573,43 @@ bool experts_supported(int ty, int cols, int rows, bool is_down) {
         ty != BIVMOE_BF16)
         return false;
     if (cols <= 0 || cols % 256) return false;
-    if (rows <= 0 || (!is_down && rows % 16)) return false;
+    if (rows <= 0 || (!is_down && rows % 32)) return false;
     return dev_row_bytes(ty, cols) % 16 == 0;
 }
 
 template <int TY, int MODE>
-static cudaError_t launch_one(const LaunchCfg& c, ExpertArgs A, int rows_max, bool only_shared) {
-    using S = Shape<MODE>;
-    A.row_stride = padded_row_stride(std::max(A.w0.row_bytes, A.s0.row_bytes));
-    A.slabs = (rows_max + S::OUT_ROWS - 1) / S::OUT_ROWS;
-    const SmemPlan plan = smem_plan<TY, MODE>(A.row_stride, A.k_max);
-    if (plan.total > 227 * 1024) return cudaErrorInvalidConfiguration;
+static cudaError_t launch_one(const LaunchCfg& c, ExpertArgs A, int rows_max) {
+    constexpr int CH = MODE == MODE_GATEUP ? 32 : 64;
+    A.chunks = (rows_max + CH - 1) / CH;
+    constexpr int smem = smem_bytes<TY>();
+    static_assert(smem <= 227 * 1024, "two stages per warp must fit in shared memory");
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(experts_kernel<TY, MODE>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    int per_sm = std::max(1, std::min(4, (227 * 1024) / (plan.total + 1024)));
-    int max_items = (only_shared ? 1 : c.n_expert + 1) * A.slabs;
-    int grid = std::min(c.sm_count * per_sm, max_items);
-    experts_kernel<TY, MODE><<<grid, EX_THREADS, plan.total, c.stream>>>(A);
+    experts_kernel<TY, MODE><<<c.sm_count, Fmt<TY>::WARPS * 32, smem, c.stream>>>(A);
     count_launch();
     return cudaGetLastError();
 }
 
 template <int MODE>
-static cudaError_t launch_typed(int ty, const LaunchCfg& c, const ExpertArgs& A, int rows_max,
-                                bool only_shared) {
+static cudaError_t launch_typed(int ty, const LaunchCfg& c, const ExpertArgs& A, int rows_max) {
     switch (ty) {
-        case BIVMOE_Q8_0: return launch_one<BIVMOE_Q8_0, MODE>(c, A, rows_max, only_shared);
-        case BIVMOE_Q4_K: return launch_one<BIVMOE_Q4_K, MODE>(c, A, rows_max, only_shared);
-        case BIVMOE_Q5_K: return launch_one<BIVMOE_Q5_K, MODE>(c, A, rows_max, only_shared);
-        case BIVMOE_Q6_K: return launch_one<BIVMOE_Q6_K, MODE>(c, A, rows_max, only_shared);
-        case BIVMOE_BF16: return launch_one<BIVMOE_BF16, MODE>(c, A, rows_max, only_shared);
+        case BIVMOE_Q8_0: return launch_one<BIVMOE_Q8_0, MODE>(c, A, rows_max);
+        case BIVMOE_Q4_K: return launch_one<BIVMOE_Q4_K, MODE>(c, A, rows_max);
+        case BIVMOE_Q5_K: return launch_one<BIVMOE_Q5_K, MODE>(c, A, rows_max);
+        case BIVMOE_Q6_K: return launch_one<BIVMOE_Q6_K, MODE>(c, A, rows_max);
+        case BIVMOE_BF16: return launch_one<BIVMOE_BF16, MODE>(c, A, rows_max);
         default: return cudaErrorInvalidValue;
     }
 }
 
 // gate+up then down, for the routed experts and the shared expert.  When the
-// shared expert's matrices have the routed experts' types (and the same
-// gate/up type) it rides in the same launches as group 0.
+// shared expert's matrices have the routed experts' types it rides in the same
+// launches (its tiles come first in the tile list); otherwise it gets its own.
 cudaError_t launch_experts(const LaunchCfg& c, const float* h, const DevStack& gate,
                            const DevStack& up, const DevStack& down, const DevStack& sh_gate,
                            const DevStack& sh_up, const DevStack& sh_down, const Workspace& ws) {
@@ -587,60 +617,50 @@ cudaError_t launch_experts(const LaunchCfg& c, const float* h, const DevStack& g
     ExpertArgs A{};
     A.order = ws.order;
     A.grp_expert = ws.grp_expert; A.grp_start = ws.grp_start; A.grp_count = ws.grp_count;
-    A.n_groups = ws.n_groups;
+    A.tile_group = ws.tile_group; A.tile_t0 = ws.tile_t0; A.n_tiles = ws.n_tiles;
     A.status = ws.status;
     A.n = c.n; A.k = c.k; A.n_expert = c.n_expert;
     A.mid_stride = std::max(c.ff, c.ff_sh);
-    A.act_q = ws.act_q; A.act_d = ws.act_d; A.act_s = ws.act_s;
-    const bool fuse_gu = c.has_shared && sh_gate.ty == gate.ty;
-    const bool fuse_dn = c.has_shared && sh_down.ty == down.ty;
+    const bool fused = c.has_shared && sh_gate.ty == gate.ty && sh_down.ty == down.ty;
     cudaError_t err;
-    // ---- gate + up
-    {
+    // ---- gate + up (SwiGLU and the Q8 rows of its output in the epilogue)
+    auto gateup = [&](int mode, int rows, int ctr, int ty, int down_ty) {
         ExpertArgs G = A;
         G.w0 = gate; G.w1 = up; G.s0 = sh_gate; G.s1 = sh_up;
-        G.x_f32 = h; G.out = ws.mid;
-        G.k_max = c.e;
-        G.work_ctr = ws.work_ctr + 0;
-        G.g_lo = c.has_shared && !fuse_gu ? 1 : 0;
-        G.g_only_one = 0;
-        if (!fuse_gu) G.s0 = DevStack{}, G.s1 = DevStack{};
-        err = launch_typed<MODE_GATEUP>(gate.ty, c, G, std::max(c.ff, fuse_gu ? c.ff_sh : 0), false);
-        if (err != cudaSuccess) return err;
-        if (c.has_shared && !fuse_gu) {
-            ExpertArgs H = A;
-            H.s0 = sh_gate; H.s1 = sh_up; H.w0 = sh_gate; H.w1 = sh_up;
-            H.x_f32 = h; H.out = ws.mid; H.k_max = c.e;
-            H.work_ctr = ws.work_ctr + 1;
-            H.g_lo = 0; H.g_only_one = 1;
-            err = launch_typed<MODE_GATEUP>(sh_gate.ty, c, H, c.ff_sh, true);
-            if (err != cudaSuccess) return err;
-        }
+        G.x_f32 = h; G.x_q = ws.act_q; G.x_ds = ws.act_ds; G.x_stride = c.e;
+        G.out = ws.mid;
+        const bool qdown = !type_uses_f32_act(down_ty);
+        G.out_q = qdown ? ws.mid_q : nullptr;
+        G.out_ds = qdown ? ws.mid_ds : nullptr;
+        G.work_ctr = ws.work_ctr + ctr;
+        G.tiles_mode = mode;
+        return launch_typed<MODE_GATEUP>(ty, c, G, rows);
+    };
+    if (fused || !c.has_shared) {
+        err = gateup(0, std::max(c.ff, c.ff_sh), 0, gate.ty, down.ty);
+    } else {
+        err = gateup(1, c.ff, 0, gate.ty, down.ty);
+        if (err == cudaSuccess) err = gateup(2, c.ff_sh, 1, sh_gate.ty, sh_down.ty);
     }
+    if (err != cudaSuccess) return err;
     mark(c, EV_GATEUP);
     // ---- down
-    {
+    auto downp = [&](int mode, int ctr, int ty) {
         ExpertArgs D = A;
         D.w0 = down; D.s0 = sh_down;
-        D.x_f32 = ws.mid; D.out = ws.pair_out;
-        D.k_max = std::max(c.ff, fuse_dn ? c.ff_sh : 0);
-        D.work_ctr = ws.work_ctr + 2;
-        D.g_lo = c.has_shared && !fuse_dn ? 1 : 0;
-        D.g_only_one = 0;
-        if (!fuse_dn) D.s0 = DevStack{};
-        err = launch_typed<MODE_DOWN>(down.ty, c, D, c.e, false);
-        if (err != cudaSuccess) return err;
-        if (c.has_shared && !fuse_dn) {
-            ExpertArgs H = A;
-            H.s0 = sh_down; H.w0 = sh_down;
-            H.x_f32 = ws.mid; H.out = ws.pair_out; H.k_max = c.ff_sh;
-            H.work_ctr = ws.work_ctr + 3;
-            H.g_lo = 0; H.g_only_one = 1;
-            err = launch_typed<MODE_DOWN>(sh_down.ty, c, H, c.e, true);
-            if (err != cudaSuccess) return err;
-        }
+        D.x_f32 = ws.mid; D.x_q = ws.mid_q; D.x_ds = ws.mid_ds; D.x_stride = A.mid_stride;
+        D.out = ws.pair_out;
+        D.work_ctr = ws.work_ctr + ctr;
+        D.tiles_mode = mode;
+        return launch_typed<MODE_DOWN>(ty, c, D, c.e);
+    };
+    if (fused || !c.has_shared) {
+        err = downp(0, 2, down.ty);
+    } else {
+        err = downp(1, 2, down.ty);
+        if (err == cudaSuccess) err = downp(2, 3, sh_down.ty);
     }
-    return cudaSuccess;
+    return err;
 }
 
 }  // namespace bivmoe

@@ -32,6 +32,7 @@ router_logits_kernel(const float* __restrict__ W, const float* __restrict__ h,
 #pragma unroll
     for (int t = 0; t < RT_TOKS; t++) xp[t] = h + (size_t)min(t0 + t, n - 1) * e + lane;
     float acc[RT_ROWS][RT_TOKS] = {};
+#pragma unroll 4
     for (int i = 0; i < e; i += 32) {
         float w[RT_ROWS], x[RT_TOKS];
 #pragma unroll
@@ -143,6 +144,7 @@ cudaError_t launch_route_topk(const LaunchCfg& c, const Workspace& ws) {
 // thread per expert walk its block's pairs in order.  With one block the three
 // phases run in a single launch.
 constexpr int SORT_TOKENS = 256, SORT_THREADS = 256;
+constexpr int SORT_TILE = 8;   // tokens per tile of the expert kernels
 
 __device__ void sort_load_ids(const int32_t* ids, int pair0, int npairs, uint16_t* s_ids) {
     for (int i = threadIdx.x; i < npairs; i += blockDim.x) s_ids[i] = (uint16_t)ids[pair0 + i];
@@ -153,40 +155,100 @@ __device__ void sort_hist(const uint16_t* s_ids, int npairs, int n_expert, int* 
     for (int i = threadIdx.x; i < npairs; i += blockDim.x) atomicAdd(&s_cnt[s_ids[i]], 1);
     __syncthreads();
 }
-// one block: bases over blocks and experts, the group list, counters reset
-__device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, int k,
-                          int has_shared) {
-    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
-        int run = 0;
-        for (int b = 0; b < nblk; b++) {
-            int c = ws.blk_counts[(size_t)b * n_expert + e];
-            ws.blk_counts[(size_t)b * n_expert + e] = run;
-            run += c;
+// exclusive scan over the block of one int per thread slot; `n_items` slots,
+// ITEMS consecutive slots per thread.  Returns the total in *total.
+template <int ITEMS>
+__device__ void block_exclusive_scan(int (&v)[ITEMS], int* s_warp, int* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    int local = 0;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) { int t = v[i]; v[i] = local; local += t; }
+    int inc = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = lane < nwarp ? s_warp[lane] : 0, winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int t = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += t;
         }
-        ws.counts[e] = run;
+        if (lane < nwarp) s_warp[lane] = winc - w;
+        if (lane == 31) *total = winc;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int off = 0, g = 0;
-        if (has_shared) {   // the heaviest group first
-            ws.grp_expert[g] = n_expert;
-            ws.grp_start[g] = n * k;
-            ws.grp_count[g] = n;
-            g++;
-        }
-        for (int e = 0; e < n_expert; e++) {
-            int c = ws.counts[e];
-            ws.offsets[e] = off;
-            if (c) {
-                ws.grp_expert[g] = e;
-                ws.grp_start[g] = off;
-                ws.grp_count[g] = c;
-                g++;
+    const int base = s_warp[warp] + inc - local;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) v[i] += base;
+    __syncthreads();
+}
+
+// one block: bases over blocks and experts, the list of non-empty groups (the
+// shared expert's first: it is the heaviest), the list of token tiles, counters reset
+constexpr int SORT_EPT = 4;   // experts per thread in the scans (n_expert <= 1024)
+__device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, int k,
+                          int has_shared) {
+    __shared__ int s_warp[32];
+    __shared__ int s_total[3];
+    int cnt[SORT_EPT], off[SORT_EPT], act[SORT_EPT], til[SORT_EPT];
+    const int e0 = threadIdx.x * SORT_EPT;
+#pragma unroll
+    for (int i = 0; i < SORT_EPT; i++) {
+        const int e = e0 + i;
+        int run = 0;
+        if (e < n_expert)
+            for (int b = 0; b < nblk; b++) {
+                int c = ws.blk_counts[(size_t)b * n_expert + e];
+                ws.blk_counts[(size_t)b * n_expert + e] = run;
+                run += c;
             }
-            off += c;
+        cnt[i] = run;
+        off[i] = run;
+        act[i] = run > 0;
+        til[i] = (run + SORT_TILE - 1) / SORT_TILE;
+    }
+    block_exclusive_scan<SORT_EPT>(off, s_warp, &s_total[0]);
+    block_exclusive_scan<SORT_EPT>(act, s_warp, &s_total[1]);
+    block_exclusive_scan<SORT_EPT>(til, s_warp, &s_total[2]);
+    const int g_sh = has_shared ? 1 : 0;
+    const int t_sh = has_shared ? (n + SORT_TILE - 1) / SORT_TILE : 0;
+#pragma unroll
+    for (int i = 0; i < SORT_EPT; i++) {
+        const int e = e0 + i;
+        if (e >= n_expert) continue;
+        ws.counts[e] = cnt[i];
+        ws.offsets[e] = off[i];
+        if (cnt[i]) {
+            const int g = g_sh + act[i];
+            ws.grp_expert[g] = e;
+            ws.grp_start[g] = off[i];
+            ws.grp_count[g] = cnt[i];
+            const int nt = (cnt[i] + SORT_TILE - 1) / SORT_TILE;
+            for (int j = 0; j < nt; j++) {
+                ws.tile_group[t_sh + til[i] + j] = g;
+                ws.tile_t0[t_sh + til[i] + j] = j * SORT_TILE;
+            }
         }
-        ws.offsets[n_expert] = off;
-        *ws.n_groups = g;
+    }
+    for (int j = threadIdx.x; j < t_sh; j += blockDim.x) {
+        ws.tile_group[j] = 0;
+        ws.tile_t0[j] = j * SORT_TILE;
+    }
+    if (threadIdx.x == 0) {
+        if (has_shared) {
+            ws.grp_expert[0] = n_expert;
+            ws.grp_start[0] = n * k;
+            ws.grp_count[0] = n;
+        }
+        ws.offsets[n_expert] = s_total[0];
+        *ws.n_groups = g_sh + s_total[1];
+        ws.n_tiles[0] = t_sh + s_total[2];
+        ws.n_tiles[1] = t_sh;
         for (int i = 0; i < 4; i++) ws.work_ctr[i] = 0;
     }
     __syncthreads();

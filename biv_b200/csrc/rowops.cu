@@ -10,7 +10,7 @@ namespace bivmoe {
 // Q8Act::quantize_into (quant.rs:368-394): one warp per 32-value block.
 __global__ void __launch_bounds__(256)
 quantize_rows_kernel(const float* __restrict__ x, int64_t n_blocks, int8_t* __restrict__ q,
-                     float* __restrict__ d, float* __restrict__ s) {
+                     float2* __restrict__ ds) {
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int64_t stride = (int64_t)gridDim.x * (blockDim.x >> 5);
@@ -18,16 +18,16 @@ quantize_rows_kernel(const float* __restrict__ x, int64_t n_blocks, int8_t* __re
         float dd, ss;
         int qi = q8_quantize_lane(x[b * 32 + lane], dd, ss);
         q[b * 32 + lane] = (int8_t)qi;
-        if (lane == 0) { d[b] = dd; s[b] = ss; }
+        if (lane == 0) ds[b] = make_float2(dd, ss);
     }
 }
 
 cudaError_t launch_quantize_rows(const LaunchCfg& c, const float* x, int rows, int cols, int8_t* q,
-                                 float* d, float* s) {
+                                 float2* ds) {
     int64_t nb = (int64_t)rows * cols / 32;
     int blocks = (int)((nb + 7) / 8);
     if (blocks > c.sm_count * 16) blocks = c.sm_count * 16;
-    quantize_rows_kernel<<<blocks, 256, 0, c.stream>>>(x, nb, q, d, s);
+    quantize_rows_kernel<<<blocks, 256, 0, c.stream>>>(x, nb, q, ds);
     count_launch();
     return cudaGetLastError();
 }
