@@ -34,7 +34,7 @@ struct Arena {   // carves 256-byte aligned pieces out of one allocation
     uint8_t* base = nullptr;
     template <class T> T* take(size_t count) {
         size_t bytes = (count * sizeof(T) + 255) & ~(size_t)255;
-        T* p = base ? (T*)(base + off) : nullptr;
+        T* p = base && count ? (T*)(base + off) : nullptr;
         off += bytes;
         return p;
     }
@@ -85,11 +85,17 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
     w.n_tiles = a.take<int32_t>(2);
     w.work_ctr = a.take<uint32_t>(4);
     w.status = a.take<int32_t>(4);
-    w.act_q = a.take<int8_t>(N * e);
-    w.act_ds = a.take<float2>(N * e / 32);
-    w.mid = a.take<float>((P + N) * mid);
-    w.mid_q = a.take<int8_t>((P + N) * mid);
-    w.mid_ds = a.take<float2>((P + N) * mid / 32);
+    const size_t R = P + N + 8;   // the last tile of a group may read 7 rows past it
+    w.act_rows = (int)R;
+    const bool qact = !type_uses_f32_act(L->gate.ty) || (L->has_shared && !type_uses_f32_act(L->sh_gate.ty));
+    const bool fact = type_uses_f32_act(L->gate.ty) || (L->has_shared && type_uses_f32_act(L->sh_gate.ty));
+    const bool qmid = !type_uses_f32_act(L->down.ty) || (L->has_shared && !type_uses_f32_act(L->sh_down.ty));
+    w.act_q = a.take<int8_t>(qact ? R * e : 0);
+    w.act_ds = a.take<float2>(qact ? R * e / 32 : 0);
+    w.act_f = a.take<float>(fact ? R * e : 0);
+    w.mid = a.take<float>(R * mid);
+    w.mid_q = a.take<int8_t>(qmid ? R * mid : 0);
+    w.mid_ds = a.take<float2>(qmid ? R * mid / 32 : 0);
     w.pair_out = a.take<float>((P + N) * e);
     w.h_norm = a.take<float>(N * e);
 }
@@ -118,34 +124,35 @@ static int check_stack(std::string* errp, const char* name, const bivmoe_experts
     return BIVMOE_OK;
 }
 
-// copies one stack to the device in the device row layout
+// copies one stack to the device and repacks it into the tiled layout
 static int upload_stack(bivmoe_layer* L, std::string* errp, const bivmoe_experts& s, DevStack* out) {
-    const int64_t grb = gguf_row_bytes(s.ggml_type, s.cols), drb = dev_row_bytes(s.ggml_type, s.cols);
+    const int64_t grb = gguf_row_bytes(s.ggml_type, s.cols);
     const int64_t mat = s.rows * grb;
     const int64_t stride = s.stride_bytes ? s.stride_bytes : mat;
+    const SliceGeom g = slice_geom(s.ggml_type);
     out->ty = s.ggml_type;
     out->cols = (int)s.cols; out->rows = (int)s.rows; out->n = (int)s.n;
-    out->row_bytes = drb;
-    out->expert_bytes = s.rows * drb;
+    out->slice_bytes = g.sl;
+    out->nslices = (int)(s.cols / g.elems);
+    out->expert_bytes = s.rows * (int64_t)out->nslices * g.sl;
     const size_t dev_bytes = (size_t)(s.n * out->expert_bytes);
     void* p = nullptr;
     CU(cudaMalloc(&p, dev_bytes));
     L->allocs.push_back(p);
     L->weight_bytes += dev_bytes;
     out->data = (uint8_t*)p;
-    const uint8_t* src = (const uint8_t*)s.data + s.offset_bytes;
-    const bool repack = s.ggml_type == BIVMOE_Q8_0 || s.ggml_type == BIVMOE_Q6_K;
-    if (!repack) {
-        CU(cudaMemcpy2D(p, (size_t)mat, src, (size_t)stride, (size_t)mat, (size_t)s.n,
-                        cudaMemcpyHostToDevice));
-        return BIVMOE_OK;
+    if (s.ggml_type == BIVMOE_Q6_K) {
+        const size_t sb = (size_t)(s.n * s.rows) * out->nslices * 2;
+        CU(cudaMalloc(&p, sb));
+        L->allocs.push_back(p);
+        L->weight_bytes += sb;
+        out->side = (uint16_t*)p;
     }
     void* staging = nullptr;
     CU(cudaMalloc(&staging, (size_t)(s.n * mat)));
-    cudaError_t e1 = cudaMemcpy2D(staging, (size_t)mat, src, (size_t)stride, (size_t)mat,
-                                  (size_t)s.n, cudaMemcpyHostToDevice);
-    if (e1 == cudaSuccess)
-        e1 = launch_repack(s.ggml_type, (const uint8_t*)staging, out->data, s.n * s.rows, s.cols, 0);
+    cudaError_t e1 = cudaMemcpy2D(staging, (size_t)mat, (const uint8_t*)s.data + s.offset_bytes,
+                                  (size_t)stride, (size_t)mat, (size_t)s.n, cudaMemcpyHostToDevice);
+    if (e1 == cudaSuccess) e1 = launch_repack(*out, (const uint8_t*)staging, 0);
     if (e1 == cudaSuccess) e1 = cudaDeviceSynchronize();
     cudaFree(staging);
     CU(e1);
@@ -289,8 +296,7 @@ static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int 
     mark(c, EV_TOPK);
     CU(launch_sort(c, L->ws));
     mark(c, EV_SORT);
-    if (!type_uses_f32_act(L->gate.ty) || (L->has_shared && !type_uses_f32_act(L->sh_gate.ty)))
-        CU(launch_quantize_rows(c, h, n, L->e, L->ws.act_q, L->ws.act_ds));
+    CU(launch_dispatch(c, h, L->ws, L->ws.act_q != nullptr, L->ws.act_f != nullptr));
     mark(c, EV_QUANT);
     CU(launch_experts(c, h, L->gate, L->up, L->down, L->sh_gate, L->sh_up, L->sh_down, L->ws));
     mark(c, EV_DOWN);
@@ -416,29 +422,50 @@ int bivmoe_tap(bivmoe_layer* L, int32_t which, void* dst, size_t bytes) {
         case BIVMOE_TAP_WEIGHTS: return copy_out(L, dst, w.weights, bytes, P * 4);
         case BIVMOE_TAP_COUNTS: return copy_out(L, dst, w.counts, bytes, ne * 4);
         case BIVMOE_TAP_ORDER: return copy_out(L, dst, w.order, bytes, P * 4);
-        case BIVMOE_TAP_ACT_Q: return copy_out(L, dst, w.act_q, bytes, n * e);
+        case BIVMOE_TAP_ACT_Q:
         case BIVMOE_TAP_ACT_D:
         case BIVMOE_TAP_ACT_S: {
-            const size_t nb = n * e / 32;
-            if (bytes != nb * 4) return set_err(errp, BIVMOE_ERR_ARGUMENT, "tap buffer size mismatch");
-            std::vector<float> tmp(nb * 2);
-            CU(cudaMemcpy(tmp.data(), w.act_ds, nb * 8, cudaMemcpyDeviceToHost));
-            for (size_t i = 0; i < nb; i++)
-                ((float*)dst)[i] = tmp[2 * i + (which == BIVMOE_TAP_ACT_S ? 1 : 0)];
+            // the tokens' rows are positions P.. of the slice-major arrays
+            if (!w.act_q) return set_err(errp, BIVMOE_ERR_ARGUMENT, "no quantised activations");
+            const size_t R = w.act_rows, nsl = e / 256;
+            const bool q = which == BIVMOE_TAP_ACT_Q;
+            if (bytes != (q ? n * e : n * e / 32 * 4))
+                return set_err(errp, BIVMOE_ERR_ARGUMENT, "tap buffer size mismatch");
+            std::vector<int8_t> tq(q ? R * e : 0);
+            std::vector<float> td(q ? 0 : R * e / 32 * 2);
+            if (q) CU(cudaMemcpy(tq.data(), w.act_q, tq.size(), cudaMemcpyDeviceToHost));
+            else CU(cudaMemcpy(td.data(), w.act_ds, td.size() * 4, cudaMemcpyDeviceToHost));
+            for (size_t t = 0; t < n; t++)
+                for (size_t sl = 0; sl < nsl; sl++) {
+                    const size_t row = sl * R + P + t;
+                    if (q) memcpy((int8_t*)dst + t * e + sl * 256, tq.data() + row * 256, 256);
+                    else
+                        for (int b = 0; b < 8; b++)
+                            ((float*)dst)[t * (e / 32) + sl * 8 + b] =
+                                td[(row * 8 + b) * 2 + (which == BIVMOE_TAP_ACT_S ? 1 : 0)];
+                }
             return BIVMOE_OK;
         }
-        case BIVMOE_TAP_MID:
-        case BIVMOE_TAP_PAIR_OUT: {
-            const bool m = which == BIVMOE_TAP_MID;
-            const size_t width = m ? (size_t)L->ff : e, stride = m ? mid : e;
-            if (bytes != P * width * 4)
-                return set_err(errp, BIVMOE_ERR_ARGUMENT, "tap buffer size mismatch");
-            std::vector<float> tmp(P * stride);
+        case BIVMOE_TAP_MID: {
+            const size_t R = w.act_rows, ffw = L->ff;
+            if (bytes != P * ffw * 4) return set_err(errp, BIVMOE_ERR_ARGUMENT, "tap buffer size mismatch");
+            std::vector<float> tmp(R * mid);
             std::vector<int32_t> pos(P);
-            CU(cudaMemcpy(tmp.data(), m ? w.mid : w.pair_out, tmp.size() * 4, cudaMemcpyDeviceToHost));
+            CU(cudaMemcpy(tmp.data(), w.mid, tmp.size() * 4, cudaMemcpyDeviceToHost));
             CU(cudaMemcpy(pos.data(), w.pos_of, P * 4, cudaMemcpyDeviceToHost));
             for (size_t p = 0; p < P; p++)
-                memcpy((float*)dst + p * width, tmp.data() + (size_t)pos[p] * stride, width * 4);
+                for (size_t sl = 0; sl < ffw / 64; sl++)
+                    memcpy((float*)dst + p * ffw + sl * 64, tmp.data() + (sl * R + pos[p]) * 64, 256);
+            return BIVMOE_OK;
+        }
+        case BIVMOE_TAP_PAIR_OUT: {
+            if (bytes != P * e * 4) return set_err(errp, BIVMOE_ERR_ARGUMENT, "tap buffer size mismatch");
+            std::vector<float> tmp(P * e);
+            std::vector<int32_t> pos(P);
+            CU(cudaMemcpy(tmp.data(), w.pair_out, tmp.size() * 4, cudaMemcpyDeviceToHost));
+            CU(cudaMemcpy(pos.data(), w.pos_of, P * 4, cudaMemcpyDeviceToHost));
+            for (size_t p = 0; p < P; p++)
+                memcpy((float*)dst + p * e, tmp.data() + (size_t)pos[p] * e, e * 4);
             return BIVMOE_OK;
         }
         case BIVMOE_TAP_SHARED_OUT:
@@ -469,18 +496,13 @@ int bivmoe_tap_block_dots(bivmoe_layer* L, int32_t matrix, int32_t expert, int32
     int32_t* dots = nullptr;
     CU(cudaMalloc((void**)&dots, (size_t)nb * 4));
     cudaError_t ce = cudaSuccess;
-    const int8_t* act = nullptr;
-    if (!is_down) {
-        act = L->ws.act_q + (size_t)act_row * L->e;
-    } else {
-        // the Q8 row of the mid vector the down product consumed
-        int32_t pos = P + act_row;
-        if (!shared) ce = cudaMemcpy(&pos, L->ws.pos_of + act_row, 4, cudaMemcpyDeviceToHost);
-        act = L->ws.mid_q + (size_t)pos * std::max(L->ff, L->ff_sh);
-    }
+    // gate/up rows meet the token's Q8 row of h (position P + token); down rows the
+    // Q8 row of the pair's mid vector at the pair's position
+    int32_t pos = P + act_row;
+    if (is_down && !shared) ce = cudaMemcpy(&pos, L->ws.pos_of + act_row, 4, cudaMemcpyDeviceToHost);
     if (ce == cudaSuccess)
-        ce = launch_block_dots(m.ty, m.data + (size_t)expert * m.expert_bytes + (size_t)row * m.row_bytes,
-                               m.cols, act, dots, 0);
+        ce = launch_block_dots(m, expert, row, is_down ? L->ws.mid_q : L->ws.act_q, L->ws.act_rows,
+                               pos, dots, 0);
     if (ce == cudaSuccess) ce = cudaMemcpy(out, dots, (size_t)nb * 4, cudaMemcpyDeviceToHost);
     cudaFree(dots);
     CU(ce);
@@ -490,7 +512,7 @@ int bivmoe_tap_block_dots(bivmoe_layer* L, int32_t matrix, int32_t expert, int32
 int bivmoe_numerics(const bivmoe_layer* L, char* buf, size_t len) {
     if (!L || !buf || !len) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or buffer");
     snprintf(buf, len,
-             "kind=cuda device=%s sms=%d repack=v%d experts=dp4a-two-rows-per-lane/warp-ring-bulk-copy "
+             "kind=cuda device=%s sms=%d repack=v%d experts=dp4a-two-rows-per-lane/warp-ring-bulk-copy/tiled-weights "
              "router=f32-avx2-order combine=ordered-fma types=%d/%d/%d",
              L->device_name.c_str(), L->sm_count, kRepackVersion, L->gate.ty, L->up.ty, L->down.ty);
     return BIVMOE_OK;

@@ -8,29 +8,31 @@
 namespace bivmoe {
 
 // ---------------------------------------------------------------------------
-// Device layout of weight rows.  GGUF blocks whose size is not a multiple of
-// 16 bytes are split into planes per row at upload so that every row starts on
-// a 16-byte boundary and bulk copies and 128-bit loads apply:
-//   Q8_0  [qs: K int8][d: K/32 f16]                       K + K/16 bytes (= 34*K/32)
-//   Q4_K  native 144-byte blocks {d, dmin, scales[12], qs[128]}
-//   Q5_K  native 176-byte blocks {d, dmin, scales[12], qh[32], qs[128]}
-//   Q6_K  [ql: nb*128][qh: nb*64][scales: nb*16][d: nb f16, padded to 16]
-//         (nb = K/256; 1680 bytes at K=2048 as in GGUF, 432 instead of 420 at K=512)
-//   BF16, F32 native
-constexpr int kRepackVersion = 1;
+// Device layout of the weights.  A matrix [rows][K] is cut into tiles of 32
+// rows by one K-slice; a tile is what one pipeline stage of the expert kernels
+// consumes, so it is stored contiguously and arrives with one bulk copy, and
+// the tiles of a row group follow each other (nslices * 32 * SL contiguous
+// bytes).  Inside a tile the bytes are unit-major, [SL/16 units][32 rows][16
+// bytes]: the lane that owns row r reads unit u at (u*32 + r)*16, so the 32
+// lanes of a warp read 512 consecutive bytes, free of bank conflicts.
+// The repack is a permutation of the GGUF bytes (nothing is widened):
+//   type   K-slice   SL   the slice's bytes of one row
+//   Q8_0   256       272  8 blocks' int8 quants (256) then their 8 f16 scales (16)
+//   Q4_K   256       144  the 144-byte super-block {d, dmin, scales[12], qs[128]}
+//   Q5_K   256       176  the 176-byte super-block {d, dmin, scales[12], qh[32], qs[128]}
+//   Q6_K   256       208  ql[128], qh[64], scales[16]; the f16 d goes to a side plane [rows][K/256]
+//   BF16   64        128  64 values
+constexpr int kRepackVersion = 2;
 
-__host__ __device__ inline int64_t dev_row_bytes(int ty, int64_t cols) {
+struct SliceGeom { int elems, sl; };
+__host__ __device__ inline SliceGeom slice_geom(int ty) {
     switch (ty) {
-        case BIVMOE_F32: return cols * 4;
-        case BIVMOE_BF16: return cols * 2;
-        case BIVMOE_Q8_0: return cols + cols / 16;
-        case BIVMOE_Q4_K: return cols / 256 * 144;
-        case BIVMOE_Q5_K: return cols / 256 * 176;
-        case BIVMOE_Q6_K: {
-            int64_t nb = cols / 256;
-            return nb * 208 + ((nb * 2 + 15) / 16) * 16;
-        }
-        default: return -1;
+        case BIVMOE_Q8_0: return {256, 272};
+        case BIVMOE_Q4_K: return {256, 144};
+        case BIVMOE_Q5_K: return {256, 176};
+        case BIVMOE_Q6_K: return {256, 208};
+        case BIVMOE_BF16: return {64, 128};
+        default: return {0, 0};
     }
 }
 __host__ __device__ inline int64_t gguf_row_bytes(int ty, int64_t cols) {
@@ -51,11 +53,20 @@ __host__ __device__ inline bool type_uses_f32_act(int ty) {  // quant.rs:75-77
 struct DevStack {          // one stack of expert matrices on the device
     int ty = 0;
     int cols = 0, rows = 0, n = 0;
+    int slice_bytes = 0;       // SL
+    int nslices = 0;           // cols / slice elems
     uint8_t* data = nullptr;
-    int64_t row_bytes = 0;     // dev_row_bytes
-    int64_t expert_bytes = 0;  // rows * row_bytes
+    uint16_t* side = nullptr;  // Q6_K: f16 d per (row, super-block)
+    int64_t expert_bytes = 0;  // rows * nslices * SL
+    // first byte of the tile of row group rt (32 rows), slice 0, of expert e
+    __host__ __device__ const uint8_t* tile(int64_t e, int rt) const {
+        return data + e * expert_bytes + (int64_t)rt * nslices * 32 * slice_bytes;
+    }
 };
 
+// Activation rows are kept "slice-major" so that the K-slice of 8 consecutive
+// rows is contiguous: quantised rows as q [K/256][R][256] int8 and
+// ds [K/256][R][8] (d, s); float rows as [K/64][R][64] f32.  R = P + n + 8.
 // Per-forward scratch.  P = n * k routed pairs; "positions" 0..P are the pairs
 // in expert-sorted order, positions P..P+n are the tokens of the shared expert.
 struct Workspace {
@@ -76,11 +87,13 @@ struct Workspace {
     int32_t* n_tiles;    // [2] all tiles; the shared group's tiles (they come first)
     uint32_t* work_ctr;  // [4] dynamic work counters, zeroed by the sort
     int32_t* status;     // [4] device-side error flags (0 = ok)
-    int8_t* act_q;       // [n][e]
-    float2* act_ds;      // [n][e/32] (d, s) per block
-    float* mid;          // [P + n][ff] silu(gate)*up, by position
-    int8_t* mid_q;       // [P + n][ff] its Q8 rows (quantised down types)
-    float2* mid_ds;      // [P + n][ff/32]
+    int act_rows;        // R: rows of every slice-major activation array
+    int8_t* act_q;       // Q8 rows of h by position (positions P.. are the tokens), slice-major
+    float2* act_ds;
+    float* act_f;        // f32 rows of h by position, slice-major (float-activation types)
+    float* mid;          // silu(gate)*up by position, slice-major f32
+    int8_t* mid_q;       // its Q8 rows (quantised down types), slice-major
+    float2* mid_ds;
     float* pair_out;     // [P + n][e], by position
     float* h_norm;       // [n][e] rms-normed rows (forward_stack)
 };
@@ -101,18 +114,17 @@ cudaError_t launch_router(const LaunchCfg& c, const float* router_dev /*[n_exper
                           const float* h, const Workspace& ws);
 cudaError_t launch_route_topk(const LaunchCfg& c, const Workspace& ws);
 cudaError_t launch_sort(const LaunchCfg& c, const Workspace& ws);
-cudaError_t launch_quantize_rows(const LaunchCfg& c, const float* x, int rows, int cols,
-                                 int8_t* q, float2* ds);
+cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace& ws, bool quant,
+                            bool f32);
 cudaError_t launch_experts(const LaunchCfg& c, const float* h, const DevStack& gate,
                            const DevStack& up, const DevStack& down, const DevStack& sh_gate,
                            const DevStack& sh_up, const DevStack& sh_down, const Workspace& ws);
 cudaError_t launch_combine(const LaunchCfg& c, const Workspace& ws, float* out, int accumulate);
 cudaError_t launch_rms_norm(const LaunchCfg& c, const float* x, const float* w, float eps,
                             float* out);
-cudaError_t launch_repack(int ty, const uint8_t* gguf_rows, uint8_t* dev_rows, int64_t n_rows,
-                          int64_t cols, cudaStream_t stream);
-cudaError_t launch_block_dots(int ty, const uint8_t* dev_row, int64_t cols, const int8_t* xq,
-                              int32_t* out, cudaStream_t stream);
+cudaError_t launch_repack(const DevStack& st, const uint8_t* gguf_rows, cudaStream_t stream);
+cudaError_t launch_block_dots(const DevStack& st, int expert, int row, const int8_t* act_q,
+                              int act_rows, int pos, int32_t* out, cudaStream_t stream);
 bool experts_supported(int ty, int cols, int rows, bool is_down);
 
 void count_launch(int n = 1);

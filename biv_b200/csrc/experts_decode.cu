@@ -8,8 +8,9 @@
 // Design.  The kernel is a grid of independent warps, one block per SM.  A
 // warp pulls work items (tile of <= 8 tokens of one group, chunk of weight
 // rows) from a counter and streams the chunk's rows from HBM through its own
-// two-slot ring in shared memory: per stage one K-slice of 64 rows (and the
-// matching K-slice of the tile's activation rows) arrives by bulk copies
+// two-slot ring in shared memory: per stage one K-slice of 64 rows (two 32-row
+// tiles, each contiguous in the device layout of common.cuh) and the matching
+// K-slice of the tile's 8 activation rows arrive by four bulk copies
 // (cp.async.bulk) on the warp's own mbarrier, so warps never synchronise with
 // each other and the copies of one stage overlap the arithmetic of the other,
 // across item boundaries too.  A lane owns two weight rows (gate row r and up
@@ -36,14 +37,14 @@ enum { MODE_GATEUP = 0, MODE_DOWN = 1 };
 struct ExpertArgs {
     DevStack w0, w1;       // routed stacks: gate, up (MODE_GATEUP) or down, - (MODE_DOWN)
     DevStack s0, s1;       // the shared expert's
-    const float* x_f32;    // float-activation types: h [n][K] (GATEUP) or mid [P+n][mid_stride] (DOWN)
-    const int8_t* x_q;     // quantised types: Q8 rows, by token (GATEUP) or by position (DOWN)
-    const float2* x_ds;    // their (d, s) per block
-    int x_stride;          // elements per activation row
-    float* out;            // GATEUP: mid [P+n][mid_stride]; DOWN: pair_out [P+n][rows]
-    int8_t* out_q;         // GATEUP with a quantised down type: Q8 rows of mid
+    // activations by position, slice-major (common.cuh): rows of h for GATEUP, of mid for DOWN
+    const float* x_f32;    // float-activation types
+    const int8_t* x_q;     // quantised types
+    const float2* x_ds;
+    int act_rows;          // R
+    float* out;            // GATEUP: mid f32, slice-major; DOWN: pair_out [P+n][rows]
+    int8_t* out_q;         // GATEUP with a quantised down type: Q8 rows of mid, slice-major
     float2* out_ds;
-    const int32_t* order;
     const int32_t* grp_expert;
     const int32_t* grp_start;
     const int32_t* grp_count;
@@ -53,7 +54,6 @@ struct ExpertArgs {
     uint32_t* work_ctr;
     int32_t* status;
     int n, k, n_expert;
-    int mid_stride;
     int tiles_mode;        // 0: every tile, 1: skip the shared group's, 2: only the shared group's
     int chunks;            // row chunks per group
 };
@@ -100,15 +100,14 @@ __device__ __forceinline__ void fence_proxy_async() {
 }
 
 // ---------------------------------------------------------------------------
-// Per-type geometry of a stage and the arithmetic of one staged K-slice.
-//   ELEMS   columns per stage
-//   STRIDE  shared-memory bytes per weight row per stage; an odd number of
-//           16-byte units, so lanes that own consecutive rows hit distinct
-//           bank groups on 128-bit loads
-//   ROW_TX  bytes the bulk copies of one row deliver
+// Per-type arithmetic of one staged K-slice.  `wa` / `wb` point at this lane's
+// row inside the two staged tiles (tile + lane*16); unit u of the row is 512*u
+// further (unit-major tiles), so byte `off` of the row's slice is WU(w, off).
+//   ELEMS   columns per stage,  SL  bytes per row per stage
 //   WARPS   warps per block that fit two stages each in 227 KB
-//   Side    per-row words too small for a bulk copy; the lane fetches them
-//           with a plain load when it issues the stage
+//   Side    per-row words kept outside the tiles (Q6_K's f16 d), fetched with a
+//           plain load when the stage is issued
+#define WU(w, off) ((w) + ((((off)) >> 4) << 9) + ((off) & 15))
 #define LO4(v) ((int)((v) & 0x0F0F0F0Fu))
 #define HI4(v) ((int)(((v) >> 4) & 0x0F0F0F0Fu))
 
@@ -123,8 +122,9 @@ __device__ __forceinline__ int dot8(const int (&w)[8], const int4& a0, const int
     s = dp4a_s8(w[7], a1.w, s);
     return s;
 }
-__device__ __forceinline__ void load8(const uint8_t* p, uint32_t (&v)[8]) {
-    const uint4 a = *(const uint4*)p, b = *(const uint4*)(p + 16);
+// the 32 bytes at offset `off` (a multiple of 16) of this lane's row slice
+__device__ __forceinline__ void load8(const uint8_t* w, int off, uint32_t (&v)[8]) {
+    const uint4 a = *(const uint4*)WU(w, off), b = *(const uint4*)WU(w, off + 16);
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
     v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
@@ -135,27 +135,23 @@ template <int TY> struct Fmt;
 
 // ---- Q8_0 (quant.rs:599-607): term = d_w * d_x * sum(q_w * q_x) ------------
 template <> struct Fmt<BIVMOE_Q8_0> {
-    static constexpr int ELEMS = 256, STRIDE = 272, WARPS = 5, ROW_TX = 272;
+    static constexpr int ELEMS = 256, SL = 272, WARPS = 5;
     static constexpr bool F32ACT = false;
     using Side = NoSide;
-    __device__ static Side side(const uint8_t*, int, int) { return {}; }
-    __device__ static void issue_row(uint8_t* dst, const uint8_t* row, int K, int s, uint64_t* bar) {
-        bulk_g2s(dst, row + 256 * (size_t)s, 256, bar);             // quants
-        bulk_g2s(dst + 256, row + K + 16 * (size_t)s, 16, bar);     // the 8 f16 scales
-    }
+    __device__ static Side side(const uint16_t*, int) { return {}; }
     __device__ static void accum2(const uint8_t* wa, const uint8_t* wb, Side, Side,
                                   const int8_t* xq, const float2* xds, int cnt,
                                   float (&accA)[EX_TT], float (&accB)[EX_TT]) {
 #pragma unroll 2
         for (int b = 0; b < 8; b++) {
             uint32_t ua[8], ub[8];
-            load8(wa + 32 * b, ua);
-            load8(wb + 32 * b, ub);
+            load8(wa, 32 * b, ua);
+            load8(wb, 32 * b, ub);
             int qa[8], qb[8];
 #pragma unroll
             for (int i = 0; i < 8; i++) { qa[i] = (int)ua[i]; qb[i] = (int)ub[i]; }
-            const float da = __half2float(*(const __half*)(wa + 256 + 2 * b));
-            const float db = __half2float(*(const __half*)(wb + 256 + 2 * b));
+            const float da = __half2float(*(const __half*)WU(wa, 256 + 2 * b));
+            const float db = __half2float(*(const __half*)WU(wb, 256 + 2 * b));
 #pragma unroll
             for (int t = 0; t < EX_TT; t++) {
                 if (t < cnt) {
@@ -173,29 +169,25 @@ template <> struct Fmt<BIVMOE_Q8_0> {
 // ---- Q4_K / Q5_K (quant.rs:609-649): per sub-block
 //      d*sc*d_x*sum(q*q_x) - dmin*m*s_x ; Q5_K adds bit sb of qh[l] as value bit 4
 template <int TY> struct FmtK45 {
-    static constexpr int BS = TY == BIVMOE_Q4_K ? 144 : 176;
     static constexpr int QOFF = TY == BIVMOE_Q4_K ? 16 : 48;
-    static constexpr int ELEMS = 256, STRIDE = BS, WARPS = 8, ROW_TX = BS;
+    static constexpr int ELEMS = 256, SL = TY == BIVMOE_Q4_K ? 144 : 176, WARPS = 8;
     static constexpr bool F32ACT = false;
     using Side = NoSide;
-    __device__ static Side side(const uint8_t*, int, int) { return {}; }
-    __device__ static void issue_row(uint8_t* dst, const uint8_t* row, int, int s, uint64_t* bar) {
-        bulk_g2s(dst, row + (size_t)BS * s, BS, bar);
-    }
+    __device__ static Side side(const uint16_t*, int) { return {}; }
     struct Hdr { float d, dmin; K4Scales sc; uint32_t qh[8]; };
-    __device__ static Hdr header(const uint8_t* blk) {
+    __device__ static Hdr header(const uint8_t* w) {
         Hdr h;
-        const uint4 v = *(const uint4*)blk;
+        const uint4 v = *(const uint4*)w;
         const __half2 dd = *(const __half2*)&v.x;
         h.d = __low2float(dd);
         h.dmin = __high2float(dd);
         h.sc = unpack_k4_scales(v.y, v.z, v.w);
-        if (TY == BIVMOE_Q5_K) load8(blk + 16, h.qh);
+        if (TY == BIVMOE_Q5_K) load8(w, 16, h.qh);
         return h;
     }
-    __device__ static void unpack(const uint8_t* blk, const Hdr& h, int j, int (&lo)[8], int (&hi)[8]) {
+    __device__ static void unpack(const uint8_t* w, const Hdr& h, int j, int (&lo)[8], int (&hi)[8]) {
         uint32_t qv[8];
-        load8(blk + QOFF + 32 * j, qv);
+        load8(w, QOFF + 32 * j, qv);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             lo[i] = LO4(qv[i]);
@@ -241,20 +233,14 @@ template <int TY> struct FmtK45 {
 template <> struct Fmt<BIVMOE_Q4_K> : FmtK45<BIVMOE_Q4_K> {};
 template <> struct Fmt<BIVMOE_Q5_K> : FmtK45<BIVMOE_Q5_K> {};
 
-// ---- Q6_K (quant.rs:651-686), device row planes [ql][qh][scales][d]: per
+// ---- Q6_K (quant.rs:651-686), slice = ql[128] qh[64] scales[16], d aside: per
 //      32-block d * d_x * (sc[2g]*sum16 + sc[2g+1]*sum16), 6-bit values minus 32
 template <> struct Fmt<BIVMOE_Q6_K> {
-    static constexpr int ELEMS = 256, STRIDE = 208, WARPS = 7, ROW_TX = 208;
+    static constexpr int ELEMS = 256, SL = 208, WARPS = 7;
     static constexpr bool F32ACT = false;
     struct Side { float d; };     // the super-block's f16 scale
-    __device__ static Side side(const uint8_t* row, int K, int s) {
-        return {__half2float(*(const __half*)(row + (size_t)(K / 256) * 208 + 2 * s))};
-    }
-    __device__ static void issue_row(uint8_t* dst, const uint8_t* row, int K, int s, uint64_t* bar) {
-        const size_t nb = K / 256;
-        bulk_g2s(dst, row + 128 * (size_t)s, 128, bar);                     // ql
-        bulk_g2s(dst + 128, row + nb * 128 + 64 * (size_t)s, 64, bar);      // qh
-        bulk_g2s(dst + 192, row + nb * 192 + 16 * (size_t)s, 16, bar);      // int8 scales
+    __device__ static Side side(const uint16_t* row_side, int s) {
+        return {__half2float(__ushort_as_half(row_side[s]))};
     }
     __device__ static void unpack(const uint32_t (&l0)[8], const uint32_t (&l1)[8],
                                   const uint32_t (&hh)[8], int kq, int (&q)[8]) {
@@ -285,9 +271,9 @@ template <> struct Fmt<BIVMOE_Q6_K> {
 #pragma unroll
         for (int n = 0; n < 2; n++) {
             uint32_t al0[8], al1[8], ah[8], bl0[8], bl1[8], bh[8];
-            load8(wa + 64 * n, al0); load8(wa + 64 * n + 32, al1); load8(wa + 128 + 32 * n, ah);
-            load8(wb + 64 * n, bl0); load8(wb + 64 * n + 32, bl1); load8(wb + 128 + 32 * n, bh);
-            const uint2 asc = *(const uint2*)(wa + 192 + 8 * n), bsc = *(const uint2*)(wb + 192 + 8 * n);
+            load8(wa, 64 * n, al0); load8(wa, 64 * n + 32, al1); load8(wa, 128 + 32 * n, ah);
+            load8(wb, 64 * n, bl0); load8(wb, 64 * n + 32, bl1); load8(wb, 128 + 32 * n, bh);
+            const uint2 asc = *(const uint2*)WU(wa, 192 + 8 * n), bsc = *(const uint2*)WU(wb, 192 + 8 * n);
 #pragma unroll
             for (int kq = 0; kq < 4; kq++) {
                 int qa[8], qb[8];
@@ -312,13 +298,10 @@ template <> struct Fmt<BIVMOE_Q6_K> {
 
 // ---- BF16 weights meet f32 activations (quant.rs:509-521, 1229-1256) -------
 template <> struct Fmt<BIVMOE_BF16> {
-    static constexpr int ELEMS = 64, STRIDE = 144, WARPS = 8, ROW_TX = 128;
+    static constexpr int ELEMS = 64, SL = 128, WARPS = 8;
     static constexpr bool F32ACT = true;
     using Side = NoSide;
-    __device__ static Side side(const uint8_t*, int, int) { return {}; }
-    __device__ static void issue_row(uint8_t* dst, const uint8_t* row, int, int s, uint64_t* bar) {
-        bulk_g2s(dst, row + 128 * (size_t)s, 128, bar);
-    }
+    __device__ static Side side(const uint16_t*, int) { return {}; }
     __device__ static void widen(const uint4& v, float (&w)[8]) {
         w[0] = __uint_as_float(v.x << 16); w[1] = __uint_as_float(v.x & 0xFFFF0000u);
         w[2] = __uint_as_float(v.y << 16); w[3] = __uint_as_float(v.y & 0xFFFF0000u);
@@ -336,8 +319,8 @@ template <> struct Fmt<BIVMOE_BF16> {
 #pragma unroll 2
         for (int u = 0; u < 8; u++) {
             float fa[8], fb[8];
-            widen(*(const uint4*)(wa + 16 * u), fa);
-            widen(*(const uint4*)(wb + 16 * u), fb);
+            widen(*(const uint4*)(wa + 512 * u), fa);
+            widen(*(const uint4*)(wb + 512 * u), fb);
 #pragma unroll
             for (int t = 0; t < EX_TT; t++) {
                 if (t < cnt) {
@@ -359,24 +342,25 @@ __host__ __device__ constexpr int act_stage_bytes() {
 }
 template <int TY>
 __host__ __device__ constexpr int stage_bytes() {
-    return EX_ROWS * Fmt<TY>::STRIDE + act_stage_bytes<TY>();
+    return EX_ROWS * Fmt<TY>::SL + act_stage_bytes<TY>();
 }
 template <int TY>
 __host__ __device__ constexpr int smem_bytes() {
     return 128 + Fmt<TY>::WARPS * 2 * stage_bytes<TY>();
 }
 
-struct Item {           // a decoded work item (warp-uniform except src_row)
+struct Item {           // a decoded work item (warp-uniform except sa, sb)
     int valid;
     int shared;         // the shared expert's group
     int expert;
     int pos0;           // first position of the tile
     int tc;             // tokens in the tile
     int r0;             // first output row of the chunk
-    int K;              // inner dimension
-    int src_row;        // lane t < tc: activation row of token t (token or position)
-    const uint8_t* pa;  // this lane's two weight rows
-    const uint8_t* pb;
+    int nst;            // stages: slices of the inner dimension
+    const uint8_t* ta;  // slice 0 of the two 32-row weight tiles; slice s is s*32*SL further
+    const uint8_t* tb;
+    const uint16_t* sa; // this lane's rows in the side plane (Q6_K)
+    const uint16_t* sb;
 };
 
 template <int TY, int MODE>
@@ -420,49 +404,41 @@ experts_kernel(const ExpertArgs A) {
         it.pos0 = start + t0;
         it.tc = min(EX_TT, cnt - t0);
         it.r0 = chunk * CH;
-        it.src_row = 0;
-        if (lane < it.tc) {
-            const int pos = it.pos0 + lane;
-            if (MODE == MODE_GATEUP) it.src_row = it.shared ? pos - P : A.order[pos] / A.k;
-            else it.src_row = pos;
-        }
         const DevStack& m0 = it.shared ? A.s0 : A.w0;
         const DevStack& m1 = MODE == MODE_GATEUP ? (it.shared ? A.s1 : A.w1) : m0;
-        const size_t e = it.shared ? 0 : it.expert;
-        const int ra = min(it.r0 + lane, m0.rows - 1);
-        const int rb = MODE == MODE_GATEUP ? ra : min(it.r0 + 32 + lane, m0.rows - 1);
-        it.pa = m0.data + e * m0.expert_bytes + (size_t)ra * m0.row_bytes;
-        it.pb = m1.data + e * m1.expert_bytes + (size_t)rb * m1.row_bytes;
-        it.K = m0.cols;
+        const int64_t e = it.shared ? 0 : it.expert;
+        // row tiles: gate and up rows r0..r0+31 (GATEUP), down rows r0..r0+31 and r0+32..r0+63
+        const int rta = min(it.r0 / 32, m0.rows / 32 - 1);
+        const int rtb = MODE == MODE_GATEUP ? rta : min(it.r0 / 32 + 1, m0.rows / 32 - 1);
+        it.ta = m0.tile(e, rta);
+        it.tb = m1.tile(e, rtb);
+        it.nst = m0.nslices;
+        it.sa = m0.side + ((size_t)e * m0.rows + rta * 32 + lane) * m0.nslices;
+        it.sb = m1.side + ((size_t)e * m1.rows + rtb * 32 + lane) * m1.nslices;
         return it;
     };
-    // issues stage `s` of an item into ring slot `slot`
+    // issues stage `s` of an item into ring slot `slot`: four contiguous copies
+    constexpr uint32_t TILE_BYTES = 32 * F::SL;
+    constexpr uint32_t ACT_BYTES = act_stage_bytes<TY>();
     auto issue = [&](const Item& it, int s, int slot) {
         uint8_t* dst = ring + (size_t)slot * SB;
         fence_proxy_async();   // the slot was last read through the generic proxy
         __syncwarp();
-        if (lane == 0)
-            mbar_expect_tx(&mbar[slot],
-                           EX_ROWS * F::ROW_TX +
-                               it.tc * (F::F32ACT ? F::ELEMS * 4 : F::ELEMS + F::ELEMS / 4));
-        __syncwarp();
-        F::issue_row(dst + (size_t)lane * F::STRIDE, it.pa, it.K, s, &mbar[slot]);
-        F::issue_row(dst + (size_t)(32 + lane) * F::STRIDE, it.pb, it.K, s, &mbar[slot]);
-        if (lane < it.tc) {
-            uint8_t* adst = dst + EX_ROWS * F::STRIDE;
+        if (lane == 0) {
+            mbar_expect_tx(&mbar[slot], 2 * TILE_BYTES + ACT_BYTES);
+            bulk_g2s(dst, it.ta + (size_t)s * TILE_BYTES, TILE_BYTES, &mbar[slot]);
+            bulk_g2s(dst + TILE_BYTES, it.tb + (size_t)s * TILE_BYTES, TILE_BYTES, &mbar[slot]);
+            uint8_t* adst = dst + 2 * TILE_BYTES;
+            const size_t row = (size_t)s * A.act_rows + it.pos0;
             if (F::F32ACT) {
-                bulk_g2s(adst + (size_t)lane * F::ELEMS * 4,
-                         A.x_f32 + (size_t)it.src_row * A.x_stride + (size_t)s * F::ELEMS, F::ELEMS * 4,
-                         &mbar[slot]);
+                bulk_g2s(adst, A.x_f32 + row * F::ELEMS, EX_TT * F::ELEMS * 4, &mbar[slot]);
             } else {
-                bulk_g2s(adst + (size_t)lane * F::ELEMS,
-                         A.x_q + (size_t)it.src_row * A.x_stride + (size_t)s * F::ELEMS, F::ELEMS,
-                         &mbar[slot]);
-                bulk_g2s(adst + EX_TT * F::ELEMS + (size_t)lane * (F::ELEMS / 32) * 8,
-                         A.x_ds + (size_t)it.src_row * (A.x_stride / 32) + (size_t)s * (F::ELEMS / 32),
-                         (F::ELEMS / 32) * 8, &mbar[slot]);
+                bulk_g2s(adst, A.x_q + row * F::ELEMS, EX_TT * F::ELEMS, &mbar[slot]);
+                bulk_g2s(adst + EX_TT * F::ELEMS, A.x_ds + row * (F::ELEMS / 32),
+                         EX_TT * (F::ELEMS / 32) * 8, &mbar[slot]);
             }
         }
+        __syncwarp();
     };
 
     Item cur = fetch();
@@ -476,14 +452,14 @@ experts_kernel(const ExpertArgs A) {
     Side sideA0{}, sideA1{}, sideB0{}, sideB1{};
     auto pump = [&]() {
         while (issued < consumed + 2) {
-            if (!p_in_next && p_stage >= cur.K / F::ELEMS) {
+            if (!p_in_next && p_stage >= cur.nst) {
                 p_in_next = 1;
                 p_stage = 0;
             }
-            if (p_in_next && (!nxt.valid || p_stage >= nxt.K / F::ELEMS)) break;
+            if (p_in_next && (!nxt.valid || p_stage >= nxt.nst)) break;
             const Item& it = p_in_next ? nxt : cur;
             const int slot = issued & 1;
-            const Side sa = F::side(it.pa, it.K, p_stage), sb = F::side(it.pb, it.K, p_stage);
+            const Side sa = F::side(it.sa, p_stage), sb = F::side(it.sb, p_stage);
             if (slot) { sideA1 = sa; sideB1 = sb; } else { sideA0 = sa; sideB0 = sb; }
             issue(it, p_stage, slot);
             p_stage++;
@@ -498,7 +474,7 @@ experts_kernel(const ExpertArgs A) {
         float accA[EX_TT], accB[EX_TT];
 #pragma unroll
         for (int t = 0; t < EX_TT; t++) accA[t] = accB[t] = 0.0f;
-        const int nst = cur.K / F::ELEMS;
+        const int nst = cur.nst;
         for (int s = 0; s < nst; s++) {
             const int slot = consumed & 1;
             if (!mbar_wait_bounded(&mbar[slot], (consumed >> 1) & 1)) {
@@ -509,9 +485,9 @@ experts_kernel(const ExpertArgs A) {
                 return;
             }
             const uint8_t* st = ring + (size_t)slot * SB;
-            const uint8_t* wa = st + (size_t)lane * F::STRIDE;
-            const uint8_t* wb = st + (size_t)(32 + lane) * F::STRIDE;
-            const uint8_t* act = st + EX_ROWS * F::STRIDE;
+            const uint8_t* wa = st + lane * 16;
+            const uint8_t* wb = st + TILE_BYTES + lane * 16;
+            const uint8_t* act = st + 2 * TILE_BYTES;
             if constexpr (F::F32ACT) {
                 F::accum2f(wa, wb, (const float*)act, cur.tc, accA, accB);
             } else {
@@ -525,23 +501,24 @@ experts_kernel(const ExpertArgs A) {
         // ---- epilogue
         const int rows = (cur.shared ? A.s0 : A.w0).rows;
         if (MODE == MODE_GATEUP) {
-            const bool row_ok = cur.r0 + lane < rows;
+            // rows r0..r0+31 of mid: one Q8 block, half a 64-wide f32 slice
+            const bool row_ok = cur.r0 < rows;
+            const int r = cur.r0 + lane;
 #pragma unroll
             for (int t = 0; t < EX_TT; t++) {
-                if (t < cur.tc) {
+                if (t < cur.tc && row_ok) {
                     // ops.rs:160-167: silu(x) = x * (1 / (1 + exp(-x)))
                     const float g = accA[t], u = accB[t];
                     const float sg = __fdiv_rn(1.0f, 1.0f + expf(-g));
-                    const float v = row_ok ? (g * sg) * u : 0.0f;
-                    const size_t o = (size_t)(cur.pos0 + t) * A.mid_stride + cur.r0 + lane;
-                    if (row_ok) A.out[o] = v;
-                    if (A.out_q) {   // Q8Act of the mid row (quant.rs:368-394): this chunk is one block
+                    const float v = (g * sg) * u;
+                    const size_t pos = cur.pos0 + t;
+                    A.out[((size_t)(r / 64) * A.act_rows + pos) * 64 + r % 64] = v;
+                    if (A.out_q) {   // Q8Act of the mid row (quant.rs:368-394)
                         float dd, ss;
                         const int q = q8_quantize_lane(v, dd, ss);
-                        if (row_ok) A.out_q[o] = (int8_t)q;
-                        if (lane == 0)
-                            A.out_ds[(size_t)(cur.pos0 + t) * (A.mid_stride / 32) + cur.r0 / 32] =
-                                make_float2(dd, ss);
+                        const size_t srow = (size_t)(r / 256) * A.act_rows + pos;
+                        A.out_q[srow * 256 + r % 256] = (int8_t)q;
+                        if (lane == 0) A.out_ds[srow * 8 + (cur.r0 % 256) / 32] = make_float2(dd, ss);
                     }
                 }
             }
@@ -572,9 +549,8 @@ bool experts_supported(int ty, int cols, int rows, bool is_down) {
     if (ty != BIVMOE_Q8_0 && ty != BIVMOE_Q4_K && ty != BIVMOE_Q5_K && ty != BIVMOE_Q6_K &&
         ty != BIVMOE_BF16)
         return false;
-    if (cols <= 0 || cols % 256) return false;
-    if (rows <= 0 || (!is_down && rows % 32)) return false;
-    return dev_row_bytes(ty, cols) % 16 == 0;
+    (void)is_down;
+    return cols > 0 && cols % 256 == 0 && rows > 0 && rows % 32 == 0;
 }
 
 template <int TY, int MODE>
@@ -610,24 +586,23 @@ static cudaError_t launch_typed(int ty, const LaunchCfg& c, const ExpertArgs& A,
 // gate+up then down, for the routed experts and the shared expert.  When the
 // shared expert's matrices have the routed experts' types it rides in the same
 // launches (its tiles come first in the tile list); otherwise it gets its own.
-cudaError_t launch_experts(const LaunchCfg& c, const float* h, const DevStack& gate,
+cudaError_t launch_experts(const LaunchCfg& c, const float* /*h: dispatched already*/, const DevStack& gate,
                            const DevStack& up, const DevStack& down, const DevStack& sh_gate,
                            const DevStack& sh_up, const DevStack& sh_down, const Workspace& ws) {
     if (gate.ty != up.ty || (c.has_shared && sh_gate.ty != sh_up.ty)) return cudaErrorInvalidValue;
     ExpertArgs A{};
-    A.order = ws.order;
     A.grp_expert = ws.grp_expert; A.grp_start = ws.grp_start; A.grp_count = ws.grp_count;
     A.tile_group = ws.tile_group; A.tile_t0 = ws.tile_t0; A.n_tiles = ws.n_tiles;
     A.status = ws.status;
     A.n = c.n; A.k = c.k; A.n_expert = c.n_expert;
-    A.mid_stride = std::max(c.ff, c.ff_sh);
+    A.act_rows = ws.act_rows;
     const bool fused = c.has_shared && sh_gate.ty == gate.ty && sh_down.ty == down.ty;
     cudaError_t err;
     // ---- gate + up (SwiGLU and the Q8 rows of its output in the epilogue)
     auto gateup = [&](int mode, int rows, int ctr, int ty, int down_ty) {
         ExpertArgs G = A;
         G.w0 = gate; G.w1 = up; G.s0 = sh_gate; G.s1 = sh_up;
-        G.x_f32 = h; G.x_q = ws.act_q; G.x_ds = ws.act_ds; G.x_stride = c.e;
+        G.x_f32 = ws.act_f; G.x_q = ws.act_q; G.x_ds = ws.act_ds;
         G.out = ws.mid;
         const bool qdown = !type_uses_f32_act(down_ty);
         G.out_q = qdown ? ws.mid_q : nullptr;
@@ -648,7 +623,7 @@ cudaError_t launch_experts(const LaunchCfg& c, const float* h, const DevStack& g
     auto downp = [&](int mode, int ctr, int ty) {
         ExpertArgs D = A;
         D.w0 = down; D.s0 = sh_down;
-        D.x_f32 = ws.mid; D.x_q = ws.mid_q; D.x_ds = ws.mid_ds; D.x_stride = A.mid_stride;
+        D.x_f32 = ws.mid; D.x_q = ws.mid_q; D.x_ds = ws.mid_ds;
         D.out = ws.pair_out;
         D.work_ctr = ws.work_ctr + ctr;
         D.tiles_mode = mode;

@@ -7,27 +7,48 @@
 namespace bivmoe {
 
 // ---------------------------------------------------------------------------
-// Q8Act::quantize_into (quant.rs:368-394): one warp per 32-value block.
-__global__ void __launch_bounds__(256)
-quantize_rows_kernel(const float* __restrict__ x, int64_t n_blocks, int8_t* __restrict__ q,
-                     float2* __restrict__ ds) {
-    const int lane = threadIdx.x & 31;
-    const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int64_t stride = (int64_t)gridDim.x * (blockDim.x >> 5);
-    for (int64_t b = warp0; b < n_blocks; b += stride) {
-        float dd, ss;
-        int qi = q8_quantize_lane(x[b * 32 + lane], dd, ss);
-        q[b * 32 + lane] = (int8_t)qi;
-        if (lane == 0) ds[b] = make_float2(dd, ss);
+// Dispatch: the rows the expert kernels consume, laid out by position
+// (slice-major, see common.cuh).  Token t's row goes to position P + t (the
+// shared expert's group) and to the position of each of its k pairs.  For
+// quantised weight types the row is quantised once, Q8Act::quantize_into
+// (quant.rs:368-394) - the reference quantises it again for every expert it is
+// routed to (model.rs:876-884), with the same result, the quantiser being a
+// function of the row alone.  One block per token, one warp per 32-value block.
+constexpr int DP_THREADS = 256, DP_MAX_K = 32;
+
+__global__ void __launch_bounds__(DP_THREADS)
+dispatch_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int quant, int f32) {
+    __shared__ int s_pos[DP_MAX_K + 1];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int P = n * k, R = ws.act_rows;
+    if (threadIdx.x < k) s_pos[threadIdx.x] = ws.pos_of[(size_t)t * k + threadIdx.x];
+    if (threadIdx.x == k) s_pos[k] = P + t;
+    __syncthreads();
+    const float* x = h + (size_t)t * e;
+    for (int b = warp; b < e / 32; b += DP_THREADS / 32) {
+        const float v = x[32 * b + lane];
+        if (quant) {
+            float dd, ss;
+            const int q = q8_quantize_lane(v, dd, ss);
+            const int sl = b / 8, bb = b % 8;
+            for (int j = 0; j <= k; j++) {
+                const size_t row = (size_t)sl * R + s_pos[j];
+                ws.act_q[row * 256 + 32 * bb + lane] = (int8_t)q;
+                if (lane == 0) ws.act_ds[row * 8 + bb] = make_float2(dd, ss);
+            }
+        }
+        if (f32) {
+            const int sl = b / 2, off = (b % 2) * 32;
+            for (int j = 0; j <= k; j++)
+                ws.act_f[((size_t)sl * R + s_pos[j]) * 64 + off + lane] = v;
+        }
     }
 }
 
-cudaError_t launch_quantize_rows(const LaunchCfg& c, const float* x, int rows, int cols, int8_t* q,
-                                 float2* ds) {
-    int64_t nb = (int64_t)rows * cols / 32;
-    int blocks = (int)((nb + 7) / 8);
-    if (blocks > c.sm_count * 16) blocks = c.sm_count * 16;
-    quantize_rows_kernel<<<blocks, 256, 0, c.stream>>>(x, nb, q, ds);
+cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace& ws, bool quant,
+                            bool f32) {
+    if (c.k > DP_MAX_K) return cudaErrorInvalidValue;
+    dispatch_kernel<<<c.n, DP_THREADS, 0, c.stream>>>(h, ws, c.n, c.k, c.e, quant ? 1 : 0, f32 ? 1 : 0);
     count_launch();
     return cudaGetLastError();
 }
@@ -122,102 +143,96 @@ cudaError_t launch_combine(const LaunchCfg& c, const Workspace& ws, float* out, 
 }
 
 // ---------------------------------------------------------------------------
-// Upload-time repack: GGUF rows -> device rows (layouts in common.cuh).  One
-// thread per source block; byte-preserving except for Q6_K's padded f16 plane.
-__global__ void repack_q8_0_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
-                                   int64_t n_rows, int64_t cols) {
-    const int64_t nb = cols / 32, total = n_rows * nb;
-    const int64_t srb = nb * 34, drb = cols + cols / 16;
+// Upload-time repack: GGUF rows -> tiled device layout (common.cuh).  One
+// thread per 16-byte unit of the destination.
+__global__ void repack_kernel(DevStack st, const uint8_t* __restrict__ src, int64_t n_rows) {
+    const int units = st.slice_bytes / 16;
+    const int64_t total = n_rows * st.nslices * units;
+    const int64_t grb = gguf_row_bytes(st.ty, st.cols);
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / nb, b = i % nb;
-        const uint8_t* s = src + r * srb + b * 34;
-        uint8_t* drow = dst + r * drb;
-        drow[cols + 2 * b] = s[0];
-        drow[cols + 2 * b + 1] = s[1];
-        for (int j = 0; j < 32; j++) drow[32 * b + j] = s[2 + j];
-    }
-}
-__global__ void repack_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
-                                  int64_t n_rows, int64_t cols) {
-    const int64_t nb = cols / 256, total = n_rows * nb;
-    const int64_t srb = nb * 210, drb = dev_row_bytes(BIVMOE_Q6_K, cols);
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / nb, b = i % nb;
-        const uint8_t* s = src + r * srb + b * 210;
-        uint8_t* drow = dst + r * drb;
-        for (int j = 0; j < 128; j++) drow[b * 128 + j] = s[j];
-        for (int j = 0; j < 64; j++) drow[nb * 128 + b * 64 + j] = s[128 + j];
-        for (int j = 0; j < 16; j++) drow[nb * 192 + b * 16 + j] = s[192 + j];
-        drow[nb * 208 + 2 * b] = s[208];
-        drow[nb * 208 + 2 * b + 1] = s[209];
-        if (b == 0)
-            for (int64_t j = nb * 208 + nb * 2; j < drb; j++) drow[j] = 0;
+        const int u = (int)(i % units);
+        const int s = (int)((i / units) % st.nslices);
+        const int64_t r = i / ((int64_t)units * st.nslices);   // row over all experts
+        const uint8_t* row = src + r * grb;
+        uint8_t* dst = st.data + ((r / 32) * st.nslices + s) * 32 * (int64_t)st.slice_bytes +
+                       ((int64_t)u * 32 + r % 32) * 16;
+        const uint8_t* from = nullptr;
+        switch (st.ty) {
+            case BIVMOE_Q4_K: from = row + 144 * (int64_t)s + 16 * u; break;
+            case BIVMOE_Q5_K: from = row + 176 * (int64_t)s + 16 * u; break;
+            case BIVMOE_BF16: from = row + 128 * (int64_t)s + 16 * u; break;
+            case BIVMOE_Q6_K: from = row + 210 * (int64_t)s + 16 * u; break;   // ql, qh, scales in order
+            case BIVMOE_Q8_0:
+                if (u < 16) from = row + 34 * (int64_t)(8 * s + u / 2) + 2 + 16 * (u % 2);
+                break;
+        }
+        if (from) {
+            for (int j = 0; j < 16; j++) dst[j] = from[j];
+        } else {   // Q8_0 unit 16: the eight f16 scales of the slice
+            for (int b = 0; b < 8; b++) {
+                dst[2 * b] = row[34 * (int64_t)(8 * s + b)];
+                dst[2 * b + 1] = row[34 * (int64_t)(8 * s + b) + 1];
+            }
+        }
+        if (st.ty == BIVMOE_Q6_K && u == 0) {
+            const uint8_t* d = row + 210 * (int64_t)s + 208;
+            st.side[r * st.nslices + s] = (uint16_t)(d[0] | (d[1] << 8));
+        }
     }
 }
 
-cudaError_t launch_repack(int ty, const uint8_t* gguf_rows, uint8_t* dev_rows, int64_t n_rows,
-                          int64_t cols, cudaStream_t stream) {
-    if (ty == BIVMOE_Q8_0) {
-        repack_q8_0_kernel<<<1024, 256, 0, stream>>>(gguf_rows, dev_rows, n_rows, cols);
-    } else if (ty == BIVMOE_Q6_K) {
-        repack_q6k_kernel<<<1024, 256, 0, stream>>>(gguf_rows, dev_rows, n_rows, cols);
-    } else {
-        return cudaMemcpyAsync(dev_rows, gguf_rows, (size_t)(n_rows * gguf_row_bytes(ty, cols)),
-                               cudaMemcpyDeviceToDevice, stream);
-    }
+cudaError_t launch_repack(const DevStack& st, const uint8_t* gguf_rows, cudaStream_t stream) {
+    repack_kernel<<<2048, 256, 0, stream>>>(st, gguf_rows, (int64_t)st.n * st.rows);
     return cudaGetLastError();
 }
 
-}  // namespace bivmoe
-
-namespace bivmoe {
-
 // ---------------------------------------------------------------------------
-// Parity tap: the int32 dot of each 32-element block of one device-layout
-// weight row with one Q8 activation row, decoded byte by byte as the
-// reference's scalar kernels define the values (quant.rs:599-686).  One thread
-// per block; not on the timed path.
-__global__ void block_dots_kernel(int ty, const uint8_t* __restrict__ w, int cols,
-                                  const int8_t* __restrict__ xq, int32_t* __restrict__ out) {
-    const int b = blockIdx.x * blockDim.x + threadIdx.x;   // 32-element block
-    if (b >= cols / 32) return;
-    const int8_t* x = xq + 32 * b;
-    const int nb = cols / 256, sbk = b / 8, sb = b % 8;
+// Parity tap: the int32 dot of each 32-element block of one weight row with one
+// Q8 activation row, decoded byte by byte as the reference's scalar kernels
+// define the values (quant.rs:599-686).  One thread per block; not on the
+// timed path.
+__device__ inline uint8_t tile_byte(const DevStack& st, const uint8_t* tile0, int r, int s, int off) {
+    return tile0[(int64_t)s * 32 * st.slice_bytes + ((off >> 4) * 32 + (r & 31)) * 16 + (off & 15)];
+}
+
+__global__ void block_dots_kernel(DevStack st, int expert, int row, const int8_t* __restrict__ act_q,
+                                  int act_rows, int pos, int32_t* __restrict__ out) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;   // 32-element block of the row
+    if (b >= st.cols / 32) return;
+    const uint8_t* t0 = st.tile(expert, row / 32);
+    const int s = b / 8, sb = b % 8;
+    const int8_t* x = act_q + ((size_t)s * act_rows + pos) * 256 + 32 * sb;
     int32_t sum = 0;
-    if (ty == BIVMOE_Q8_0) {
-        for (int l = 0; l < 32; l++) sum += (int)(int8_t)w[32 * b + l] * x[l];
-    } else if (ty == BIVMOE_Q4_K || ty == BIVMOE_Q5_K) {
-        const uint8_t* blk = w + (size_t)sbk * (ty == BIVMOE_Q4_K ? 144 : 176);
-        const uint8_t* qs = blk + (ty == BIVMOE_Q4_K ? 16 : 48) + 32 * (sb / 2);
+    if (st.ty == BIVMOE_Q8_0) {
+        for (int l = 0; l < 32; l++) sum += (int)(int8_t)tile_byte(st, t0, row, s, 32 * sb + l) * x[l];
+    } else if (st.ty == BIVMOE_Q4_K || st.ty == BIVMOE_Q5_K) {
+        const int qoff = (st.ty == BIVMOE_Q4_K ? 16 : 48) + 32 * (sb / 2);
         for (int l = 0; l < 32; l++) {
-            int q = (qs[l] >> (4 * (sb % 2))) & 0xF;
-            if (ty == BIVMOE_Q5_K) q |= ((blk[16 + l] >> sb) & 1) << 4;
+            int q = (tile_byte(st, t0, row, s, qoff + l) >> (4 * (sb % 2))) & 0xF;
+            if (st.ty == BIVMOE_Q5_K) q |= ((tile_byte(st, t0, row, s, 16 + l) >> sb) & 1) << 4;
             sum += q * x[l];
         }
-    } else if (ty == BIVMOE_Q6_K) {
+    } else if (st.ty == BIVMOE_Q6_K) {
         const int n = sb / 4, kq = sb % 4;
-        const uint8_t* ql = w + (size_t)sbk * 128 + 64 * n + 32 * (kq & 1);
-        const uint8_t* qh = w + (size_t)nb * 128 + (size_t)sbk * 64 + 32 * n;
-        const int8_t* sc = (const int8_t*)w + (size_t)nb * 192 + (size_t)sbk * 16 + 8 * n + 2 * kq;
         for (int half = 0; half < 2; half++) {
             int32_t part = 0;
             for (int l = 16 * half; l < 16 * half + 16; l++) {
-                const int nib = kq >= 2 ? ql[l] >> 4 : ql[l] & 0xF;
-                const int q = (nib | (((qh[l] >> (2 * kq)) & 3) << 4)) - 32;
-                part += q * x[l];
+                const int ql = tile_byte(st, t0, row, s, 64 * n + 32 * (kq & 1) + l);
+                const int qh = tile_byte(st, t0, row, s, 128 + 32 * n + l);
+                const int nib = kq >= 2 ? ql >> 4 : ql & 0xF;
+                part += ((nib | (((qh >> (2 * kq)) & 3) << 4)) - 32) * x[l];
             }
-            sum += sc[half] * part;
+            sum += (int)(int8_t)tile_byte(st, t0, row, s, 192 + 8 * n + 2 * kq + half) * part;
         }
     }
     out[b] = sum;
 }
 
-cudaError_t launch_block_dots(int ty, const uint8_t* dev_row, int64_t cols, const int8_t* xq,
-                              int32_t* out, cudaStream_t stream) {
-    const int nb = (int)(cols / 32);
-    block_dots_kernel<<<(nb + 63) / 64, 64, 0, stream>>>(ty, dev_row, (int)cols, xq, out);
+cudaError_t launch_block_dots(const DevStack& st, int expert, int row, const int8_t* act_q,
+                              int act_rows, int pos, int32_t* out, cudaStream_t stream) {
+    const int nb = st.cols / 32;
+    block_dots_kernel<<<(nb + 63) / 64, 64, 0, stream>>>(st, expert, row, act_q, act_rows, pos, out);
     return cudaGetLastError();
 }
 
