@@ -48,7 +48,7 @@ struct bivmoe_layer {
     int device = 0, sm_count = 0;
     int e = 0, n_expert = 0, k = 0, ff = 0, ff_sh = 0, max_tokens = 0;
     bool has_shared = false;
-    DevStack gate, up, down, sh_gate, sh_up, sh_down;
+    DevTiles gate_up, down, sh_gate_up, sh_down;
     float* router = nullptr;      // [n_expert + 1][e]; the last row is the shared-gate vector
     float* post_norm = nullptr;   // [e]
     float norm_eps = 0.0f;
@@ -87,14 +87,14 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
     w.status = a.take<int32_t>(4);
     const size_t R = P + N + 8;   // the last tile of a group may read 7 rows past it
     w.act_rows = (int)R;
-    const bool qact = !type_uses_f32_act(L->gate.ty) || (L->has_shared && !type_uses_f32_act(L->sh_gate.ty));
-    const bool fact = type_uses_f32_act(L->gate.ty) || (L->has_shared && type_uses_f32_act(L->sh_gate.ty));
+    const bool qact = !type_uses_f32_act(L->gate_up.ty) || (L->has_shared && !type_uses_f32_act(L->sh_gate_up.ty));
+    const bool fact = type_uses_f32_act(L->gate_up.ty) || (L->has_shared && type_uses_f32_act(L->sh_gate_up.ty));
     const bool qmid = !type_uses_f32_act(L->down.ty) || (L->has_shared && !type_uses_f32_act(L->sh_down.ty));
-    w.act_q = a.take<int8_t>(qact ? R * e : 0);
+    w.act_q = a.take<int8_t>(qact ? R * (e / 256) * kActQStride : 0);
     w.act_ds = a.take<float2>(qact ? R * e / 32 : 0);
     w.act_f = a.take<float>(fact ? R * e : 0);
     w.mid = a.take<float>(R * mid);
-    w.mid_q = a.take<int8_t>(qmid ? R * mid : 0);
+    w.mid_q = a.take<int8_t>(qmid ? R * (mid / 256) * kActQStride : 0);
     w.mid_ds = a.take<float2>(qmid ? R * mid / 32 : 0);
     w.pair_out = a.take<float>((P + N) * e);
     w.h_norm = a.take<float>(N * e);
@@ -124,38 +124,46 @@ static int check_stack(std::string* errp, const char* name, const bivmoe_experts
     return BIVMOE_OK;
 }
 
-// copies one stack to the device and repacks it into the tiled layout
-static int upload_stack(bivmoe_layer* L, std::string* errp, const bivmoe_experts& s, DevStack* out) {
-    const int64_t grb = gguf_row_bytes(s.ggml_type, s.cols);
-    const int64_t mat = s.rows * grb;
-    const int64_t stride = s.stride_bytes ? s.stride_bytes : mat;
-    const SliceGeom g = slice_geom(s.ggml_type);
-    out->ty = s.ggml_type;
-    out->cols = (int)s.cols; out->rows = (int)s.rows; out->n = (int)s.n;
+// Copies one product's stacks (gate and up, or down alone) to the device and
+// repacks them into the tiled layout.
+static int upload_tiles(bivmoe_layer* L, std::string* errp, const bivmoe_experts* a,
+                        const bivmoe_experts* b, int chunk_rows, DevTiles* out) {
+    const SliceGeom g = slice_geom(a->ggml_type);
+    out->ty = a->ggml_type;
+    out->cols = (int)a->cols; out->rows = (int)a->rows; out->n = (int)a->n;
+    out->chunk_rows = chunk_rows;
+    out->chunks = (int)(a->rows / chunk_rows);
     out->slice_bytes = g.sl;
-    out->nslices = (int)(s.cols / g.elems);
-    out->expert_bytes = s.rows * (int64_t)out->nslices * g.sl;
-    const size_t dev_bytes = (size_t)(s.n * out->expert_bytes);
+    out->nslices = (int)(a->cols / g.elems);
+    out->expert_bytes = (int64_t)out->chunks * out->nslices * 4 * 32 * g.sl;
+    const size_t dev_bytes = (size_t)(a->n * out->expert_bytes);
     void* p = nullptr;
     CU(cudaMalloc(&p, dev_bytes));
     L->allocs.push_back(p);
     L->weight_bytes += dev_bytes;
     out->data = (uint8_t*)p;
-    if (s.ggml_type == BIVMOE_Q6_K) {
-        const size_t sb = (size_t)(s.n * s.rows) * out->nslices * 2;
+    if (a->ggml_type == BIVMOE_Q6_K) {
+        const size_t sb = (size_t)a->n * out->chunks * 4 * 32 * out->nslices * 2;
         CU(cudaMalloc(&p, sb));
         L->allocs.push_back(p);
         L->weight_bytes += sb;
         out->side = (uint16_t*)p;
     }
-    void* staging = nullptr;
-    CU(cudaMalloc(&staging, (size_t)(s.n * mat)));
-    cudaError_t e1 = cudaMemcpy2D(staging, (size_t)mat, (const uint8_t*)s.data + s.offset_bytes,
-                                  (size_t)stride, (size_t)mat, (size_t)s.n, cudaMemcpyHostToDevice);
-    if (e1 == cudaSuccess) e1 = launch_repack(*out, (const uint8_t*)staging, 0);
-    if (e1 == cudaSuccess) e1 = cudaDeviceSynchronize();
-    cudaFree(staging);
-    CU(e1);
+    const bivmoe_experts* srcs[2] = {a, b};
+    for (int i = 0; i < 2; i++) {
+        const bivmoe_experts* s = srcs[i];
+        if (!s) continue;
+        const int64_t mat = s->rows * gguf_row_bytes(s->ggml_type, s->cols);
+        const int64_t stride = s->stride_bytes ? s->stride_bytes : mat;
+        void* staging = nullptr;
+        CU(cudaMalloc(&staging, (size_t)(s->n * mat)));
+        cudaError_t e1 = cudaMemcpy2D(staging, (size_t)mat, (const uint8_t*)s->data + s->offset_bytes,
+                                      (size_t)stride, (size_t)mat, (size_t)s->n, cudaMemcpyHostToDevice);
+        if (e1 == cudaSuccess) e1 = launch_repack(*out, (const uint8_t*)staging, 2 * i, 0);
+        if (e1 == cudaSuccess) e1 = cudaDeviceSynchronize();
+        cudaFree(staging);
+        CU(e1);
+    }
     return BIVMOE_OK;
 }
 
@@ -222,12 +230,11 @@ int bivmoe_create(const bivmoe_desc* d, bivmoe_layer** out) {
     L->ff = d->n_ff_exp; L->ff_sh = d->n_ff_shexp; L->max_tokens = d->max_tokens;
     L->has_shared = shared;
     auto fail = [&](int code) { g_error = g_error.empty() ? L->error : g_error; bivmoe_destroy(L); return code; };
-    if ((rc = upload_stack(L, errp, d->gate, &L->gate)) || (rc = upload_stack(L, errp, d->up, &L->up)) ||
-        (rc = upload_stack(L, errp, d->down, &L->down)))
+    if ((rc = upload_tiles(L, errp, &d->gate, &d->up, 64, &L->gate_up)) ||
+        (rc = upload_tiles(L, errp, &d->down, nullptr, 128, &L->down)))
         return fail(rc);
-    if (shared && ((rc = upload_stack(L, errp, d->sh_gate, &L->sh_gate)) ||
-                   (rc = upload_stack(L, errp, d->sh_up, &L->sh_up)) ||
-                   (rc = upload_stack(L, errp, d->sh_down, &L->sh_down))))
+    if (shared && ((rc = upload_tiles(L, errp, &d->sh_gate, &d->sh_up, 64, &L->sh_gate_up)) ||
+                   (rc = upload_tiles(L, errp, &d->sh_down, nullptr, 128, &L->sh_down))))
         return fail(rc);
     auto cu_fail = [&](cudaError_t e, const char* what) {
         set_err(errp, e == cudaErrorMemoryAllocation ? BIVMOE_ERR_OOM : BIVMOE_ERR_CUDA, "%s: %s",
@@ -298,7 +305,7 @@ static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int 
     mark(c, EV_SORT);
     CU(launch_dispatch(c, h, L->ws, L->ws.act_q != nullptr, L->ws.act_f != nullptr));
     mark(c, EV_QUANT);
-    CU(launch_experts(c, h, L->gate, L->up, L->down, L->sh_gate, L->sh_up, L->sh_down, L->ws));
+    CU(launch_experts(c, L->gate_up, L->down, L->sh_gate_up, L->sh_down, L->ws));
     mark(c, EV_DOWN);
     CU(launch_combine(c, L->ws, out, accumulate));
     mark(c, EV_COMBINE);
@@ -431,14 +438,14 @@ int bivmoe_tap(bivmoe_layer* L, int32_t which, void* dst, size_t bytes) {
             const bool q = which == BIVMOE_TAP_ACT_Q;
             if (bytes != (q ? n * e : n * e / 32 * 4))
                 return set_err(errp, BIVMOE_ERR_ARGUMENT, "tap buffer size mismatch");
-            std::vector<int8_t> tq(q ? R * e : 0);
+            std::vector<int8_t> tq(q ? R * nsl * kActQStride : 0);
             std::vector<float> td(q ? 0 : R * e / 32 * 2);
             if (q) CU(cudaMemcpy(tq.data(), w.act_q, tq.size(), cudaMemcpyDeviceToHost));
             else CU(cudaMemcpy(td.data(), w.act_ds, td.size() * 4, cudaMemcpyDeviceToHost));
             for (size_t t = 0; t < n; t++)
                 for (size_t sl = 0; sl < nsl; sl++) {
                     const size_t row = sl * R + P + t;
-                    if (q) memcpy((int8_t*)dst + t * e + sl * 256, tq.data() + row * 256, 256);
+                    if (q) memcpy((int8_t*)dst + t * e + sl * 256, tq.data() + row * kActQStride, 256);
                     else
                         for (int b = 0; b < 8; b++)
                             ((float*)dst)[t * (e / 32) + sl * 8 + b] =
@@ -481,11 +488,11 @@ int bivmoe_tap_block_dots(bivmoe_layer* L, int32_t matrix, int32_t expert, int32
     std::string* errp = &L->error;
     CU(cudaSetDevice(L->device));
     CU(cudaDeviceSynchronize());
-    const DevStack* stacks[6] = {&L->gate, &L->up, &L->down, &L->sh_gate, &L->sh_up, &L->sh_down};
     if (matrix < 0 || matrix > 5 || (matrix >= 3 && !L->has_shared))
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "matrix %d", matrix);
-    const DevStack& m = *stacks[matrix];
     const bool shared = matrix >= 3, is_down = matrix % 3 == 2;
+    const DevTiles& m = is_down ? (shared ? L->sh_down : L->down) : (shared ? L->sh_gate_up : L->gate_up);
+    const int tile_base = matrix % 3 == 1 ? 2 : 0;   // up rows are tiles 2, 3 of a gate+up chunk
     const int n = L->last_n, P = n * L->k;
     if (expert < 0 || expert >= m.n || row < 0 || row >= m.rows || act_row < 0 ||
         act_row >= (is_down && !shared ? P : n))
@@ -501,8 +508,8 @@ int bivmoe_tap_block_dots(bivmoe_layer* L, int32_t matrix, int32_t expert, int32
     int32_t pos = P + act_row;
     if (is_down && !shared) ce = cudaMemcpy(&pos, L->ws.pos_of + act_row, 4, cudaMemcpyDeviceToHost);
     if (ce == cudaSuccess)
-        ce = launch_block_dots(m, expert, row, is_down ? L->ws.mid_q : L->ws.act_q, L->ws.act_rows,
-                               pos, dots, 0);
+        ce = launch_block_dots(m, tile_base, expert, row, is_down ? L->ws.mid_q : L->ws.act_q,
+                               L->ws.act_rows, pos, dots, 0);
     if (ce == cudaSuccess) ce = cudaMemcpy(out, dots, (size_t)nb * 4, cudaMemcpyDeviceToHost);
     cudaFree(dots);
     CU(ce);
@@ -512,9 +519,9 @@ int bivmoe_tap_block_dots(bivmoe_layer* L, int32_t matrix, int32_t expert, int32
 int bivmoe_numerics(const bivmoe_layer* L, char* buf, size_t len) {
     if (!L || !buf || !len) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or buffer");
     snprintf(buf, len,
-             "kind=cuda device=%s sms=%d repack=v%d experts=dp4a-two-rows-per-lane/warp-ring-bulk-copy/tiled-weights "
+             "kind=cuda device=%s sms=%d repack=v%d experts=mma.sync-s8-block-dots/bulk-copy-ring/tiled-weights "
              "router=f32-avx2-order combine=ordered-fma types=%d/%d/%d",
-             L->device_name.c_str(), L->sm_count, kRepackVersion, L->gate.ty, L->up.ty, L->down.ty);
+             L->device_name.c_str(), L->sm_count, kRepackVersion, L->gate_up.ty, L->gate_up.ty, L->down.ty);
     return BIVMOE_OK;
 }
 

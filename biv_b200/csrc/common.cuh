@@ -8,21 +8,24 @@
 namespace bivmoe {
 
 // ---------------------------------------------------------------------------
-// Device layout of the weights.  A matrix [rows][K] is cut into tiles of 32
-// rows by one K-slice; a tile is what one pipeline stage of the expert kernels
-// consumes, so it is stored contiguously and arrives with one bulk copy, and
-// the tiles of a row group follow each other (nslices * 32 * SL contiguous
-// bytes).  Inside a tile the bytes are unit-major, [SL/16 units][32 rows][16
-// bytes]: the lane that owns row r reads unit u at (u*32 + r)*16, so the 32
-// lanes of a warp read 512 consecutive bytes, free of bank conflicts.
-// The repack is a permutation of the GGUF bytes (nothing is widened):
+// Device layout of the weights.  The expert kernels work on chunks of rows: 64
+// gate rows together with the same 64 up rows, or 128 down rows.  A chunk is
+// four tiles of 32 rows, and what one pipeline stage consumes - one K-slice of
+// those four tiles - is stored contiguously (4 * 32 * SL bytes, one bulk copy),
+// the K-slices of a chunk following each other:
+//     [expert][chunk][K-slice][tile 0..3][SL/16 units][32 rows][16 bytes]
+// gate+up chunks: tiles 0,1 = gate rows 0-31, 32-63 of the chunk, tiles 2,3 = up rows.
+// Inside a tile the bytes are unit-major: the lane that owns row r reads unit u
+// at (u*32 + r)*16, so the lanes of a warp read consecutive 16-byte pieces,
+// free of bank conflicts.  The repack is a permutation of the GGUF bytes
+// (nothing is widened):
 //   type   K-slice   SL   the slice's bytes of one row
 //   Q8_0   256       272  8 blocks' int8 quants (256) then their 8 f16 scales (16)
 //   Q4_K   256       144  the 144-byte super-block {d, dmin, scales[12], qs[128]}
 //   Q5_K   256       176  the 176-byte super-block {d, dmin, scales[12], qh[32], qs[128]}
-//   Q6_K   256       208  ql[128], qh[64], scales[16]; the f16 d goes to a side plane [rows][K/256]
+//   Q6_K   256       208  ql[128], qh[64], scales[16]; the f16 d goes to a side plane
 //   BF16   64        128  64 values
-constexpr int kRepackVersion = 2;
+constexpr int kRepackVersion = 3;
 
 struct SliceGeom { int elems, sl; };
 __host__ __device__ inline SliceGeom slice_geom(int ty) {
@@ -50,23 +53,29 @@ __host__ __device__ inline bool type_uses_f32_act(int ty) {  // quant.rs:75-77
     return ty == BIVMOE_F32 || ty == BIVMOE_BF16;
 }
 
-struct DevStack {          // one stack of expert matrices on the device
+struct DevTiles {          // the tiles of one product (gate+up, or down) of a stack of experts
     int ty = 0;
-    int cols = 0, rows = 0, n = 0;
+    int cols = 0;              // inner dimension K
+    int rows = 0;              // rows of one source matrix (ff for gate and up, n_embd for down)
+    int n = 0;                 // experts
+    int chunks = 0;            // chunks per expert: rows/64 (gate+up) or rows/128 (down)
+    int chunk_rows = 0;        // source rows per chunk: 64 or 128
     int slice_bytes = 0;       // SL
     int nslices = 0;           // cols / slice elems
     uint8_t* data = nullptr;
-    uint16_t* side = nullptr;  // Q6_K: f16 d per (row, super-block)
-    int64_t expert_bytes = 0;  // rows * nslices * SL
-    // first byte of the tile of row group rt (32 rows), slice 0, of expert e
-    __host__ __device__ const uint8_t* tile(int64_t e, int rt) const {
-        return data + e * expert_bytes + (int64_t)rt * nslices * 32 * slice_bytes;
+    uint16_t* side = nullptr;  // Q6_K: f16 d, [expert][chunk][tile][32 rows][nslices]
+    int64_t expert_bytes = 0;  // chunks * nslices * 4 * 32 * SL
+    // first byte of K-slice s of a chunk (its four tiles follow each other)
+    __host__ __device__ const uint8_t* stage(int64_t e, int chunk, int s) const {
+        return data + e * expert_bytes + ((int64_t)chunk * nslices + s) * 4 * 32 * slice_bytes;
     }
 };
 
 // Activation rows are kept "slice-major" so that the K-slice of 8 consecutive
-// rows is contiguous: quantised rows as q [K/256][R][256] int8 and
+// rows is contiguous: quantised rows as q [K/256][R][272] int8 (256 values and
+// 16 bytes of padding, which spreads 8 rows over the shared-memory banks) and
 // ds [K/256][R][8] (d, s); float rows as [K/64][R][64] f32.  R = P + n + 8.
+constexpr int kActQStride = 272;
 // Per-forward scratch.  P = n * k routed pairs; "positions" 0..P are the pairs
 // in expert-sorted order, positions P..P+n are the tokens of the shared expert.
 struct Workspace {
@@ -116,15 +125,16 @@ cudaError_t launch_route_topk(const LaunchCfg& c, const Workspace& ws);
 cudaError_t launch_sort(const LaunchCfg& c, const Workspace& ws);
 cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace& ws, bool quant,
                             bool f32);
-cudaError_t launch_experts(const LaunchCfg& c, const float* h, const DevStack& gate,
-                           const DevStack& up, const DevStack& down, const DevStack& sh_gate,
-                           const DevStack& sh_up, const DevStack& sh_down, const Workspace& ws);
+cudaError_t launch_experts(const LaunchCfg& c, const DevTiles& gate_up, const DevTiles& down,
+                           const DevTiles& sh_gate_up, const DevTiles& sh_down, const Workspace& ws);
 cudaError_t launch_combine(const LaunchCfg& c, const Workspace& ws, float* out, int accumulate);
 cudaError_t launch_rms_norm(const LaunchCfg& c, const float* x, const float* w, float eps,
                             float* out);
-cudaError_t launch_repack(const DevStack& st, const uint8_t* gguf_rows, cudaStream_t stream);
-cudaError_t launch_block_dots(const DevStack& st, int expert, int row, const int8_t* act_q,
-                              int act_rows, int pos, int32_t* out, cudaStream_t stream);
+cudaError_t launch_repack(const DevTiles& dst, const uint8_t* gguf_rows, int tile_base,
+                          cudaStream_t stream);
+cudaError_t launch_block_dots(const DevTiles& t, int tile_base, int expert, int row,
+                              const int8_t* act_q, int act_rows, int pos, int32_t* out,
+                              cudaStream_t stream);
 bool experts_supported(int ty, int cols, int rows, bool is_down);
 
 void count_launch(int n = 1);

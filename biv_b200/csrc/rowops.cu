@@ -33,7 +33,7 @@ dispatch_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, 
             const int sl = b / 8, bb = b % 8;
             for (int j = 0; j <= k; j++) {
                 const size_t row = (size_t)sl * R + s_pos[j];
-                ws.act_q[row * 256 + 32 * bb + lane] = (int8_t)q;
+                ws.act_q[row * kActQStride + 32 * bb + lane] = (int8_t)q;
                 if (lane == 0) ws.act_ds[row * 8 + bb] = make_float2(dd, ss);
             }
         }
@@ -144,21 +144,28 @@ cudaError_t launch_combine(const LaunchCfg& c, const Workspace& ws, float* out, 
 
 // ---------------------------------------------------------------------------
 // Upload-time repack: GGUF rows -> tiled device layout (common.cuh).  One
-// thread per 16-byte unit of the destination.
-__global__ void repack_kernel(DevStack st, const uint8_t* __restrict__ src, int64_t n_rows) {
-    const int units = st.slice_bytes / 16;
-    const int64_t total = n_rows * st.nslices * units;
-    const int64_t grb = gguf_row_bytes(st.ty, st.cols);
+// thread per 16-byte unit of the destination.  `tile_base` places the source
+// matrix inside the chunk: 0 for gate and for down, 2 for up.
+__global__ void repack_kernel(DevTiles dt, const uint8_t* __restrict__ src, int tile_base) {
+    const int units = dt.slice_bytes / 16;
+    const int64_t n_rows = (int64_t)dt.n * dt.rows;
+    const int64_t total = n_rows * dt.nslices * units;
+    const int64_t grb = gguf_row_bytes(dt.ty, dt.cols);
+    const int64_t tile_bytes = 32 * (int64_t)dt.slice_bytes;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
         const int u = (int)(i % units);
-        const int s = (int)((i / units) % st.nslices);
-        const int64_t r = i / ((int64_t)units * st.nslices);   // row over all experts
-        const uint8_t* row = src + r * grb;
-        uint8_t* dst = st.data + ((r / 32) * st.nslices + s) * 32 * (int64_t)st.slice_bytes +
-                       ((int64_t)u * 32 + r % 32) * 16;
+        const int s = (int)((i / units) % dt.nslices);
+        const int64_t rg = i / ((int64_t)units * dt.nslices);   // row over all experts
+        const int64_t e = rg / dt.rows;
+        const int r = (int)(rg % dt.rows);
+        const int chunk = r / dt.chunk_rows, tile = tile_base + (r % dt.chunk_rows) / 32, rr = r % 32;
+        const uint8_t* row = src + rg * grb;
+        uint8_t* dst = dt.data + e * dt.expert_bytes +
+                       (((int64_t)chunk * dt.nslices + s) * 4 + tile) * tile_bytes +
+                       ((int64_t)u * 32 + rr) * 16;
         const uint8_t* from = nullptr;
-        switch (st.ty) {
+        switch (dt.ty) {
             case BIVMOE_Q4_K: from = row + 144 * (int64_t)s + 16 * u; break;
             case BIVMOE_Q5_K: from = row + 176 * (int64_t)s + 16 * u; break;
             case BIVMOE_BF16: from = row + 128 * (int64_t)s + 16 * u; break;
@@ -175,15 +182,17 @@ __global__ void repack_kernel(DevStack st, const uint8_t* __restrict__ src, int6
                 dst[2 * b + 1] = row[34 * (int64_t)(8 * s + b) + 1];
             }
         }
-        if (st.ty == BIVMOE_Q6_K && u == 0) {
+        if (dt.ty == BIVMOE_Q6_K && u == 0) {
             const uint8_t* d = row + 210 * (int64_t)s + 208;
-            st.side[r * st.nslices + s] = (uint16_t)(d[0] | (d[1] << 8));
+            dt.side[((((int64_t)e * dt.chunks + chunk) * 4 + tile) * 32 + rr) * dt.nslices + s] =
+                (uint16_t)(d[0] | (d[1] << 8));
         }
     }
 }
 
-cudaError_t launch_repack(const DevStack& st, const uint8_t* gguf_rows, cudaStream_t stream) {
-    repack_kernel<<<2048, 256, 0, stream>>>(st, gguf_rows, (int64_t)st.n * st.rows);
+cudaError_t launch_repack(const DevTiles& dst, const uint8_t* gguf_rows, int tile_base,
+                          cudaStream_t stream) {
+    repack_kernel<<<2048, 256, 0, stream>>>(dst, gguf_rows, tile_base);
     return cudaGetLastError();
 }
 
@@ -192,47 +201,52 @@ cudaError_t launch_repack(const DevStack& st, const uint8_t* gguf_rows, cudaStre
 // Q8 activation row, decoded byte by byte as the reference's scalar kernels
 // define the values (quant.rs:599-686).  One thread per block; not on the
 // timed path.
-__device__ inline uint8_t tile_byte(const DevStack& st, const uint8_t* tile0, int r, int s, int off) {
-    return tile0[(int64_t)s * 32 * st.slice_bytes + ((off >> 4) * 32 + (r & 31)) * 16 + (off & 15)];
+__device__ inline uint8_t tile_byte(const DevTiles& t, const uint8_t* tile0, int rr, int s, int off) {
+    // tile0: the row's tile in K-slice 0; the same tile of slice s is s * 4 tiles further
+    return tile0[(int64_t)s * 4 * 32 * t.slice_bytes + ((off >> 4) * 32 + rr) * 16 + (off & 15)];
 }
 
-__global__ void block_dots_kernel(DevStack st, int expert, int row, const int8_t* __restrict__ act_q,
-                                  int act_rows, int pos, int32_t* __restrict__ out) {
+__global__ void block_dots_kernel(DevTiles t, int tile_base, int expert, int row,
+                                  const int8_t* __restrict__ act_q, int act_rows, int pos,
+                                  int32_t* __restrict__ out) {
     const int b = blockIdx.x * blockDim.x + threadIdx.x;   // 32-element block of the row
-    if (b >= st.cols / 32) return;
-    const uint8_t* t0 = st.tile(expert, row / 32);
+    if (b >= t.cols / 32) return;
+    const int chunk = row / t.chunk_rows, tile = tile_base + (row % t.chunk_rows) / 32, rr = row % 32;
+    const uint8_t* t0 = t.stage(expert, chunk, 0) + (int64_t)tile * 32 * t.slice_bytes;
     const int s = b / 8, sb = b % 8;
-    const int8_t* x = act_q + ((size_t)s * act_rows + pos) * 256 + 32 * sb;
+    const int8_t* x = act_q + ((size_t)s * act_rows + pos) * kActQStride + 32 * sb;
     int32_t sum = 0;
-    if (st.ty == BIVMOE_Q8_0) {
-        for (int l = 0; l < 32; l++) sum += (int)(int8_t)tile_byte(st, t0, row, s, 32 * sb + l) * x[l];
-    } else if (st.ty == BIVMOE_Q4_K || st.ty == BIVMOE_Q5_K) {
-        const int qoff = (st.ty == BIVMOE_Q4_K ? 16 : 48) + 32 * (sb / 2);
+    if (t.ty == BIVMOE_Q8_0) {
+        for (int l = 0; l < 32; l++) sum += (int)(int8_t)tile_byte(t, t0, rr, s, 32 * sb + l) * x[l];
+    } else if (t.ty == BIVMOE_Q4_K || t.ty == BIVMOE_Q5_K) {
+        const int qoff = (t.ty == BIVMOE_Q4_K ? 16 : 48) + 32 * (sb / 2);
         for (int l = 0; l < 32; l++) {
-            int q = (tile_byte(st, t0, row, s, qoff + l) >> (4 * (sb % 2))) & 0xF;
-            if (st.ty == BIVMOE_Q5_K) q |= ((tile_byte(st, t0, row, s, 16 + l) >> sb) & 1) << 4;
+            int q = (tile_byte(t, t0, rr, s, qoff + l) >> (4 * (sb % 2))) & 0xF;
+            if (t.ty == BIVMOE_Q5_K) q |= ((tile_byte(t, t0, rr, s, 16 + l) >> sb) & 1) << 4;
             sum += q * x[l];
         }
-    } else if (st.ty == BIVMOE_Q6_K) {
+    } else if (t.ty == BIVMOE_Q6_K) {
         const int n = sb / 4, kq = sb % 4;
         for (int half = 0; half < 2; half++) {
             int32_t part = 0;
             for (int l = 16 * half; l < 16 * half + 16; l++) {
-                const int ql = tile_byte(st, t0, row, s, 64 * n + 32 * (kq & 1) + l);
-                const int qh = tile_byte(st, t0, row, s, 128 + 32 * n + l);
+                const int ql = tile_byte(t, t0, rr, s, 64 * n + 32 * (kq & 1) + l);
+                const int qh = tile_byte(t, t0, rr, s, 128 + 32 * n + l);
                 const int nib = kq >= 2 ? ql >> 4 : ql & 0xF;
                 part += ((nib | (((qh >> (2 * kq)) & 3) << 4)) - 32) * x[l];
             }
-            sum += (int)(int8_t)tile_byte(st, t0, row, s, 192 + 8 * n + 2 * kq + half) * part;
+            sum += (int)(int8_t)tile_byte(t, t0, rr, s, 192 + 8 * n + 2 * kq + half) * part;
         }
     }
     out[b] = sum;
 }
 
-cudaError_t launch_block_dots(const DevStack& st, int expert, int row, const int8_t* act_q,
-                              int act_rows, int pos, int32_t* out, cudaStream_t stream) {
-    const int nb = st.cols / 32;
-    block_dots_kernel<<<(nb + 63) / 64, 64, 0, stream>>>(st, expert, row, act_q, act_rows, pos, out);
+cudaError_t launch_block_dots(const DevTiles& t, int tile_base, int expert, int row,
+                              const int8_t* act_q, int act_rows, int pos, int32_t* out,
+                              cudaStream_t stream) {
+    const int nb = t.cols / 32;
+    block_dots_kernel<<<(nb + 63) / 64, 64, 0, stream>>>(t, tile_base, expert, row, act_q, act_rows,
+                                                         pos, out);
     return cudaGetLastError();
 }
 
