@@ -169,7 +169,7 @@ def config_of(wl, args, world):
                         f"top-{l.n_expert_used} + shared expert, ff {l.n_ff_exp}, "
                         f"gate/up {W.TYPE_NAMES[l.gate.ty]} down {W.TYPE_NAMES[l.down.ty]}, seed {wl.seed}",
             "tokens_per_gpu": wl.n, "parallelism": "replicas" if world > 1 else "single",
-            "l2": f"steps rotate over {WEIGHT_COPIES} resident copies of the layer's weights "
+            "l2": f"steps rotate over {max(1, args.copies)} resident copies of the layer's weights "
                   "(working set > 126 MB L2), no flush"}
 
 
@@ -182,6 +182,10 @@ def main():
     ap.add_argument("--workload", default="decode_q4k")
     ap.add_argument("--tokens", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--copies", type=int, default=WEIGHT_COPIES,
+                    help="resident copies of the layer the timed loop rotates over")
+    ap.add_argument("--quick", action="store_true",
+                    help="warm-up and timed loop only (the command profilers wrap)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -201,7 +205,8 @@ def main():
 
     wl = make_workload(args.workload, args)
     layer, n = wl.layer, wl.n
-    copies = [Moe(layer, n, device=local) for _ in range(WEIGHT_COPIES)]
+    ncopies = max(1, args.copies)
+    copies = [Moe(layer, n, device=local) for _ in range(ncopies)]
     h = torch.from_numpy(wl.h).cuda()
     out = torch.empty_like(h)
     h_pin = torch.from_numpy(wl.h).pin_memory()
@@ -213,7 +218,7 @@ def main():
         torch.cuda.synchronize()
 
     def step(i):
-        copies[i % WEIGHT_COPIES].moe_(h, out, accumulate=False)
+        copies[i % ncopies].moe_(h, out, accumulate=False)
 
     for i in range(warmup):
         step(i)
@@ -233,20 +238,24 @@ def main():
     barrier()
     launches = launch_count() - l0
     ms = e0.elapsed_time(e1)
+    if args.quick:
+        if rank == 0:
+            print(json.dumps({"quick": True, "ms_per_step": ms / args.steps, "steps": args.steps}))
+        return
     # ---- end to end: host rows in, host delta out, through the host-buffer call
     for i in range(3):
-        copies[i % WEIGHT_COPIES].moe_host(h_pin, out_pin)
+        copies[i % ncopies].moe_host(h_pin, out_pin)
     barrier()
     t0 = time.perf_counter()
     for i in range(args.steps):
-        copies[i % WEIGHT_COPIES].moe_host(h_pin, out_pin)
+        copies[i % ncopies].moe_host(h_pin, out_pin)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     # ---- the dominant kernel alone, events around each launch (separate loop so
     #      the events do not perturb the number above)
     k_ms, stage_ms = [], []
     for i in range(min(args.steps, 100)):
-        prof = copies[i % WEIGHT_COPIES].profile(h, out)
+        prof = copies[i % ncopies].profile(h, out)
         k_ms.append(prof["gateup"])
         stage_ms.append(prof)
     # keep the clocks sampler fed for long enough to see the load

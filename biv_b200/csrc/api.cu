@@ -72,7 +72,7 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
     w.weights = a.take<float>(P);
     w.counts = a.take<int32_t>(ne);
     w.offsets = a.take<int32_t>(ne + 1);
-    w.order = a.take<int32_t>(P);
+    w.order = a.take<int32_t>(((N + 7) / 8) * 8 + P + 8 * ne + 8);
     w.pos_of = a.take<int32_t>(P);
     w.blk_counts = a.take<int32_t>(((N + 255) / 256) * ne);
     w.grp_expert = a.take<int32_t>(ne + 1);
@@ -85,7 +85,8 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
     w.n_tiles = a.take<int32_t>(2);
     w.work_ctr = a.take<uint32_t>(4);
     w.status = a.take<int32_t>(4);
-    const size_t R = P + N + 8;   // the last tile of a group may read 7 rows past it
+    // positions: the tokens (shared group), then the routed groups, each padded to 8
+    const size_t R = ((N + 7) / 8) * 8 + P + 8 * ne + 8;
     w.act_rows = (int)R;
     const bool qact = !type_uses_f32_act(L->gate_up.ty) || (L->has_shared && !type_uses_f32_act(L->sh_gate_up.ty));
     const bool fact = type_uses_f32_act(L->gate_up.ty) || (L->has_shared && type_uses_f32_act(L->sh_gate_up.ty));
@@ -96,7 +97,7 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
     w.mid = a.take<float>(R * mid);
     w.mid_q = a.take<int8_t>(qmid ? R * (mid / 256) * kActQStride : 0);
     w.mid_ds = a.take<float2>(qmid ? R * mid / 32 : 0);
-    w.pair_out = a.take<float>((P + N) * e);
+    w.pair_out = a.take<float>(R * e);
     w.h_norm = a.take<float>(N * e);
 }
 
@@ -428,23 +429,38 @@ int bivmoe_tap(bivmoe_layer* L, int32_t which, void* dst, size_t bytes) {
         case BIVMOE_TAP_IDS: return copy_out(L, dst, w.ids, bytes, P * 4);
         case BIVMOE_TAP_WEIGHTS: return copy_out(L, dst, w.weights, bytes, P * 4);
         case BIVMOE_TAP_COUNTS: return copy_out(L, dst, w.counts, bytes, ne * 4);
-        case BIVMOE_TAP_ORDER: return copy_out(L, dst, w.order, bytes, P * 4);
+        case BIVMOE_TAP_ORDER: {   // the padded position space, compacted expert by expert
+            if (bytes != P * 4) return set_err(errp, BIVMOE_ERR_ARGUMENT, "tap buffer size mismatch");
+            std::vector<int32_t> cnt(ne), off(ne + 1), ord(w.act_rows);
+            CU(cudaMemcpy(cnt.data(), w.counts, ne * 4, cudaMemcpyDeviceToHost));
+            CU(cudaMemcpy(off.data(), w.offsets, (ne + 1) * 4, cudaMemcpyDeviceToHost));
+            CU(cudaMemcpy(ord.data(), w.order, ord.size() * 4, cudaMemcpyDeviceToHost));
+            size_t o = 0;
+            for (size_t x = 0; x < ne; x++)
+                for (int j = 0; j < cnt[x]; j++) ((int32_t*)dst)[o++] = ord[off[x] + j];
+            return BIVMOE_OK;
+        }
         case BIVMOE_TAP_ACT_Q:
         case BIVMOE_TAP_ACT_D:
         case BIVMOE_TAP_ACT_S: {
-            // the tokens' rows are positions P.. of the slice-major arrays
+            // the tokens' rows are positions 0..n of the slice-major arrays
             if (!w.act_q) return set_err(errp, BIVMOE_ERR_ARGUMENT, "no quantised activations");
             const size_t R = w.act_rows, nsl = e / 256;
             const bool q = which == BIVMOE_TAP_ACT_Q;
             if (bytes != (q ? n * e : n * e / 32 * 4))
                 return set_err(errp, BIVMOE_ERR_ARGUMENT, "tap buffer size mismatch");
+            // a token's row: its position in the shared group, else its first pair's position
+            std::vector<int32_t> tpos(n);
+            for (size_t t = 0; t < n; t++) tpos[t] = (int32_t)t;
+            if (!L->has_shared)
+                CU(cudaMemcpy2D(tpos.data(), 4, w.pos_of, (size_t)k * 4, 4, n, cudaMemcpyDeviceToHost));
             std::vector<int8_t> tq(q ? R * nsl * kActQStride : 0);
             std::vector<float> td(q ? 0 : R * e / 32 * 2);
             if (q) CU(cudaMemcpy(tq.data(), w.act_q, tq.size(), cudaMemcpyDeviceToHost));
             else CU(cudaMemcpy(td.data(), w.act_ds, td.size() * 4, cudaMemcpyDeviceToHost));
             for (size_t t = 0; t < n; t++)
                 for (size_t sl = 0; sl < nsl; sl++) {
-                    const size_t row = sl * R + P + t;
+                    const size_t row = sl * R + tpos[t];
                     if (q) memcpy((int8_t*)dst + t * e + sl * 256, tq.data() + row * kActQStride, 256);
                     else
                         for (int b = 0; b < 8; b++)
@@ -467,7 +483,7 @@ int bivmoe_tap(bivmoe_layer* L, int32_t which, void* dst, size_t bytes) {
         }
         case BIVMOE_TAP_PAIR_OUT: {
             if (bytes != P * e * 4) return set_err(errp, BIVMOE_ERR_ARGUMENT, "tap buffer size mismatch");
-            std::vector<float> tmp(P * e);
+            std::vector<float> tmp((size_t)w.act_rows * e);
             std::vector<int32_t> pos(P);
             CU(cudaMemcpy(tmp.data(), w.pair_out, tmp.size() * 4, cudaMemcpyDeviceToHost));
             CU(cudaMemcpy(pos.data(), w.pos_of, P * 4, cudaMemcpyDeviceToHost));
@@ -477,7 +493,7 @@ int bivmoe_tap(bivmoe_layer* L, int32_t which, void* dst, size_t bytes) {
         }
         case BIVMOE_TAP_SHARED_OUT:
             if (!L->has_shared) return set_err(errp, BIVMOE_ERR_ARGUMENT, "no shared expert");
-            return copy_out(L, dst, w.pair_out + P * e, bytes, n * e * 4);
+            return copy_out(L, dst, w.pair_out, bytes, n * e * 4);
         default: return set_err(errp, BIVMOE_ERR_ARGUMENT, "unknown tap %d", which);
     }
 }
@@ -503,10 +519,12 @@ int bivmoe_tap_block_dots(bivmoe_layer* L, int32_t matrix, int32_t expert, int32
     int32_t* dots = nullptr;
     CU(cudaMalloc((void**)&dots, (size_t)nb * 4));
     cudaError_t ce = cudaSuccess;
-    // gate/up rows meet the token's Q8 row of h (position P + token); down rows the
+    // gate/up rows meet the token's Q8 row of h (position = token); down rows the
     // Q8 row of the pair's mid vector at the pair's position
-    int32_t pos = P + act_row;
+    int32_t pos = act_row;
     if (is_down && !shared) ce = cudaMemcpy(&pos, L->ws.pos_of + act_row, 4, cudaMemcpyDeviceToHost);
+    if (!is_down && !L->has_shared)
+        ce = cudaMemcpy(&pos, L->ws.pos_of + (size_t)act_row * L->k, 4, cudaMemcpyDeviceToHost);
     if (ce == cudaSuccess)
         ce = launch_block_dots(m, tile_base, expert, row, is_down ? L->ws.mid_q : L->ws.act_q,
                                L->ws.act_rows, pos, dots, 0);

@@ -16,7 +16,7 @@ namespace bivmoe {
 // element in ascending i, and the 32 lanes are then summed as
 // (k0+k1)+(k2+k3) per lane j (lane = 8k+j), then j with j+4, j+2, j+1.  A warp
 // lane per accumulator lane and the butterfly 8,16,4,2,1 give the same bits.
-constexpr int RT_ROWS = 4, RT_TOKS = 4, RT_WARPS = 4;
+constexpr int RT_ROWS = 4, RT_TOKS = 4, RT_WARPS = 4, RT_UNROLL = 8;   // n_embd % 256 == 0
 
 __global__ void __launch_bounds__(RT_WARPS * 32)
 router_logits_kernel(const float* __restrict__ W, const float* __restrict__ h,
@@ -32,17 +32,23 @@ router_logits_kernel(const float* __restrict__ W, const float* __restrict__ h,
 #pragma unroll
     for (int t = 0; t < RT_TOKS; t++) xp[t] = h + (size_t)min(t0 + t, n - 1) * e + lane;
     float acc[RT_ROWS][RT_TOKS] = {};
-#pragma unroll 4
-    for (int i = 0; i < e; i += 32) {
-        float w[RT_ROWS], x[RT_TOKS];
+    // RT_UNROLL steps of loads are issued before their multiply-adds so that the
+    // loads of a batch are in flight together; the order of the adds is unchanged
+    for (int i0 = 0; i0 < e; i0 += 32 * RT_UNROLL) {
+        float w[RT_UNROLL][RT_ROWS], x[RT_UNROLL][RT_TOKS];
 #pragma unroll
-        for (int r = 0; r < RT_ROWS; r++) w[r] = __ldg(wp[r] + i);
+        for (int u = 0; u < RT_UNROLL; u++) {
 #pragma unroll
-        for (int t = 0; t < RT_TOKS; t++) x[t] = __ldg(xp[t] + i);
+            for (int r = 0; r < RT_ROWS; r++) w[u][r] = __ldg(wp[r] + i0 + 32 * u);
 #pragma unroll
-        for (int r = 0; r < RT_ROWS; r++)
+            for (int t = 0; t < RT_TOKS; t++) x[u][t] = __ldg(xp[t] + i0 + 32 * u);
+        }
 #pragma unroll
-            for (int t = 0; t < RT_TOKS; t++) acc[r][t] = fmaf(w[r], x[t], acc[r][t]);
+        for (int u = 0; u < RT_UNROLL; u++)
+#pragma unroll
+            for (int r = 0; r < RT_ROWS; r++)
+#pragma unroll
+                for (int t = 0; t < RT_TOKS; t++) acc[r][t] = fmaf(w[u][r], x[u][t], acc[r][t]);
     }
 #pragma unroll
     for (int r = 0; r < RT_ROWS; r++)
@@ -188,11 +194,15 @@ __device__ void block_exclusive_scan(int (&v)[ITEMS], int* s_warp, int* total) {
     __syncthreads();
 }
 
-// one block: bases over blocks and experts, the list of non-empty groups (the
-// shared expert's first: it is the heaviest), the list of token tiles, counters reset
+// One block: bases over blocks and experts, the list of non-empty groups, the
+// list of token tiles, counters reset.  Positions: the shared expert's group
+// (the tokens, in order) comes first at position 0; every routed group starts
+// at a multiple of 8 so that a tile of 8 positions never straddles two groups.
+// `s_cnt` (shared memory) holds the per-expert counts when one block sorts
+// everything; otherwise they are summed from the per-block counts.
 constexpr int SORT_EPT = 4;   // experts per thread in the scans (n_expert <= 1024)
 __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, int k,
-                          int has_shared) {
+                          int has_shared, const int* s_cnt, int* s_off) {
     __shared__ int s_warp[32];
     __shared__ int s_total[3];
     int cnt[SORT_EPT], off[SORT_EPT], act[SORT_EPT], til[SORT_EPT];
@@ -201,32 +211,41 @@ __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, in
     for (int i = 0; i < SORT_EPT; i++) {
         const int e = e0 + i;
         int run = 0;
-        if (e < n_expert)
-            for (int b = 0; b < nblk; b++) {
-                int c = ws.blk_counts[(size_t)b * n_expert + e];
-                ws.blk_counts[(size_t)b * n_expert + e] = run;
-                run += c;
+        if (e < n_expert) {
+            if (s_cnt) {
+                run = s_cnt[e];
+            } else {
+                for (int b = 0; b < nblk; b++) {
+                    int c = ws.blk_counts[(size_t)b * n_expert + e];
+                    ws.blk_counts[(size_t)b * n_expert + e] = run;
+                    run += c;
+                }
             }
+        }
         cnt[i] = run;
-        off[i] = run;
-        act[i] = run > 0;
         til[i] = (run + SORT_TILE - 1) / SORT_TILE;
+        off[i] = til[i] * SORT_TILE;
+        act[i] = run > 0;
     }
+    __syncthreads();   // s_cnt is read; s_off may alias it
     block_exclusive_scan<SORT_EPT>(off, s_warp, &s_total[0]);
     block_exclusive_scan<SORT_EPT>(act, s_warp, &s_total[1]);
     block_exclusive_scan<SORT_EPT>(til, s_warp, &s_total[2]);
     const int g_sh = has_shared ? 1 : 0;
     const int t_sh = has_shared ? (n + SORT_TILE - 1) / SORT_TILE : 0;
+    const int p_sh = t_sh * SORT_TILE;
 #pragma unroll
     for (int i = 0; i < SORT_EPT; i++) {
         const int e = e0 + i;
         if (e >= n_expert) continue;
+        const int start = p_sh + off[i];
         ws.counts[e] = cnt[i];
-        ws.offsets[e] = off[i];
+        ws.offsets[e] = start;
+        if (s_off) s_off[e] = start;
         if (cnt[i]) {
             const int g = g_sh + act[i];
             ws.grp_expert[g] = e;
-            ws.grp_start[g] = off[i];
+            ws.grp_start[g] = start;
             ws.grp_count[g] = cnt[i];
             const int nt = (cnt[i] + SORT_TILE - 1) / SORT_TILE;
             for (int j = 0; j < nt; j++) {
@@ -242,10 +261,10 @@ __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, in
     if (threadIdx.x == 0) {
         if (has_shared) {
             ws.grp_expert[0] = n_expert;
-            ws.grp_start[0] = n * k;
+            ws.grp_start[0] = 0;
             ws.grp_count[0] = n;
         }
-        ws.offsets[n_expert] = s_total[0];
+        ws.offsets[n_expert] = p_sh + s_total[0];
         *ws.n_groups = g_sh + s_total[1];
         ws.n_tiles[0] = t_sh + s_total[2];
         ws.n_tiles[1] = t_sh;
@@ -253,10 +272,11 @@ __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, in
     }
     __syncthreads();
 }
+// one thread per expert walks the block's pairs in order
 __device__ void sort_scatter(const Workspace& ws, const uint16_t* s_ids, int pair0, int npairs,
-                             int n_expert, int blk) {
+                             int n_expert, int blk, const int* s_off) {
     for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
-        int pos = ws.offsets[e] + ws.blk_counts[(size_t)blk * n_expert + e];
+        int pos = s_off ? s_off[e] : ws.offsets[e] + ws.blk_counts[(size_t)blk * n_expert + e];
         for (int i = 0; i < npairs; i++)
             if (s_ids[i] == e) {
                 ws.order[pos] = pair0 + i;
@@ -275,21 +295,26 @@ sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int phase)
     const int blk = blockIdx.x;
     const int tok0 = blk * SORT_TOKENS, ntok = min(SORT_TOKENS, n - tok0);
     const int pair0 = tok0 * k, npairs = ntok * k;
-    if (phase == 0 || phase == 1) {
+    if (phase == 0) {   // one block does everything, counts and bases stay in shared memory
+        sort_load_ids(ws.ids, pair0, npairs, s_ids);
+        __syncthreads();
+        sort_hist(s_ids, npairs, n_expert, s_cnt);
+        sort_scan(ws, n_expert, 1, n, k, has_shared, s_cnt, s_cnt);
+        sort_scatter(ws, s_ids, pair0, npairs, n_expert, 0, s_cnt);
+        return;
+    }
+    if (phase == 1) {
         sort_load_ids(ws.ids, pair0, npairs, s_ids);
         __syncthreads();
         sort_hist(s_ids, npairs, n_expert, s_cnt);
         for (int e = threadIdx.x; e < n_expert; e += blockDim.x)
             ws.blk_counts[(size_t)blk * n_expert + e] = s_cnt[e];
-        __syncthreads();
     }
-    if (phase == 0 || phase == 2) sort_scan(ws, n_expert, nblk, n, k, has_shared);
-    if (phase == 0 || phase == 3) {
-        if (phase == 3) {
-            sort_load_ids(ws.ids, pair0, npairs, s_ids);
-            __syncthreads();
-        }
-        sort_scatter(ws, s_ids, pair0, npairs, n_expert, blk);
+    if (phase == 2) sort_scan(ws, n_expert, nblk, n, k, has_shared, nullptr, nullptr);
+    if (phase == 3) {
+        sort_load_ids(ws.ids, pair0, npairs, s_ids);
+        __syncthreads();
+        sort_scatter(ws, s_ids, pair0, npairs, n_expert, blk, nullptr);
     }
 }
 

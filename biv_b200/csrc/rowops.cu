@@ -8,7 +8,7 @@ namespace bivmoe {
 
 // ---------------------------------------------------------------------------
 // Dispatch: the rows the expert kernels consume, laid out by position
-// (slice-major, see common.cuh).  Token t's row goes to position P + t (the
+// (slice-major, see common.cuh).  Token t's row goes to position t (the
 // shared expert's group) and to the position of each of its k pairs.  For
 // quantised weight types the row is quantised once, Q8Act::quantize_into
 // (quant.rs:368-394) - the reference quantises it again for every expert it is
@@ -17,30 +17,45 @@ namespace bivmoe {
 constexpr int DP_THREADS = 256, DP_MAX_K = 32;
 
 __global__ void __launch_bounds__(DP_THREADS)
-dispatch_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int quant, int f32) {
+dispatch_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int quant, int f32,
+                int has_shared) {
     __shared__ int s_pos[DP_MAX_K + 1];
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int P = n * k, R = ws.act_rows;
+    const int R = ws.act_rows;
     if (threadIdx.x < k) s_pos[threadIdx.x] = ws.pos_of[(size_t)t * k + threadIdx.x];
-    if (threadIdx.x == k) s_pos[k] = P + t;
+    // the shared expert's group is positions 0..n; without one, position t belongs to
+    // a routed group and the extra copy is dropped (the first pair's position is repeated)
+    if (threadIdx.x == k) s_pos[k] = has_shared ? t : ws.pos_of[(size_t)t * k];
     __syncthreads();
     const float* x = h + (size_t)t * e;
-    for (int b = warp; b < e / 32; b += DP_THREADS / 32) {
-        const float v = x[32 * b + lane];
-        if (quant) {
-            float dd, ss;
-            const int q = q8_quantize_lane(v, dd, ss);
-            const int sl = b / 8, bb = b % 8;
-            for (int j = 0; j <= k; j++) {
-                const size_t row = (size_t)sl * R + s_pos[j];
-                ws.act_q[row * kActQStride + 32 * bb + lane] = (int8_t)q;
-                if (lane == 0) ws.act_ds[row * 8 + bb] = make_float2(dd, ss);
-            }
+    constexpr int NW = DP_THREADS / 32, U = 4;   // U loads in flight per lane
+    for (int b0 = warp; b0 < e / 32; b0 += NW * U) {
+        float vv[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int b = b0 + u * NW;
+            vv[u] = b < e / 32 ? x[32 * b + lane] : 0.0f;
         }
-        if (f32) {
-            const int sl = b / 2, off = (b % 2) * 32;
-            for (int j = 0; j <= k; j++)
-                ws.act_f[((size_t)sl * R + s_pos[j]) * 64 + off + lane] = v;
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int b = b0 + u * NW;
+            if (b >= e / 32) break;
+            const float v = vv[u];
+            if (quant) {
+                float dd, ss;
+                const int q = q8_quantize_lane(v, dd, ss);
+                const int sl = b / 8, bb = b % 8;
+                for (int j = 0; j <= k; j++) {
+                    const size_t row = (size_t)sl * R + s_pos[j];
+                    ws.act_q[row * kActQStride + 32 * bb + lane] = (int8_t)q;
+                    if (lane == 0) ws.act_ds[row * 8 + bb] = make_float2(dd, ss);
+                }
+            }
+            if (f32) {
+                const int sl = b / 2, off = (b % 2) * 32;
+                for (int j = 0; j <= k; j++)
+                    ws.act_f[((size_t)sl * R + s_pos[j]) * 64 + off + lane] = v;
+            }
         }
     }
 }
@@ -48,7 +63,8 @@ dispatch_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, 
 cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace& ws, bool quant,
                             bool f32) {
     if (c.k > DP_MAX_K) return cudaErrorInvalidValue;
-    dispatch_kernel<<<c.n, DP_THREADS, 0, c.stream>>>(h, ws, c.n, c.k, c.e, quant ? 1 : 0, f32 ? 1 : 0);
+    dispatch_kernel<<<c.n, DP_THREADS, 0, c.stream>>>(h, ws, c.n, c.k, c.e, quant ? 1 : 0, f32 ? 1 : 0,
+                                                      c.has_shared);
     count_launch();
     return cudaGetLastError();
 }
@@ -120,7 +136,7 @@ combine_kernel(Workspace ws, float* __restrict__ out, int n, int k, int e, int n
         acc.z = fmaf(w, y.z, acc.z); acc.w = fmaf(w, y.w, acc.w);
     }
     if (has_shared) {
-        const float4 y = *(const float4*)(ws.pair_out + ((size_t)n * k + t) * e + c4 * 4);
+        const float4 y = *(const float4*)(ws.pair_out + (size_t)t * e + c4 * 4);
         const float w = s_gate;
         acc.x = fmaf(w, y.x, acc.x); acc.y = fmaf(w, y.y, acc.y);
         acc.z = fmaf(w, y.z, acc.z); acc.w = fmaf(w, y.w, acc.w);
