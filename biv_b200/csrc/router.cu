@@ -16,39 +16,79 @@ namespace bivmoe {
 // element in ascending i, and the 32 lanes are then summed as
 // (k0+k1)+(k2+k3) per lane j (lane = 8k+j), then j with j+4, j+2, j+1.  A warp
 // lane per accumulator lane and the butterfly 8,16,4,2,1 give the same bits.
-constexpr int RT_ROWS = 4, RT_TOKS = 4, RT_WARPS = 4, RT_UNROLL = 8;   // n_embd % 256 == 0
+constexpr int RT_ROWS = 4, RT_TOKS = 4;          // register tile of one warp
+constexpr int RT_BROWS = 8, RT_BTOKS = 16;       // rows and tokens of one block (8 warps)
+constexpr int RT_THREADS = 256;
+constexpr uint32_t RT_WAIT_LIMIT = 1u << 20;
 
-__global__ void __launch_bounds__(RT_WARPS * 32)
+__device__ __forceinline__ uint32_t rt_smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// The block's 8 weight rows and 16 activation rows are brought into shared memory
+// with one bulk copy each, all in flight together, so the kernel pays one memory
+// round trip instead of one per step of the dot.
+__global__ void __launch_bounds__(RT_THREADS, 1)
 router_logits_kernel(const float* __restrict__ W, const float* __restrict__ h,
-                     float* __restrict__ logits, int n, int e, int n_rows) {
+                     float* __restrict__ logits, int n, int e, int n_rows, int* status) {
+    extern __shared__ __align__(128) uint8_t rt_smem[];
+    uint64_t* bar = (uint64_t*)rt_smem;
+    float* s_w = (float*)(rt_smem + 128);              // [RT_BROWS][e]
+    float* s_x = s_w + (size_t)RT_BROWS * e;           // [RT_BTOKS][e]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int r0 = blockIdx.x * RT_ROWS;
-    const int t0 = (blockIdx.y * RT_WARPS + warp) * RT_TOKS;
-    if (t0 >= n) return;
-    const float* wp[RT_ROWS];
-    const float* xp[RT_TOKS];
-#pragma unroll
-    for (int r = 0; r < RT_ROWS; r++) wp[r] = W + (size_t)min(r0 + r, n_rows - 1) * e + lane;
-#pragma unroll
-    for (int t = 0; t < RT_TOKS; t++) xp[t] = h + (size_t)min(t0 + t, n - 1) * e + lane;
-    float acc[RT_ROWS][RT_TOKS] = {};
-    // RT_UNROLL steps of loads are issued before their multiply-adds so that the
-    // loads of a batch are in flight together; the order of the adds is unchanged
-    for (int i0 = 0; i0 < e; i0 += 32 * RT_UNROLL) {
-        float w[RT_UNROLL][RT_ROWS], x[RT_UNROLL][RT_TOKS];
-#pragma unroll
-        for (int u = 0; u < RT_UNROLL; u++) {
-#pragma unroll
-            for (int r = 0; r < RT_ROWS; r++) w[u][r] = __ldg(wp[r] + i0 + 32 * u);
-#pragma unroll
-            for (int t = 0; t < RT_TOKS; t++) x[u][t] = __ldg(xp[t] + i0 + 32 * u);
+    const int br0 = blockIdx.x * RT_BROWS, bt0 = blockIdx.y * RT_BTOKS;
+    const uint32_t row_bytes = (uint32_t)e * 4;
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(rt_smem_u32(bar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 0) {
+        if (lane == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(rt_smem_u32(bar)),
+                         "r"(row_bytes * (RT_BROWS + RT_BTOKS))
+                         : "memory");
+        __syncwarp();
+        if (lane < RT_BROWS + RT_BTOKS) {   // rows past the end repeat the last one; never stored
+            const float* src = lane < RT_BROWS ? W + (size_t)min(br0 + lane, n_rows - 1) * e
+                                               : h + (size_t)min(bt0 + lane - RT_BROWS, n - 1) * e;
+            float* dst = lane < RT_BROWS ? s_w + (size_t)lane * e : s_x + (size_t)(lane - RT_BROWS) * e;
+            asm volatile(
+                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+                    "r"(rt_smem_u32(dst)),
+                "l"(src), "r"(row_bytes), "r"(rt_smem_u32(bar))
+                : "memory");
         }
+    }
+    bool ok = false;
+    for (uint32_t i = 0; i < RT_WAIT_LIMIT && !ok; i++) {
+        uint32_t p;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(p)
+            : "r"(rt_smem_u32(bar))
+            : "memory");
+        ok = p != 0;
+    }
+    if (!ok) {   // bounded wait gave up: every thread waits on the same barrier
+        if (threadIdx.x == 0) atomicExch(status, BIVMOE_ERR_TIMEOUT);
+        return;
+    }
+    const int r0 = (warp & 1) * RT_ROWS, t0 = (warp >> 1) * RT_TOKS;   // inside the block
+    float acc[RT_ROWS][RT_TOKS] = {};
+#pragma unroll 4
+    for (int i = lane; i < e; i += 32) {
+        float w[RT_ROWS], x[RT_TOKS];
 #pragma unroll
-        for (int u = 0; u < RT_UNROLL; u++)
+        for (int r = 0; r < RT_ROWS; r++) w[r] = s_w[(size_t)(r0 + r) * e + i];
 #pragma unroll
-            for (int r = 0; r < RT_ROWS; r++)
+        for (int t = 0; t < RT_TOKS; t++) x[t] = s_x[(size_t)(t0 + t) * e + i];
 #pragma unroll
-                for (int t = 0; t < RT_TOKS; t++) acc[r][t] = fmaf(w[u][r], x[u][t], acc[r][t]);
+        for (int r = 0; r < RT_ROWS; r++)
+#pragma unroll
+            for (int t = 0; t < RT_TOKS; t++) acc[r][t] = fmaf(w[r], x[t], acc[r][t]);
     }
 #pragma unroll
     for (int r = 0; r < RT_ROWS; r++)
@@ -60,17 +100,26 @@ router_logits_kernel(const float* __restrict__ W, const float* __restrict__ h,
             v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
             v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
             v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
-            if (lane == 0 && r0 + r < n_rows && t0 + t < n)
-                logits[(size_t)(t0 + t) * n_rows + r0 + r] = v;
+            const int row = br0 + r0 + r, tok = bt0 + t0 + t;
+            if (lane == 0 && row < n_rows && tok < n) logits[(size_t)tok * n_rows + row] = v;
         }
 }
 
 cudaError_t launch_router(const LaunchCfg& c, const float* router_dev, const float* h,
                           const Workspace& ws) {
     int n_rows = c.n_expert + 1;
-    dim3 grid((n_rows + RT_ROWS - 1) / RT_ROWS, (c.n + RT_WARPS * RT_TOKS - 1) / (RT_WARPS * RT_TOKS));
-    router_logits_kernel<<<grid, RT_WARPS * 32, 0, c.stream>>>(router_dev, h, ws.logits, c.n, c.e,
-                                                               n_rows);
+    const int smem = 128 + (RT_BROWS + RT_BTOKS) * c.e * 4;
+    if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t err = cudaFuncSetAttribute(router_logits_kernel,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (err != cudaSuccess) return err;
+        attr_set = true;
+    }
+    dim3 grid((n_rows + RT_BROWS - 1) / RT_BROWS, (c.n + RT_BTOKS - 1) / RT_BTOKS);
+    router_logits_kernel<<<grid, RT_THREADS, smem, c.stream>>>(router_dev, h, ws.logits, c.n, c.e,
+                                                               n_rows, ws.status);
     count_launch();
     return cudaGetLastError();
 }
@@ -97,8 +146,17 @@ route_topk_kernel(const float* __restrict__ logits, int32_t* __restrict__ ids,
     for (int i = lane; i < n_expert; i += 32) p[i] = expf(__fsub_rn(l[i], mx));
     __syncwarp();
     float sum = 0.0f;
-    if (lane == 0)
-        for (int i = 0; i < n_expert; i++) sum = __fadd_rn(sum, p[i]);
+    if (lane == 0) {   // the order of the adds is the reference's; the loads are batched
+        int i = 0;
+        for (; i + 8 <= n_expert; i += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) v[u] = p[i + u];
+#pragma unroll
+            for (int u = 0; u < 8; u++) sum = __fadd_rn(sum, v[u]);
+        }
+        for (; i < n_expert; i++) sum = __fadd_rn(sum, p[i]);
+    }
     sum = __shfl_sync(0xffffffffu, sum, 0);
     const float inv = __fdiv_rn(1.0f, sum);
     for (int i = lane; i < n_expert; i += 32) p[i] = __fmul_rn(p[i], inv);
@@ -272,17 +330,29 @@ __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, in
     }
     __syncthreads();
 }
-// one thread per expert walks the block's pairs in order
-__device__ void sort_scatter(const Workspace& ws, const uint16_t* s_ids, int pair0, int npairs,
-                             int n_expert, int blk, const int* s_off) {
-    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
-        int pos = s_off ? s_off[e] : ws.offsets[e] + ws.blk_counts[(size_t)blk * n_expert + e];
-        for (int i = 0; i < npairs; i++)
-            if (s_ids[i] == e) {
-                ws.order[pos] = pair0 + i;
-                ws.pos_of[pair0 + i] = pos;
-                pos++;
-            }
+// A token selects an expert at most once, so the rank of pair (t, j) inside its
+// expert is the number of earlier tokens of the block that selected the expert:
+// a popcount over the expert's token bitmask.
+__device__ void sort_build_masks(const uint16_t* s_ids, int npairs, int k, int n_expert,
+                                 uint32_t* s_mask) {
+    for (int i = threadIdx.x; i < n_expert * (SORT_TOKENS / 32); i += blockDim.x) s_mask[i] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+        const int t = i / k;
+        atomicOr(&s_mask[s_ids[i] * (SORT_TOKENS / 32) + (t >> 5)], 1u << (t & 31));
+    }
+    __syncthreads();
+}
+__device__ void sort_scatter(const Workspace& ws, const uint16_t* s_ids, const uint32_t* s_mask,
+                             int pair0, int npairs, int k, int n_expert, int blk, const int* s_off) {
+    for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+        const int e = s_ids[i], t = i / k;
+        const uint32_t* m = s_mask + e * (SORT_TOKENS / 32);
+        int rank = __popc(m[t >> 5] & ((1u << (t & 31)) - 1u));
+        for (int w = 0; w < (t >> 5); w++) rank += __popc(m[w]);
+        const int pos = (s_off ? s_off[e] : ws.offsets[e] + ws.blk_counts[(size_t)blk * n_expert + e]) + rank;
+        ws.order[pos] = pair0 + i;
+        ws.pos_of[pair0 + i] = pos;
     }
 }
 
@@ -291,6 +361,7 @@ sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int phase)
     extern __shared__ uint8_t sort_smem[];
     uint16_t* s_ids = (uint16_t*)sort_smem;
     int* s_cnt = (int*)(sort_smem + (((size_t)SORT_TOKENS * k * 2 + 15) & ~(size_t)15));
+    uint32_t* s_mask = (uint32_t*)(s_cnt + n_expert);
     const int nblk = (n + SORT_TOKENS - 1) / SORT_TOKENS;
     const int blk = blockIdx.x;
     const int tok0 = blk * SORT_TOKENS, ntok = min(SORT_TOKENS, n - tok0);
@@ -299,8 +370,9 @@ sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int phase)
         sort_load_ids(ws.ids, pair0, npairs, s_ids);
         __syncthreads();
         sort_hist(s_ids, npairs, n_expert, s_cnt);
+        sort_build_masks(s_ids, npairs, k, n_expert, s_mask);
         sort_scan(ws, n_expert, 1, n, k, has_shared, s_cnt, s_cnt);
-        sort_scatter(ws, s_ids, pair0, npairs, n_expert, 0, s_cnt);
+        sort_scatter(ws, s_ids, s_mask, pair0, npairs, k, n_expert, 0, s_cnt);
         return;
     }
     if (phase == 1) {
@@ -314,13 +386,21 @@ sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int phase)
     if (phase == 3) {
         sort_load_ids(ws.ids, pair0, npairs, s_ids);
         __syncthreads();
-        sort_scatter(ws, s_ids, pair0, npairs, n_expert, blk, nullptr);
+        sort_build_masks(s_ids, npairs, k, n_expert, s_mask);
+        sort_scatter(ws, s_ids, s_mask, pair0, npairs, k, n_expert, blk, nullptr);
     }
 }
 
 cudaError_t launch_sort(const LaunchCfg& c, const Workspace& ws) {
     const int nblk = (c.n + SORT_TOKENS - 1) / SORT_TOKENS;
-    size_t smem = (((size_t)SORT_TOKENS * c.k * 2 + 15) & ~(size_t)15) + (size_t)c.n_expert * 4;
+    size_t smem = (((size_t)SORT_TOKENS * c.k * 2 + 15) & ~(size_t)15) + (size_t)c.n_expert * 4 +
+                  (size_t)c.n_expert * (SORT_TOKENS / 32) * 4;   // <= 16 + 4 + 32 KiB
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t err = cudaFuncSetAttribute(sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        if (err != cudaSuccess) return err;
+        attr_set = true;
+    }
     if (nblk == 1) {
         sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, 0);
         count_launch();

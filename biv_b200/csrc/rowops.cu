@@ -29,7 +29,8 @@ dispatch_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, 
     __syncthreads();
     const float* x = h + (size_t)t * e;
     constexpr int NW = DP_THREADS / 32, U = 4;   // U loads in flight per lane
-    for (int b0 = warp; b0 < e / 32; b0 += NW * U) {
+    // blockIdx.y halves the row between two blocks
+    for (int b0 = blockIdx.y * NW * U + warp; b0 < e / 32; b0 += gridDim.y * NW * U) {
         float vv[U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
@@ -63,7 +64,7 @@ dispatch_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, 
 cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace& ws, bool quant,
                             bool f32) {
     if (c.k > DP_MAX_K) return cudaErrorInvalidValue;
-    dispatch_kernel<<<c.n, DP_THREADS, 0, c.stream>>>(h, ws, c.n, c.k, c.e, quant ? 1 : 0, f32 ? 1 : 0,
+    dispatch_kernel<<<dim3(c.n, 2), DP_THREADS, 0, c.stream>>>(h, ws, c.n, c.k, c.e, quant ? 1 : 0, f32 ? 1 : 0,
                                                       c.has_shared);
     count_launch();
     return cudaGetLastError();
