@@ -91,12 +91,10 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
     const bool qact = !type_uses_f32_act(L->gate_up.ty) || (L->has_shared && !type_uses_f32_act(L->sh_gate_up.ty));
     const bool fact = type_uses_f32_act(L->gate_up.ty) || (L->has_shared && type_uses_f32_act(L->sh_gate_up.ty));
     const bool qmid = !type_uses_f32_act(L->down.ty) || (L->has_shared && !type_uses_f32_act(L->sh_down.ty));
-    w.act_q = a.take<int8_t>(qact ? R * (e / 256) * kActQStride : 0);
-    w.act_ds = a.take<float2>(qact ? R * e / 32 : 0);
+    w.act_t = a.take<uint8_t>(qact ? (e / 256) * (R / 8) * kActTileBytes : 0);
     w.act_f = a.take<float>(fact ? R * e : 0);
     w.mid = a.take<float>(R * mid);
-    w.mid_q = a.take<int8_t>(qmid ? R * (mid / 256) * kActQStride : 0);
-    w.mid_ds = a.take<float2>(qmid ? R * mid / 32 : 0);
+    w.mid_t = a.take<uint8_t>(qmid ? (mid / 256) * (R / 8) * kActTileBytes : 0);
     w.pair_out = a.take<float>(R * e);
     w.h_norm = a.take<float>(N * e);
 }
@@ -304,7 +302,7 @@ static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int 
     mark(c, EV_TOPK);
     CU(launch_sort(c, L->ws));
     mark(c, EV_SORT);
-    CU(launch_dispatch(c, h, L->ws, L->ws.act_q != nullptr, L->ws.act_f != nullptr));
+    CU(launch_dispatch(c, h, L->ws, L->ws.act_t != nullptr, L->ws.act_f != nullptr));
     mark(c, EV_QUANT);
     CU(launch_experts(c, L->gate_up, L->down, L->sh_gate_up, L->sh_down, L->ws));
     mark(c, EV_DOWN);
@@ -444,7 +442,7 @@ int bivmoe_tap(bivmoe_layer* L, int32_t which, void* dst, size_t bytes) {
         case BIVMOE_TAP_ACT_D:
         case BIVMOE_TAP_ACT_S: {
             // the tokens' rows are positions 0..n of the slice-major arrays
-            if (!w.act_q) return set_err(errp, BIVMOE_ERR_ARGUMENT, "no quantised activations");
+            if (!w.act_t) return set_err(errp, BIVMOE_ERR_ARGUMENT, "no quantised activations");
             const size_t R = w.act_rows, nsl = e / 256;
             const bool q = which == BIVMOE_TAP_ACT_Q;
             if (bytes != (q ? n * e : n * e / 32 * 4))
@@ -454,18 +452,17 @@ int bivmoe_tap(bivmoe_layer* L, int32_t which, void* dst, size_t bytes) {
             for (size_t t = 0; t < n; t++) tpos[t] = (int32_t)t;
             if (!L->has_shared)
                 CU(cudaMemcpy2D(tpos.data(), 4, w.pos_of, (size_t)k * 4, 4, n, cudaMemcpyDeviceToHost));
-            std::vector<int8_t> tq(q ? R * nsl * kActQStride : 0);
-            std::vector<float> td(q ? 0 : R * e / 32 * 2);
-            if (q) CU(cudaMemcpy(tq.data(), w.act_q, tq.size(), cudaMemcpyDeviceToHost));
-            else CU(cudaMemcpy(td.data(), w.act_ds, td.size() * 4, cudaMemcpyDeviceToHost));
+            std::vector<uint8_t> rec(nsl * (R / 8) * kActTileBytes);
+            CU(cudaMemcpy(rec.data(), w.act_t, rec.size(), cudaMemcpyDeviceToHost));
             for (size_t t = 0; t < n; t++)
                 for (size_t sl = 0; sl < nsl; sl++) {
-                    const size_t row = sl * R + tpos[t];
-                    if (q) memcpy((int8_t*)dst + t * e + sl * 256, tq.data() + row * kActQStride, 256);
+                    const uint8_t* r0 = rec.data() + (sl * (R / 8) + tpos[t] / 8) * kActTileBytes;
+                    const int tk = tpos[t] % 8;
+                    if (q) memcpy((int8_t*)dst + t * e + sl * 256, r0 + tk * kActQStride, 256);
                     else
                         for (int b = 0; b < 8; b++)
-                            ((float*)dst)[t * (e / 32) + sl * 8 + b] =
-                                td[(row * 8 + b) * 2 + (which == BIVMOE_TAP_ACT_S ? 1 : 0)];
+                            ((float*)dst)[t * (e / 32) + sl * 8 + b] = *(const float*)(
+                                r0 + (which == BIVMOE_TAP_ACT_S ? kActOffS : kActOffDx) + (b * 8 + tk) * 4);
                 }
             return BIVMOE_OK;
         }
@@ -526,7 +523,7 @@ int bivmoe_tap_block_dots(bivmoe_layer* L, int32_t matrix, int32_t expert, int32
     if (!is_down && !L->has_shared)
         ce = cudaMemcpy(&pos, L->ws.pos_of + (size_t)act_row * L->k, 4, cudaMemcpyDeviceToHost);
     if (ce == cudaSuccess)
-        ce = launch_block_dots(m, tile_base, expert, row, is_down ? L->ws.mid_q : L->ws.act_q,
+        ce = launch_block_dots(m, tile_base, expert, row, is_down ? L->ws.mid_t : L->ws.act_t,
                                L->ws.act_rows, pos, dots, 0);
     if (ce == cudaSuccess) ce = cudaMemcpy(out, dots, (size_t)nb * 4, cudaMemcpyDeviceToHost);
     cudaFree(dots);

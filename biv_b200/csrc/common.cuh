@@ -71,11 +71,32 @@ struct DevTiles {          // the tiles of one product (gate+up, or down) of a s
     }
 };
 
-// Activation rows are kept "slice-major" so that the K-slice of 8 consecutive
-// rows is contiguous: quantised rows as q [K/256][R][272] int8 (256 values and
-// 16 bytes of padding, which spreads 8 rows over the shared-memory banks) and
-// ds [K/256][R][8] (d, s); float rows as [K/64][R][64] f32.  R = P + n + 8.
+// Activation rows live in a position space in which every group starts at a
+// multiple of 8, so a tile of 8 positions belongs to one group.  Quantised rows
+// (Q8Act, quant.rs:352-394) are stored as one record per (K-slice of 256, tile):
+//     q     [8 tokens][272]  int8: 256 values + 16 bytes of padding that spreads
+//                            the 8 rows over the shared-memory banks
+//     dx    [8 blocks][8 tokens] f32: the block scales d
+//     s_hi  [8 blocks][8 tokens] f32: s = d*sum(q) split in two tf32-exact parts
+//     s_lo                            (11 + 11 mantissa bits), for the tensor-core min term
+//     s     [8 blocks][8 tokens] f32: s itself (read by the taps only)
+// which is what one pipeline stage of the expert kernels copies (all but `s`).
+// Float rows (BF16 weights) are [K/64][R][64] f32.  R = ceil8(n) + n*k + 8*n_expert + 8.
 constexpr int kActQStride = 272;
+constexpr int kActOffDx = 8 * kActQStride, kActOffSHi = kActOffDx + 256, kActOffSLo = kActOffSHi + 256,
+              kActOffS = kActOffSLo + 256;
+constexpr int kActCopyBytes = kActOffS;        // 2944: what a stage copies
+constexpr int kActTileBytes = kActOffS + 256;  // 3200
+// the two tf32-exact parts of an f32 (the tensor core ignores the low 13 mantissa bits)
+__host__ __device__ inline void split_tf32(float v, float* hi, float* lo) {
+    union { float f; uint32_t u; } a, b;
+    a.f = v;
+    a.u &= 0xFFFFE000u;
+    b.f = v - a.f;
+    b.u &= 0xFFFFE000u;
+    *hi = a.f;
+    *lo = b.f;
+}
 // Per-forward scratch.  P = n * k routed pairs; "positions" 0..P are the pairs
 // in expert-sorted order, positions P..P+n are the tokens of the shared expert.
 struct Workspace {
@@ -96,13 +117,11 @@ struct Workspace {
     int32_t* n_tiles;    // [2] all tiles; the shared group's tiles (they come first)
     uint32_t* work_ctr;  // [4] dynamic work counters, zeroed by the sort
     int32_t* status;     // [4] device-side error flags (0 = ok)
-    int act_rows;        // R: rows of every slice-major activation array
-    int8_t* act_q;       // Q8 rows of h by position (positions P.. are the tokens), slice-major
-    float2* act_ds;
+    int act_rows;        // R: positions
+    uint8_t* act_t;      // Q8 records of h, [n_embd/256][R/8] tiles (quantised gate/up types)
     float* act_f;        // f32 rows of h by position, slice-major (float-activation types)
-    float* mid;          // silu(gate)*up by position, slice-major f32
-    int8_t* mid_q;       // its Q8 rows (quantised down types), slice-major
-    float2* mid_ds;
+    float* mid;          // silu(gate)*up by position, slice-major f32 [ff/64][R][64]
+    uint8_t* mid_t;      // its Q8 records, [ff/256][R/8] tiles (quantised down types)
     float* pair_out;     // [P + n][e], by position
     float* h_norm;       // [n][e] rms-normed rows (forward_stack)
 };
@@ -133,7 +152,7 @@ cudaError_t launch_rms_norm(const LaunchCfg& c, const float* x, const float* w, 
 cudaError_t launch_repack(const DevTiles& dst, const uint8_t* gguf_rows, int tile_base,
                           cudaStream_t stream);
 cudaError_t launch_block_dots(const DevTiles& t, int tile_base, int expert, int row,
-                              const int8_t* act_q, int act_rows, int pos, int32_t* out,
+                              const uint8_t* act_t, int act_rows, int pos, int32_t* out,
                               cudaStream_t stream);
 bool experts_supported(int ty, int cols, int rows, bool is_down);
 

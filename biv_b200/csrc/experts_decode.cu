@@ -22,6 +22,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "formats.cuh"
@@ -30,7 +31,7 @@ namespace bivmoe {
 
 constexpr int EX_TT = 8;                       // tokens per tile
 constexpr int EX_THREADS = 128;                // four warps
-constexpr uint32_t EX_WAIT_LIMIT = 1u << 20;   // bounded mbarrier spin
+constexpr uint32_t EX_WAIT_LIMIT = 1u << 16;   // bounded mbarrier wait: tries of up to 20 us each
 
 enum { MODE_GATEUP = 0, MODE_DOWN = 1 };
 
@@ -38,12 +39,10 @@ struct ExpertArgs {
     DevTiles w, sh;        // the routed experts' and the shared expert's tiles for this product
     // activations by position, slice-major (common.cuh): rows of h for GATEUP, of mid for DOWN
     const float* x_f32;    // float-activation types
-    const int8_t* x_q;     // quantised types
-    const float2* x_ds;
+    const uint8_t* x_t;    // quantised types: the Q8 records, [K/256][R/8]
     int act_rows;          // R
-    float* out;            // GATEUP: mid f32, slice-major; DOWN: pair_out [P+n][rows]
-    int8_t* out_q;         // GATEUP with a quantised down type: Q8 rows of mid, slice-major
-    float2* out_ds;
+    float* out;            // GATEUP: mid f32, slice-major; DOWN: pair_out [R][rows]
+    uint8_t* out_t;        // GATEUP with a quantised down type: the Q8 records of mid
     const int32_t* grp_expert;
     const int32_t* grp_start;
     const int32_t* grp_count;
@@ -55,6 +54,7 @@ struct ExpertArgs {
     int n, k, n_expert;
     int tiles_mode;        // 0: every tile, 1: skip the shared group's, 2: only the shared group's
     int chunks;            // row chunks per group in this launch
+    uint32_t wait_hint_ns; // how long one mbarrier try may sleep
 };
 
 // ---------------------------------------------------------------------------
@@ -70,21 +70,21 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                  "r"(bytes)
                  : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)   // may sleep up to hint_ns per try
         : "memory");
     return ok != 0;
 }
 // Waits for a phase with an iteration limit; false when it gave up.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
     for (uint32_t i = 0; i < EX_WAIT_LIMIT; i++)
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait(bar, parity, hint_ns)) return true;
     return false;
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -108,6 +108,14 @@ __device__ __forceinline__ void mma_s8_k32(int (&d)[4], const int (&a)[4], int b
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
 }
+// the same with unsigned A bytes (u8 x s8)
+__device__ __forceinline__ void mma_u8s8_k32(int (&d)[4], const int (&a)[4], int b0, int b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+}
 // the k = 16 form: a0 (row g, k 4c..4c+3), a1 (row g+8), b0 (k 4c..4c+3, column g)
 __device__ __forceinline__ void mma_s8_k16(int (&d)[4], int a0, int a1, int b0) {
     asm volatile(
@@ -117,18 +125,28 @@ __device__ __forceinline__ void mma_s8_k16(int (&d)[4], int a0, int a1, int b0) 
         : "r"(a0), "r"(a1), "r"(b0), "r"(0));
 }
 
+// D[16x8] += A[16x8] * B[8x8] in tf32 with f32 accumulation.  a0 (row g, k c), a1 (row g+8, k c),
+// a2 (row g, k c+4), a3 (row g+8, k c+4); b0 (k c, column g), b1 (k c+4, column g); D as above.
+__device__ __forceinline__ void mma_tf32_k8(float (&d)[4], const float (&a)[4], float b0, float b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(__float_as_uint(a[0])), "r"(__float_as_uint(a[1])), "r"(__float_as_uint(a[2])),
+          "r"(__float_as_uint(a[3])), "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
+}
+
 // ---------------------------------------------------------------------------
 // Per-type arithmetic of one staged K-slice for one warp.
 //   rowp[mt][r]  this lane's two rows (g, g+8) of the warp's two 16-row MMA tiles:
 //                tile + row*16; unit u of the row is 512*u further, so byte `off`
 //                of the row's slice is WU(p, off)
-//   actq         the tile's Q8 rows, [8 tokens][272 bytes] (256 values + padding
-//                that spreads the tokens over the banks)
-//   ds           their (d, s) per block, [8 tokens][8 blocks]
+//   act          the tile's Q8 record (common.cuh): q rows [8 tokens][272 bytes], then
+//                dx, s_hi, s_lo as [8 blocks][8 tokens] f32
 //   acc[mt][i]   i = 2*r + tt: row g+8r, token 2c+tt
 #define WU(w, off) ((w) + ((((off)) >> 4) << 9) + ((off) & 15))
 #define LDS32(p) (*(const uint32_t*)(p))
-constexpr int ACT_Q_STRIDE = 272;
+constexpr int ACT_Q_STRIDE = kActQStride;
 
 struct NoSide {};
 
@@ -136,26 +154,26 @@ template <int TY> struct Fmt;
 
 // ---- Q8_0 (quant.rs:599-607): term = d_w * d_x * sum(q_w * q_x) ------------
 template <> struct Fmt<BIVMOE_Q8_0> {
-    static constexpr int ELEMS = 256, SL = 272, MINB = 3;
+    static constexpr int ELEMS = 256, SL = 272, MINB = 2;   // 2 x 37.7 KB stages per block
     static constexpr bool F32ACT = false;
     using Side = NoSide;
-    __device__ static void compute(const uint8_t* const (&rowp)[2][2], Side, const uint8_t* actq,
-                                   const float2* ds, float (&acc)[2][4], int g, int c) {
+    __device__ static void compute(const uint8_t* const (&rowp)[2][2], Side, const uint8_t* act,
+                                   float (&acc)[2][4], int g, int c) {
+        const float* dxp = (const float*)(act + kActOffDx);
         uint4 dwv[2][2];   // the 8 f16 scales of each row's slice (unit 16)
 #pragma unroll
         for (int mt = 0; mt < 2; mt++)
 #pragma unroll
             for (int r = 0; r < 2; r++) dwv[mt][r] = *(const uint4*)WU(rowp[mt][r], 256);
-        const uint8_t* xrow = actq + g * ACT_Q_STRIDE + 4 * c;
+        const uint8_t* xrow = act + g * ACT_Q_STRIDE + 4 * c;
 #pragma unroll
         for (int j = 0; j < 4; j++) {       // blocks 2j and 2j+1
-            const float4 x0 = *(const float4*)(ds + (2 * c) * 8 + 2 * j);       // token 2c: d s d s
-            const float4 x1 = *(const float4*)(ds + (2 * c + 1) * 8 + 2 * j);   // token 2c+1
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 const int b = 2 * j + h;
                 const int b0 = (int)LDS32(xrow + 32 * b), b1 = (int)LDS32(xrow + 32 * b + 16);
-                const float dx[2] = {h ? x0.z : x0.x, h ? x1.z : x1.x};
+                const float2 dxv = *(const float2*)(dxp + b * 8 + 2 * c);   // tokens 2c, 2c+1
+                const float dx[2] = {dxv.x, dxv.y};
 #pragma unroll
                 for (int mt = 0; mt < 2; mt++) {
                     int a[4], I[4];
@@ -186,8 +204,11 @@ template <int TY> struct FmtK45 {
     static constexpr int ELEMS = 256, SL = TY == BIVMOE_Q4_K ? 144 : 176, MINB = 4;
     static constexpr bool F32ACT = false;
     using Side = NoSide;
-    __device__ static void compute(const uint8_t* const (&rowp)[2][2], Side, const uint8_t* actq,
-                                   const float2* ds, float (&acc)[2][4], int g, int c) {
+    __device__ static void compute(const uint8_t* const (&rowp)[2][2], Side, const uint8_t* act,
+                                   float (&acc)[2][4], int g, int c) {
+        const float* dxp = (const float*)(act + kActOffDx);
+        const float* shi = (const float*)(act + kActOffSHi);
+        const float* slo = (const float*)(act + kActOffSLo);
         float d[2][2], dmin[2][2];
         K4Scales sc[2][2];
         uint32_t qh[2][2][2];
@@ -205,12 +226,30 @@ template <int TY> struct FmtK45 {
                     qh[mt][r][1] = LDS32(WU(rowp[mt][r], 32) + 4 * c);
                 }
             }
-        float tS[2][4] = {}, tM[2][4] = {};
-        const uint8_t* xrow = actq + g * ACT_Q_STRIDE + 4 * c;
+        // The min term sum_b m[r][b] * s[t][b] of the stage is a 16x8x8 product: on the
+        // tensor core in tf32, exact because m is a 6-bit integer and s comes split in
+        // two tf32-exact parts.  Lane (g, c) supplies m of blocks c, c+4 and s of token g.
+        float tM[2][4] = {};
+        {
+            const float bh0 = shi[c * 8 + g], bh1 = shi[(c + 4) * 8 + g];
+            const float bl0 = slo[c * 8 + g], bl1 = slo[(c + 4) * 8 + g];
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                float a[4];
+                a[0] = (float)((sc[mt][0].m_lo >> (8 * c)) & 0xFF);
+                a[1] = (float)((sc[mt][1].m_lo >> (8 * c)) & 0xFF);
+                a[2] = (float)((sc[mt][0].m_hi >> (8 * c)) & 0xFF);
+                a[3] = (float)((sc[mt][1].m_hi >> (8 * c)) & 0xFF);
+                mma_tf32_k8(tM[mt], a, bh0, bh1);
+                mma_tf32_k8(tM[mt], a, bl0, bl1);
+            }
+        }
+        float tS[2][4] = {};
+        const uint8_t* xrow = act + g * ACT_Q_STRIDE + 4 * c;
 #pragma unroll
         for (int j = 0; j < 4; j++) {       // sub-blocks 2j (low nibbles) and 2j+1 (high nibbles)
-            const float4 x0 = *(const float4*)(ds + (2 * c) * 8 + 2 * j);       // token 2c: d s d s
-            const float4 x1 = *(const float4*)(ds + (2 * c + 1) * 8 + 2 * j);   // token 2c+1
+            const float2 xa = *(const float2*)(dxp + (2 * j) * 8 + 2 * c);       // d of tokens 2c, 2c+1
+            const float2 xb = *(const float2*)(dxp + (2 * j + 1) * 8 + 2 * c);
             const int blo0 = (int)LDS32(xrow + 64 * j), blo1 = (int)LDS32(xrow + 64 * j + 16);
             const int bhi0 = (int)LDS32(xrow + 64 * j + 32), bhi1 = (int)LDS32(xrow + 64 * j + 48);
 #pragma unroll
@@ -224,31 +263,30 @@ template <int TY> struct FmtK45 {
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     alo[i] = (int)(w[i] & 0x0F0F0F0Fu);
-                    ahi[i] = (int)((w[i] >> 4) & 0x0F0F0F0Fu);
-                    if (TY == BIVMOE_Q5_K) {
+                    if (TY == BIVMOE_Q4_K) {
+                        // the high nibbles stay in place: unsigned bytes worth 16x the value,
+                        // the exact factor 1/16 goes into the scale
+                        ahi[i] = (int)(w[i] & 0xF0F0F0F0u);
+                    } else {
+                        ahi[i] = (int)((w[i] >> 4) & 0x0F0F0F0Fu);
                         const uint32_t hb = qh[mt][i & 1][i >> 1];
                         alo[i] |= (int)(((hb >> (2 * j)) & 0x01010101u) << 4);
                         ahi[i] |= (int)(((hb >> (2 * j + 1)) & 0x01010101u) << 4);
                     }
                 }
-                mma_s8_k32(I, alo, blo0, blo1);
+                mma_u8s8_k32(I, alo, blo0, blo1);
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
-                    const float scf = (float)k4_scale(sc[mt][r], 2 * j), mf = (float)k4_min(sc[mt][r], 2 * j);
-                    tS[mt][2 * r] = fmaf(scf, x0.x * (float)I[2 * r], tS[mt][2 * r]);
-                    tS[mt][2 * r + 1] = fmaf(scf, x1.x * (float)I[2 * r + 1], tS[mt][2 * r + 1]);
-                    tM[mt][2 * r] = fmaf(mf, x0.y, tM[mt][2 * r]);
-                    tM[mt][2 * r + 1] = fmaf(mf, x1.y, tM[mt][2 * r + 1]);
+                    const float scf = (float)k4_scale(sc[mt][r], 2 * j);
+                    tS[mt][2 * r] = fmaf(scf, xa.x * (float)I[2 * r], tS[mt][2 * r]);
+                    tS[mt][2 * r + 1] = fmaf(scf, xa.y * (float)I[2 * r + 1], tS[mt][2 * r + 1]);
                 }
-                mma_s8_k32(I, ahi, bhi0, bhi1);
+                mma_u8s8_k32(I, ahi, bhi0, bhi1);
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
-                    const float scf = (float)k4_scale(sc[mt][r], 2 * j + 1),
-                                mf = (float)k4_min(sc[mt][r], 2 * j + 1);
-                    tS[mt][2 * r] = fmaf(scf, x0.z * (float)I[2 * r], tS[mt][2 * r]);
-                    tS[mt][2 * r + 1] = fmaf(scf, x1.z * (float)I[2 * r + 1], tS[mt][2 * r + 1]);
-                    tM[mt][2 * r] = fmaf(mf, x0.w, tM[mt][2 * r]);
-                    tM[mt][2 * r + 1] = fmaf(mf, x1.w, tM[mt][2 * r + 1]);
+                    const float scf = (float)k4_scale(sc[mt][r], 2 * j + 1) * (TY == BIVMOE_Q4_K ? 0.0625f : 1.0f);
+                    tS[mt][2 * r] = fmaf(scf, xb.x * (float)I[2 * r], tS[mt][2 * r]);
+                    tS[mt][2 * r + 1] = fmaf(scf, xb.y * (float)I[2 * r + 1], tS[mt][2 * r + 1]);
                 }
             }
         }
@@ -275,14 +313,15 @@ template <> struct Fmt<BIVMOE_Q6_K> {
         const uint32_t t = v ^ 0x20202020u;
         return (int)(t | ((t & 0x20202020u) * 7u));
     }
-    __device__ static void compute(const uint8_t* const (&rowp)[2][2], Side sd, const uint8_t* actq,
-                                   const float2* ds, float (&acc)[2][4], int g, int c) {
+    __device__ static void compute(const uint8_t* const (&rowp)[2][2], Side sd, const uint8_t* act,
+                                   float (&acc)[2][4], int g, int c) {
+        const float* dxp = (const float*)(act + kActOffDx);
         uint4 scv[2][2];   // the 16 int8 scales of each row's super-block (unit 12)
 #pragma unroll
         for (int mt = 0; mt < 2; mt++)
 #pragma unroll
             for (int r = 0; r < 2; r++) scv[mt][r] = *(const uint4*)WU(rowp[mt][r], 192);
-        const uint8_t* xrow = actq + g * ACT_Q_STRIDE + 4 * c;
+        const uint8_t* xrow = act + g * ACT_Q_STRIDE + 4 * c;
 #pragma unroll
         for (int n = 0; n < 2; n++) {
             uint32_t qh[2][2][2];   // [mt][r][lhalf]
@@ -306,7 +345,8 @@ template <> struct Fmt<BIVMOE_Q6_K> {
 #pragma unroll
                 for (int hi = 0; hi < 2; hi++) {
                     const int kq = par + 2 * hi, xb = 4 * n + kq;
-                    const float dx0 = ds[(2 * c) * 8 + xb].x, dx1 = ds[(2 * c + 1) * 8 + xb].x;
+                    const float2 dxv = *(const float2*)(dxp + xb * 8 + 2 * c);
+                    const float dx0 = dxv.x, dx1 = dxv.y;
                     const int b0 = (int)LDS32(xrow + 32 * xb), b1 = (int)LDS32(xrow + 32 * xb + 16);
 #pragma unroll
                     for (int mt = 0; mt < 2; mt++) {
@@ -378,28 +418,28 @@ template <> struct Fmt<BIVMOE_BF16> {
 // ---------------------------------------------------------------------------
 template <int TY>
 __host__ __device__ constexpr int act_stage_bytes() {
-    return Fmt<TY>::F32ACT ? EX_TT * Fmt<TY>::ELEMS * 4
-                           : EX_TT * ACT_Q_STRIDE + EX_TT * (Fmt<TY>::ELEMS / 32) * 8;
+    return Fmt<TY>::F32ACT ? EX_TT * Fmt<TY>::ELEMS * 4 : kActCopyBytes;
 }
 template <int TY>
 __host__ __device__ constexpr int stage_bytes() {
     return 4 * 32 * Fmt<TY>::SL + act_stage_bytes<TY>();
 }
-constexpr int EX_SMEM_HEAD = 64 + EX_TT * 64 * 4;   // barriers, item slots; the SwiGLU staging
+constexpr int EX_SMEM_HEAD = 64 + EX_TT * 64 * 4;   // barriers, counter slots; the SwiGLU staging
 template <int TY>
 __host__ __device__ constexpr int smem_bytes() {
     return EX_SMEM_HEAD + 2 * stage_bytes<TY>();
 }
 
-struct Item {           // a decoded work item (block-uniform)
+struct Item {           // a decoded work item (block-uniform): a token tile x a run of chunks
     int valid;
     int shared;         // the shared expert's group
     int expert;
-    int chunk;
+    int chunk0;         // first chunk; the item's chunks are consecutive in memory
+    int nsl;            // K-slices per chunk
+    int nst;            // stages of the item: chunks * nsl (0: nothing to do for this group)
     int pos0;           // first position of the tile
     int tc;             // tokens in the tile
-    int nst;            // stages: slices of the inner dimension
-    const uint8_t* src; // slice 0 of the chunk's four tiles; slice s is s * 4 * 32 * SL further
+    const uint8_t* src; // stage 0; stage s is s * 4 * 32 * SL further
 };
 
 template <int TY, int MODE>
@@ -428,28 +468,32 @@ experts_kernel(const ExpertArgs A) {
     const int tiles_all = A.n_tiles[0], tiles_sh = A.n_tiles[1];
     const int tile_lo = A.tiles_mode == 1 ? tiles_sh : 0;
     const int tile_hi = A.tiles_mode == 2 ? tiles_sh : tiles_all;
-    const int total = (tile_hi - tile_lo) * A.chunks;
+    // an item takes EX_CG consecutive chunks (gate+up: 1, down: 4), i.e. 8 stages at
+    // the qwen35moe shapes, so that claiming the next item a few stages before the end
+    // of the current one hides the claim
+    constexpr int CG = MODE == MODE_GATEUP ? 1 : 4;
+    const int groups_of_chunks = (A.chunks + CG - 1) / CG;
+    const int total = (tile_hi - tile_lo) * groups_of_chunks;
     int n_fetch = 0;
 
-    // pulls the next item off the counter and decodes it (whole block)
+    // decodes the item whose counter value thread 0 left in s_item (whole block)
     auto fetch = [&]() -> Item {
         Item it;
-        const int par = n_fetch++ & 1;
-        if (tid == 0) s_item[par] = (int)atomicAdd(A.work_ctr, 1u);
-        __syncthreads();
-        const int idx = s_item[par];
+        const int idx = s_item[n_fetch & 1];
+        n_fetch++;
         it.valid = idx < total;
         if (!it.valid) return it;
-        const int tile = tile_lo + idx / A.chunks;
-        it.chunk = idx % A.chunks;
+        const int tile = tile_lo + idx / groups_of_chunks;
+        it.chunk0 = (idx % groups_of_chunks) * CG;
         const int gi = A.tile_group[tile], t0 = A.tile_t0[tile];
         it.expert = A.grp_expert[gi];
         it.shared = it.expert == A.n_expert;
         it.pos0 = A.grp_start[gi] + t0;
         it.tc = min(EX_TT, A.grp_count[gi] - t0);
         const DevTiles& m = it.shared ? A.sh : A.w;
-        it.nst = m.nslices;
-        it.src = m.stage(it.shared ? 0 : it.expert, min(it.chunk, m.chunks - 1), 0);
+        it.nsl = m.nslices;
+        it.nst = max(0, min(CG, m.chunks - it.chunk0)) * m.nslices;
+        it.src = m.stage(it.shared ? 0 : it.expert, min(it.chunk0, max(m.chunks - 1, 0)), 0);
         return it;
     };
     // issues stage `s` of an item into ring slot `slot` (one thread)
@@ -459,13 +503,13 @@ experts_kernel(const ExpertArgs A) {
         mbar_expect_tx(&mbar[slot], W_BYTES + ACT_BYTES);
         bulk_g2s(dst, it.src + (size_t)s * W_BYTES, W_BYTES, &mbar[slot]);
         uint8_t* adst = dst + W_BYTES;
-        const size_t row = (size_t)s * A.act_rows + it.pos0;
+        const int sl = s % it.nsl;   // the K-slice of this stage
         if (F::F32ACT) {
+            const size_t row = (size_t)sl * A.act_rows + it.pos0;
             bulk_g2s(adst, A.x_f32 + row * F::ELEMS, EX_TT * F::ELEMS * 4, &mbar[slot]);
-        } else {
-            bulk_g2s(adst, A.x_q + row * ACT_Q_STRIDE, EX_TT * ACT_Q_STRIDE, &mbar[slot]);
-            bulk_g2s(adst + EX_TT * ACT_Q_STRIDE, A.x_ds + row * (F::ELEMS / 32),
-                     EX_TT * (F::ELEMS / 32) * 8, &mbar[slot]);
+        } else {   // the tile's Q8 record of this K-slice (pos0 is a multiple of 8)
+            bulk_g2s(adst, A.x_t + ((size_t)sl * (A.act_rows / 8) + it.pos0 / 8) * kActTileBytes,
+                     kActCopyBytes, &mbar[slot]);
         }
     };
     // this lane's rows inside a staged chunk: [mt][r] -> tile index, row in tile
@@ -480,28 +524,35 @@ experts_kernel(const ExpertArgs A) {
     auto side_of = [&](const Item& it, int s) -> Side {
         if constexpr (TY == BIVMOE_Q6_K) {
             const DevTiles& m = it.shared ? A.sh : A.w;
-            const size_t base = ((size_t)(it.shared ? 0 : it.expert) * m.chunks + min(it.chunk, m.chunks - 1)) * 4;
+            const size_t base = ((size_t)(it.shared ? 0 : it.expert) * m.chunks + it.chunk0 + s / it.nsl) * 4;
             Side v;
 #pragma unroll
             for (int mt = 0; mt < 2; mt++)
 #pragma unroll
                 for (int r = 0; r < 2; r++)
                     v.d[mt][r] = __half2float(__ushort_as_half(
-                        m.side[((base + tile_of[mt]) * 32 + row_of[mt] + g + 8 * r) * m.nslices + s]));
+                        m.side[((base + tile_of[mt]) * 32 + row_of[mt] + g + 8 * r) * m.nslices + s % it.nsl]));
             return v;
         } else {
             return Side{};
         }
     };
 
+    if (tid == 0) s_item[0] = (int)atomicAdd(A.work_ctr, 1u);
+    __syncthreads();
     Item cur = fetch();
     if (!cur.valid) return;
     Item nxt;
     nxt.valid = 0;
+    nxt.nst = 0;
     // The stages of successive items form one stream; stream stage q lives in
     // slot q & 1.  `issued` runs at most two ahead of `consumed`; the producer
-    // cursor (p_in_next, p_stage) names the next stage to issue.
+    // cursor (p_in_next, p_stage) names the next stage to issue.  The next item
+    // is claimed EX_LEAD stages before the current one ends: early enough to hide
+    // the claim, late enough that blocks do not hoard items they will not start soon.
+    constexpr int EX_LEAD = 4;
     int issued = 0, consumed = 0, p_in_next = 0, p_stage = 0;
+    int nxt_claimed = 0, pf = 0;
     Side side0{}, side1{};
     auto pump = [&]() {
         while (issued < consumed + 2) {
@@ -520,22 +571,29 @@ experts_kernel(const ExpertArgs A) {
         }
     };
     pump();
-    nxt = fetch();
-    pump();
 
     while (true) {
         float acc[2][4] = {};
         float accf[EX_TT];
 #pragma unroll
         for (int t = 0; t < EX_TT; t++) accf[t] = 0.0f;
+        if (cur.nst == 0 && !nxt_claimed) {   // nothing to do for this group: claim the next right away
+            if (tid == 0) s_item[n_fetch & 1] = (int)atomicAdd(A.work_ctr, 1u);
+            __syncthreads();
+            nxt = fetch();
+            nxt_claimed = 1;
+            pump();
+        }
         for (int s = 0; s < cur.nst; s++) {
+            const bool claim = !nxt_claimed && cur.nst - s <= EX_LEAD;
+            if (claim && tid == 0) pf = (int)atomicAdd(A.work_ctr, 1u);
             const int slot = consumed & 1;
-            if (!mbar_wait_bounded(&mbar[slot], (consumed >> 1) & 1)) {
+            if (!mbar_wait_bounded(&mbar[slot], (consumed >> 1) & 1, A.wait_hint_ns)) {
                 // every thread waits on the same barrier, so all give up together: flag
                 // it, give the other slot's copies the same bounded wait, leave
                 if (tid == 0) atomicExch(A.status, BIVMOE_ERR_TIMEOUT);
                 if (issued > consumed + 1)
-                    mbar_wait_bounded(&mbar[slot ^ 1], ((consumed + 1) >> 1) & 1);
+                    mbar_wait_bounded(&mbar[slot ^ 1], ((consumed + 1) >> 1) & 1, A.wait_hint_ns);
                 return;
             }
             const uint8_t* st = ring + (size_t)slot * SB;
@@ -555,78 +613,96 @@ experts_kernel(const ExpertArgs A) {
 #pragma unroll
                     for (int r = 0; r < 2; r++)
                         rowp[mt][r] = st + (size_t)tile_of[mt] * TILE + (row_of[mt] + g + 8 * r) * 16;
-                F::compute(rowp, slot ? side1 : side0, act, (const float2*)(act + EX_TT * ACT_Q_STRIDE),
-                           acc, g, c);
+                F::compute(rowp, slot ? side1 : side0, act, acc, g, c);
             }
-            __syncthreads();   // every warp is done with the slot
+            if (claim && tid == 0) s_item[n_fetch & 1] = pf;
+            __syncthreads();   // every warp is done with the slot; the claimed value is visible
             consumed++;
+            if (claim) {
+                nxt = fetch();
+                nxt_claimed = 1;
+            }
             pump();
-        }
-        // ---- epilogue
-        const DevTiles& m = cur.shared ? A.sh : A.w;
-        const bool chunk_ok = cur.chunk < m.chunks;
-        if (MODE == MODE_GATEUP) {
-            // SwiGLU into the staging tile [token][64 rows of the chunk]
-            if constexpr (F::F32ACT) {
+            if ((s + 1) % cur.nsl) continue;
+            // ---- epilogue of the chunk that just ended
+            const int chunk = cur.chunk0 + s / cur.nsl;
+            const int rows = (cur.shared ? A.sh : A.w).rows;
+            if (MODE == MODE_GATEUP) {
+                // SwiGLU into the staging tile [token][64 rows of the chunk]
+                if constexpr (F::F32ACT) {
 #pragma unroll
-                for (int t = 0; t < EX_TT; t++) {
-                    const float u = __shfl_down_sync(0xffffffffu, accf[t], 16);
-                    if (lane < 16) {
-                        const float gt = accf[t];
-                        s_mid[t * 64 + 16 * warp + lane] = (gt * __fdiv_rn(1.0f, 1.0f + expf(-gt))) * u;
+                    for (int t = 0; t < EX_TT; t++) {
+                        const float u = __shfl_down_sync(0xffffffffu, accf[t], 16);
+                        if (lane < 16) {
+                            const float gt = accf[t];
+                            s_mid[t * 64 + 16 * warp + lane] = (gt * __fdiv_rn(1.0f, 1.0f + expf(-gt))) * u;
+                        }
                     }
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    // ops.rs:160-167: silu(x) = x * (1 / (1 + exp(-x)))
-                    const float gt = acc[0][i], u = acc[1][i];
-                    s_mid[(2 * c + (i & 1)) * 64 + 16 * warp + g + 8 * (i >> 1)] =
-                        (gt * __fdiv_rn(1.0f, 1.0f + expf(-gt))) * u;
-                }
-            }
-            __syncthreads();
-            // rows of mid: f32 (slice-major by 64) and, for quantised down types, the
-            // Q8Act of each 32-row block (quant.rs:368-394); one warp per (token, block)
-            for (int p = warp; p < 2 * cur.tc && chunk_ok; p += EX_THREADS / 32) {
-                const int t = p >> 1, blk = p & 1;
-                const float v = s_mid[t * 64 + 32 * blk + lane];
-                const int r = cur.chunk * CH + 32 * blk + lane;
-                const size_t pos = cur.pos0 + t;
-                A.out[((size_t)(r / 64) * A.act_rows + pos) * 64 + r % 64] = v;
-                if (A.out_q) {
-                    float dd, ss;
-                    const int q = q8_quantize_lane(v, dd, ss);
-                    const size_t srow = (size_t)(r / 256) * A.act_rows + pos;
-                    A.out_q[srow * ACT_Q_STRIDE + r % 256] = (int8_t)q;
-                    if (lane == 0) A.out_ds[srow * 8 + (r % 256) / 32] = make_float2(dd, ss);
-                }
-            }
-        } else if (chunk_ok) {
-            const int rows = m.rows;
-            if constexpr (F::F32ACT) {
-#pragma unroll
-                for (int t = 0; t < EX_TT; t++)
-                    if (t < cur.tc)
-                        A.out[(size_t)(cur.pos0 + t) * rows + cur.chunk * CH + 32 * warp + lane] = accf[t];
-            } else {
-#pragma unroll
-                for (int mt = 0; mt < 2; mt++)
+                } else {
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
-                        const int t = 2 * c + (i & 1);
-                        if (t < cur.tc)
-                            A.out[(size_t)(cur.pos0 + t) * rows + cur.chunk * CH + 32 * warp + 16 * mt +
-                                  g + 8 * (i >> 1)] = acc[mt][i];
+                        // ops.rs:160-167: silu(x) = x * (1 / (1 + exp(-x)))
+                        const float gt = acc[0][i], u = acc[1][i];
+                        s_mid[(2 * c + (i & 1)) * 64 + 16 * warp + g + 8 * (i >> 1)] =
+                            (gt * __fdiv_rn(1.0f, 1.0f + expf(-gt))) * u;
                     }
+                }
+                __syncthreads();
+                // rows of mid: f32 (slice-major by 64) and, for quantised down types, the
+                // Q8Act of each 32-row block (quant.rs:368-394); one warp per (token, block)
+                for (int p = warp; p < 2 * cur.tc; p += EX_THREADS / 32) {
+                    const int t = p >> 1, blk = p & 1;
+                    const float v = s_mid[t * 64 + 32 * blk + lane];
+                    const int r = chunk * CH + 32 * blk + lane;
+                    const size_t pos = cur.pos0 + t;
+                    A.out[((size_t)(r / 64) * A.act_rows + pos) * 64 + r % 64] = v;
+                    if (A.out_t) {
+                        float dd, ss;
+                        const int q = q8_quantize_lane(v, dd, ss);
+                        uint8_t* rec = A.out_t + ((size_t)(r / 256) * (A.act_rows / 8) + pos / 8) * kActTileBytes;
+                        rec[(pos % 8) * ACT_Q_STRIDE + r % 256] = (uint8_t)(int8_t)q;
+                        if (lane < 4) {
+                            float shi, slo;
+                            split_tf32(ss, &shi, &slo);
+                            const float val = lane == 0 ? dd : lane == 1 ? shi : lane == 2 ? slo : ss;
+                            *(float*)(rec + kActOffDx + 256 * lane + (((r % 256) / 32) * 8 + pos % 8) * 4) = val;
+                        }
+                    }
+                }
+                // s_mid is rewritten after the next chunk's stages, which have barriers
+            } else {
+                if constexpr (F::F32ACT) {
+#pragma unroll
+                    for (int t = 0; t < EX_TT; t++)
+                        if (t < cur.tc)
+                            A.out[(size_t)(cur.pos0 + t) * rows + chunk * CH + 32 * warp + lane] = accf[t];
+                } else {
+#pragma unroll
+                    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int t = 2 * c + (i & 1);
+                            if (t < cur.tc)
+                                A.out[(size_t)(cur.pos0 + t) * rows + chunk * CH + 32 * warp + 16 * mt +
+                                      g + 8 * (i >> 1)] = acc[mt][i];
+                        }
+                }
             }
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) acc[mt][i] = 0.0f;
+#pragma unroll
+            for (int t = 0; t < EX_TT; t++) accf[t] = 0.0f;
         }
         if (!nxt.valid) break;
-        // the stream already runs inside `nxt`: it becomes the current item
+        // the stream may already run inside `nxt`: it becomes the current item
         cur = nxt;
+        nxt.valid = 0;
+        nxt.nst = 0;
+        nxt_claimed = 0;
         if (p_in_next) p_in_next = 0;
         else p_stage = 0;
-        nxt = fetch();
         pump();
     }
 }
@@ -681,6 +757,11 @@ cudaError_t launch_experts(const LaunchCfg& c, const DevTiles& gate_up, const De
     A.status = ws.status;
     A.n = c.n; A.k = c.k; A.n_expert = c.n_expert;
     A.act_rows = ws.act_rows;
+    {
+        static int hint = -1;
+        if (hint < 0) { const char* e = getenv("BIVMOE_WAIT_HINT"); hint = e ? atoi(e) : 1000; }
+        A.wait_hint_ns = (uint32_t)hint;
+    }
     const bool fused = c.has_shared && sh_gate_up.ty == gate_up.ty && sh_down.ty == down.ty;
     cudaError_t err;
     // ---- gate + up (SwiGLU and the Q8 rows of its output in the epilogue)
@@ -689,11 +770,9 @@ cudaError_t launch_experts(const LaunchCfg& c, const DevTiles& gate_up, const De
         G.w = gate_up; G.sh = sh_gate_up;
         if (mode == 1) G.sh = DevTiles{};
         if (mode == 2) G.w = DevTiles{};
-        G.x_f32 = ws.act_f; G.x_q = ws.act_q; G.x_ds = ws.act_ds;
+        G.x_f32 = ws.act_f; G.x_t = ws.act_t;
         G.out = ws.mid;
-        const bool qdown = !type_uses_f32_act(down_ty);
-        G.out_q = qdown ? ws.mid_q : nullptr;
-        G.out_ds = qdown ? ws.mid_ds : nullptr;
+        G.out_t = type_uses_f32_act(down_ty) ? nullptr : ws.mid_t;
         G.work_ctr = ws.work_ctr + ctr;
         G.tiles_mode = mode;
         return launch_typed<MODE_GATEUP>(ty, c, G);
@@ -712,7 +791,7 @@ cudaError_t launch_experts(const LaunchCfg& c, const DevTiles& gate_up, const De
         D.w = down; D.sh = sh_down;
         if (mode == 1) D.sh = DevTiles{};
         if (mode == 2) D.w = DevTiles{};
-        D.x_f32 = ws.mid; D.x_q = ws.mid_q; D.x_ds = ws.mid_ds;
+        D.x_f32 = ws.mid; D.x_t = ws.mid_t;
         D.out = ws.pair_out;
         D.work_ctr = ws.work_ctr + ctr;
         D.tiles_mode = mode;

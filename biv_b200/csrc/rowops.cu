@@ -46,10 +46,16 @@ dispatch_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, 
                 float dd, ss;
                 const int q = q8_quantize_lane(v, dd, ss);
                 const int sl = b / 8, bb = b % 8;
+                float shi, slo;
+                split_tf32(ss, &shi, &slo);
                 for (int j = 0; j <= k; j++) {
-                    const size_t row = (size_t)sl * R + s_pos[j];
-                    ws.act_q[row * kActQStride + 32 * bb + lane] = (int8_t)q;
-                    if (lane == 0) ws.act_ds[row * 8 + bb] = make_float2(dd, ss);
+                    const int pos = s_pos[j];
+                    uint8_t* rec = ws.act_t + ((size_t)sl * (R / 8) + pos / 8) * kActTileBytes;
+                    rec[(pos % 8) * kActQStride + 32 * bb + lane] = (uint8_t)(int8_t)q;
+                    if (lane < 4) {
+                        const float val = lane == 0 ? dd : lane == 1 ? shi : lane == 2 ? slo : ss;
+                        *(float*)(rec + kActOffDx + 256 * lane + (bb * 8 + pos % 8) * 4) = val;
+                    }
                 }
             }
             if (f32) {
@@ -224,14 +230,15 @@ __device__ inline uint8_t tile_byte(const DevTiles& t, const uint8_t* tile0, int
 }
 
 __global__ void block_dots_kernel(DevTiles t, int tile_base, int expert, int row,
-                                  const int8_t* __restrict__ act_q, int act_rows, int pos,
+                                  const uint8_t* __restrict__ act_t, int act_rows, int pos,
                                   int32_t* __restrict__ out) {
     const int b = blockIdx.x * blockDim.x + threadIdx.x;   // 32-element block of the row
     if (b >= t.cols / 32) return;
     const int chunk = row / t.chunk_rows, tile = tile_base + (row % t.chunk_rows) / 32, rr = row % 32;
     const uint8_t* t0 = t.stage(expert, chunk, 0) + (int64_t)tile * 32 * t.slice_bytes;
     const int s = b / 8, sb = b % 8;
-    const int8_t* x = act_q + ((size_t)s * act_rows + pos) * kActQStride + 32 * sb;
+    const int8_t* x = (const int8_t*)act_t + ((size_t)s * (act_rows / 8) + pos / 8) * kActTileBytes +
+                      (pos % 8) * kActQStride + 32 * sb;
     int32_t sum = 0;
     if (t.ty == BIVMOE_Q8_0) {
         for (int l = 0; l < 32; l++) sum += (int)(int8_t)tile_byte(t, t0, rr, s, 32 * sb + l) * x[l];
@@ -259,10 +266,10 @@ __global__ void block_dots_kernel(DevTiles t, int tile_base, int expert, int row
 }
 
 cudaError_t launch_block_dots(const DevTiles& t, int tile_base, int expert, int row,
-                              const int8_t* act_q, int act_rows, int pos, int32_t* out,
+                              const uint8_t* act_t, int act_rows, int pos, int32_t* out,
                               cudaStream_t stream) {
     const int nb = t.cols / 32;
-    block_dots_kernel<<<(nb + 63) / 64, 64, 0, stream>>>(t, tile_base, expert, row, act_q, act_rows,
+    block_dots_kernel<<<(nb + 63) / 64, 64, 0, stream>>>(t, tile_base, expert, row, act_t, act_rows,
                                                          pos, out);
     return cudaGetLastError();
 }
