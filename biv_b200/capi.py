@@ -18,10 +18,12 @@ STATUS_NAMES = {1: "argument", 2: "unsupported (NoKernel)", 3: "out of memory", 
 (TAP_LOGITS, TAP_IDS, TAP_WEIGHTS, TAP_COUNTS, TAP_ORDER, TAP_ACT_Q, TAP_ACT_D, TAP_ACT_S,
  TAP_MID, TAP_PAIR_OUT, TAP_SHARED_OUT, TAP_SHARED_GATE) = range(12)
 
+ROUTE_NOALLOC_MAX_LOGITS = 512 * 257
+
 # every symbol include/bivmoe.h declares
 SYMBOLS = ["bivmoe_create", "bivmoe_destroy", "bivmoe_forward", "bivmoe_forward_host", "bivmoe_forward_profile",
            "bivmoe_set_post_norm", "bivmoe_forward_stack", "bivmoe_tap", "bivmoe_tap_block_dots",
-           "bivmoe_numerics", "bivmoe_memory", "bivmoe_launch_count", "bivmoe_last_error",
+           "bivmoe_route_noalloc", "bivmoe_numerics", "bivmoe_memory", "bivmoe_launch_count", "bivmoe_last_error",
            "bivmoe_global_error"]
 
 
@@ -72,6 +74,7 @@ def lib():
         L.bivmoe_forward_stack.argtypes = [C.POINTER(vp), i32, vp, i32, vp]
         L.bivmoe_tap.argtypes = [vp, i32, vp, C.c_size_t]
         L.bivmoe_tap_block_dots.argtypes = [vp, i32, i32, i32, i32, vp]
+        L.bivmoe_route_noalloc.argtypes = [vp, vp, i32, vp, vp, vp]
         L.bivmoe_numerics.argtypes = [vp, C.c_char_p, C.c_size_t]
         L.bivmoe_memory.argtypes = [vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
         L.bivmoe_launch_count.restype = C.c_uint64

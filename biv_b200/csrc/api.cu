@@ -166,6 +166,21 @@ static int upload_tiles(bivmoe_layer* L, std::string* errp, const bivmoe_experts
     return BIVMOE_OK;
 }
 
+namespace bivmoe {
+// A read-only view of the routing tensors for entry points kept in other files;
+// with `error_or_null` it instead records that text as the layer's last error.
+int layer_route_view(bivmoe_layer* L, RouteView* out, const char* error_or_null) {
+    if (!L) return BIVMOE_ERR_ARGUMENT;
+    if (error_or_null) {
+        L->error = error_or_null;
+        return BIVMOE_OK;
+    }
+    *out = RouteView{L->device, L->sm_count, L->e, L->n_expert, L->k, L->has_shared ? 1 : 0,
+                     L->router, L->ws.status};
+    return BIVMOE_OK;
+}
+}  // namespace bivmoe
+
 extern "C" {
 
 const char* bivmoe_global_error(void) { return g_error.c_str(); }

@@ -158,4 +158,12 @@ bool experts_supported(int ty, int cols, int rows, bool is_down);
 
 void count_launch(int n = 1);
 
+// what the routing step needs to know about a layer (filled by api.cu)
+struct RouteView {
+    int device, sm_count, e, n_expert, k, has_shared;
+    const float* router;   // device, [n_expert + 1][e]
+    int32_t* status;       // the layer's device status word
+};
+int layer_route_view(bivmoe_layer* layer, RouteView* out, const char* error_or_null);
+
 }  // namespace bivmoe

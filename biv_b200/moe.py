@@ -118,6 +118,22 @@ class Moe:
         self.last_n = n
         return dict(zip(self.STAGES, [float(v) for v in ms]))
 
+    def route_noalloc(self, h, ids_out, weights_out):
+        """The routing step alone, through the entry point that allocates nothing:
+        fills the caller's ``ids_out`` [n, k] int32 and ``weights_out`` [n, k] f32
+        (device tensors) for device rows ``h``.  Limited to
+        ``n * (n_expert + 1) <= capi.ROUTE_NOALLOC_MAX_LOGITS``."""
+        import torch
+        n = h.numel() // self.n_embd
+        assert h.is_cuda and h.dtype == torch.float32 and h.is_contiguous()
+        assert ids_out.is_cuda and ids_out.dtype == torch.int32 and ids_out.is_contiguous()
+        assert weights_out.is_cuda and weights_out.dtype == torch.float32 and weights_out.is_contiguous()
+        assert ids_out.numel() == n * self.k and weights_out.numel() == n * self.k
+        capi.check(capi.lib().bivmoe_route_noalloc(self._h, C.c_void_p(h.data_ptr()), n,
+                                                   C.c_void_p(ids_out.data_ptr()),
+                                                   C.c_void_p(weights_out.data_ptr()),
+                                                   self._stream()), self._h)
+
     def set_post_norm(self, w, eps: float):
         w = np.ascontiguousarray(w, dtype=np.float32)
         assert w.size == self.n_embd

@@ -161,6 +161,31 @@ BIVMOE_API int bivmoe_tap(bivmoe_layer* layer, int32_t which, void* host_dst, si
 BIVMOE_API int bivmoe_tap_block_dots(bivmoe_layer* layer, int32_t matrix, int32_t expert, int32_t row,
                           int32_t act_row, int32_t* out);
 
+/* The routing step alone - router product, softmax, the k best experts and their
+ * renormalised weights (what `route` computes per token, model.rs:259-268) - for
+ * callers that cannot allocate device memory: code running under a stream capture,
+ * inside another framework's memory pool, or in a latency-critical loop where a
+ * cudaMalloc (which synchronises the device) is not acceptable.  It has no
+ * counterpart in the reference; it exists because every other entry point relies
+ * on the workspace `bivmoe_create` allocated.
+ *
+ * The call allocates nothing.  Its scratch (the router logits) is a fixed array
+ * built into the library, `BIVMOE_ROUTE_NOALLOC_MAX_LOGITS` floats, which every GPU
+ * that loads the library holds until the process exits; a call with
+ * n * (n_expert + 1) beyond that limit is rejected with BIVMOE_ERR_ARGUMENT.
+ * `h_dev` [n][n_embd] f32, `ids_dev` [n][n_expert_used] i32 and `weights_dev`
+ * [n][n_expert_used] f32 are the caller's device buffers; results equal the
+ * BIVMOE_TAP_IDS / BIVMOE_TAP_WEIGHTS of `bivmoe_forward` on the same rows.
+ *
+ * The first call on a device looks up the array's device address (a host-side
+ * set-up step): make that first call before starting any stream capture.  All
+ * calls share the one array, which keeps the previous call's logits; each call
+ * overwrites every entry it reads, so nothing needs clearing, but two calls that
+ * overlap on the GPU (different streams) race on it - serialise them. */
+#define BIVMOE_ROUTE_NOALLOC_MAX_LOGITS (512 * 257)
+BIVMOE_API int bivmoe_route_noalloc(bivmoe_layer* layer, const float* h_dev, int32_t n,
+                                    int32_t* ids_dev, float* weights_dev, void* stream);
+
 /* What decides the numbers besides code and weights, as `Engine::numerics`
  * reports (engine.rs:42-46): device, kernel variants, repack version. */
 BIVMOE_API int bivmoe_numerics(const bivmoe_layer* layer, char* buf, size_t len);
