@@ -217,6 +217,12 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # a side stream: the library replays its launch sequence as a CUDA graph, which the
+    # legacy default stream cannot capture
+    side = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    torch.cuda.set_stream(side)
+
     def step(i):
         copies[i % ncopies].moe_(h, out, accumulate=False)
 

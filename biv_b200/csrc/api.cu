@@ -59,6 +59,18 @@ struct bivmoe_layer {
     float* host_in = nullptr;            // device staging of forward_host
     float* host_out = nullptr;
     int last_n = 0;
+    // the launch sequence of the last forward call, replayed as a CUDA graph while the
+    // call's arguments stay the same (an engine passes the same scratch buffers each pass)
+    struct {
+        cudaGraphExec_t exec = nullptr;
+        const float* h = nullptr;
+        float* out = nullptr;
+        int n = -1, accumulate = -1;
+        cudaStream_t stream = nullptr;
+        int seen = 0;            // identical calls seen; the graph is built on the second
+    } graph;
+    bool use_graph = true;
+    int launches_per_forward = 0;
     std::string error, device_name;
     std::vector<void*> allocs;
 };
@@ -192,6 +204,7 @@ uint64_t bivmoe_launch_count(void) { return g_launches.load(); }
 void bivmoe_destroy(bivmoe_layer* L) {
     if (!L) return;
     cudaSetDevice(L->device);
+    if (L->graph.exec) cudaGraphExecDestroy(L->graph.exec);
     for (void* p : L->allocs) cudaFree(p);
     if (L->own_stream) cudaStreamDestroy(L->own_stream);
     delete L;
@@ -326,10 +339,65 @@ static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int 
     return BIVMOE_OK;
 }
 
+// forward_impl, replayed from a CUDA graph when the same call repeats: the seven
+// launches then cost one graph launch and run back to back on the device.
+static int forward_graphed(bivmoe_layer* L, const float* h, float* out, int n, int accumulate,
+                           cudaStream_t stream) {
+    std::string* errp = &L->error;
+    auto& G = L->graph;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    // (the legacy default stream cannot be captured)
+    if (!L->use_graph || n <= 0 || stream == nullptr || stream == cudaStreamLegacy ||
+        cudaStreamIsCapturing(stream, &cap) != cudaSuccess ||
+        cap != cudaStreamCaptureStatusNone)
+        return forward_impl(L, h, out, n, accumulate, stream);   // also when the caller captures us
+    const bool same = G.h == h && G.out == out && G.n == n && G.accumulate == accumulate &&
+                      G.stream == stream;
+    if (same && G.exec) {
+        L->last_n = n;
+        CU(cudaGraphLaunch(G.exec, stream));
+        count_launch(L->launches_per_forward);
+        return BIVMOE_OK;
+    }
+    if (!same) {
+        if (G.exec) { cudaGraphExecDestroy(G.exec); G.exec = nullptr; }
+        G.h = h; G.out = out; G.n = n; G.accumulate = accumulate; G.stream = stream;
+        G.seen = 0;
+    }
+    if (++G.seen < 2)   // the first call runs plainly (it also sets the kernels' attributes)
+        return forward_impl(L, h, out, n, accumulate, stream);
+    cudaGraph_t graph = nullptr;
+    const uint64_t before = bivmoe_launch_count();
+    CU(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+    int rc = forward_impl(L, h, out, n, accumulate, stream);
+    cudaError_t ce = cudaStreamEndCapture(stream, &graph);
+    L->launches_per_forward = (int)(bivmoe_launch_count() - before);
+    if (rc || ce != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        L->use_graph = false;   // fall back to plain launches for good
+        cudaGetLastError();
+        return rc ? rc : forward_impl(L, h, out, n, accumulate, stream);
+    }
+    ce = cudaGraphInstantiate(&G.exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ce != cudaSuccess) {
+        G.exec = nullptr;
+        L->use_graph = false;
+        cudaGetLastError();
+        return forward_impl(L, h, out, n, accumulate, stream);
+    }
+    CU(cudaGraphLaunch(G.exec, stream));
+    return BIVMOE_OK;
+}
+
 int bivmoe_forward(bivmoe_layer* L, const float* h_dev, float* out_dev, int32_t n,
                    int32_t accumulate, void* stream) {
     if (!L) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer");
-    return forward_impl(L, h_dev, out_dev, n, accumulate, (cudaStream_t)stream);
+    if (!h_dev || !out_dev) return set_err(&L->error, BIVMOE_ERR_ARGUMENT, "null activation pointer");
+    if (n < 0 || n > L->max_tokens)
+        return set_err(&L->error, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens = %d", n,
+                       L->max_tokens);
+    return forward_graphed(L, h_dev, out_dev, n, accumulate, (cudaStream_t)stream);
 }
 
 int bivmoe_forward_profile(bivmoe_layer* L, const float* h_dev, float* out_dev, int32_t n,
@@ -378,7 +446,7 @@ int bivmoe_forward_host(bivmoe_layer* L, const float* h_host, float* out_host, i
     const size_t bytes = (size_t)n * L->e * 4;
     cudaStream_t s = L->own_stream;
     CU(cudaMemcpyAsync(L->host_in, h_host, bytes, cudaMemcpyHostToDevice, s));
-    int rc = forward_impl(L, L->host_in, L->host_out, n, 0, s);
+    int rc = forward_graphed(L, L->host_in, L->host_out, n, 0, s);
     if (rc) return rc;
     CU(cudaMemcpyAsync(out_host, L->host_out, bytes, cudaMemcpyDeviceToHost, s));
     return read_status(L, s);

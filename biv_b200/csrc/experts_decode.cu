@@ -108,13 +108,19 @@ __device__ __forceinline__ void mma_s8_k32(int (&d)[4], const int (&a)[4], int b
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
 }
-// the same with unsigned A bytes (u8 x s8)
-__device__ __forceinline__ void mma_u8s8_k32(int (&d)[4], const int (&a)[4], int b0, int b1) {
+// The same with unsigned A bytes (u8 x s8), returning the sums as floats: the
+// accumulator starts at the bit pattern of 1.5 * 2^23, so the int32 result read as
+// an f32 is 12582912 + sum exactly (|sum| < 2^22), and one f32 subtraction - on the
+// multiply-add pipe instead of a conversion on the integer pipe - gives float(sum).
+__device__ __forceinline__ void mma_u8s8_k32_f(float (&f)[4], const int (&a)[4], int b0, int b1) {
+    int d[4];
     asm volatile(
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%10,%10,%10,%10};"
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0x4B400000));
+#pragma unroll
+    for (int i = 0; i < 4; i++) f[i] = __fsub_rn(__int_as_float(d[i]), 12582912.0f);
 }
 // the k = 16 form: a0 (row g, k 4c..4c+3), a1 (row g+8), b0 (k 4c..4c+3, column g)
 __device__ __forceinline__ void mma_s8_k16(int (&d)[4], int a0, int a1, int b0) {
@@ -259,7 +265,8 @@ template <int TY> struct FmtK45 {
                 w[1] = LDS32(WU(rowp[mt][1], QOFF + 32 * j) + 4 * c);
                 w[2] = LDS32(WU(rowp[mt][0], QOFF + 32 * j + 16) + 4 * c);
                 w[3] = LDS32(WU(rowp[mt][1], QOFF + 32 * j + 16) + 4 * c);
-                int alo[4], ahi[4], I[4];
+                int alo[4], ahi[4];
+                float I[4];   // the int32 block dots, exactly, as floats
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     alo[i] = (int)(w[i] & 0x0F0F0F0Fu);
@@ -274,19 +281,19 @@ template <int TY> struct FmtK45 {
                         ahi[i] |= (int)(((hb >> (2 * j + 1)) & 0x01010101u) << 4);
                     }
                 }
-                mma_u8s8_k32(I, alo, blo0, blo1);
+                mma_u8s8_k32_f(I, alo, blo0, blo1);
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
                     const float scf = (float)k4_scale(sc[mt][r], 2 * j);
-                    tS[mt][2 * r] = fmaf(scf, xa.x * (float)I[2 * r], tS[mt][2 * r]);
-                    tS[mt][2 * r + 1] = fmaf(scf, xa.y * (float)I[2 * r + 1], tS[mt][2 * r + 1]);
+                    tS[mt][2 * r] = fmaf(scf, xa.x * I[2 * r], tS[mt][2 * r]);
+                    tS[mt][2 * r + 1] = fmaf(scf, xa.y * I[2 * r + 1], tS[mt][2 * r + 1]);
                 }
-                mma_u8s8_k32(I, ahi, bhi0, bhi1);
+                mma_u8s8_k32_f(I, ahi, bhi0, bhi1);
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
                     const float scf = (float)k4_scale(sc[mt][r], 2 * j + 1) * (TY == BIVMOE_Q4_K ? 0.0625f : 1.0f);
-                    tS[mt][2 * r] = fmaf(scf, xb.x * (float)I[2 * r], tS[mt][2 * r]);
-                    tS[mt][2 * r + 1] = fmaf(scf, xb.y * (float)I[2 * r + 1], tS[mt][2 * r + 1]);
+                    tS[mt][2 * r] = fmaf(scf, xb.x * I[2 * r], tS[mt][2 * r]);
+                    tS[mt][2 * r + 1] = fmaf(scf, xb.y * I[2 * r + 1], tS[mt][2 * r + 1]);
                 }
             }
         }

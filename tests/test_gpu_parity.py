@@ -204,3 +204,31 @@ def test_errors_are_statuses_not_crashes():
         assert ei.value.code == capi.ERR_ARGUMENT
     finally:
         m.close()
+
+
+def test_repeated_calls_replay_a_graph_with_the_same_result():
+    # the library replays its launch sequence as a CUDA graph when a call repeats with
+    # the same buffers on a capturable stream; results must not change
+    import torch
+    from biv_b200.moe import Moe
+    wl = W.decode_q4k(n=40, **W.SMALL)
+    m = Moe(wl.layer, wl.n)
+    try:
+        h = torch.from_numpy(wl.h).cuda()
+        want = m.moe(h).clone()                  # plain launches (default stream)
+        s = torch.cuda.Stream()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(s):
+            out = torch.empty_like(h)
+            for _ in range(4):                   # the second call builds the graph
+                out.zero_()
+                m.moe_(h, out, accumulate=False)
+                s.synchronize()
+                assert torch.equal(out, want)
+            h2 = torch.from_numpy(W.decode_q4k(n=40, seed=5, **W.SMALL).h).cuda()
+            h.copy_(h2)                          # same buffers, new rows: routing changes
+            m.moe_(h, out, accumulate=False)
+            s.synchronize()
+        assert torch.equal(out, m.moe(h2))
+    finally:
+        m.close()
