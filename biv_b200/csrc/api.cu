@@ -146,7 +146,7 @@ static int upload_tiles(bivmoe_layer* L, std::string* errp, const bivmoe_experts
     out->chunks = (int)(a->rows / chunk_rows);
     out->slice_bytes = g.sl;
     out->nslices = (int)(a->cols / g.elems);
-    out->expert_bytes = (int64_t)out->chunks * out->nslices * 4 * 32 * g.sl;
+    out->expert_bytes = (int64_t)out->chunks * out->nslices * kChunkRows * g.sl;
     const size_t dev_bytes = (size_t)(a->n * out->expert_bytes);
     void* p = nullptr;
     CU(cudaMalloc(&p, dev_bytes));
@@ -154,7 +154,7 @@ static int upload_tiles(bivmoe_layer* L, std::string* errp, const bivmoe_experts
     L->weight_bytes += dev_bytes;
     out->data = (uint8_t*)p;
     if (a->ggml_type == BIVMOE_Q6_K) {
-        const size_t sb = (size_t)a->n * out->chunks * 4 * 32 * out->nslices * 2;
+        const size_t sb = (size_t)a->n * out->chunks * kChunkRows * out->nslices * 2;
         CU(cudaMalloc(&p, sb));
         L->allocs.push_back(p);
         L->weight_bytes += sb;
@@ -541,7 +541,9 @@ int bivmoe_tap(bivmoe_layer* L, int32_t which, void* dst, size_t bytes) {
                 for (size_t sl = 0; sl < nsl; sl++) {
                     const uint8_t* r0 = rec.data() + (sl * (R / 8) + tpos[t] / 8) * kActTileBytes;
                     const int tk = tpos[t] % 8;
-                    if (q) memcpy((int8_t*)dst + t * e + sl * 256, r0 + tk * kActQStride, 256);
+                    if (q)
+                        for (int i = 0; i < 256; i++)
+                            ((int8_t*)dst)[t * e + sl * 256 + i] = (int8_t)r0[act_q_off(tk, i)];
                     else
                         for (int b = 0; b < 8; b++)
                             ((float*)dst)[t * (e / 32) + sl * 8 + b] = *(const float*)(

@@ -8,24 +8,27 @@
 namespace bivmoe {
 
 // ---------------------------------------------------------------------------
-// Device layout of the weights.  The expert kernels work on chunks of rows: 64
-// gate rows together with the same 64 up rows, or 128 down rows.  A chunk is
-// four tiles of 32 rows, and what one pipeline stage consumes - one K-slice of
-// those four tiles - is stored contiguously (4 * 32 * SL bytes, one bulk copy),
-// the K-slices of a chunk following each other:
-//     [expert][chunk][K-slice][tile 0..3][SL/16 units][32 rows][16 bytes]
-// gate+up chunks: tiles 0,1 = gate rows 0-31, 32-63 of the chunk, tiles 2,3 = up rows.
-// Inside a tile the bytes are unit-major: the lane that owns row r reads unit u
-// at (u*32 + r)*16, so the lanes of a warp read consecutive 16-byte pieces,
-// free of bank conflicts.  The repack is a permutation of the GGUF bytes
-// (nothing is widened):
+// Device layout of the weights.  The expert kernels work on chunks of 128 rows:
+// 64 gate rows (chunk rows 0-63) together with the same 64 up rows (64-127), or
+// 128 down rows.  What one pipeline stage consumes - one K-slice of a chunk - is
+// stored contiguously (128 * SL bytes, one bulk copy), the K-slices of a chunk
+// and then the chunks of an expert following each other:
+//     [expert][chunk][K-slice][SL/16 units][128 rows][16 bytes]
+// The bytes of a slice are unit-major: row r's 16-byte unit u sits at
+// (u*128 + r)*16.  Lanes that own consecutive rows therefore read consecutive
+// 16-byte pieces (no shared-memory bank conflicts), and for int8 and bf16 data
+// two consecutive units are exactly the canonical K-major, unswizzled operand
+// layout of the tensor core: 8 rows x 16 bytes contiguous, 128 bytes from one
+// 8-row group to the next, 2048 bytes from one 16-byte K step to the next.
+// The repack is a permutation of the GGUF bytes (nothing is widened):
 //   type   K-slice   SL   the slice's bytes of one row
 //   Q8_0   256       272  8 blocks' int8 quants (256) then their 8 f16 scales (16)
 //   Q4_K   256       144  the 144-byte super-block {d, dmin, scales[12], qs[128]}
 //   Q5_K   256       176  the 176-byte super-block {d, dmin, scales[12], qh[32], qs[128]}
 //   Q6_K   256       208  ql[128], qh[64], scales[16]; the f16 d goes to a side plane
 //   BF16   64        128  64 values
-constexpr int kRepackVersion = 3;
+constexpr int kRepackVersion = 4;
+constexpr int kChunkRows = 128;
 
 struct SliceGeom { int elems, sl; };
 __host__ __device__ inline SliceGeom slice_geom(int ty) {
@@ -63,30 +66,32 @@ struct DevTiles {          // the tiles of one product (gate+up, or down) of a s
     int slice_bytes = 0;       // SL
     int nslices = 0;           // cols / slice elems
     uint8_t* data = nullptr;
-    uint16_t* side = nullptr;  // Q6_K: f16 d, [expert][chunk][tile][32 rows][nslices]
-    int64_t expert_bytes = 0;  // chunks * nslices * 4 * 32 * SL
-    // first byte of K-slice s of a chunk (its four tiles follow each other)
+    uint16_t* side = nullptr;  // Q6_K: f16 d, [expert][chunk][128 rows][nslices]
+    int64_t expert_bytes = 0;  // chunks * nslices * 128 * SL
+    // first byte of K-slice s of a chunk
     __host__ __device__ const uint8_t* stage(int64_t e, int chunk, int s) const {
-        return data + e * expert_bytes + ((int64_t)chunk * nslices + s) * 4 * 32 * slice_bytes;
+        return data + e * expert_bytes + ((int64_t)chunk * nslices + s) * kChunkRows * slice_bytes;
     }
 };
 
 // Activation rows live in a position space in which every group starts at a
 // multiple of 8, so a tile of 8 positions belongs to one group.  Quantised rows
 // (Q8Act, quant.rs:352-394) are stored as one record per (K-slice of 256, tile):
-//     q     [8 tokens][272]  int8: 256 values + 16 bytes of padding that spreads
-//                            the 8 rows over the shared-memory banks
+//     q     [16 units][8 tokens][16] int8: unit-major like the weights, so that 8
+//                            tokens x 16 bytes are contiguous (bank-conflict free
+//                            fragment loads; the tensor core's canonical K-major layout)
 //     dx    [8 blocks][8 tokens] f32: the block scales d
 //     s_hi  [8 blocks][8 tokens] f32: s = d*sum(q) split in two tf32-exact parts
 //     s_lo                            (11 + 11 mantissa bits), for the tensor-core min term
 //     s     [8 blocks][8 tokens] f32: s itself (read by the taps only)
 // which is what one pipeline stage of the expert kernels copies (all but `s`).
 // Float rows (BF16 weights) are [K/64][R][64] f32.  R = ceil8(n) + n*k + 8*n_expert + 8.
-constexpr int kActQStride = 272;
-constexpr int kActOffDx = 8 * kActQStride, kActOffSHi = kActOffDx + 256, kActOffSLo = kActOffSHi + 256,
+constexpr int kActOffDx = 2048, kActOffSHi = kActOffDx + 256, kActOffSLo = kActOffSHi + 256,
               kActOffS = kActOffSLo + 256;
-constexpr int kActCopyBytes = kActOffS;        // 2944: what a stage copies
-constexpr int kActTileBytes = kActOffS + 256;  // 3200
+constexpr int kActCopyBytes = kActOffS;        // 2816: what a stage copies
+constexpr int kActTileBytes = kActOffS + 256;  // 3072
+// byte offset inside a record of element i (0..255) of token tk (0..7)
+__host__ __device__ inline int act_q_off(int tk, int i) { return ((i >> 4) * 8 + tk) * 16 + (i & 15); }
 // the two tf32-exact parts of an f32 (the tensor core ignores the low 13 mantissa bits)
 __host__ __device__ inline void split_tf32(float v, float* hi, float* lo) {
     union { float f; uint32_t u; } a, b;

@@ -9,10 +9,9 @@
 // up to 8 tokens of one group times a chunk of weight rows (64 gate rows with
 // their 64 up rows, or 128 down rows) - from a counter.  The device layout
 // (common.cuh) stores what one pipeline stage needs, one K-slice of the
-// chunk's four 32-row tiles, contiguously: a stage arrives as one bulk copy of
-// weights plus the K-slice of the tile's activation rows (cp.async.bulk on an
-// mbarrier), double-buffered, and the stream of stages runs on across item
-// boundaries.  Each 32-element block dot is an int8 tensor-core product
+// chunk's 128 rows, contiguously: a stage arrives as one bulk copy of weights
+// plus one of the tile's activation record (cp.async.bulk on an mbarrier),
+// double-buffered, and the stream of stages runs on across item boundaries.  Each 32-element block dot is an int8 tensor-core product
 // (mma.sync m16n8k32, 16 weight rows x 8 tokens): its int32 results are the
 // reference's block dots, scaled in f32 by the weight block scale and the
 // activation block scale.  The measured __dp4a rate of this GPU (64 lanes per
@@ -145,14 +144,15 @@ __device__ __forceinline__ void mma_tf32_k8(float (&d)[4], const float (&a)[4], 
 // ---------------------------------------------------------------------------
 // Per-type arithmetic of one staged K-slice for one warp.
 //   rowp[mt][r]  this lane's two rows (g, g+8) of the warp's two 16-row MMA tiles:
-//                tile + row*16; unit u of the row is 512*u further, so byte `off`
-//                of the row's slice is WU(p, off)
-//   act          the tile's Q8 record (common.cuh): q rows [8 tokens][272 bytes], then
-//                dx, s_hi, s_lo as [8 blocks][8 tokens] f32
+//                slice + row*16; unit u of the row is 2048*u further (128 rows x 16
+//                bytes), so byte `off` of the row's slice is WU(p, off)
+//   act          the tile's Q8 record (common.cuh): q as [16 units][8 tokens][16 bytes],
+//                then dx, s_hi, s_lo as [8 blocks][8 tokens] f32
+//   XQ(act,u)    this lane's B-fragment word of unit u: token g, bytes 4c..4c+3
 //   acc[mt][i]   i = 2*r + tt: row g+8r, token 2c+tt
-#define WU(w, off) ((w) + ((((off)) >> 4) << 9) + ((off) & 15))
+#define WU(w, off) ((w) + ((((off)) >> 4) << 11) + ((off) & 15))
 #define LDS32(p) (*(const uint32_t*)(p))
-constexpr int ACT_Q_STRIDE = kActQStride;
+#define XQ(xlane, u) ((int)LDS32((xlane) + (u) * 128))
 
 struct NoSide {};
 
@@ -171,13 +171,13 @@ template <> struct Fmt<BIVMOE_Q8_0> {
         for (int mt = 0; mt < 2; mt++)
 #pragma unroll
             for (int r = 0; r < 2; r++) dwv[mt][r] = *(const uint4*)WU(rowp[mt][r], 256);
-        const uint8_t* xrow = act + g * ACT_Q_STRIDE + 4 * c;
+        const uint8_t* xlane = act + g * 16 + 4 * c;
 #pragma unroll
         for (int j = 0; j < 4; j++) {       // blocks 2j and 2j+1
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 const int b = 2 * j + h;
-                const int b0 = (int)LDS32(xrow + 32 * b), b1 = (int)LDS32(xrow + 32 * b + 16);
+                const int b0 = XQ(xlane, 2 * b), b1 = XQ(xlane, 2 * b + 1);
                 const float2 dxv = *(const float2*)(dxp + b * 8 + 2 * c);   // tokens 2c, 2c+1
                 const float dx[2] = {dxv.x, dxv.y};
 #pragma unroll
@@ -251,13 +251,13 @@ template <int TY> struct FmtK45 {
             }
         }
         float tS[2][4] = {};
-        const uint8_t* xrow = act + g * ACT_Q_STRIDE + 4 * c;
+        const uint8_t* xlane = act + g * 16 + 4 * c;
 #pragma unroll
         for (int j = 0; j < 4; j++) {       // sub-blocks 2j (low nibbles) and 2j+1 (high nibbles)
             const float2 xa = *(const float2*)(dxp + (2 * j) * 8 + 2 * c);       // d of tokens 2c, 2c+1
             const float2 xb = *(const float2*)(dxp + (2 * j + 1) * 8 + 2 * c);
-            const int blo0 = (int)LDS32(xrow + 64 * j), blo1 = (int)LDS32(xrow + 64 * j + 16);
-            const int bhi0 = (int)LDS32(xrow + 64 * j + 32), bhi1 = (int)LDS32(xrow + 64 * j + 48);
+            const int blo0 = XQ(xlane, 4 * j), blo1 = XQ(xlane, 4 * j + 1);
+            const int bhi0 = XQ(xlane, 4 * j + 2), bhi1 = XQ(xlane, 4 * j + 3);
 #pragma unroll
             for (int mt = 0; mt < 2; mt++) {
                 uint32_t w[4];
@@ -328,7 +328,7 @@ template <> struct Fmt<BIVMOE_Q6_K> {
         for (int mt = 0; mt < 2; mt++)
 #pragma unroll
             for (int r = 0; r < 2; r++) scv[mt][r] = *(const uint4*)WU(rowp[mt][r], 192);
-        const uint8_t* xrow = act + g * ACT_Q_STRIDE + 4 * c;
+        const uint8_t* xlane = act + g * 16 + 4 * c;
 #pragma unroll
         for (int n = 0; n < 2; n++) {
             uint32_t qh[2][2][2];   // [mt][r][lhalf]
@@ -354,7 +354,7 @@ template <> struct Fmt<BIVMOE_Q6_K> {
                     const int kq = par + 2 * hi, xb = 4 * n + kq;
                     const float2 dxv = *(const float2*)(dxp + xb * 8 + 2 * c);
                     const float dx0 = dxv.x, dx1 = dxv.y;
-                    const int b0 = (int)LDS32(xrow + 32 * xb), b1 = (int)LDS32(xrow + 32 * xb + 16);
+                    const int b0 = XQ(xlane, 2 * xb), b1 = XQ(xlane, 2 * xb + 1);
 #pragma unroll
                     for (int mt = 0; mt < 2; mt++) {
                         int a[2][2];   // [lhalf][r]
@@ -405,7 +405,7 @@ template <> struct Fmt<BIVMOE_BF16> {
 #pragma unroll 2
         for (int u = 0; u < 8; u++) {
             float w[8];
-            widen(*(const uint4*)(wrow + 512 * u), w);
+            widen(*(const uint4*)(wrow + 2048 * u), w);
 #pragma unroll
             for (int t = 0; t < EX_TT; t++) {
                 if (t < cnt) {
@@ -429,7 +429,7 @@ __host__ __device__ constexpr int act_stage_bytes() {
 }
 template <int TY>
 __host__ __device__ constexpr int stage_bytes() {
-    return 4 * 32 * Fmt<TY>::SL + act_stage_bytes<TY>();
+    return kChunkRows * Fmt<TY>::SL + act_stage_bytes<TY>();
 }
 constexpr int EX_SMEM_HEAD = 64 + EX_TT * 64 * 4;   // barriers, counter slots; the SwiGLU staging
 template <int TY>
@@ -446,7 +446,7 @@ struct Item {           // a decoded work item (block-uniform): a token tile x a
     int nst;            // stages of the item: chunks * nsl (0: nothing to do for this group)
     int pos0;           // first position of the tile
     int tc;             // tokens in the tile
-    const uint8_t* src; // stage 0; stage s is s * 4 * 32 * SL further
+    const uint8_t* src; // stage 0; stage s is s * 128 * SL further
 };
 
 template <int TY, int MODE>
@@ -455,7 +455,7 @@ experts_kernel(const ExpertArgs A) {
     using F = Fmt<TY>;
     using Side = typename F::Side;
     constexpr int SB = stage_bytes<TY>();
-    constexpr uint32_t TILE = 32 * F::SL, W_BYTES = 4 * TILE, ACT_BYTES = act_stage_bytes<TY>();
+    constexpr uint32_t W_BYTES = kChunkRows * F::SL, ACT_BYTES = act_stage_bytes<TY>();
     constexpr int CH = MODE == MODE_GATEUP ? 64 : 128;   // output rows per chunk
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* mbar = (uint64_t*)smem;          // [2]
@@ -519,26 +519,26 @@ experts_kernel(const ExpertArgs A) {
                      kActCopyBytes, &mbar[slot]);
         }
     };
-    // this lane's rows inside a staged chunk: [mt][r] -> tile index, row in tile
-    int tile_of[2], row_of[2];
-    if (MODE == MODE_GATEUP) {   // warp w: gate rows 16w..16w+15 and the same up rows
-        tile_of[0] = warp >> 1; tile_of[1] = 2 + (warp >> 1);
-        row_of[0] = row_of[1] = (warp & 1) * 16;
+    // the first chunk row of this warp's two 16-row MMA tiles
+    int row_of[2];
+    if (MODE == MODE_GATEUP) {   // warp w: gate rows 16w..16w+15 and the same up rows (64 further)
+        row_of[0] = 16 * warp;
+        row_of[1] = 64 + 16 * warp;
     } else {                     // warp w: down rows 32w..32w+31
-        tile_of[0] = tile_of[1] = warp;
-        row_of[0] = 0; row_of[1] = 16;
+        row_of[0] = 32 * warp;
+        row_of[1] = 32 * warp + 16;
     }
     auto side_of = [&](const Item& it, int s) -> Side {
         if constexpr (TY == BIVMOE_Q6_K) {
             const DevTiles& m = it.shared ? A.sh : A.w;
-            const size_t base = ((size_t)(it.shared ? 0 : it.expert) * m.chunks + it.chunk0 + s / it.nsl) * 4;
+            const size_t base = ((size_t)(it.shared ? 0 : it.expert) * m.chunks + it.chunk0 + s / it.nsl) * kChunkRows;
             Side v;
 #pragma unroll
             for (int mt = 0; mt < 2; mt++)
 #pragma unroll
                 for (int r = 0; r < 2; r++)
                     v.d[mt][r] = __half2float(__ushort_as_half(
-                        m.side[((base + tile_of[mt]) * 32 + row_of[mt] + g + 8 * r) * m.nslices + s % it.nsl]));
+                        m.side[(base + row_of[mt] + g + 8 * r) * m.nslices + s % it.nsl]));
             return v;
         } else {
             return Side{};
@@ -608,10 +608,8 @@ experts_kernel(const ExpertArgs A) {
             if constexpr (F::F32ACT) {
                 // a lane per weight row: GATEUP lanes 0-15 gate rows, 16-31 up rows
                 const uint8_t* wrow;
-                if (MODE == MODE_GATEUP)
-                    wrow = st + (size_t)tile_of[lane >> 4] * TILE + (row_of[0] + (lane & 15)) * 16;
-                else
-                    wrow = st + (size_t)warp * TILE + lane * 16;
+                if (MODE == MODE_GATEUP) wrow = st + (row_of[lane >> 4] + (lane & 15)) * 16;
+                else wrow = st + (32 * warp + lane) * 16;
                 F::compute_f32(wrow, (const float*)act, cur.tc, accf);
             } else {
                 const uint8_t* rowp[2][2];
@@ -619,7 +617,7 @@ experts_kernel(const ExpertArgs A) {
                 for (int mt = 0; mt < 2; mt++)
 #pragma unroll
                     for (int r = 0; r < 2; r++)
-                        rowp[mt][r] = st + (size_t)tile_of[mt] * TILE + (row_of[mt] + g + 8 * r) * 16;
+                        rowp[mt][r] = st + (row_of[mt] + g + 8 * r) * 16;
                 F::compute(rowp, slot ? side1 : side0, act, acc, g, c);
             }
             if (claim && tid == 0) s_item[n_fetch & 1] = pf;
@@ -667,7 +665,7 @@ experts_kernel(const ExpertArgs A) {
                         float dd, ss;
                         const int q = q8_quantize_lane(v, dd, ss);
                         uint8_t* rec = A.out_t + ((size_t)(r / 256) * (A.act_rows / 8) + pos / 8) * kActTileBytes;
-                        rec[(pos % 8) * ACT_Q_STRIDE + r % 256] = (uint8_t)(int8_t)q;
+                        rec[act_q_off((int)(pos % 8), r % 256)] = (uint8_t)(int8_t)q;
                         if (lane < 4) {
                             float shi, slo;
                             split_tf32(ss, &shi, &slo);

@@ -51,7 +51,7 @@ dispatch_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, 
                 for (int j = 0; j <= k; j++) {
                     const int pos = s_pos[j];
                     uint8_t* rec = ws.act_t + ((size_t)sl * (R / 8) + pos / 8) * kActTileBytes;
-                    rec[(pos % 8) * kActQStride + 32 * bb + lane] = (uint8_t)(int8_t)q;
+                    rec[act_q_off(pos % 8, 32 * bb + lane)] = (uint8_t)(int8_t)q;
                     if (lane < 4) {
                         const float val = lane == 0 ? dd : lane == 1 ? shi : lane == 2 ? slo : ss;
                         *(float*)(rec + kActOffDx + 256 * lane + (bb * 8 + pos % 8) * 4) = val;
@@ -168,13 +168,13 @@ cudaError_t launch_combine(const LaunchCfg& c, const Workspace& ws, float* out, 
 // ---------------------------------------------------------------------------
 // Upload-time repack: GGUF rows -> tiled device layout (common.cuh).  One
 // thread per 16-byte unit of the destination.  `tile_base` places the source
-// matrix inside the chunk: 0 for gate and for down, 2 for up.
+// matrix inside the chunk: 0 for gate and for down, 2 for up (chunk rows 64..127).
 __global__ void repack_kernel(DevTiles dt, const uint8_t* __restrict__ src, int tile_base) {
     const int units = dt.slice_bytes / 16;
     const int64_t n_rows = (int64_t)dt.n * dt.rows;
     const int64_t total = n_rows * dt.nslices * units;
     const int64_t grb = gguf_row_bytes(dt.ty, dt.cols);
-    const int64_t tile_bytes = 32 * (int64_t)dt.slice_bytes;
+    const int64_t slice_tile_bytes = kChunkRows * (int64_t)dt.slice_bytes;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
         const int u = (int)(i % units);
@@ -182,11 +182,11 @@ __global__ void repack_kernel(DevTiles dt, const uint8_t* __restrict__ src, int 
         const int64_t rg = i / ((int64_t)units * dt.nslices);   // row over all experts
         const int64_t e = rg / dt.rows;
         const int r = (int)(rg % dt.rows);
-        const int chunk = r / dt.chunk_rows, tile = tile_base + (r % dt.chunk_rows) / 32, rr = r % 32;
+        const int chunk = r / dt.chunk_rows, vrow = tile_base * 32 + r % dt.chunk_rows;
         const uint8_t* row = src + rg * grb;
         uint8_t* dst = dt.data + e * dt.expert_bytes +
-                       (((int64_t)chunk * dt.nslices + s) * 4 + tile) * tile_bytes +
-                       ((int64_t)u * 32 + rr) * 16;
+                       ((int64_t)chunk * dt.nslices + s) * slice_tile_bytes +
+                       ((int64_t)u * kChunkRows + vrow) * 16;
         const uint8_t* from = nullptr;
         switch (dt.ty) {
             case BIVMOE_Q4_K: from = row + 144 * (int64_t)s + 16 * u; break;
@@ -207,7 +207,7 @@ __global__ void repack_kernel(DevTiles dt, const uint8_t* __restrict__ src, int 
         }
         if (dt.ty == BIVMOE_Q6_K && u == 0) {
             const uint8_t* d = row + 210 * (int64_t)s + 208;
-            dt.side[((((int64_t)e * dt.chunks + chunk) * 4 + tile) * 32 + rr) * dt.nslices + s] =
+            dt.side[(((int64_t)e * dt.chunks + chunk) * kChunkRows + vrow) * dt.nslices + s] =
                 (uint16_t)(d[0] | (d[1] << 8));
         }
     }
@@ -224,9 +224,9 @@ cudaError_t launch_repack(const DevTiles& dst, const uint8_t* gguf_rows, int til
 // Q8 activation row, decoded byte by byte as the reference's scalar kernels
 // define the values (quant.rs:599-686).  One thread per block; not on the
 // timed path.
-__device__ inline uint8_t tile_byte(const DevTiles& t, const uint8_t* tile0, int rr, int s, int off) {
-    // tile0: the row's tile in K-slice 0; the same tile of slice s is s * 4 tiles further
-    return tile0[(int64_t)s * 4 * 32 * t.slice_bytes + ((off >> 4) * 32 + rr) * 16 + (off & 15)];
+__device__ inline uint8_t tile_byte(const DevTiles& t, const uint8_t* chunk0, int vrow, int s, int off) {
+    // chunk0: K-slice 0 of the row's chunk; byte `off` of the row's slice s
+    return chunk0[(int64_t)s * kChunkRows * t.slice_bytes + ((off >> 4) * kChunkRows + vrow) * 16 + (off & 15)];
 }
 
 __global__ void block_dots_kernel(DevTiles t, int tile_base, int expert, int row,
@@ -234,11 +234,12 @@ __global__ void block_dots_kernel(DevTiles t, int tile_base, int expert, int row
                                   int32_t* __restrict__ out) {
     const int b = blockIdx.x * blockDim.x + threadIdx.x;   // 32-element block of the row
     if (b >= t.cols / 32) return;
-    const int chunk = row / t.chunk_rows, tile = tile_base + (row % t.chunk_rows) / 32, rr = row % 32;
-    const uint8_t* t0 = t.stage(expert, chunk, 0) + (int64_t)tile * 32 * t.slice_bytes;
+    const int chunk = row / t.chunk_rows, rr = tile_base * 32 + row % t.chunk_rows;
+    const uint8_t* t0 = t.stage(expert, chunk, 0);
     const int s = b / 8, sb = b % 8;
-    const int8_t* x = (const int8_t*)act_t + ((size_t)s * (act_rows / 8) + pos / 8) * kActTileBytes +
-                      (pos % 8) * kActQStride + 32 * sb;
+    const int8_t* rec = (const int8_t*)act_t + ((size_t)s * (act_rows / 8) + pos / 8) * kActTileBytes;
+    int8_t x[32];
+    for (int l = 0; l < 32; l++) x[l] = rec[act_q_off(pos % 8, 32 * sb + l)];
     int32_t sum = 0;
     if (t.ty == BIVMOE_Q8_0) {
         for (int l = 0; l < 32; l++) sum += (int)(int8_t)tile_byte(t, t0, rr, s, 32 * sb + l) * x[l];
