@@ -2,6 +2,7 @@
 // workspace, the forward sequence and the parity taps.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -69,6 +70,7 @@ struct bivmoe_layer {
         cudaStream_t stream = nullptr;
         int seen = 0;            // identical calls seen; the graph is built on the second
     } graph;
+    int prefill_min = 0;   // set at create when the tcgen05 kernels support the layer's types
     bool use_graph = true;
     int launches_per_forward = 0;
     std::string error, device_name;
@@ -84,7 +86,7 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
     w.weights = a.take<float>(P);
     w.counts = a.take<int32_t>(ne);
     w.offsets = a.take<int32_t>(ne + 1);
-    w.order = a.take<int32_t>(((N + 7) / 8) * 8 + P + 8 * ne + 8);
+    w.order = a.take<int32_t>(((N + 7) / 8) * 8 + P + 8 * ne + 8 + kPrefillTile);
     w.pos_of = a.take<int32_t>(P);
     w.blk_counts = a.take<int32_t>(((N + 255) / 256) * ne);
     w.grp_expert = a.take<int32_t>(ne + 1);
@@ -95,10 +97,15 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
     w.tile_group = a.take<int32_t>(tiles);
     w.tile_t0 = a.take<int32_t>(tiles);
     w.n_tiles = a.take<int32_t>(2);
-    w.work_ctr = a.take<uint32_t>(4);
+    const size_t ptiles = (P + N) / kPrefillTile + ne + 2;
+    w.ptile_group = a.take<int32_t>(ptiles);
+    w.ptile_t0 = a.take<int32_t>(ptiles);
+    w.n_ptiles = a.take<int32_t>(2);
+    w.work_ctr = a.take<uint32_t>(8);
     w.status = a.take<int32_t>(4);
     // positions: the tokens (shared group), then the routed groups, each padded to 8
-    const size_t R = ((N + 7) / 8) * 8 + P + 8 * ne + 8;
+    // (+128: a tile of the tcgen05 kernels copies 128 positions from its first one)
+    const size_t R = ((N + 7) / 8) * 8 + P + 8 * ne + 8 + kPrefillTile;
     w.act_rows = (int)R;
     const bool qact = !type_uses_f32_act(L->gate_up.ty) || (L->has_shared && !type_uses_f32_act(L->sh_gate_up.ty));
     const bool fact = type_uses_f32_act(L->gate_up.ty) || (L->has_shared && type_uses_f32_act(L->sh_gate_up.ty));
@@ -280,6 +287,13 @@ int bivmoe_create(const bivmoe_desc* d, bivmoe_layer** out) {
     if (shared && (ce = cudaMemcpy(L->router + (size_t)L->n_expert * L->e, d->sh_gate_inp,
                                    (size_t)L->e * 4, cudaMemcpyHostToDevice)) != cudaSuccess)
         return cu_fail(ce, "shared gate upload");
+    // groups of at least this many tokens run on the tcgen05 kernels, where they exist
+    // for the layer's types (shared expert of the same types, or none)
+    if (prefill_supported(L->gate_up.ty, L->down.ty) &&
+        (!shared || (L->sh_gate_up.ty == L->gate_up.ty && L->sh_down.ty == L->down.ty))) {
+        const char* env = getenv("BIVMOE_PREFILL_MIN");
+        L->prefill_min = env ? atoi(env) : 96;
+    }
     Arena probe;
     layout_workspace(L, probe);
     L->ws_bytes = probe.off;
@@ -323,6 +337,7 @@ static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int 
     if (n == 0) return BIVMOE_OK;
     LaunchCfg c{stream, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh, L->has_shared ? 1 : 0, L->sm_count};
     c.ev = ev;
+    c.prefill_min = L->prefill_min;
     mark(c, EV_START);
     CU(launch_router(c, L->router, h, L->ws));
     mark(c, EV_ROUTER);
@@ -333,6 +348,8 @@ static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int 
     CU(launch_dispatch(c, h, L->ws, L->ws.act_t != nullptr, L->ws.act_f != nullptr));
     mark(c, EV_QUANT);
     CU(launch_experts(c, L->gate_up, L->down, L->sh_gate_up, L->sh_down, L->ws));
+    if (c.prefill_min > 0)
+        CU(launch_experts_prefill(c, L->gate_up, L->down, L->sh_gate_up, L->sh_down, L->ws));
     mark(c, EV_DOWN);
     CU(launch_combine(c, L->ws, out, accumulate));
     mark(c, EV_COMBINE);

@@ -29,6 +29,7 @@ namespace bivmoe {
 //   BF16   64        128  64 values
 constexpr int kRepackVersion = 4;
 constexpr int kChunkRows = 128;
+constexpr int kPrefillTile = 128;   // tokens per tile of the tcgen05 kernels
 
 struct SliceGeom { int elems, sl; };
 __host__ __device__ inline SliceGeom slice_geom(int ty) {
@@ -120,7 +121,10 @@ struct Workspace {
     int32_t* tile_group; // [tiles] tile -> group; a tile is <= 8 consecutive positions of a group
     int32_t* tile_t0;    // [tiles] first token of the tile inside its group
     int32_t* n_tiles;    // [2] all tiles; the shared group's tiles (they come first)
-    uint32_t* work_ctr;  // [4] dynamic work counters, zeroed by the sort
+    int32_t* ptile_group;// [ptiles] tiles of 128 positions of the prefill-sized groups
+    int32_t* ptile_t0;
+    int32_t* n_ptiles;   // [2] all prefill tiles; the shared group's (they come first)
+    uint32_t* work_ctr;  // [8] dynamic work counters, zeroed by the sort
     int32_t* status;     // [4] device-side error flags (0 = ok)
     int act_rows;        // R: positions
     uint8_t* act_t;      // Q8 records of h, [n_embd/256][R/8] tiles (quantised gate/up types)
@@ -135,6 +139,7 @@ struct LaunchCfg {
     cudaStream_t stream;
     int n, k, e, n_expert, ff, ff_sh, has_shared;
     int sm_count;
+    int prefill_min = 0;         // groups with at least this many tokens go to the tcgen05 kernels (0: none)
     cudaEvent_t* ev = nullptr;   // optional: events recorded between the stages (profiling call)
 };
 enum { EV_START = 0, EV_ROUTER, EV_TOPK, EV_SORT, EV_QUANT, EV_GATEUP, EV_DOWN, EV_COMBINE, EV_COUNT };
@@ -160,6 +165,10 @@ cudaError_t launch_block_dots(const DevTiles& t, int tile_base, int expert, int 
                               const uint8_t* act_t, int act_rows, int pos, int32_t* out,
                               cudaStream_t stream);
 bool experts_supported(int ty, int cols, int rows, bool is_down);
+bool prefill_supported(int gate_up_ty, int down_ty);
+cudaError_t launch_experts_prefill(const LaunchCfg& c, const DevTiles& gate_up, const DevTiles& down,
+                                   const DevTiles& sh_gate_up, const DevTiles& sh_down,
+                                   const Workspace& ws);
 
 void count_launch(int n = 1);
 

@@ -1,0 +1,435 @@
+// Grouped expert products for prefill-sized groups (Q8_0 weights) on the 5th
+// generation tensor cores: tcgen05.mma kind::i8 with the accumulator in tensor
+// memory, operands staged in shared memory by bulk copies.
+// Reference: the same functions as experts_decode.cu (dense_ffn,
+// engine/src/model.rs:1119-1126, over the Q8_0 dot, engine/src/quant.rs:599-607),
+// for experts whose token list is long (model.rs:875-889).
+//
+// Design.  One block per SM, ten warps: a copy warp, an MMA warp and eight
+// epilogue warps.  A work item is a tile of 128 tokens of one group times a
+// chunk of 128 weight rows (64 gate rows with their 64 up rows, or 128 down
+// rows).  The device layouts of common.cuh are already the tensor core's
+// canonical K-major operand layouts, so a stage - one K-slice of 256 columns:
+// 128 rows x 272 bytes of weights and the 16 activation records of the tile -
+// is two bulk copies (cp.async.bulk) and no shuffling.  The reference scales
+// every 32-element block dot by its own pair of scales, so the products cannot
+// accumulate across blocks inside the tensor core: each block is one MMA
+// (M = 128 rows, N = 128 tokens, K = 32) into one of two tensor-memory buffers,
+// which the epilogue warps drain (tcgen05.ld), convert, scale by d_w * d_x and
+// add to f32 accumulators in registers while the next MMA runs.  The int32
+// values read from tensor memory are the reference's block dots exactly.
+// Every wait is bounded; a wait that gives up records BIVMOE_ERR_TIMEOUT, the
+// block leaves its loops, frees its tensor memory and returns.
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cstdlib>
+
+#include "common.cuh"
+#include "formats.cuh"
+
+namespace bivmoe {
+
+constexpr int PF_NT = kPrefillTile;                  // tokens per tile = MMA N
+constexpr int PF_EPI_WARPS = 8;
+constexpr int PF_THREADS = 32 * (2 + PF_EPI_WARPS);  // warp 0 copies, warp 1 issues MMAs
+constexpr int PF_SL = 272;                           // Q8_0: bytes per row per K-slice
+constexpr uint32_t PF_W_BYTES = kChunkRows * PF_SL;                // 34816
+constexpr uint32_t PF_X_BYTES = (PF_NT / 8) * kActTileBytes;       // 49152
+constexpr uint32_t PF_STAGE = PF_W_BYTES + PF_X_BYTES;             // 83968
+constexpr uint32_t PF_HEAD = 1024;
+constexpr uint32_t PF_XCHG = 64 * PF_NT * 4;                        // SwiGLU exchange, 32 KiB
+constexpr uint32_t PF_SMEM = PF_HEAD + 2 * PF_STAGE + PF_XCHG;      // 201728
+constexpr uint32_t PF_TMEM_COLS = 256;                              // two buffers of 128 columns
+constexpr uint32_t PF_WAIT_TRIES = 1u << 16;                        // x up to 20 us each
+
+enum { PF_GATEUP = 0, PF_DOWN = 1 };
+
+struct PrefillArgs {
+    DevTiles w, sh;
+    const uint8_t* x_t;    // Q8 records of the inputs by position, [K/256][R/8]
+    int act_rows;          // R
+    float* out;            // GATEUP: mid f32 slice-major; DOWN: pair_out [R][rows]
+    uint8_t* out_t;        // GATEUP: Q8 records of mid
+    const int32_t* grp_expert;
+    const int32_t* grp_start;
+    const int32_t* grp_count;
+    const int32_t* ptile_group;
+    const int32_t* ptile_t0;
+    const int32_t* n_ptiles;
+    int32_t* status;
+    int n_expert;
+    int tiles_mode;        // 0: every tile, 1: skip the shared group's, 2: only the shared group's
+    int chunks;
+};
+
+// ---------------------------------------------------------------------------
+// PTX helpers
+__device__ __forceinline__ uint32_t pf_smem(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void pf_bar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pf_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void pf_bar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pf_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void pf_bar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pf_smem(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+// bounded wait for the phase of parity `parity`; false when it gave up
+__device__ __forceinline__ bool pf_bar_wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < PF_WAIT_TRIES; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(pf_smem(bar)), "r"(parity), "r"(20000u)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void pf_bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+            "r"(pf_smem(dst)),
+        "l"(src), "r"(bytes), "r"(pf_smem(bar))
+        : "memory");
+}
+// Shared-memory matrix descriptor, K-major, no swizzle: 8 rows x 16 bytes are
+// contiguous; `sbo` bytes from one 8-row group to the next, `lbo` bytes from
+// one 16-byte K step to the next.
+__device__ __forceinline__ uint64_t pf_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) |
+           ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
+}
+// kind::i8 instruction descriptor: s32 accumulator, signed 8-bit A and B, both K-major
+__device__ __forceinline__ uint32_t pf_idesc(int m, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void pf_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, 0, 0;\n\t"   // overwrite the accumulator: every block dot stands alone
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc)
+        : "memory");
+}
+__device__ __forceinline__ void pf_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     pf_smem(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void pf_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void pf_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// 32 consecutive columns of this warp's 32 lanes of tensor memory
+__device__ __forceinline__ void pf_tmem_ld32(uint32_t taddr, int (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+          "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void pf_tmem_wait_ld() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct PfItem {
+    int shared, expert, chunk, pos0, tc, nst;
+    const uint8_t* wsrc;   // stage 0 of the chunk's weights; stage s is s * PF_W_BYTES further
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(PF_THREADS, 1)
+experts_prefill_kernel(const PrefillArgs A) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* full = (uint64_t*)smem;            // [2] copies landed
+    uint64_t* empty = full + 2;                  // [2] stage free: MMAs done + 8 epilogue warps
+    uint64_t* tfull = full + 4;                  // [2] a block dot is in tensor memory
+    uint64_t* tempty = full + 6;                 // [2] drained by the 8 epilogue warps
+    uint64_t* xbar = full + 7 + 1;               // [1] meeting point of the 8 epilogue warps
+    uint32_t* s_tmem = (uint32_t*)(smem + 128);
+    int* s_abort = (int*)(smem + 132);
+    uint8_t* stages = smem + PF_HEAD;
+    float* s_xchg = (float*)(smem + PF_HEAD + 2 * PF_STAGE);   // [128 tokens][64 rows]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int CH = MODE == PF_GATEUP ? 64 : 128;   // output rows per chunk
+
+    if (tid == 0) {
+        for (int i = 0; i < 2; i++) {
+            pf_bar_init(&full[i], 1);
+            pf_bar_init(&empty[i], 1 + PF_EPI_WARPS);
+            pf_bar_init(&tfull[i], 1);
+            pf_bar_init(&tempty[i], PF_EPI_WARPS);
+        }
+        pf_bar_init(xbar, PF_EPI_WARPS);
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {   // tensor memory: 256 columns for the whole kernel
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         pf_smem(s_tmem)),
+                     "r"(PF_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pf_fence_before();
+    __syncthreads();
+    pf_fence_after();
+    const uint32_t tmem = *s_tmem;
+
+    const int tiles_all = A.n_ptiles[0], tiles_sh = A.n_ptiles[1];
+    const int tile_lo = A.tiles_mode == 1 ? tiles_sh : 0;
+    const int tile_hi = A.tiles_mode == 2 ? tiles_sh : tiles_all;
+    const int total = (tile_hi - tile_lo) * A.chunks;
+
+    // items are dealt round-robin: every role walks the same sequence on its own
+    auto decode = [&](int idx) -> PfItem {
+        PfItem it;
+        const int tile = tile_lo + idx / A.chunks;
+        it.chunk = idx % A.chunks;
+        const int gi = A.ptile_group[tile], t0 = A.ptile_t0[tile];
+        it.expert = A.grp_expert[gi];
+        it.shared = it.expert == A.n_expert;
+        it.pos0 = A.grp_start[gi] + t0;
+        it.tc = min(PF_NT, A.grp_count[gi] - t0);
+        const DevTiles& m = it.shared ? A.sh : A.w;
+        it.nst = it.chunk < m.chunks ? m.nslices : 0;
+        it.wsrc = m.stage(it.shared ? 0 : it.expert, min(it.chunk, max(m.chunks - 1, 0)), 0);
+        return it;
+    };
+    auto give_up = [&]() {
+        atomicExch(A.status, BIVMOE_ERR_TIMEOUT);
+        atomicExch(s_abort, 1);
+    };
+
+    if (warp == 0) {
+        // ---------------- copy warp: two bulk copies per stage
+        if (lane == 0) {
+            uint32_t q = 0;
+            bool dead = false;
+            for (int idx = blockIdx.x; idx < total && !dead && !*(volatile int*)s_abort; idx += gridDim.x) {
+                const PfItem it = decode(idx);
+                for (int s = 0; s < it.nst && !dead; s++, q++) {
+                    const uint32_t slot = q & 1;
+                    if (!pf_bar_wait(&empty[slot], ((q >> 1) & 1) ^ 1)) { give_up(); dead = true; break; }
+                    uint8_t* dst = stages + slot * PF_STAGE;
+                    pf_bar_expect_tx(&full[slot], PF_STAGE);
+                    pf_bulk_g2s(dst, it.wsrc + (size_t)s * PF_W_BYTES, PF_W_BYTES, &full[slot]);
+                    pf_bulk_g2s(dst + PF_W_BYTES,
+                                A.x_t + ((size_t)s * (A.act_rows / 8) + it.pos0 / 8) * kActTileBytes,
+                                PF_X_BYTES, &full[slot]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA warp: one thread issues one MMA per 32-column block
+        if (lane == 0) {
+            const uint32_t idesc = pf_idesc(kChunkRows, PF_NT);
+            uint32_t q = 0, kb = 0;
+            bool dead = false;
+            for (int idx = blockIdx.x; idx < total && !dead && !*(volatile int*)s_abort; idx += gridDim.x) {
+                const PfItem it = decode(idx);
+                for (int s = 0; s < it.nst && !dead; s++, q++) {
+                    const uint32_t slot = q & 1;
+                    if (!pf_bar_wait(&full[slot], (q >> 1) & 1)) { give_up(); dead = true; break; }
+                    const uint32_t wa = pf_smem(stages + slot * PF_STAGE);
+                    const uint32_t xa = wa + PF_W_BYTES;
+                    for (int b = 0; b < 8 && !dead; b++, kb++) {
+                        const uint32_t buf = kb & 1;
+                        if (!pf_bar_wait(&tempty[buf], ((kb >> 1) & 1) ^ 1)) { give_up(); dead = true; break; }
+                        pf_fence_after();
+                        // A: rows of the chunk, units 2b and 2b+1: 8-row groups 128 B apart,
+                        //    K steps 2048 B apart.  B: tokens, units 2b, 2b+1 of each record:
+                        //    8-token groups one record apart, K steps 128 B apart.
+                        const uint64_t ad = pf_desc(wa + 2 * b * (kChunkRows * 16), kChunkRows * 16, 128);
+                        const uint64_t bd = pf_desc(xa + 2 * b * 128, 128, kActTileBytes);
+                        pf_mma_i8(tmem + buf * PF_NT, ad, bd, idesc);
+                        pf_commit(&tfull[buf]);
+                    }
+                    if (!dead) pf_commit(&empty[slot]);   // the stage's operands are no longer read
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue warps
+        const int ew = warp - 2;                 // 0..7
+        const int quad = warp & 3;               // the tensor-memory lanes this warp may read
+        const int half = ew >> 2;                // which 64 of the 128 token columns
+        const int row = 32 * quad + lane;        // chunk row = tensor-memory lane
+        const uint32_t tlane = tmem + ((uint32_t)(32 * quad) << 16);
+        uint32_t q = 0, kb = 0, xphase = 0;
+        // the eight epilogue warps meet (bounded): false when the wait gave up
+        auto meet = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0) pf_bar_arrive(xbar);
+            const bool ok = pf_bar_wait(xbar, xphase);
+            xphase ^= 1;
+            return ok;
+        };
+        for (int idx = blockIdx.x; idx < total && !*(volatile int*)s_abort; idx += gridDim.x) {
+            const PfItem it = decode(idx);
+            float acc[64];
+#pragma unroll
+            for (int i = 0; i < 64; i++) acc[i] = 0.0f;
+            bool ok = true;
+            for (int s = 0; s < it.nst && ok; s++, q++) {
+                const uint32_t slot = q & 1;
+                if (!pf_bar_wait(&full[slot], (q >> 1) & 1)) { ok = false; break; }
+                const uint8_t* wst = stages + slot * PF_STAGE;
+                const uint8_t* xst = wst + PF_W_BYTES;
+                const uint4 dwv = *(const uint4*)(wst + 16 * (kChunkRows * 16) + row * 16);   // 8 f16 scales
+                for (int b = 0; b < 8 && ok; b++, kb++) {
+                    const uint32_t buf = kb & 1;
+                    if (!pf_bar_wait(&tfull[buf], (kb >> 1) & 1)) { ok = false; break; }
+                    pf_fence_after();
+                    const uint32_t wv = (&dwv.x)[b >> 1];
+                    const float dw = __half2float(__ushort_as_half((unsigned short)(wv >> (16 * (b & 1)))));
+#pragma unroll
+                    for (int hh = 0; hh < 2; hh++) {
+                        int v[32];
+                        pf_tmem_ld32(tlane + buf * PF_NT + half * 64 + hh * 32, v);
+                        pf_tmem_wait_ld();
+                        if (hh == 1) {   // both loads done: the buffer may be overwritten
+                            pf_fence_before();
+                            __syncwarp();
+                            if (lane == 0) pf_bar_arrive(&tempty[buf]);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {   // a record: 8 tokens
+                            const int rec = half * 8 + hh * 4 + j;
+                            const float4* dxp =
+                                (const float4*)(xst + rec * kActTileBytes + kActOffDx + b * 32);
+                            const float4 d0 = dxp[0], d1 = dxp[1];
+                            const float dx[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+#pragma unroll
+                            for (int t = 0; t < 8; t++) {
+                                const int i = hh * 32 + j * 8 + t;
+                                acc[i] = fmaf(dw, dx[t] * (float)v[j * 8 + t], acc[i]);
+                            }
+                        }
+                    }
+                }
+                if (ok) {
+                    __syncwarp();
+                    if (lane == 0) pf_bar_arrive(&empty[slot]);   // done with the stage's scales
+                }
+            }
+            if (!ok) { if (lane == 0) give_up(); break; }
+            if (it.nst == 0) continue;
+            // ---- the item's outputs: column i of this thread is token half*64 + i
+            if (MODE == PF_GATEUP) {
+                // rows 64..127 are up rows: hand them to the threads that own the gate rows
+                if (quad >= 2) {
+#pragma unroll
+                    for (int i = 0; i < 64; i++) s_xchg[(half * 64 + i) * 64 + (row - 64)] = acc[i];
+                }
+                if (!meet()) { if (lane == 0) give_up(); break; }
+                if (quad < 2) {
+                    const int r = it.chunk * CH + row;   // row of mid
+#pragma unroll 4
+                    for (int i = 0; i < 64; i++) {
+                        const int tok = half * 64 + i;
+                        if (tok >= it.tc) break;          // uniform across the warp
+                        const float gt = acc[i], u = s_xchg[tok * 64 + row];
+                        // ops.rs:160-167: silu(x) = x * (1 / (1 + exp(-x)))
+                        const float v = (gt * __fdiv_rn(1.0f, 1.0f + expf(-gt))) * u;
+                        const size_t pos = (size_t)it.pos0 + tok;
+                        A.out[((size_t)(r / 64) * A.act_rows + pos) * 64 + r % 64] = v;
+                        // Q8Act of the mid row (quant.rs:368-394): the warp's 32 rows are one block
+                        float dd, ss;
+                        const int qv = q8_quantize_lane(v, dd, ss);
+                        uint8_t* rec = A.out_t + ((size_t)(r / 256) * (A.act_rows / 8) + pos / 8) * kActTileBytes;
+                        rec[act_q_off((int)(pos % 8), r % 256)] = (uint8_t)(int8_t)qv;
+                        if (lane < 4) {
+                            float shi, slo;
+                            split_tf32(ss, &shi, &slo);
+                            const float val = lane == 0 ? dd : lane == 1 ? shi : lane == 2 ? slo : ss;
+                            *(float*)(rec + kActOffDx + 256 * lane + (((r % 256) / 32) * 8 + pos % 8) * 4) = val;
+                        }
+                    }
+                }
+                if (!meet()) { if (lane == 0) give_up(); break; }   // the exchange tile is free again
+            } else {
+                const int rows = (it.shared ? A.sh : A.w).rows;
+#pragma unroll 4
+                for (int i = 0; i < 64; i++) {
+                    const int tok = half * 64 + i;
+                    if (tok >= it.tc) break;
+                    A.out[((size_t)it.pos0 + tok) * rows + it.chunk * CH + row] = acc[i];
+                }
+            }
+        }
+    }
+    pf_fence_before();
+    __syncthreads();
+    pf_fence_after();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
+                     "r"(PF_TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+
+bool prefill_supported(int gate_up_ty, int down_ty) {
+    return gate_up_ty == BIVMOE_Q8_0 && down_ty == BIVMOE_Q8_0;
+}
+
+template <int MODE>
+static cudaError_t launch_prefill_one(const LaunchCfg& c, PrefillArgs A) {
+    A.chunks = std::max(A.w.chunks, A.sh.chunks);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(experts_prefill_kernel<MODE>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    experts_prefill_kernel<MODE><<<c.sm_count, PF_THREADS, PF_SMEM, c.stream>>>(A);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// gate+up then down for the groups the sort put on the prefill tile list
+cudaError_t launch_experts_prefill(const LaunchCfg& c, const DevTiles& gate_up, const DevTiles& down,
+                                   const DevTiles& sh_gate_up, const DevTiles& sh_down,
+                                   const Workspace& ws) {
+    PrefillArgs A{};
+    A.grp_expert = ws.grp_expert; A.grp_start = ws.grp_start; A.grp_count = ws.grp_count;
+    A.ptile_group = ws.ptile_group; A.ptile_t0 = ws.ptile_t0; A.n_ptiles = ws.n_ptiles;
+    A.status = ws.status;
+    A.n_expert = c.n_expert;
+    A.act_rows = ws.act_rows;
+    A.tiles_mode = 0;
+    PrefillArgs G = A;
+    G.w = gate_up; G.sh = sh_gate_up;
+    G.x_t = ws.act_t; G.out = ws.mid; G.out_t = ws.mid_t;
+    cudaError_t err = launch_prefill_one<PF_GATEUP>(c, G);
+    if (err != cudaSuccess) return err;
+    PrefillArgs D = A;
+    D.w = down; D.sh = sh_down;
+    D.x_t = ws.mid_t; D.out = ws.pair_out; D.out_t = nullptr;
+    return launch_prefill_one<PF_DOWN>(c, D);
+}
+
+}  // namespace bivmoe

@@ -260,10 +260,10 @@ __device__ void block_exclusive_scan(int (&v)[ITEMS], int* s_warp, int* total) {
 // everything; otherwise they are summed from the per-block counts.
 constexpr int SORT_EPT = 4;   // experts per thread in the scans (n_expert <= 1024)
 __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, int k,
-                          int has_shared, const int* s_cnt, int* s_off) {
+                          int has_shared, int prefill_min, const int* s_cnt, int* s_off) {
     __shared__ int s_warp[32];
-    __shared__ int s_total[3];
-    int cnt[SORT_EPT], off[SORT_EPT], act[SORT_EPT], til[SORT_EPT];
+    __shared__ int s_total[4];
+    int cnt[SORT_EPT], off[SORT_EPT], act[SORT_EPT], til[SORT_EPT], ptl[SORT_EPT];
     const int e0 = threadIdx.x * SORT_EPT;
 #pragma unroll
     for (int i = 0; i < SORT_EPT; i++) {
@@ -280,18 +280,25 @@ __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, in
                 }
             }
         }
+        // a group of at least prefill_min tokens is cut into tiles of 128 for the
+        // tcgen05 kernels, a smaller one into tiles of 8 for the decode kernels
+        const bool big = prefill_min > 0 && run >= prefill_min;
         cnt[i] = run;
-        til[i] = (run + SORT_TILE - 1) / SORT_TILE;
-        off[i] = til[i] * SORT_TILE;
+        off[i] = (run + SORT_TILE - 1) / SORT_TILE * SORT_TILE;
+        til[i] = big ? 0 : off[i] / SORT_TILE;
+        ptl[i] = big ? (run + kPrefillTile - 1) / kPrefillTile : 0;
         act[i] = run > 0;
     }
     __syncthreads();   // s_cnt is read; s_off may alias it
     block_exclusive_scan<SORT_EPT>(off, s_warp, &s_total[0]);
     block_exclusive_scan<SORT_EPT>(act, s_warp, &s_total[1]);
     block_exclusive_scan<SORT_EPT>(til, s_warp, &s_total[2]);
+    block_exclusive_scan<SORT_EPT>(ptl, s_warp, &s_total[3]);
     const int g_sh = has_shared ? 1 : 0;
-    const int t_sh = has_shared ? (n + SORT_TILE - 1) / SORT_TILE : 0;
-    const int p_sh = t_sh * SORT_TILE;
+    const bool big_sh = has_shared && prefill_min > 0 && n >= prefill_min;
+    const int p_sh = has_shared ? (n + SORT_TILE - 1) / SORT_TILE * SORT_TILE : 0;
+    const int t_sh = has_shared && !big_sh ? p_sh / SORT_TILE : 0;
+    const int pt_sh = big_sh ? (n + kPrefillTile - 1) / kPrefillTile : 0;
 #pragma unroll
     for (int i = 0; i < SORT_EPT; i++) {
         const int e = e0 + i;
@@ -305,16 +312,26 @@ __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, in
             ws.grp_expert[g] = e;
             ws.grp_start[g] = start;
             ws.grp_count[g] = cnt[i];
-            const int nt = (cnt[i] + SORT_TILE - 1) / SORT_TILE;
+            const bool big = prefill_min > 0 && cnt[i] >= prefill_min;
+            const int nt = big ? 0 : (cnt[i] + SORT_TILE - 1) / SORT_TILE;
             for (int j = 0; j < nt; j++) {
                 ws.tile_group[t_sh + til[i] + j] = g;
                 ws.tile_t0[t_sh + til[i] + j] = j * SORT_TILE;
+            }
+            const int npt = big ? (cnt[i] + kPrefillTile - 1) / kPrefillTile : 0;
+            for (int j = 0; j < npt; j++) {
+                ws.ptile_group[pt_sh + ptl[i] + j] = g;
+                ws.ptile_t0[pt_sh + ptl[i] + j] = j * kPrefillTile;
             }
         }
     }
     for (int j = threadIdx.x; j < t_sh; j += blockDim.x) {
         ws.tile_group[j] = 0;
         ws.tile_t0[j] = j * SORT_TILE;
+    }
+    for (int j = threadIdx.x; j < pt_sh; j += blockDim.x) {
+        ws.ptile_group[j] = 0;
+        ws.ptile_t0[j] = j * kPrefillTile;
     }
     if (threadIdx.x == 0) {
         if (has_shared) {
@@ -326,7 +343,9 @@ __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, in
         *ws.n_groups = g_sh + s_total[1];
         ws.n_tiles[0] = t_sh + s_total[2];
         ws.n_tiles[1] = t_sh;
-        for (int i = 0; i < 4; i++) ws.work_ctr[i] = 0;
+        ws.n_ptiles[0] = pt_sh + s_total[3];
+        ws.n_ptiles[1] = pt_sh;
+        for (int i = 0; i < 8; i++) ws.work_ctr[i] = 0;
     }
     __syncthreads();
 }
@@ -357,7 +376,7 @@ __device__ void sort_scatter(const Workspace& ws, const uint16_t* s_ids, const u
 }
 
 __global__ void __launch_bounds__(SORT_THREADS)
-sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int phase) {
+sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int prefill_min, int phase) {
     extern __shared__ uint8_t sort_smem[];
     uint16_t* s_ids = (uint16_t*)sort_smem;
     int* s_cnt = (int*)(sort_smem + (((size_t)SORT_TOKENS * k * 2 + 15) & ~(size_t)15));
@@ -371,7 +390,7 @@ sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int phase)
         __syncthreads();
         sort_hist(s_ids, npairs, n_expert, s_cnt);
         sort_build_masks(s_ids, npairs, k, n_expert, s_mask);
-        sort_scan(ws, n_expert, 1, n, k, has_shared, s_cnt, s_cnt);
+        sort_scan(ws, n_expert, 1, n, k, has_shared, prefill_min, s_cnt, s_cnt);
         sort_scatter(ws, s_ids, s_mask, pair0, npairs, k, n_expert, 0, s_cnt);
         return;
     }
@@ -382,7 +401,7 @@ sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int phase)
         for (int e = threadIdx.x; e < n_expert; e += blockDim.x)
             ws.blk_counts[(size_t)blk * n_expert + e] = s_cnt[e];
     }
-    if (phase == 2) sort_scan(ws, n_expert, nblk, n, k, has_shared, nullptr, nullptr);
+    if (phase == 2) sort_scan(ws, n_expert, nblk, n, k, has_shared, prefill_min, nullptr, nullptr);
     if (phase == 3) {
         sort_load_ids(ws.ids, pair0, npairs, s_ids);
         __syncthreads();
@@ -402,12 +421,12 @@ cudaError_t launch_sort(const LaunchCfg& c, const Workspace& ws) {
         attr_set = true;
     }
     if (nblk == 1) {
-        sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, 0);
+        sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, 0);
         count_launch();
     } else {
-        sort_kernel<<<nblk, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, 1);
-        sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, 2);
-        sort_kernel<<<nblk, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, 3);
+        sort_kernel<<<nblk, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, 1);
+        sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, 2);
+        sort_kernel<<<nblk, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, 3);
         count_launch(3);
     }
     return cudaGetLastError();

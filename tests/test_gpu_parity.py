@@ -232,3 +232,13 @@ def test_repeated_calls_replay_a_graph_with_the_same_result():
         assert torch.equal(out, m.moe(h2))
     finally:
         m.close()
+
+
+def test_prefill_sized_groups_q8_0():
+    # groups of hundreds of tokens: the tcgen05 kernels (tiles of 128 tokens, several
+    # K-slices, ragged last tiles) beside decode-sized groups in the same pass
+    wl = W.prefill_q8_0(n=700, n_embd=512, n_expert=8, k=2, ff=512, ff_sh=512)
+    got, ref = run_case(wl)
+    counts = np.bincount(oracle.moe_forward(wl.layer, wl.h, taps=True)[1]["ids"].reshape(-1),
+                         minlength=8)
+    assert counts.max() >= 128 and counts.min() < counts.max()   # the shape exercises both paths
