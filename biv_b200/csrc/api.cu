@@ -104,7 +104,7 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
     w.work_ctr = a.take<uint32_t>(8);
     w.status = a.take<int32_t>(4);
     // positions: the tokens (shared group), then the routed groups, each padded to 8
-    // (+128: a tile of the tcgen05 kernels copies 128 positions from its first one)
+    // (+kPrefillTile: a tile of the tcgen05 kernels copies that many positions from its first one)
     const size_t R = ((N + 7) / 8) * 8 + P + 8 * ne + 8 + kPrefillTile;
     w.act_rows = (int)R;
     const bool qact = !type_uses_f32_act(L->gate_up.ty) || (L->has_shared && !type_uses_f32_act(L->sh_gate_up.ty));

@@ -29,7 +29,7 @@ namespace bivmoe {
 //   BF16   64        128  64 values
 constexpr int kRepackVersion = 4;
 constexpr int kChunkRows = 128;
-constexpr int kPrefillTile = 128;   // tokens per tile of the tcgen05 kernels
+constexpr int kPrefillTile = 96;    // tokens per tile of the tcgen05 kernels
 
 struct SliceGeom { int elems, sl; };
 __host__ __device__ inline SliceGeom slice_geom(int ty) {

@@ -5,19 +5,26 @@
 // engine/src/model.rs:1119-1126, over the Q8_0 dot, engine/src/quant.rs:599-607),
 // for experts whose token list is long (model.rs:875-889).
 //
-// Design.  One block per SM, ten warps: a copy warp, an MMA warp and eight
-// epilogue warps.  A work item is a tile of 128 tokens of one group times a
-// chunk of 128 weight rows (64 gate rows with their 64 up rows, or 128 down
+// Design.  One block per SM, thirteen warps: one warp whose lane 0 issues the
+// copies and whose lane 1 issues the MMAs, and twelve epilogue warps (three per
+// tensor-memory lane quadrant, 32 token columns each, which keeps a thread's
+// accumulators and one drained block within 128 registers).  A work item is a
+// tile of 96 tokens of one group times a chunk of 128 weight rows (64 gate rows with their 64 up rows, or 128 down
 // rows).  The device layouts of common.cuh are already the tensor core's
 // canonical K-major operand layouts, so a stage - one K-slice of 256 columns:
-// 128 rows x 272 bytes of weights and the 16 activation records of the tile -
+// 128 rows x 272 bytes of weights and the 12 activation records of the tile -
 // is two bulk copies (cp.async.bulk) and no shuffling.  The reference scales
 // every 32-element block dot by its own pair of scales, so the products cannot
 // accumulate across blocks inside the tensor core: each block is one MMA
-// (M = 128 rows, N = 128 tokens, K = 32) into one of two tensor-memory buffers,
-// which the epilogue warps drain (tcgen05.ld), convert, scale by d_w * d_x and
-// add to f32 accumulators in registers while the next MMA runs.  The int32
-// values read from tensor memory are the reference's block dots exactly.
+// (M = 128 rows, N = 96 tokens, K = 32) into one of four tensor-memory buffers,
+// which the epilogue warps drain (tcgen05.ld), scale by d_w * d_x and add to f32
+// accumulators in registers while the next MMA runs.  The int32 values in tensor
+// memory are the reference's block dots exactly.  To keep the epilogue - the
+// bottleneck: three f32 operations per 32 multiply-adds - short, the MMA
+// accumulates onto tensor memory that the epilogue re-arms with the bit pattern of
+// 1.5 * 2^23 after each drain: the int32 result read as f32 is then
+// 12582912 + dot exactly, one f32 subtraction replaces the int-to-float
+// conversion, and all three operations run two tokens at a time (f32x2).
 // Every wait is bounded; a wait that gives up records BIVMOE_ERR_TIMEOUT, the
 // block leaves its loops, frees its tensor memory and returns.
 #include <cuda_fp16.h>
@@ -31,16 +38,20 @@
 namespace bivmoe {
 
 constexpr int PF_NT = kPrefillTile;                  // tokens per tile = MMA N
-constexpr int PF_EPI_WARPS = 8;
-constexpr int PF_THREADS = 32 * (2 + PF_EPI_WARPS);  // warp 0 copies, warp 1 issues MMAs
+constexpr int PF_EPI_WARPS = 12;                     // three per tensor-memory lane quadrant
+constexpr int PF_COLS = PF_NT / (PF_EPI_WARPS / 4);  // token columns per epilogue thread
+static_assert(PF_COLS == 32, "an epilogue thread drains one 32-column load per block dot");
+constexpr int PF_THREADS = 32 * (1 + PF_EPI_WARPS);  // warp 0: lane 0 copies, lane 1 issues MMAs
 constexpr int PF_SL = 272;                           // Q8_0: bytes per row per K-slice
 constexpr uint32_t PF_W_BYTES = kChunkRows * PF_SL;                // 34816
-constexpr uint32_t PF_X_BYTES = (PF_NT / 8) * kActTileBytes;       // 49152
-constexpr uint32_t PF_STAGE = PF_W_BYTES + PF_X_BYTES;             // 83968
+constexpr uint32_t PF_X_BYTES = (PF_NT / 8) * kActTileBytes;       // 36864
+constexpr uint32_t PF_STAGE = PF_W_BYTES + PF_X_BYTES;             // 71680
 constexpr uint32_t PF_HEAD = 1024;
-constexpr uint32_t PF_XCHG = 64 * PF_NT * 4;                        // SwiGLU exchange, 32 KiB
-constexpr uint32_t PF_SMEM = PF_HEAD + 2 * PF_STAGE + PF_XCHG;      // 201728
-constexpr uint32_t PF_TMEM_COLS = 256;                              // two buffers of 128 columns
+constexpr uint32_t PF_XCHG = 64 * PF_NT * 4;                        // SwiGLU exchange, 24 KiB
+constexpr uint32_t PF_SMEM = PF_HEAD + 2 * PF_STAGE + PF_XCHG;      // 168960
+constexpr uint32_t PF_TMEM_COLS = 512;                              // four buffers, 128 columns apart
+constexpr uint32_t PF_TBUF = 4;
+constexpr uint32_t PF_TSTRIDE = PF_TMEM_COLS / PF_TBUF;
 constexpr uint32_t PF_WAIT_TRIES = 1u << 16;                        // x up to 20 us each
 
 enum { PF_GATEUP = 0, PF_DOWN = 1 };
@@ -115,7 +126,7 @@ __device__ __forceinline__ uint32_t pf_idesc(int m, int n) {
 __device__ __forceinline__ void pf_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, 0, 0;\n\t"   // overwrite the accumulator: every block dot stands alone
+        "setp.ne.b32 p, 1, 0;\n\t"   // accumulate onto the buffer the epilogue armed with 1.5 * 2^23
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc)
         : "memory");
@@ -148,6 +159,38 @@ __device__ __forceinline__ void pf_tmem_ld32(uint32_t taddr, int (&v)[32]) {
 __device__ __forceinline__ void pf_tmem_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// arms 32 columns of this warp's lanes with one value
+__device__ __forceinline__ void pf_tmem_st32(uint32_t taddr, int x) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};" ::
+            "r"(taddr),
+        "r"(x)
+        : "memory");
+}
+__device__ __forceinline__ void pf_tmem_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// two f32 lanes per instruction (sm_100): d = a * b + c, d = a * b, d = a + b
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk(float lo, float hi) {
+    return (f32x2)__float_as_uint(lo) | ((f32x2)__float_as_uint(hi) << 32);
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 
 struct PfItem {
     int shared, expert, chunk, pos0, tc, nst;
@@ -159,14 +202,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
 experts_prefill_kernel(const PrefillArgs A) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* full = (uint64_t*)smem;            // [2] copies landed
-    uint64_t* empty = full + 2;                  // [2] stage free: MMAs done + 8 epilogue warps
-    uint64_t* tfull = full + 4;                  // [2] a block dot is in tensor memory
-    uint64_t* tempty = full + 6;                 // [2] drained by the 8 epilogue warps
-    uint64_t* xbar = full + 7 + 1;               // [1] meeting point of the 8 epilogue warps
-    uint32_t* s_tmem = (uint32_t*)(smem + 128);
-    int* s_abort = (int*)(smem + 132);
+    uint64_t* empty = full + 2;                  // [2] stage free: MMAs done + the epilogue warps
+    uint64_t* tfull = full + 16;                 // [4] a block dot is in tensor memory
+    uint64_t* tempty = full + 20;                // [4] drained and re-armed by the epilogue warps
+    uint64_t* xbar = full + 8;                   // [1] meeting point of the epilogue warps
+    uint64_t* armed = full + 9;                  // [1] every tensor-memory buffer holds the bias
+    uint32_t* s_tmem = (uint32_t*)(smem + 256);
+    int* s_abort = (int*)(smem + 260);
     uint8_t* stages = smem + PF_HEAD;
-    float* s_xchg = (float*)(smem + PF_HEAD + 2 * PF_STAGE);   // [128 tokens][64 rows]
+    float* s_xchg = (float*)(smem + PF_HEAD + 2 * PF_STAGE);   // [96 tokens][64 rows]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int CH = MODE == PF_GATEUP ? 64 : 128;   // output rows per chunk
 
@@ -174,14 +218,17 @@ experts_prefill_kernel(const PrefillArgs A) {
         for (int i = 0; i < 2; i++) {
             pf_bar_init(&full[i], 1);
             pf_bar_init(&empty[i], 1 + PF_EPI_WARPS);
+        }
+        for (int i = 0; i < (int)PF_TBUF; i++) {
             pf_bar_init(&tfull[i], 1);
             pf_bar_init(&tempty[i], PF_EPI_WARPS);
         }
         pf_bar_init(xbar, PF_EPI_WARPS);
+        pf_bar_init(armed, PF_EPI_WARPS);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {   // tensor memory: 256 columns for the whole kernel
+    if (warp == 0) {   // tensor memory: all 512 columns for the whole kernel
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          pf_smem(s_tmem)),
@@ -219,8 +266,8 @@ experts_prefill_kernel(const PrefillArgs A) {
         atomicExch(s_abort, 1);
     };
 
-    if (warp == 0) {
-        // ---------------- copy warp: two bulk copies per stage
+    if (warp == 0 && lane != 1) {
+        // ---------------- copy thread: two bulk copies per stage
         if (lane == 0) {
             uint32_t q = 0;
             bool dead = false;
@@ -238,12 +285,13 @@ experts_prefill_kernel(const PrefillArgs A) {
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA warp: one thread issues one MMA per 32-column block
-        if (lane == 0) {
+    } else if (warp == 0) {
+        // ---------------- MMA thread: one MMA per 32-column block
+        {
             const uint32_t idesc = pf_idesc(kChunkRows, PF_NT);
             uint32_t q = 0, kb = 0;
             bool dead = false;
+            if (!pf_bar_wait(armed, 0)) { give_up(); dead = true; }
             for (int idx = blockIdx.x; idx < total && !dead && !*(volatile int*)s_abort; idx += gridDim.x) {
                 const PfItem it = decode(idx);
                 for (int s = 0; s < it.nst && !dead; s++, q++) {
@@ -252,15 +300,15 @@ experts_prefill_kernel(const PrefillArgs A) {
                     const uint32_t wa = pf_smem(stages + slot * PF_STAGE);
                     const uint32_t xa = wa + PF_W_BYTES;
                     for (int b = 0; b < 8 && !dead; b++, kb++) {
-                        const uint32_t buf = kb & 1;
-                        if (!pf_bar_wait(&tempty[buf], ((kb >> 1) & 1) ^ 1)) { give_up(); dead = true; break; }
+                        const uint32_t buf = kb % PF_TBUF;
+                        if (!pf_bar_wait(&tempty[buf], ((kb / PF_TBUF) & 1) ^ 1)) { give_up(); dead = true; break; }
                         pf_fence_after();
                         // A: rows of the chunk, units 2b and 2b+1: 8-row groups 128 B apart,
                         //    K steps 2048 B apart.  B: tokens, units 2b, 2b+1 of each record:
                         //    8-token groups one record apart, K steps 128 B apart.
                         const uint64_t ad = pf_desc(wa + 2 * b * (kChunkRows * 16), kChunkRows * 16, 128);
                         const uint64_t bd = pf_desc(xa + 2 * b * 128, 128, kActTileBytes);
-                        pf_mma_i8(tmem + buf * PF_NT, ad, bd, idesc);
+                        pf_mma_i8(tmem + buf * PF_TSTRIDE, ad, bd, idesc);
                         pf_commit(&tfull[buf]);
                     }
                     if (!dead) pf_commit(&empty[slot]);   // the stage's operands are no longer read
@@ -269,13 +317,23 @@ experts_prefill_kernel(const PrefillArgs A) {
         }
     } else {
         // ---------------- epilogue warps
-        const int ew = warp - 2;                 // 0..7
+        const int ew = warp - 1;                 // 0..11
         const int quad = warp & 3;               // the tensor-memory lanes this warp may read
-        const int half = ew >> 2;                // which 64 of the 128 token columns
+        const int cg = ew >> 2;                  // which 32 of the 96 token columns
         const int row = 32 * quad + lane;        // chunk row = tensor-memory lane
-        const uint32_t tlane = tmem + ((uint32_t)(32 * quad) << 16);
+        const uint32_t tlane = tmem + ((uint32_t)(32 * quad) << 16) + cg * PF_COLS;
+        constexpr int MAGIC = 0x4B400000;        // the bits of 12582912.0f = 1.5 * 2^23
+        const f32x2 neg_magic = pk(-12582912.0f, -12582912.0f);
         uint32_t q = 0, kb = 0, xphase = 0;
-        // the eight epilogue warps meet (bounded): false when the wait gave up
+        // arm every buffer; the MMA thread's first waits on `tempty` fall through,
+        // so it meets the epilogue warps on `armed` first
+#pragma unroll
+        for (int tb = 0; tb < (int)PF_TBUF; tb++) pf_tmem_st32(tlane + tb * PF_TSTRIDE, MAGIC);
+        pf_tmem_wait_st();
+        pf_fence_before();
+        __syncwarp();
+        if (lane == 0) pf_bar_arrive(armed);
+        // the epilogue warps meet (bounded): false when the wait gave up
         auto meet = [&]() -> bool {
             __syncwarp();
             if (lane == 0) pf_bar_arrive(xbar);
@@ -285,44 +343,43 @@ experts_prefill_kernel(const PrefillArgs A) {
         };
         for (int idx = blockIdx.x; idx < total && !*(volatile int*)s_abort; idx += gridDim.x) {
             const PfItem it = decode(idx);
-            float acc[64];
+            f32x2 acc[PF_COLS / 2];   // tokens cg*32 + 2i, 2i+1
 #pragma unroll
-            for (int i = 0; i < 64; i++) acc[i] = 0.0f;
+            for (int i = 0; i < PF_COLS / 2; i++) acc[i] = 0ull;
             bool ok = true;
             for (int s = 0; s < it.nst && ok; s++, q++) {
                 const uint32_t slot = q & 1;
                 if (!pf_bar_wait(&full[slot], (q >> 1) & 1)) { ok = false; break; }
                 const uint8_t* wst = stages + slot * PF_STAGE;
-                const uint8_t* xst = wst + PF_W_BYTES;
+                const uint8_t* xst = wst + PF_W_BYTES + (cg * (PF_COLS / 8)) * kActTileBytes + kActOffDx;
                 const uint4 dwv = *(const uint4*)(wst + 16 * (kChunkRows * 16) + row * 16);   // 8 f16 scales
                 for (int b = 0; b < 8 && ok; b++, kb++) {
-                    const uint32_t buf = kb & 1;
-                    if (!pf_bar_wait(&tfull[buf], (kb >> 1) & 1)) { ok = false; break; }
+                    const uint32_t buf = kb % PF_TBUF;
+                    if (!pf_bar_wait(&tfull[buf], (kb / PF_TBUF) & 1)) { ok = false; break; }
                     pf_fence_after();
-                    const uint32_t wv = (&dwv.x)[b >> 1];
+                    // drain this warp's 32 columns, re-arm them, hand the buffer back
+                    int v[32];
+                    pf_tmem_ld32(tlane + buf * PF_TSTRIDE, v);
+                    pf_tmem_wait_ld();
+                    pf_tmem_st32(tlane + buf * PF_TSTRIDE, MAGIC);
+                    pf_tmem_wait_st();
+                    pf_fence_before();
+                    __syncwarp();
+                    if (lane == 0) pf_bar_arrive(&tempty[buf]);
+                    const uint32_t wv = (b & 4) ? ((b & 2) ? dwv.w : dwv.z) : ((b & 2) ? dwv.y : dwv.x);
                     const float dw = __half2float(__ushort_as_half((unsigned short)(wv >> (16 * (b & 1)))));
+                    const f32x2 dw2 = pk(dw, dw);
 #pragma unroll
-                    for (int hh = 0; hh < 2; hh++) {
-                        int v[32];
-                        pf_tmem_ld32(tlane + buf * PF_NT + half * 64 + hh * 32, v);
-                        pf_tmem_wait_ld();
-                        if (hh == 1) {   // both loads done: the buffer may be overwritten
-                            pf_fence_before();
-                            __syncwarp();
-                            if (lane == 0) pf_bar_arrive(&tempty[buf]);
-                        }
+                    for (int j = 0; j < 4; j++) {   // a record: 8 tokens, their d_x of block b
+                        const ulonglong2* dxp = (const ulonglong2*)(xst + j * kActTileBytes + b * 32);
+                        const ulonglong2 d01 = dxp[0], d23 = dxp[1];
+                        const f32x2 dxs[4] = {d01.x, d01.y, d23.x, d23.y};
 #pragma unroll
-                        for (int j = 0; j < 4; j++) {   // a record: 8 tokens
-                            const int rec = half * 8 + hh * 4 + j;
-                            const float4* dxp =
-                                (const float4*)(xst + rec * kActTileBytes + kActOffDx + b * 32);
-                            const float4 d0 = dxp[0], d1 = dxp[1];
-                            const float dx[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
-#pragma unroll
-                            for (int t = 0; t < 8; t++) {
-                                const int i = hh * 32 + j * 8 + t;
-                                acc[i] = fmaf(dw, dx[t] * (float)v[j * 8 + t], acc[i]);
-                            }
+                        for (int t = 0; t < 4; t++) {
+                            const int i = j * 4 + t;
+                            // the int32 block dots, exactly, as floats: (12582912 + dot) - 12582912
+                            const f32x2 f = add2(pk(__int_as_float(v[2 * i]), __int_as_float(v[2 * i + 1])), neg_magic);
+                            acc[i] = fma2(dw2, mul2(dxs[t], f), acc[i]);
                         }
                     }
                 }
@@ -333,21 +390,31 @@ experts_prefill_kernel(const PrefillArgs A) {
             }
             if (!ok) { if (lane == 0) give_up(); break; }
             if (it.nst == 0) continue;
-            // ---- the item's outputs: column i of this thread is token half*64 + i
+            // ---- the item's outputs: column i of this thread is token cg*32 + i
+            auto accf = [&](int i) -> float {   // column i of this thread
+                const f32x2 p = acc[i >> 1];
+                return __uint_as_float((uint32_t)((i & 1) ? p >> 32 : p));
+            };
             if (MODE == PF_GATEUP) {
-                // rows 64..127 are up rows: hand them to the threads that own the gate rows
-                if (quad >= 2) {
+                // Thread (row, cg) of quadrants 0-1 holds gate row `row`, its partner in
+                // quadrants 2-3 the up row of the same output, for the same 32 tokens.
+                // Each finishes half of the tokens: the gate thread hands over its gate
+                // values of tokens 16..31, the up thread its up values of tokens 0..15.
+                const int half = quad >> 1;              // 0: gate rows, finishes tokens 0..15
+                const int orow = row & 63;               // output row within the chunk
 #pragma unroll
-                    for (int i = 0; i < 64; i++) s_xchg[(half * 64 + i) * 64 + (row - 64)] = acc[i];
-                }
+                for (int i = 0; i < 16; i++)
+                    s_xchg[(cg * PF_COLS + (half ? i : 16 + i)) * 64 + orow] = accf(half ? i : 16 + i);
                 if (!meet()) { if (lane == 0) give_up(); break; }
-                if (quad < 2) {
-                    const int r = it.chunk * CH + row;   // row of mid
-#pragma unroll 4
-                    for (int i = 0; i < 64; i++) {
-                        const int tok = half * 64 + i;
+                {
+                    const int r = it.chunk * CH + orow;   // row of mid
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const int tok = cg * PF_COLS + 16 * half + i;
                         if (tok >= it.tc) break;          // uniform across the warp
-                        const float gt = acc[i], u = s_xchg[tok * 64 + row];
+                        const float other = s_xchg[tok * 64 + orow];
+                        const float gt = half ? other : accf(i);
+                        const float u = half ? accf(16 + i) : other;
                         // ops.rs:160-167: silu(x) = x * (1 / (1 + exp(-x)))
                         const float v = (gt * __fdiv_rn(1.0f, 1.0f + expf(-gt))) * u;
                         const size_t pos = (size_t)it.pos0 + tok;
@@ -368,11 +435,11 @@ experts_prefill_kernel(const PrefillArgs A) {
                 if (!meet()) { if (lane == 0) give_up(); break; }   // the exchange tile is free again
             } else {
                 const int rows = (it.shared ? A.sh : A.w).rows;
-#pragma unroll 4
-                for (int i = 0; i < 64; i++) {
-                    const int tok = half * 64 + i;
+#pragma unroll
+                for (int i = 0; i < PF_COLS; i++) {
+                    const int tok = cg * PF_COLS + i;
                     if (tok >= it.tc) break;
-                    A.out[((size_t)it.pos0 + tok) * rows + it.chunk * CH + row] = acc[i];
+                    A.out[((size_t)it.pos0 + tok) * rows + it.chunk * CH + row] = accf(i);
                 }
             }
         }
