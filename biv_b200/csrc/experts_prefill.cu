@@ -19,12 +19,15 @@
 // (M = 128 rows, N = 96 tokens, K = 32) into one of four tensor-memory buffers,
 // which the epilogue warps drain (tcgen05.ld), scale by d_w * d_x and add to f32
 // accumulators in registers while the next MMA runs.  The int32 values in tensor
-// memory are the reference's block dots exactly.  To keep the epilogue - the
-// bottleneck: three f32 operations per 32 multiply-adds - short, the MMA
-// accumulates onto tensor memory that the epilogue re-arms with the bit pattern of
-// 1.5 * 2^23 after each drain: the int32 result read as f32 is then
-// 12582912 + dot exactly, one f32 subtraction replaces the int-to-float
-// conversion, and all three operations run two tokens at a time (f32x2).
+// memory are the reference's block dots exactly.  The epilogue is the bottleneck
+// by construction - per 32 multiply-adds of the tensor core it converts one
+// int32 and does two f32 operations - so it is kept short: the conversion runs
+// on the conversion pipe, the scaling two tokens at a time (f32x2) on the FMA
+// pipe, and a buffer is handed back to the MMA thread as soon as it is in
+// registers.  (Letting the MMA accumulate onto a buffer pre-set to the bits of
+// 1.5 * 2^23, so that the int32 read as f32 needs a subtraction instead of a
+// conversion, measured slower: re-arming the buffer with tcgen05.st moves
+// 177 B/clk/SM at most, which costs more than the conversions.)
 // Every wait is bounded; a wait that gives up records BIVMOE_ERR_TIMEOUT, the
 // block leaves its loops, frees its tensor memory and returns.
 #include <cuda_fp16.h>
@@ -126,7 +129,7 @@ __device__ __forceinline__ uint32_t pf_idesc(int m, int n) {
 __device__ __forceinline__ void pf_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, 1, 0;\n\t"   // accumulate onto the buffer the epilogue armed with 1.5 * 2^23
+        "setp.ne.b32 p, 0, 0;\n\t"   // overwrite the buffer: a block dot is not accumulated
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc)
         : "memory");
@@ -159,19 +162,7 @@ __device__ __forceinline__ void pf_tmem_ld32(uint32_t taddr, int (&v)[32]) {
 __device__ __forceinline__ void pf_tmem_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-// arms 32 columns of this warp's lanes with one value
-__device__ __forceinline__ void pf_tmem_st32(uint32_t taddr, int x) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};" ::
-            "r"(taddr),
-        "r"(x)
-        : "memory");
-}
-__device__ __forceinline__ void pf_tmem_wait_st() {
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-// two f32 lanes per instruction (sm_100): d = a * b + c, d = a * b, d = a + b
+// two f32 lanes per instruction (sm_100): d = a * b + c, d = a * b
 typedef unsigned long long f32x2;
 __device__ __forceinline__ f32x2 pk(float lo, float hi) {
     return (f32x2)__float_as_uint(lo) | ((f32x2)__float_as_uint(hi) << 32);
@@ -184,11 +175,6 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
 __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
     f32x2 d;
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
-    f32x2 d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
 
@@ -204,9 +190,8 @@ experts_prefill_kernel(const PrefillArgs A) {
     uint64_t* full = (uint64_t*)smem;            // [2] copies landed
     uint64_t* empty = full + 2;                  // [2] stage free: MMAs done + the epilogue warps
     uint64_t* tfull = full + 16;                 // [4] a block dot is in tensor memory
-    uint64_t* tempty = full + 20;                // [4] drained and re-armed by the epilogue warps
+    uint64_t* tempty = full + 20;                // [4] drained by the epilogue warps
     uint64_t* xbar = full + 8;                   // [1] meeting point of the epilogue warps
-    uint64_t* armed = full + 9;                  // [1] every tensor-memory buffer holds the bias
     uint32_t* s_tmem = (uint32_t*)(smem + 256);
     int* s_abort = (int*)(smem + 260);
     uint8_t* stages = smem + PF_HEAD;
@@ -224,7 +209,6 @@ experts_prefill_kernel(const PrefillArgs A) {
             pf_bar_init(&tempty[i], PF_EPI_WARPS);
         }
         pf_bar_init(xbar, PF_EPI_WARPS);
-        pf_bar_init(armed, PF_EPI_WARPS);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -291,7 +275,6 @@ experts_prefill_kernel(const PrefillArgs A) {
             const uint32_t idesc = pf_idesc(kChunkRows, PF_NT);
             uint32_t q = 0, kb = 0;
             bool dead = false;
-            if (!pf_bar_wait(armed, 0)) { give_up(); dead = true; }
             for (int idx = blockIdx.x; idx < total && !dead && !*(volatile int*)s_abort; idx += gridDim.x) {
                 const PfItem it = decode(idx);
                 for (int s = 0; s < it.nst && !dead; s++, q++) {
@@ -322,17 +305,7 @@ experts_prefill_kernel(const PrefillArgs A) {
         const int cg = ew >> 2;                  // which 32 of the 96 token columns
         const int row = 32 * quad + lane;        // chunk row = tensor-memory lane
         const uint32_t tlane = tmem + ((uint32_t)(32 * quad) << 16) + cg * PF_COLS;
-        constexpr int MAGIC = 0x4B400000;        // the bits of 12582912.0f = 1.5 * 2^23
-        const f32x2 neg_magic = pk(-12582912.0f, -12582912.0f);
         uint32_t q = 0, kb = 0, xphase = 0;
-        // arm every buffer; the MMA thread's first waits on `tempty` fall through,
-        // so it meets the epilogue warps on `armed` first
-#pragma unroll
-        for (int tb = 0; tb < (int)PF_TBUF; tb++) pf_tmem_st32(tlane + tb * PF_TSTRIDE, MAGIC);
-        pf_tmem_wait_st();
-        pf_fence_before();
-        __syncwarp();
-        if (lane == 0) pf_bar_arrive(armed);
         // the epilogue warps meet (bounded): false when the wait gave up
         auto meet = [&]() -> bool {
             __syncwarp();
@@ -357,12 +330,10 @@ experts_prefill_kernel(const PrefillArgs A) {
                     const uint32_t buf = kb % PF_TBUF;
                     if (!pf_bar_wait(&tfull[buf], (kb / PF_TBUF) & 1)) { ok = false; break; }
                     pf_fence_after();
-                    // drain this warp's 32 columns, re-arm them, hand the buffer back
+                    // drain this warp's 32 columns and hand the buffer back
                     int v[32];
                     pf_tmem_ld32(tlane + buf * PF_TSTRIDE, v);
                     pf_tmem_wait_ld();
-                    pf_tmem_st32(tlane + buf * PF_TSTRIDE, MAGIC);
-                    pf_tmem_wait_st();
                     pf_fence_before();
                     __syncwarp();
                     if (lane == 0) pf_bar_arrive(&tempty[buf]);
@@ -377,8 +348,8 @@ experts_prefill_kernel(const PrefillArgs A) {
 #pragma unroll
                         for (int t = 0; t < 4; t++) {
                             const int i = j * 4 + t;
-                            // the int32 block dots, exactly, as floats: (12582912 + dot) - 12582912
-                            const f32x2 f = add2(pk(__int_as_float(v[2 * i]), __int_as_float(v[2 * i + 1])), neg_magic);
+                            // the int32 block dots, exact as floats (below 2^24)
+                            const f32x2 f = pk(__int2float_rn(v[2 * i]), __int2float_rn(v[2 * i + 1]));
                             acc[i] = fma2(dw2, mul2(dxs[t], f), acc[i]);
                         }
                     }
