@@ -24,7 +24,8 @@ ROUTE_NOALLOC_MAX_LOGITS = 512 * 257
 SYMBOLS = ["bivmoe_create", "bivmoe_destroy", "bivmoe_forward", "bivmoe_forward_host", "bivmoe_forward_profile",
            "bivmoe_set_post_norm", "bivmoe_forward_stack", "bivmoe_tap", "bivmoe_tap_block_dots",
            "bivmoe_route_noalloc", "bivmoe_numerics", "bivmoe_memory", "bivmoe_launch_count", "bivmoe_last_error",
-           "bivmoe_global_error"]
+           "bivmoe_global_error", "bivmoe_ep_create", "bivmoe_ep_route", "bivmoe_ep_shared",
+           "bivmoe_ep_experts", "bivmoe_ep_combine", "bivmoe_ep_status"]
 
 
 class BivMoeError(RuntimeError):
@@ -75,6 +76,12 @@ def lib():
         L.bivmoe_tap.argtypes = [vp, i32, vp, C.c_size_t]
         L.bivmoe_tap_block_dots.argtypes = [vp, i32, i32, i32, i32, vp]
         L.bivmoe_route_noalloc.argtypes = [vp, vp, i32, vp, vp, vp]
+        L.bivmoe_ep_create.argtypes = [C.POINTER(Desc), i32, i32, i32, C.POINTER(vp)]
+        L.bivmoe_ep_route.argtypes = [vp, vp, i32, vp, vp, vp]
+        L.bivmoe_ep_shared.argtypes = [vp, vp, vp]
+        L.bivmoe_ep_experts.argtypes = [vp, vp, vp, i32, vp, vp]
+        L.bivmoe_ep_combine.argtypes = [vp, vp, vp, i32, i32, vp]
+        L.bivmoe_ep_status.argtypes = [vp, vp]
         L.bivmoe_numerics.argtypes = [vp, C.c_char_p, C.c_size_t]
         L.bivmoe_memory.argtypes = [vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
         L.bivmoe_launch_count.restype = C.c_uint64

@@ -71,16 +71,26 @@ struct bivmoe_layer {
         int seen = 0;            // identical calls seen; the graph is built on the second
     } graph;
     int prefill_min = 0;   // set at create when the tcgen05 kernels support the layer's types
+    // expert parallelism (bivmoe_ep_create): this rank's experts are global ids
+    // ep_rank * n_local .. +n_local; `ws` serves the rank's own tokens (routing over all
+    // experts, the shared expert), `ws_owner` the rows received for the local experts
+    int ep_rank = 0, ep_world = 1, n_local = 0, max_recv = 0, ep_n = 0;
+    Workspace ws_owner{};
+    int32_t* ep_compact_start = nullptr;   // [n_expert + 1]
+    int32_t* ep_compact_pos = nullptr;     // [max_tokens * k] pair -> slot among the sent rows
     bool use_graph = true;
     int launches_per_forward = 0;
     std::string error, device_name;
     std::vector<void*> allocs;
 };
 
-static void layout_workspace(bivmoe_layer* L, Arena& a) {
-    const size_t N = (size_t)L->max_tokens, P = N * L->k, ne = L->n_expert, e = L->e;
+// One workspace: `N` rows of `k` pairs over `ne` experts.  `routed_rows` false: only
+// the shared group's positions get activation buffers (the home side of expert
+// parallelism, whose routed rows are computed elsewhere).
+static void layout_one(bivmoe_layer* L, Arena& a, Workspace& w, size_t N, size_t k, size_t ne,
+                       bool routed_rows) {
+    const size_t P = N * k, e = L->e;
     const size_t mid = std::max(L->ff, L->ff_sh);
-    Workspace& w = L->ws;
     w.logits = a.take<float>(N * (ne + 1));
     w.ids = a.take<int32_t>(P);
     w.weights = a.take<float>(P);
@@ -105,7 +115,7 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
     w.status = a.take<int32_t>(4);
     // positions: the tokens (shared group), then the routed groups, each padded to 8
     // (+kPrefillTile: a tile of the tcgen05 kernels copies that many positions from its first one)
-    const size_t R = ((N + 7) / 8) * 8 + P + 8 * ne + 8 + kPrefillTile;
+    const size_t R = ((N + 7) / 8) * 8 + (routed_rows ? P + 8 * ne : 0) + 8 + kPrefillTile;
     w.act_rows = (int)R;
     const bool qact = !type_uses_f32_act(L->gate_up.ty) || (L->has_shared && !type_uses_f32_act(L->sh_gate_up.ty));
     const bool fact = type_uses_f32_act(L->gate_up.ty) || (L->has_shared && type_uses_f32_act(L->sh_gate_up.ty));
@@ -116,6 +126,17 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
     w.mid_t = a.take<uint8_t>(qmid ? (mid / 256) * (R / 8) * kActTileBytes : 0);
     w.pair_out = a.take<float>(R * e);
     w.h_norm = a.take<float>(N * e);
+}
+
+static void layout_workspace(bivmoe_layer* L, Arena& a) {
+    if (L->ep_world <= 1) {
+        layout_one(L, a, L->ws, (size_t)L->max_tokens, (size_t)L->k, (size_t)L->n_expert, true);
+        return;
+    }
+    layout_one(L, a, L->ws, (size_t)L->max_tokens, (size_t)L->k, (size_t)L->n_expert, false);
+    layout_one(L, a, L->ws_owner, (size_t)L->max_recv, 1, (size_t)L->n_local, true);
+    L->ep_compact_start = a.take<int32_t>((size_t)L->n_expert + 1);
+    L->ep_compact_pos = a.take<int32_t>((size_t)L->max_tokens * L->k);
 }
 
 #define CU(call)                                                                          \
@@ -217,10 +238,18 @@ void bivmoe_destroy(bivmoe_layer* L) {
     delete L;
 }
 
-int bivmoe_create(const bivmoe_desc* d, bivmoe_layer** out) {
+static int create_impl(const bivmoe_desc* d, int ep_rank, int ep_world, int max_recv,
+                       bivmoe_layer** out) {
     std::string* errp = nullptr;
     if (out) *out = nullptr;
     if (!d || !out) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null descriptor or output");
+    if (ep_world < 1 || ep_rank < 0 || ep_rank >= ep_world)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "rank %d outside 0..%d", ep_rank, ep_world);
+    if (ep_world > 1 && (d->n_expert % ep_world || max_recv <= 0))
+        return set_err(errp, BIVMOE_ERR_ARGUMENT,
+                       "%d experts do not split over %d ranks, or max_recv_rows %d is not positive",
+                       d->n_expert, ep_world, max_recv);
+    const int n_local = d->n_expert / ep_world;
     if (d->n_embd <= 0 || d->n_expert <= 0 || d->n_ff_exp <= 0 || d->max_tokens <= 0 || !d->router)
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "non-positive dimension or null router");
     // model.rs:108-112: 1 <= n_expert_used <= n_expert
@@ -232,9 +261,9 @@ int bivmoe_create(const bivmoe_desc* d, bivmoe_layer** out) {
     if (d->n_embd % 256)
         return set_err(errp, BIVMOE_ERR_UNSUPPORTED, "n_embd %d is not a multiple of 256", d->n_embd);
     int rc;
-    if ((rc = check_stack(errp, "ffn_gate_exps", d->gate, d->n_embd, d->n_ff_exp, d->n_expert, false)) ||
-        (rc = check_stack(errp, "ffn_up_exps", d->up, d->n_embd, d->n_ff_exp, d->n_expert, false)) ||
-        (rc = check_stack(errp, "ffn_down_exps", d->down, d->n_ff_exp, d->n_embd, d->n_expert, true)))
+    if ((rc = check_stack(errp, "ffn_gate_exps", d->gate, d->n_embd, d->n_ff_exp, n_local, false)) ||
+        (rc = check_stack(errp, "ffn_up_exps", d->up, d->n_embd, d->n_ff_exp, n_local, false)) ||
+        (rc = check_stack(errp, "ffn_down_exps", d->down, d->n_ff_exp, d->n_embd, n_local, true)))
         return rc;
     if (d->gate.ggml_type != d->up.ggml_type)
         return set_err(errp, BIVMOE_ERR_UNSUPPORTED, "gate and up of different types");
@@ -263,6 +292,7 @@ int bivmoe_create(const bivmoe_desc* d, bivmoe_layer** out) {
     L->e = d->n_embd; L->n_expert = d->n_expert; L->k = d->n_expert_used;
     L->ff = d->n_ff_exp; L->ff_sh = d->n_ff_shexp; L->max_tokens = d->max_tokens;
     L->has_shared = shared;
+    L->ep_rank = ep_rank; L->ep_world = ep_world; L->n_local = n_local; L->max_recv = max_recv;
     auto fail = [&](int code) { g_error = g_error.empty() ? L->error : g_error; bivmoe_destroy(L); return code; };
     if ((rc = upload_tiles(L, errp, &d->gate, &d->up, 64, &L->gate_up)) ||
         (rc = upload_tiles(L, errp, &d->down, nullptr, 128, &L->down)))
@@ -306,11 +336,21 @@ int bivmoe_create(const bivmoe_desc* d, bivmoe_layer** out) {
     real.base = L->ws_mem;
     layout_workspace(L, real);
     if ((ce = cudaMemset(L->ws.status, 0, 16)) != cudaSuccess) return cu_fail(ce, "status");
+    if (ep_world > 1 && (ce = cudaMemset(L->ws_owner.status, 0, 16)) != cudaSuccess)
+        return cu_fail(ce, "status");
     if ((ce = cudaStreamCreateWithFlags(&L->own_stream, cudaStreamNonBlocking)) != cudaSuccess)
         return cu_fail(ce, "stream");
     if ((ce = cudaDeviceSynchronize()) != cudaSuccess) return cu_fail(ce, "upload");
     *out = L;
     return BIVMOE_OK;
+}
+
+int bivmoe_create(const bivmoe_desc* d, bivmoe_layer** out) { return create_impl(d, 0, 1, 0, out); }
+
+int bivmoe_ep_create(const bivmoe_desc* d, int32_t ep_rank, int32_t ep_world, int32_t max_recv_rows,
+                     bivmoe_layer** out) {
+    if (ep_world == 1) return create_impl(d, 0, 1, 0, out);
+    return create_impl(d, ep_rank, ep_world, max_recv_rows, out);
 }
 
 int bivmoe_set_post_norm(bivmoe_layer* L, const float* w, float eps) {
@@ -333,6 +373,9 @@ static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int 
     if (!h || !out) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null activation pointer");
     if (n < 0 || n > L->max_tokens)
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens = %d", n, L->max_tokens);
+    if (L->ep_world > 1)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT,
+                       "the layer holds 1/%d of the experts: use the bivmoe_ep_* steps", L->ep_world);
     L->last_n = n;
     if (n == 0) return BIVMOE_OK;
     LaunchCfg c{stream, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh, L->has_shared ? 1 : 0, L->sm_count};
@@ -351,7 +394,7 @@ static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int 
     if (c.prefill_min > 0)
         CU(launch_experts_prefill(c, L->gate_up, L->down, L->sh_gate_up, L->sh_down, L->ws));
     mark(c, EV_DOWN);
-    CU(launch_combine(c, L->ws, out, accumulate));
+    CU(launch_combine(c, L->ws, L->ws.pair_out, L->ws.pos_of, out, accumulate));
     mark(c, EV_COMBINE);
     return BIVMOE_OK;
 }
@@ -415,6 +458,120 @@ int bivmoe_forward(bivmoe_layer* L, const float* h_dev, float* out_dev, int32_t 
         return set_err(&L->error, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens = %d", n,
                        L->max_tokens);
     return forward_graphed(L, h_dev, out_dev, n, accumulate, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------
+// expert parallelism: the device steps between the caller's two exchanges
+
+static int ep_check(bivmoe_layer* L, const char* what) {
+    if (!L) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer");
+    if (L->ep_world <= 1)
+        return set_err(&L->error, BIVMOE_ERR_ARGUMENT, "%s: the layer was not made by bivmoe_ep_create "
+                       "with more than one rank", what);
+    return BIVMOE_OK;
+}
+
+int bivmoe_ep_route(bivmoe_layer* L, const float* h_dev, int32_t n, float* send_rows_dev,
+                    int32_t* send_counts_dev, void* stream) {
+    if (int rc = ep_check(L, "bivmoe_ep_route")) return rc;
+    std::string* errp = &L->error;
+    if (!h_dev || !send_rows_dev || !send_counts_dev)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "null pointer");
+    if (n < 0 || n > L->max_tokens)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens = %d", n, L->max_tokens);
+    cudaStream_t s = (cudaStream_t)stream;
+    L->ep_n = n;
+    L->last_n = n;
+    if (n == 0) {
+        CU(cudaMemsetAsync(send_counts_dev, 0, (size_t)L->n_expert * 4, s));
+        return BIVMOE_OK;
+    }
+    LaunchCfg c{s, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh, L->has_shared ? 1 : 0, L->sm_count};
+    // the shared expert's group alone is computed here; its size decides its kernel
+    c.prefill_min = L->prefill_min;
+    CU(launch_router(c, L->router, h_dev, L->ws));
+    CU(launch_route_topk(c, L->ws));
+    CU(launch_sort(c, L->ws));
+    CU(launch_ep_gather(c, h_dev, L->ws, L->ep_compact_start, L->ep_compact_pos, send_rows_dev,
+                        send_counts_dev));
+    return BIVMOE_OK;
+}
+
+int bivmoe_ep_shared(bivmoe_layer* L, const float* h_dev, void* stream) {
+    if (int rc = ep_check(L, "bivmoe_ep_shared")) return rc;
+    std::string* errp = &L->error;
+    const int n = L->ep_n;
+    if (!L->has_shared || n == 0) return BIVMOE_OK;
+    if (!h_dev) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    LaunchCfg c{s, n, 0, L->e, L->n_expert, L->ff, L->ff_sh, 1, L->sm_count};   // k = 0: no pair rows
+    c.prefill_min = L->prefill_min;
+    c.only_shared = 1;
+    CU(launch_dispatch(c, h_dev, L->ws, L->ws.act_t != nullptr && !type_uses_f32_act(L->sh_gate_up.ty),
+                       L->ws.act_f != nullptr && type_uses_f32_act(L->sh_gate_up.ty)));
+    c.k = L->k;
+    CU(launch_experts(c, L->gate_up, L->down, L->sh_gate_up, L->sh_down, L->ws));
+    if (c.prefill_min > 0)
+        CU(launch_experts_prefill(c, L->gate_up, L->down, L->sh_gate_up, L->sh_down, L->ws));
+    return BIVMOE_OK;
+}
+
+int bivmoe_ep_experts(bivmoe_layer* L, const float* recv_rows_dev, const int32_t* recv_counts_dev,
+                      int32_t m, float* out_rows_dev, void* stream) {
+    if (int rc = ep_check(L, "bivmoe_ep_experts")) return rc;
+    std::string* errp = &L->error;
+    if (m < 0 || m > L->max_recv)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "m = %d outside 0..max_recv_rows = %d", m, L->max_recv);
+    if (m == 0) return BIVMOE_OK;
+    if (!recv_rows_dev || !recv_counts_dev || !out_rows_dev)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "null pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    // the received rows are a k = 1 routing result over the local experts, no shared expert
+    LaunchCfg c{s, m, 1, L->e, L->n_local, L->ff, 0, 0, L->sm_count};
+    c.prefill_min = L->prefill_min;
+    const Workspace& w = L->ws_owner;
+    const DevTiles none{};
+    CU(launch_ep_expand(c, recv_counts_dev, L->ep_world, w));
+    CU(launch_sort(c, w));
+    CU(launch_dispatch(c, recv_rows_dev, w, w.act_t != nullptr && !type_uses_f32_act(L->gate_up.ty),
+                       w.act_f != nullptr && type_uses_f32_act(L->gate_up.ty)));
+    CU(launch_experts(c, L->gate_up, L->down, none, none, w));
+    if (c.prefill_min > 0) CU(launch_experts_prefill(c, L->gate_up, L->down, none, none, w));
+    CU(launch_combine(c, w, w.pair_out, w.pos_of, out_rows_dev, 0));   // weight 1: rows in arrival order
+    return BIVMOE_OK;
+}
+
+int bivmoe_ep_combine(bivmoe_layer* L, const float* returned_rows_dev, float* out_dev, int32_t n,
+                      int32_t accumulate, void* stream) {
+    if (int rc = ep_check(L, "bivmoe_ep_combine")) return rc;
+    std::string* errp = &L->error;
+    if (n != L->ep_n)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d, but bivmoe_ep_route ran on %d rows", n, L->ep_n);
+    if (n == 0) return BIVMOE_OK;
+    if (!returned_rows_dev || !out_dev) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null pointer");
+    LaunchCfg c{(cudaStream_t)stream, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh,
+                L->has_shared ? 1 : 0, L->sm_count};
+    CU(launch_combine(c, L->ws, returned_rows_dev, L->ep_compact_pos, out_dev, accumulate));
+    return BIVMOE_OK;
+}
+
+int bivmoe_ep_status(bivmoe_layer* L, void* stream) {
+    if (int rc = ep_check(L, "bivmoe_ep_status")) return rc;
+    std::string* errp = &L->error;
+    cudaStream_t s = (cudaStream_t)stream;
+    int32_t st[2] = {0, 0};
+    CU(cudaMemcpyAsync(&st[0], L->ws.status, 4, cudaMemcpyDeviceToHost, s));
+    CU(cudaMemcpyAsync(&st[1], L->ws_owner.status, 4, cudaMemcpyDeviceToHost, s));
+    CU(cudaStreamSynchronize(s));
+    if (st[0] || st[1]) {
+        cudaMemsetAsync(L->ws.status, 0, 16, s);
+        cudaMemsetAsync(L->ws_owner.status, 0, 16, s);
+        const int code = st[0] ? st[0] : st[1];
+        return set_err(errp, code, code == BIVMOE_ERR_TIMEOUT
+                                       ? "a device-side bounded wait gave up"
+                                       : "the received-row count differs from the sum of the count matrix");
+    }
+    return BIVMOE_OK;
 }
 
 int bivmoe_forward_profile(bivmoe_layer* L, const float* h_dev, float* out_dev, int32_t n,

@@ -140,6 +140,7 @@ struct LaunchCfg {
     int n, k, e, n_expert, ff, ff_sh, has_shared;
     int sm_count;
     int prefill_min = 0;         // groups with at least this many tokens go to the tcgen05 kernels (0: none)
+    int only_shared = 0;         // expert launches cover the shared expert's group alone (expert parallelism)
     cudaEvent_t* ev = nullptr;   // optional: events recorded between the stages (profiling call)
 };
 enum { EV_START = 0, EV_ROUTER, EV_TOPK, EV_SORT, EV_QUANT, EV_GATEUP, EV_DOWN, EV_COMBINE, EV_COUNT };
@@ -156,7 +157,15 @@ cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace&
                             bool f32);
 cudaError_t launch_experts(const LaunchCfg& c, const DevTiles& gate_up, const DevTiles& down,
                            const DevTiles& sh_gate_up, const DevTiles& sh_down, const Workspace& ws);
-cudaError_t launch_combine(const LaunchCfg& c, const Workspace& ws, float* out, int accumulate);
+// `routed_rows` [.][e] indexed by `routed_pos[pair]`: the workspace's pair_out and pos_of,
+// or under expert parallelism the rows the owners returned and their compact slots
+cudaError_t launch_combine(const LaunchCfg& c, const Workspace& ws, const float* routed_rows,
+                           const int32_t* routed_pos, float* out, int accumulate);
+cudaError_t launch_ep_gather(const LaunchCfg& c, const float* h, const Workspace& ws,
+                             int32_t* compact_start, int32_t* compact_pos, float* send_rows,
+                             int32_t* counts_out);
+cudaError_t launch_ep_expand(const LaunchCfg& c, const int32_t* recv_counts, int world,
+                             const Workspace& ws);
 cudaError_t launch_rms_norm(const LaunchCfg& c, const float* x, const float* w, float eps,
                             float* out);
 cudaError_t launch_repack(const DevTiles& dst, const uint8_t* gguf_rows, int tile_base,

@@ -782,7 +782,9 @@ cudaError_t launch_experts(const LaunchCfg& c, const DevTiles& gate_up, const De
         G.tiles_mode = mode;
         return launch_typed<MODE_GATEUP>(ty, c, G);
     };
-    if (fused || !c.has_shared) {
+    if (c.only_shared) {
+        err = gateup(2, 1, sh_gate_up.ty, sh_down.ty);
+    } else if (fused || !c.has_shared) {
         err = gateup(0, 0, gate_up.ty, down.ty);
     } else {
         err = gateup(1, 0, gate_up.ty, down.ty);
@@ -802,7 +804,9 @@ cudaError_t launch_experts(const LaunchCfg& c, const DevTiles& gate_up, const De
         D.tiles_mode = mode;
         return launch_typed<MODE_DOWN>(ty, c, D);
     };
-    if (fused || !c.has_shared) {
+    if (c.only_shared) {
+        err = downp(2, 3, sh_down.ty);
+    } else if (fused || !c.has_shared) {
         err = downp(0, 2, down.ty);
     } else {
         err = downp(1, 2, down.ty);

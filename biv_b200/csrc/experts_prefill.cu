@@ -458,7 +458,7 @@ cudaError_t launch_experts_prefill(const LaunchCfg& c, const DevTiles& gate_up, 
     A.status = ws.status;
     A.n_expert = c.n_expert;
     A.act_rows = ws.act_rows;
-    A.tiles_mode = 0;
+    A.tiles_mode = c.only_shared ? 2 : 0;
     PrefillArgs G = A;
     G.w = gate_up; G.sh = sh_gate_up;
     G.x_t = ws.act_t; G.out = ws.mid; G.out_t = ws.mid_t;

@@ -114,8 +114,9 @@ cudaError_t launch_rms_norm(const LaunchCfg& c, const float* x, const float* w, 
 constexpr int CB_THREADS = 256, CB_MAX_K = 32;
 
 __global__ void __launch_bounds__(CB_THREADS)
-combine_kernel(Workspace ws, float* __restrict__ out, int n, int k, int e, int n_expert,
-               int has_shared, int accumulate) {
+combine_kernel(Workspace ws, const float* __restrict__ routed_rows,
+               const int32_t* __restrict__ routed_pos, float* __restrict__ out, int n, int k, int e,
+               int n_expert, int has_shared, int accumulate) {
     __shared__ int s_pos[CB_MAX_K];
     __shared__ float s_w[CB_MAX_K];
     __shared__ float s_gate;
@@ -125,7 +126,7 @@ combine_kernel(Workspace ws, float* __restrict__ out, int n, int k, int e, int n
         const int my = ws.ids[(size_t)t * k + threadIdx.x];
         int rank = 0;
         for (int j = 0; j < k; j++) rank += ws.ids[(size_t)t * k + j] < my;
-        s_pos[rank] = ws.pos_of[(size_t)t * k + threadIdx.x];
+        s_pos[rank] = routed_pos[(size_t)t * k + threadIdx.x];
         s_w[rank] = ws.weights[(size_t)t * k + threadIdx.x];
     }
     if (threadIdx.x == 32 && has_shared) {
@@ -137,7 +138,7 @@ combine_kernel(Workspace ws, float* __restrict__ out, int n, int k, int e, int n
     if (c4 * 4 >= e) return;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int j = 0; j < k; j++) {
-        const float4 y = *(const float4*)(ws.pair_out + (size_t)s_pos[j] * e + c4 * 4);
+        const float4 y = *(const float4*)(routed_rows + (size_t)s_pos[j] * e + c4 * 4);
         const float w = s_w[j];
         acc.x = fmaf(w, y.x, acc.x); acc.y = fmaf(w, y.y, acc.y);
         acc.z = fmaf(w, y.z, acc.z); acc.w = fmaf(w, y.w, acc.w);
@@ -156,11 +157,12 @@ combine_kernel(Workspace ws, float* __restrict__ out, int n, int k, int e, int n
     *o = acc;
 }
 
-cudaError_t launch_combine(const LaunchCfg& c, const Workspace& ws, float* out, int accumulate) {
+cudaError_t launch_combine(const LaunchCfg& c, const Workspace& ws, const float* routed_rows,
+                           const int32_t* routed_pos, float* out, int accumulate) {
     if (c.k > CB_MAX_K || c.e % 4) return cudaErrorInvalidValue;
     dim3 grid(c.n, (c.e / 4 + CB_THREADS - 1) / CB_THREADS);
-    combine_kernel<<<grid, CB_THREADS, 0, c.stream>>>(ws, out, c.n, c.k, c.e, c.n_expert,
-                                                      c.has_shared, accumulate);
+    combine_kernel<<<grid, CB_THREADS, 0, c.stream>>>(ws, routed_rows, routed_pos, out, c.n, c.k, c.e,
+                                                      c.n_expert, c.has_shared, accumulate);
     count_launch();
     return cudaGetLastError();
 }

@@ -1,0 +1,218 @@
+"""Expert parallelism: one process per GPU, experts sharded ``n_expert / W`` per
+rank, token rows exchanged with two all-to-alls (``torch.distributed``: NCCL
+over NVLink between GPUs; gloo between CPU processes in the tests).
+
+The reference has no multi-device path (one ``MTLDevice``,
+engine/src/metal/mod.rs:450-462; the CPU backend loops over the experts in one
+process, engine/src/model.rs:875), so this module mirrors nothing there: it
+runs ``Model::moe`` (model.rs:861-898) split at its two natural seams - after
+routing (rows leave for the ranks that own their experts) and after the expert
+products (outputs return to the rows' home rank for the weighted sum).
+
+``ep_plan`` and ``ep_pass`` are the host logic, independent of where the rows
+live; the arithmetic is behind a ``steps`` object - ``DeviceSteps`` below calls
+the ``bivmoe_ep_*`` entry points of ``libbivmoe.so`` and is the only
+implementation this package ships.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, replace
+from typing import List, Optional
+
+import numpy as np
+
+from . import capi
+from .workloads import ExpertStack, MoeLayer
+
+
+@dataclass
+class EpPlan:
+    """What one rank sends and receives, from everyone's per-expert row counts."""
+    send_splits: List[int]      # rows this rank sends to each rank (its rows are in expert order)
+    recv_splits: List[int]      # rows it receives from each rank
+    recv_counts: np.ndarray     # int32 [W][n_local]: rows from source s for local expert x
+    m: int                      # rows received in all
+
+
+def ep_plan(counts_all: np.ndarray, rank: int) -> EpPlan:
+    """``counts_all`` [W][n_expert]: row s = how many rows rank s has for every
+    expert (global id).  Rank r owns experts ``[r * n_local, (r + 1) * n_local)``."""
+    W, E = counts_all.shape
+    assert E % W == 0 and 0 <= rank < W
+    nl = E // W
+    per_dest = counts_all.reshape(W, W, nl).sum(axis=2)         # [source][dest]
+    recv_counts = np.ascontiguousarray(counts_all[:, rank * nl:(rank + 1) * nl], dtype=np.int32)
+    return EpPlan([int(v) for v in per_dest[rank]], [int(v) for v in per_dest[:, rank]],
+                  recv_counts, int(recv_counts.sum()))
+
+
+def local_experts(layer: MoeLayer, rank: int, world: int) -> MoeLayer:
+    """The layer as rank ``rank`` holds it: its slice of every ``*_exps`` stack (a
+    byte range of the same tensor - experts are outermost, model.rs:353), the
+    router and the shared expert whole."""
+    assert layer.n_expert % world == 0
+    nl = layer.n_expert // world
+
+    def cut(st: ExpertStack) -> ExpertStack:
+        return ExpertStack(st.ty, st.cols, st.rows, nl, st.data, st.stride,
+                           st.offset + rank * nl * st.stride)
+    return replace(layer, gate=cut(layer.gate), up=cut(layer.up), down=cut(layer.down))
+
+
+class TorchComm:
+    """The two collectives of a pass over a ``torch.distributed`` process group
+    (NCCL between GPUs, gloo between CPU processes)."""
+
+    def __init__(self, group=None):
+        self.group = group
+
+    def all_gather(self, out_flat, piece):
+        import torch.distributed as dist
+        dist.all_gather_into_tensor(out_flat, piece, group=self.group)
+
+    def all_to_all(self, recv, send, recv_splits, send_splits):
+        import torch.distributed as dist
+        dist.all_to_all_single(recv, send, recv_splits, send_splits, group=self.group)
+
+
+def ep_pass(steps, h, out, accumulate: bool, comm=None):
+    """One pass of the layer over this rank's rows ``h`` [n, n_embd] into ``out``.
+
+    ``steps`` supplies ``rank``, ``world``, ``n_expert``, ``k`` and
+    ``route(h) -> (send_rows, send_counts)``, ``shared(h)``,
+    ``rows(count) -> tensor [count, n_embd]`` (scratch, two distinct buffers in turn),
+    ``experts(recv_rows, recv_counts, m) -> out_rows`` and
+    ``combine(returned_rows, out, accumulate)``; ``comm`` the two collectives
+    (``TorchComm`` over the default process group when None)."""
+    import torch
+    comm = comm or TorchComm()
+    W, rank = steps.world, steps.rank
+    send_rows, send_counts = steps.route(h)
+    flat = torch.empty((W * steps.n_expert,), dtype=torch.int32, device=send_counts.device)
+    comm.all_gather(flat, send_counts)
+    counts_all = flat.view(W, steps.n_expert)
+    counts_host = counts_all.cpu().numpy()          # the one host synchronisation of the pass
+    plan = ep_plan(counts_host, rank)
+    steps.shared(h)                                  # overlaps the exchange where it can
+    recv_rows = steps.rows(plan.m)
+    comm.all_to_all(recv_rows, send_rows, plan.recv_splits, plan.send_splits)
+    nl = steps.n_expert // W
+    recv_counts = counts_all[:, rank * nl:(rank + 1) * nl].contiguous()
+    out_rows = steps.experts(recv_rows, recv_counts, plan.m)
+    returned = steps.rows(send_rows.shape[0])
+    comm.all_to_all(returned, out_rows, plan.send_splits, plan.recv_splits)
+    steps.combine(returned, out, accumulate)
+    return plan
+
+
+class DeviceSteps:
+    """The ``bivmoe_ep_*`` entry points on one B200 (torch for memory and streams)."""
+
+    def __init__(self, layer: MoeLayer, max_tokens: int, rank: int, world: int, device: int = 0,
+                 max_recv_rows: Optional[int] = None):
+        import torch
+        from .moe import fill_desc
+        self._h = None
+        self.rank, self.world, self.device = rank, world, device
+        self.n_embd, self.n_expert, self.k = layer.n_embd, layer.n_expert, layer.n_expert_used
+        self.max_tokens = max_tokens
+        nl = layer.n_expert // world
+        self.max_recv = max_recv_rows or world * max_tokens * min(self.k, nl)
+        local = local_experts(layer, rank, world)
+        d, self._keep = fill_desc(local, max_tokens, device)
+        d.n_expert = layer.n_expert
+        h = C.c_void_p()
+        capi.check(capi.lib().bivmoe_ep_create(C.byref(d), rank, world, self.max_recv, C.byref(h)))
+        self._h = h
+        dev = torch.device("cuda", device)
+        self._send = torch.empty((max_tokens * self.k, self.n_embd), dtype=torch.float32, device=dev)
+        self._counts = torch.empty((self.n_expert,), dtype=torch.int32, device=dev)
+        self._bufs = [torch.empty((max(self.max_recv, max_tokens * self.k), self.n_embd),
+                                  dtype=torch.float32, device=dev) for _ in range(2)]
+        self._out_rows = torch.empty((self.max_recv, self.n_embd), dtype=torch.float32, device=dev)
+        self._turn = 0
+        self._side = torch.cuda.Stream(device=dev)
+        self._n = 0
+
+    def close(self):
+        if self._h is not None:
+            capi.lib().bivmoe_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _stream(self, s=None):
+        import torch
+        s = s or torch.cuda.current_stream(self.device)
+        return C.c_void_p(s.cuda_stream)
+
+    def route(self, h):
+        import torch
+        assert h.is_cuda and h.dtype == torch.float32 and h.is_contiguous()
+        n = h.numel() // self.n_embd
+        self._n = n
+        capi.check(capi.lib().bivmoe_ep_route(self._h, C.c_void_p(h.data_ptr()), n,
+                                              C.c_void_p(self._send.data_ptr()),
+                                              C.c_void_p(self._counts.data_ptr()), self._stream()),
+                   self._h)
+        return self._send[:n * self.k], self._counts
+
+    def shared(self, h):
+        import torch
+        cur = torch.cuda.current_stream(self.device)
+        self._side.wait_stream(cur)
+        capi.check(capi.lib().bivmoe_ep_shared(self._h, C.c_void_p(h.data_ptr()),
+                                               self._stream(self._side)), self._h)
+
+    def rows(self, count: int):
+        self._turn ^= 1
+        return self._bufs[self._turn][:count]
+
+    def experts(self, recv_rows, recv_counts, m: int):
+        capi.check(capi.lib().bivmoe_ep_experts(self._h, C.c_void_p(recv_rows.data_ptr()),
+                                                C.c_void_p(recv_counts.data_ptr()), m,
+                                                C.c_void_p(self._out_rows.data_ptr()),
+                                                self._stream()), self._h)
+        return self._out_rows[:m]
+
+    def combine(self, returned, out, accumulate: bool):
+        import torch
+        torch.cuda.current_stream(self.device).wait_stream(self._side)   # the shared expert is done
+        capi.check(capi.lib().bivmoe_ep_combine(self._h, C.c_void_p(returned.data_ptr()),
+                                                C.c_void_p(out.data_ptr()), self._n,
+                                                int(accumulate), self._stream()), self._h)
+
+    def status(self):
+        capi.check(capi.lib().bivmoe_ep_status(self._h, self._stream()), self._h)
+
+
+class EpMoe:
+    """``Moe`` (moe.py) for a layer whose experts are spread over the ranks of a
+    process group; every rank passes its own rows."""
+
+    def __init__(self, layer: MoeLayer, max_tokens: int, rank: int, world: int, device: int = 0,
+                 comm=None, max_recv_rows: Optional[int] = None):
+        self.steps = DeviceSteps(layer, max_tokens, rank, world, device, max_recv_rows)
+        self.comm = comm or TorchComm()
+        self.n_embd = layer.n_embd
+        self.last_plan: Optional[EpPlan] = None
+
+    def moe_(self, h, out, accumulate: bool = True):
+        self.last_plan = ep_pass(self.steps, h, out, accumulate, self.comm)
+        return out
+
+    def moe(self, h):
+        import torch
+        out = torch.empty_like(h)
+        return self.moe_(h, out, accumulate=False)
+
+    def status(self):
+        self.steps.status()
+
+    def close(self):
+        self.steps.close()

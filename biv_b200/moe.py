@@ -30,24 +30,31 @@ def _experts(st: Optional[ExpertStack]) -> capi.Experts:
     return e
 
 
+def fill_desc(layer: MoeLayer, max_tokens: int, device: int):
+    """The ``bivmoe_desc`` of a layer, and the host arrays it points into (keep them
+    alive until the create call returns)."""
+    d = capi.Desc()
+    d.n_embd, d.n_expert, d.n_expert_used = layer.n_embd, layer.n_expert, layer.n_expert_used
+    d.n_ff_exp, d.n_ff_shexp = layer.n_ff_exp, layer.n_ff_shexp if layer.has_shared else 0
+    d.max_tokens, d.device = max_tokens, device
+    keep = [np.ascontiguousarray(layer.router, dtype=np.float32)]
+    d.router = keep[0].ctypes.data
+    d.gate, d.up, d.down = _experts(layer.gate), _experts(layer.up), _experts(layer.down)
+    if layer.has_shared:
+        d.sh_gate, d.sh_up, d.sh_down = (_experts(layer.sh_gate), _experts(layer.sh_up),
+                                         _experts(layer.sh_down))
+        keep.append(np.ascontiguousarray(layer.sh_gate_inp, dtype=np.float32))
+        d.sh_gate_inp = keep[1].ctypes.data
+    return d, keep
+
+
 class Moe:
     """One MoE feed-forward layer resident on a B200."""
 
     def __init__(self, layer: MoeLayer, max_tokens: int, device: int = 0):
         self._h = None
         L = capi.lib()
-        d = capi.Desc()
-        d.n_embd, d.n_expert, d.n_expert_used = layer.n_embd, layer.n_expert, layer.n_expert_used
-        d.n_ff_exp, d.n_ff_shexp = layer.n_ff_exp, layer.n_ff_shexp if layer.has_shared else 0
-        d.max_tokens, d.device = max_tokens, device
-        router = np.ascontiguousarray(layer.router, dtype=np.float32)
-        d.router = router.ctypes.data
-        d.gate, d.up, d.down = _experts(layer.gate), _experts(layer.up), _experts(layer.down)
-        if layer.has_shared:
-            d.sh_gate, d.sh_up, d.sh_down = (_experts(layer.sh_gate), _experts(layer.sh_up),
-                                             _experts(layer.sh_down))
-            gi = np.ascontiguousarray(layer.sh_gate_inp, dtype=np.float32)
-            d.sh_gate_inp = gi.ctypes.data
+        d, self._keep = fill_desc(layer, max_tokens, device)
         h = C.c_void_p()
         capi.check(L.bivmoe_create(C.byref(d), C.byref(h)))
         self._h = h

@@ -186,6 +186,61 @@ BIVMOE_API int bivmoe_tap_block_dots(bivmoe_layer* layer, int32_t matrix, int32_
 BIVMOE_API int bivmoe_route_noalloc(bivmoe_layer* layer, const float* h_dev, int32_t n,
                                     int32_t* ids_dev, float* weights_dev, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * Expert parallelism.  The reference runs on one device (one MTLDevice,
+ * engine/src/metal/mod.rs:450-462; the CPU backend loops over the experts in
+ * one process, engine/src/model.rs:875), so these entry points replace nothing
+ * there: they split `Model::moe` (model.rs:861-898) into the steps either side
+ * of two all-to-all exchanges that the CALLER performs (NCCL grouped
+ * send/receive, or any transport that moves device rows), one process per GPU.
+ *
+ * Rank r of W holds experts [r * n_expert / W, (r + 1) * n_expert / W): `gate`,
+ * `up`, `down` of the descriptor describe those n_expert / W experts only (for
+ * a GGUF tensor: the same `data` and `stride_bytes`, `offset_bytes` advanced to
+ * the rank's first expert, `n` = n_expert / W); `n_expert`, the router, the
+ * shared expert and its gate vector are the whole layer's, on every rank.  Each
+ * rank is the home of its own token rows.  One pass:
+ *
+ *   1. bivmoe_ep_route    home: router, top-k, sort; writes the token rows in
+ *                         expert order (so: destination-rank order) to
+ *                         `send_rows_dev` [n * k][n_embd] and the number of rows
+ *                         per expert to `send_counts_dev` [n_expert].
+ *   2. caller             exchanges the counts (every rank needs row r of every
+ *                         rank's counts: an all-gather), then the rows: rank d
+ *                         receives, from every source in rank order, that
+ *                         source's rows for d's experts.
+ *      bivmoe_ep_shared   home, any time after step 1 (e.g. on a second stream,
+ *                         during the exchange): the shared expert over the rank's
+ *                         own rows.
+ *   3. bivmoe_ep_experts  owner: `recv_rows_dev` [m][n_embd] ordered by source,
+ *                         then expert; `recv_counts_dev` [W][n_expert / W] = how
+ *                         many rows each source sent for each local expert (m is
+ *                         their sum).  Writes silu(gate x) * (up x) -> down for
+ *                         every row to `out_rows_dev` [m][n_embd], in the same
+ *                         order, unweighted.
+ *   4. caller             sends every row's output back where the row came from.
+ *   5. bivmoe_ep_combine  home: out[t] (+)= sum_j w[t,j] * returned row of pair
+ *                         (t, j), in ascending expert id, + sigmoid(gate) *
+ *                         shared[t] - the arithmetic and order of bivmoe_forward.
+ *
+ * All steps are asynchronous on `stream`; the caller orders them against its
+ * exchanges.  `max_tokens` bounds n (a rank's own rows), `max_recv_rows` bounds m
+ * (a safe value is W * max_tokens * min(n_expert_used, n_expert / W)).
+ * bivmoe_ep_status synchronises the stream and reports device-side failures
+ * (a bounded wait that gave up; an m that is not the sum of the count matrix).
+ * With W = 1 bivmoe_ep_create is bivmoe_create and bivmoe_forward applies. */
+BIVMOE_API int bivmoe_ep_create(const bivmoe_desc* desc, int32_t ep_rank, int32_t ep_world,
+                                int32_t max_recv_rows, bivmoe_layer** out);
+BIVMOE_API int bivmoe_ep_route(bivmoe_layer* layer, const float* h_dev, int32_t n,
+                               float* send_rows_dev, int32_t* send_counts_dev, void* stream);
+BIVMOE_API int bivmoe_ep_shared(bivmoe_layer* layer, const float* h_dev, void* stream);
+BIVMOE_API int bivmoe_ep_experts(bivmoe_layer* layer, const float* recv_rows_dev,
+                                 const int32_t* recv_counts_dev, int32_t m, float* out_rows_dev,
+                                 void* stream);
+BIVMOE_API int bivmoe_ep_combine(bivmoe_layer* layer, const float* returned_rows_dev, float* out_dev,
+                                 int32_t n, int32_t accumulate, void* stream);
+BIVMOE_API int bivmoe_ep_status(bivmoe_layer* layer, void* stream);
+
 /* What decides the numbers besides code and weights, as `Engine::numerics`
  * reports (engine.rs:42-46): device, kernel variants, repack version. */
 BIVMOE_API int bivmoe_numerics(const bivmoe_layer* layer, char* buf, size_t len);

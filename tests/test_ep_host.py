@@ -1,0 +1,142 @@
+"""Expert parallelism, host side: two gloo ranks on the CPU run ``ep_pass`` (the
+count exchange, the split sizes, the two all-to-alls, the order in which rows
+travel and return) with the oracle standing in for the device steps, and must
+reproduce the single-process oracle on each rank's rows bit for bit."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+import oracle
+from biv_b200 import workloads as wl
+from biv_b200.ep import ep_pass, ep_plan, local_experts
+
+torch = pytest.importorskip("torch")
+
+
+class OracleSteps:
+    """The five steps of ``ep_pass`` restated on numpy rows with the CPU oracle."""
+
+    def __init__(self, layer, rank, world):
+        self.layer, self.rank, self.world = layer, rank, world
+        self.n_expert, self.k, self.n_embd = layer.n_expert, layer.n_expert_used, layer.n_embd
+        self.local = local_experts(layer, rank, world)
+        self.level = oracle.host_level()
+
+    def route(self, h):
+        hn = h.numpy()
+        _, tap = oracle.moe_forward(self.layer, hn, taps=True)
+        self.tap, self.n = tap, hn.shape[0]
+        send = hn[tap["order"] // self.k]
+        return torch.from_numpy(np.ascontiguousarray(send)), torch.from_numpy(tap["counts"].copy())
+
+    def shared(self, h):
+        pass   # the tap of route() already holds the shared expert's rows
+
+    def rows(self, count):
+        return torch.empty((count, self.n_embd), dtype=torch.float32)
+
+    def experts(self, recv_rows, recv_counts, m):
+        rows, cnt = recv_rows.numpy(), recv_counts.numpy()
+        nl = self.n_expert // self.world
+        out = np.empty_like(rows)
+        at = 0
+        for s in range(self.world):
+            for x in range(nl):
+                c = int(cnt[s, x])
+                if c:
+                    out[at:at + c] = self._ffn(x, rows[at:at + c])
+                    at += c
+        assert at == m
+        return torch.from_numpy(out)
+
+    def _ffn(self, x, rows):
+        """silu(gate x) * (up x) -> down of local expert x, through the oracle's layer
+        with that one expert: its routing weight is exactly one."""
+        L = self.local
+
+        def one(st):
+            return wl.ExpertStack(st.ty, st.cols, st.rows, 1, st.data, st.stride, st.offset + x * st.stride)
+        sub = wl.MoeLayer(L.n_embd, 1, 1, L.n_ff_exp, 0, np.zeros((1, L.n_embd), np.float32),
+                          one(L.gate), one(L.up), one(L.down))
+        return oracle.moe_forward(sub, rows)
+
+    @staticmethod
+    def _sigmoid(g):
+        """ops.rs:160-162, with the C library's expf as the oracle uses it."""
+        import ctypes
+        f = oracle.lib().orc_sigmoid
+        f.restype, f.argtypes = ctypes.c_float, [ctypes.c_float]
+        return f(float(g))
+
+    def combine(self, returned, out, accumulate):
+        ret, tap, k = returned.numpy(), self.tap, self.k
+        slot = np.empty(self.n * k, np.int64)
+        slot[tap["order"]] = np.arange(self.n * k)          # pair -> where its row travelled
+        res = np.zeros((self.n, self.n_embd), np.float32)
+        for t in range(self.n):
+            for j in np.argsort(tap["ids"][t], kind="stable"):   # ascending expert id
+                res[t] = oracle.axpy(self.level, res[t], float(tap["weights"][t, j]), ret[slot[t * k + j]])
+            if self.layer.has_shared:
+                res[t] = oracle.axpy(self.level, res[t], float(self._sigmoid(tap["shared_gate"][t])),
+                                     tap["shared_out"][t])
+        o = out.numpy()
+        o[...] = o + res if accumulate else res
+
+
+def _worker(rank, world, port, cfg, n_per_rank):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        w = getattr(wl, cfg)(n=world * n_per_rank, **wl.SMALL)
+        layer = w.layers[0]
+        h = np.ascontiguousarray(w.h[rank * n_per_rank:(rank + 1) * n_per_rank])
+        steps = OracleSteps(layer, rank, world)
+        out = torch.zeros((n_per_rank, layer.n_embd), dtype=torch.float32)
+        plan = ep_pass(steps, torch.from_numpy(h), out, False)
+        want = oracle.moe_forward(layer, h)
+        assert plan.m == int(plan.recv_counts.sum()) and sum(plan.send_splits) == n_per_rank * layer.n_expert_used
+        np.testing.assert_array_equal(out.numpy(), want)
+        # every rank's received rows, summed, are every pair
+        total = torch.tensor([plan.m])
+        dist.all_reduce(total)
+        assert int(total) == world * n_per_rank * layer.n_expert_used
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("cfg", ["parity_q8_0", "ep_bf16"])
+def test_two_gloo_ranks_reproduce_the_single_process_oracle(cfg):
+    import torch.multiprocessing as mp
+    mp.spawn(_worker, args=(2, _free_port(), cfg, 12), nprocs=2, join=True)
+
+
+def test_plan_is_consistent_across_ranks():
+    rng = np.random.default_rng(0)
+    W, E = 4, 32
+    counts = rng.integers(0, 9, size=(W, E)).astype(np.int32)
+    counts[1, 8:16] = 0                                      # a rank that sends nothing to rank 1
+    plans = [ep_plan(counts, r) for r in range(W)]
+    for r in range(W):
+        assert sum(plans[r].send_splits) == counts[r].sum()
+        for d in range(W):
+            assert plans[r].send_splits[d] == plans[d].recv_splits[r]
+            assert plans[d].recv_counts[r].sum() == plans[r].send_splits[d]
+    assert plans[1].recv_splits[1] == 0
+
+
+def test_local_experts_are_a_byte_range_of_the_same_tensor():
+    layer = wl.parity_q8_0(n=4, **wl.SMALL).layers[0]
+    for r in range(4):
+        loc = local_experts(layer, r, 4)
+        assert loc.gate.data is layer.gate.data and loc.gate.n == layer.n_expert // 4
+        for x in range(loc.gate.n):
+            np.testing.assert_array_equal(loc.down.expert(x), layer.down.expert(r * loc.gate.n + x))

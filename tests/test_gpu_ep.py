@@ -1,0 +1,219 @@
+"""Expert parallelism on the GPU, through the bivmoe_ep_* entry points.
+
+One GPU: W ranks as threads of this process, each with its own layer object on
+cuda:0, exchanging rows through ``ThreadComm`` (tensor copies between barriers).
+This runs the device steps exactly as W processes would, without a second GPU.
+Two or more GPUs: the same pass as real processes over NCCL.
+
+Gates: every rank's output equals the single-GPU layer's output on the same rows
+bit for bit when both take the decode kernels (small row counts), and is within
+the layer tolerance of the CPU oracle always.
+"""
+import os
+import socket
+import threading
+
+import numpy as np
+import pytest
+
+import oracle
+from biv_b200 import workloads as W
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+class ThreadComm:
+    """The two collectives of ``ep_pass`` between threads of one process whose
+    tensors live on one device and are produced on one stream."""
+
+    class Shared:
+        def __init__(self, world):
+            self.world = world
+            self.barrier = threading.Barrier(world)
+            self.slots = [None] * world
+
+    def __init__(self, shared, rank):
+        self.sh, self.rank = shared, rank
+
+    def _publish(self, value):
+        self.sh.slots[self.rank] = value
+        self.sh.barrier.wait()
+        got = list(self.sh.slots)
+        self.sh.barrier.wait()
+        return got
+
+    def all_gather(self, out_flat, piece):
+        pieces = self._publish(piece)
+        n = piece.numel()
+        for r, p in enumerate(pieces):
+            out_flat[r * n:(r + 1) * n].copy_(p)
+        self.sh.barrier.wait()          # nobody's piece is overwritten before all have read it
+
+    def all_to_all(self, recv, send, recv_splits, send_splits):
+        sends = self._publish((send, send_splits))
+        at = 0
+        for r, (rows, splits) in enumerate(sends):
+            lo = sum(splits[:self.rank])
+            c = splits[self.rank]
+            assert c == recv_splits[r]
+            recv[at:at + c].copy_(rows[lo:lo + c])
+            at += c
+        self.sh.barrier.wait()
+
+
+def _run_threads(world, layer, h, max_tokens):
+    import torch
+    from biv_b200.ep import EpMoe
+    n_per = h.shape[0] // world
+    shared = ThreadComm.Shared(world)
+    outs, errs = [None] * world, [None] * world
+    plans = [None] * world
+
+    def rank_main(r):
+        try:
+            torch.cuda.set_device(0)
+            m = EpMoe(layer, max_tokens, r, world, 0, comm=ThreadComm(shared, r))
+            try:
+                hr = torch.from_numpy(np.ascontiguousarray(h[r * n_per:(r + 1) * n_per])).cuda()
+                for _ in range(2):       # twice: the scratch buffers are reused
+                    out = m.moe(hr)
+                m.status()
+                outs[r] = out.cpu().numpy()
+                plans[r] = m.last_plan
+            finally:
+                m.close()
+        except BaseException as e:      # noqa: BLE001 - reported by the main thread
+            errs[r] = e
+            shared.barrier.abort()
+
+    ts = [threading.Thread(target=rank_main, args=(r,)) for r in range(world)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    for e in errs:
+        if e is not None and not isinstance(e, threading.BrokenBarrierError):
+            raise e
+    for e in errs:
+        if e is not None:
+            raise e
+    return np.concatenate(outs), plans
+
+
+def _small(cfg, n):
+    if cfg == "mtp_stack":      # Q5_K gate/up, Q6_K down; one layer of the stack
+        return W.mtp_stack(n_seq=n // 5, n_tok=5, n_layers=1, **W.SMALL)
+    return getattr(W, cfg)(n=n, **W.SMALL)
+
+
+def _single_gpu(layer, h):
+    import torch
+    from biv_b200.moe import Moe
+    m = Moe(layer, h.shape[0])
+    try:
+        out = m.moe(torch.from_numpy(h).cuda())
+        torch.cuda.synchronize()
+        return out.cpu().numpy()
+    finally:
+        m.close()
+
+
+@pytest.mark.parametrize("cfg,world,n", [("parity_q8_0", 2, 16), ("decode_q4k", 4, 24),
+                                         ("mtp_stack", 2, 10), ("ep_bf16", 2, 32),
+                                         ("ep_bf16", 4, 12)])
+def test_ranks_as_threads_match_the_single_gpu_layer(cfg, world, n):
+    wl = _small(cfg, n)
+    layer, h = wl.layers[0], np.ascontiguousarray(wl.h)
+    got, plans = _run_threads(world, layer, h, max_tokens=n // world)
+    # a rank routes its rows alone, so the reference is the layer applied per rank
+    n_per = n // world
+    want = np.concatenate([_single_gpu(layer, np.ascontiguousarray(h[r * n_per:(r + 1) * n_per]))
+                           for r in range(world)])
+    np.testing.assert_array_equal(got, want)
+    ref = oracle.moe_forward(layer, h)
+    assert rel_err(got, ref) < TOL
+    assert sum(p.m for p in plans) == n * layer.n_expert_used
+
+
+def test_full_size_layer_two_ranks_as_threads():
+    """The BF16 configuration at its real shape, 512 rows: groups large and small."""
+    wl = W.ep_bf16(n=512)
+    layer, h = wl.layers[0], np.ascontiguousarray(wl.h)
+    got, _ = _run_threads(2, layer, h, max_tokens=256)
+    ref = oracle.moe_forward(layer, h, threads=oracle.max_threads())
+    assert rel_err(got, ref) < TOL
+
+
+def test_steps_reject_a_plain_layer_and_bad_sizes():
+    import ctypes as C
+    import torch
+    from biv_b200 import capi
+    from biv_b200.ep import DeviceSteps
+    from biv_b200.moe import Moe
+    wl = W.parity_q8_0(n=8, **W.SMALL)
+    m = Moe(wl.layers[0], 8)
+    try:
+        with pytest.raises(capi.BivMoeError) as ei:
+            capi.check(capi.lib().bivmoe_ep_status(m._h, None), m._h)
+        assert ei.value.code == capi.ERR_ARGUMENT
+    finally:
+        m.close()
+    st = DeviceSteps(wl.layers[0], 8, 0, 2, 0)
+    try:
+        h = torch.from_numpy(wl.h).cuda()
+        with pytest.raises(capi.BivMoeError):       # more rows than max_tokens
+            st.route(torch.cat([h, h]))
+        with pytest.raises(capi.BivMoeError):       # a whole-layer call on a sharded layer
+            capi.check(capi.lib().bivmoe_forward(st._h, C.c_void_p(h.data_ptr()),
+                                                 C.c_void_p(h.data_ptr()), 8, 0, None), st._h)
+        # a received-row count that is not the sum of the count matrix is reported
+        st.route(h)
+        counts = torch.zeros((2, 8), dtype=torch.int32, device="cuda")
+        counts[0, 0] = 3
+        st.experts(st.rows(4), counts, 4)
+        with pytest.raises(capi.BivMoeError) as ei:
+            st.status()
+        assert ei.value.code == capi.ERR_ARGUMENT
+    finally:
+        st.close()
+
+
+def _nccl_worker(rank, world, port, cfg, n, tmp):
+    import torch
+    import torch.distributed as dist
+    from biv_b200.ep import EpMoe
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        wl = getattr(W, cfg)(n=n, **W.SMALL)
+        layer, n_per = wl.layers[0], n // world
+        h = np.ascontiguousarray(wl.h[rank * n_per:(rank + 1) * n_per])
+        m = EpMoe(layer, n_per, rank, world, rank)
+        out = m.moe(torch.from_numpy(h).cuda(rank))
+        m.status()
+        np.save(os.path.join(tmp, f"out{rank}.npy"), out.cpu().numpy())
+        m.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("cfg", ["parity_q8_0", "ep_bf16"])
+def test_two_processes_over_nccl(cfg, tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    n, world = 32, 2
+    mp.spawn(_nccl_worker, args=(world, port, cfg, n, str(tmp_path)), nprocs=world, join=True)
+    wl = getattr(W, cfg)(n=n, **W.SMALL)
+    layer = wl.layers[0]
+    got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
+    ref = oracle.moe_forward(layer, wl.h)
+    assert rel_err(got, ref) < TOL
