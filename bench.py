@@ -163,6 +163,79 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def time_ep(layer, h_rank, steps, warmup, rank, world, local):
+    """Expert-parallel passes of the layer: this rank's rows in, experts sharded
+    n_expert / world per GPU, rows exchanged over NCCL.  Device time of `steps`
+    passes, max over ranks; also this rank's output of the last pass."""
+    import torch
+    import torch.distributed as dist
+    from biv_b200.ep import EpMoe
+    n = h_rank.shape[0]
+    m = EpMoe(layer, n, rank, world, local)
+    h = torch.from_numpy(h_rank).cuda()
+    out = torch.empty_like(h)
+    for _ in range(max(3, warmup)):
+        m.moe_(h, out, accumulate=False)
+    m.status()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        m.moe_(h, out, accumulate=False)
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    m.status()
+    recv = m.last_plan.m
+    res = out.cpu().numpy()
+    m.close()
+    return float(t[0]) / steps, recv, res
+
+
+def run_ep_workload(args, wl, rank, world, local):
+    """`--workload ep_bf16` on more than one GPU: the configuration's rows split
+    over the ranks (strong scaling), one JSON line."""
+    import torch
+    import torch.distributed as dist
+    layer = wl.layer
+    n_per = wl.n // world
+    h_rank = np.ascontiguousarray(wl.h[rank * n_per:(rank + 1) * n_per])
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms, recv, _ = time_ep(layer, h_rank, args.steps, args.warmup, rank, world, local)
+    sampler.stop_flag = True
+    sampler.join()
+    if rank == 0:
+        _, tf_peak, peak_kind = load_peaks()
+        k, e, ff = layer.n_expert_used, layer.n_embd, layer.n_ff_exp
+        flops = 2.0 * wl.n * (k + 1) * 3 * e * ff
+        row_bytes = e * 4
+        line = {
+            "metric": METRIC, "value": n_per * world / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 weights x f32 activations, f32 accumulation", "data": "synthetic",
+            "config": {"workload": f"{wl.name}: {wl.n} tokens over {world} GPUs, hidden {e}, "
+                                   f"{layer.n_expert} experts top-{k} + shared expert, ff {ff}, "
+                                   f"BF16, seed {wl.seed}",
+                       "tokens_per_gpu": n_per, "parallelism": f"ep{world}",
+                       "experts_per_gpu": layer.n_expert // world,
+                       "l2": "weights and rows of one pass exceed the 126 MB L2, no flush"},
+            "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12 / world,
+                         "peak": tf_peak, "peak_kind": f"of {peak_kind}", "unit": "TFLOP/s",
+                         "frac": flops / (ms * 1e-3) / 1e12 / world / tf_peak if tf_peak else None,
+                         "traffic": None, "scope": "whole pass per GPU, exchanges included"},
+            "exchange": {"rows_received_rank0": recv, "bytes_each_way_rank0": recv * row_bytes,
+                         "transport": "NCCL all_to_all_single over NVLink, f32 rows"},
+            "gpu_launches": None, "clocks": sampler.summary(),
+        }
+        print(json.dumps(line))
+    dist.destroy_process_group()
+
+
 def config_of(wl, args, world):
     l = wl.layer
     return {"workload": f"{wl.name}: {wl.n} tokens per GPU, hidden {l.n_embd}, {l.n_expert} experts "
@@ -204,6 +277,8 @@ def main():
     warmup = max(args.warmup, 3)
 
     wl = make_workload(args.workload, args)
+    if world > 1 and args.workload == "ep_bf16":
+        return run_ep_workload(args, wl, rank, world, local)
     layer, n = wl.layer, wl.n
     ncopies = max(1, args.copies)
     copies = [Moe(layer, n, device=local) for _ in range(ncopies)]
@@ -280,6 +355,18 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])
+    # ---- the same shape with the experts sharded over the GPUs instead of replicated:
+    #      every rank passes its own n rows, rows travel to the experts' owners and back
+    ep = None
+    if world > 1 and layer.n_expert % world == 0:
+        torch.cuda.set_stream(torch.cuda.default_stream())
+        h_rank = np.random.default_rng(1000 + rank).standard_normal((n, layer.n_embd), dtype=np.float32)
+        ep_ms, ep_recv, _ = time_ep(layer, h_rank, min(args.steps, 100), 5, rank, world, local)
+        ep = {"value": world * n / (ep_ms * 1e-3), "unit": UNIT, "ms_per_step": ep_ms,
+              "parallelism": f"ep{world}", "experts_per_gpu": layer.n_expert // world,
+              "tokens_per_gpu": n, "rows_received_rank0": ep_recv,
+              "note": "experts sharded, two NCCL all-to-alls and one host-read count exchange "
+                      "per pass; `value` above is the replicated (no-exchange) arrangement"}
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -310,6 +397,8 @@ def main():
         "gpu_launches": launches,
         "clocks": sampler.summary(),
     }
+    if ep:
+        line["ep"] = ep
     if not args.no_cpu:
         cpu, _ = time_cpu(wl)
         line["cpu_baseline"] = cpu

@@ -71,6 +71,7 @@ struct bivmoe_layer {
         int seen = 0;            // identical calls seen; the graph is built on the second
     } graph;
     int prefill_min = 0;   // set at create when the tcgen05 kernels support the layer's types
+    int prefill_tile = kPrefillTile;
     // expert parallelism (bivmoe_ep_create): this rank's experts are global ids
     // ep_rank * n_local .. +n_local; `ws` serves the rank's own tokens (routing over all
     // experts, the shared expert), `ws_owner` the rows received for the local experts
@@ -96,7 +97,7 @@ static void layout_one(bivmoe_layer* L, Arena& a, Workspace& w, size_t N, size_t
     w.weights = a.take<float>(P);
     w.counts = a.take<int32_t>(ne);
     w.offsets = a.take<int32_t>(ne + 1);
-    w.order = a.take<int32_t>(((N + 7) / 8) * 8 + P + 8 * ne + 8 + kPrefillTile);
+    w.order = a.take<int32_t>(((N + 7) / 8) * 8 + P + 8 * ne + 8 + kPrefillPad);
     w.pos_of = a.take<int32_t>(P);
     w.blk_counts = a.take<int32_t>(((N + 255) / 256) * ne);
     w.grp_expert = a.take<int32_t>(ne + 1);
@@ -114,14 +115,17 @@ static void layout_one(bivmoe_layer* L, Arena& a, Workspace& w, size_t N, size_t
     w.work_ctr = a.take<uint32_t>(8);
     w.status = a.take<int32_t>(4);
     // positions: the tokens (shared group), then the routed groups, each padded to 8
-    // (+kPrefillTile: a tile of the tcgen05 kernels copies that many positions from its first one)
-    const size_t R = ((N + 7) / 8) * 8 + (routed_rows ? P + 8 * ne : 0) + 8 + kPrefillTile;
+    // (+kPrefillPad: a tile of the tcgen05 kernels copies up to that many positions from its first one)
+    const size_t R = ((N + 7) / 8) * 8 + (routed_rows ? P + 8 * ne : 0) + 8 + kPrefillPad;
     w.act_rows = (int)R;
     const bool qact = !type_uses_f32_act(L->gate_up.ty) || (L->has_shared && !type_uses_f32_act(L->sh_gate_up.ty));
     const bool fact = type_uses_f32_act(L->gate_up.ty) || (L->has_shared && type_uses_f32_act(L->sh_gate_up.ty));
     const bool qmid = !type_uses_f32_act(L->down.ty) || (L->has_shared && !type_uses_f32_act(L->sh_down.ty));
     w.act_t = a.take<uint8_t>(qact ? (e / 256) * (R / 8) * kActTileBytes : 0);
     w.act_f = a.take<float>(fact ? R * e : 0);
+    const bool brec = L->prefill_min > 0 && L->gate_up.ty == BIVMOE_BF16;   // bf16 hi/lo records
+    w.act_b = a.take<uint8_t>(brec ? (e / 64) * (R / 8) * kActBRec : 0);
+    w.mid_b = a.take<uint8_t>(brec ? (mid / 64) * (R / 8) * kActBRec : 0);
     w.mid = a.take<float>(R * mid);
     w.mid_t = a.take<uint8_t>(qmid ? (mid / 256) * (R / 8) * kActTileBytes : 0);
     w.pair_out = a.take<float>(R * e);
@@ -323,6 +327,7 @@ static int create_impl(const bivmoe_desc* d, int ep_rank, int ep_world, int max_
         (!shared || (L->sh_gate_up.ty == L->gate_up.ty && L->sh_down.ty == L->down.ty))) {
         const char* env = getenv("BIVMOE_PREFILL_MIN");
         L->prefill_min = env ? atoi(env) : 96;
+        L->prefill_tile = L->gate_up.ty == BIVMOE_BF16 ? kPrefillTileBf16 : kPrefillTile;
     }
     Arena probe;
     layout_workspace(L, probe);
@@ -381,6 +386,7 @@ static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int 
     LaunchCfg c{stream, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh, L->has_shared ? 1 : 0, L->sm_count};
     c.ev = ev;
     c.prefill_min = L->prefill_min;
+    c.prefill_tile = L->prefill_tile;
     mark(c, EV_START);
     CU(launch_router(c, L->router, h, L->ws));
     mark(c, EV_ROUTER);
@@ -489,6 +495,7 @@ int bivmoe_ep_route(bivmoe_layer* L, const float* h_dev, int32_t n, float* send_
     LaunchCfg c{s, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh, L->has_shared ? 1 : 0, L->sm_count};
     // the shared expert's group alone is computed here; its size decides its kernel
     c.prefill_min = L->prefill_min;
+    c.prefill_tile = L->prefill_tile;
     CU(launch_router(c, L->router, h_dev, L->ws));
     CU(launch_route_topk(c, L->ws));
     CU(launch_sort(c, L->ws));
@@ -506,6 +513,7 @@ int bivmoe_ep_shared(bivmoe_layer* L, const float* h_dev, void* stream) {
     cudaStream_t s = (cudaStream_t)stream;
     LaunchCfg c{s, n, 0, L->e, L->n_expert, L->ff, L->ff_sh, 1, L->sm_count};   // k = 0: no pair rows
     c.prefill_min = L->prefill_min;
+    c.prefill_tile = L->prefill_tile;
     c.only_shared = 1;
     CU(launch_dispatch(c, h_dev, L->ws, L->ws.act_t != nullptr && !type_uses_f32_act(L->sh_gate_up.ty),
                        L->ws.act_f != nullptr && type_uses_f32_act(L->sh_gate_up.ty)));
@@ -529,6 +537,7 @@ int bivmoe_ep_experts(bivmoe_layer* L, const float* recv_rows_dev, const int32_t
     // the received rows are a k = 1 routing result over the local experts, no shared expert
     LaunchCfg c{s, m, 1, L->e, L->n_local, L->ff, 0, 0, L->sm_count};
     c.prefill_min = L->prefill_min;
+    c.prefill_tile = L->prefill_tile;
     const Workspace& w = L->ws_owner;
     const DevTiles none{};
     CU(launch_ep_expand(c, recv_counts_dev, L->ep_world, w));

@@ -29,7 +29,9 @@ namespace bivmoe {
 //   BF16   64        128  64 values
 constexpr int kRepackVersion = 4;
 constexpr int kChunkRows = 128;
-constexpr int kPrefillTile = 96;    // tokens per tile of the tcgen05 kernels
+constexpr int kPrefillTile = 96;    // tokens per tile of the tcgen05 kernel for Q8_0
+constexpr int kPrefillTileBf16 = 128;   // and for BF16
+constexpr int kPrefillPad = 128;    // positions a tile's copy may run past the last group
 
 struct SliceGeom { int elems, sl; };
 __host__ __device__ inline SliceGeom slice_geom(int ty) {
@@ -87,6 +89,14 @@ struct DevTiles {          // the tiles of one product (gate+up, or down) of a s
 //     s     [8 blocks][8 tokens] f32: s itself (read by the taps only)
 // which is what one pipeline stage of the expert kernels copies (all but `s`).
 // Float rows (BF16 weights) are [K/64][R][64] f32.  R = ceil8(n) + n*k + 8*n_expert + 8.
+// For the BF16 tensor-core kernel the float rows are also kept as two bf16
+// terms, x = hi + lo up to 2^-17 |x| (hi = bf16(x), lo = bf16(x - hi)), one
+// record per (K-slice of 64, tile of 8 positions):
+//     hi    [8 units][8 tokens][8 bf16]   the canonical K-major operand layout
+//     lo    the same, 1024 bytes further
+constexpr int kActBRec = 2048, kActBLo = 1024;
+// byte offset inside a record of element i (0..63) of token tk (0..7), hi term
+__host__ __device__ inline int act_b_off(int tk, int i) { return ((i >> 3) * 8 + tk) * 16 + (i & 7) * 2; }
 constexpr int kActOffDx = 2048, kActOffSHi = kActOffDx + 256, kActOffSLo = kActOffSHi + 256,
               kActOffS = kActOffSLo + 256;
 constexpr int kActCopyBytes = kActOffS;        // 2816: what a stage copies
@@ -129,6 +139,8 @@ struct Workspace {
     int act_rows;        // R: positions
     uint8_t* act_t;      // Q8 records of h, [n_embd/256][R/8] tiles (quantised gate/up types)
     float* act_f;        // f32 rows of h by position, slice-major (float-activation types)
+    uint8_t* act_b;      // bf16 hi/lo records of h, [n_embd/64][R/8] (BF16 layers with the tcgen05 kernels)
+    uint8_t* mid_b;      // the same of silu(gate)*up, [ff/64][R/8]
     float* mid;          // silu(gate)*up by position, slice-major f32 [ff/64][R][64]
     uint8_t* mid_t;      // its Q8 records, [ff/256][R/8] tiles (quantised down types)
     float* pair_out;     // [P + n][e], by position
@@ -140,6 +152,7 @@ struct LaunchCfg {
     int n, k, e, n_expert, ff, ff_sh, has_shared;
     int sm_count;
     int prefill_min = 0;         // groups with at least this many tokens go to the tcgen05 kernels (0: none)
+    int prefill_tile = kPrefillTile;   // positions per tile of the tcgen05 kernel in use
     int only_shared = 0;         // expert launches cover the shared expert's group alone (expert parallelism)
     cudaEvent_t* ev = nullptr;   // optional: events recorded between the stages (profiling call)
 };
@@ -175,6 +188,9 @@ cudaError_t launch_block_dots(const DevTiles& t, int tile_base, int expert, int 
                               cudaStream_t stream);
 bool experts_supported(int ty, int cols, int rows, bool is_down);
 bool prefill_supported(int gate_up_ty, int down_ty);
+cudaError_t launch_experts_prefill_bf16(const LaunchCfg& c, const DevTiles& gate_up, const DevTiles& down,
+                                        const DevTiles& sh_gate_up, const DevTiles& sh_down,
+                                        const Workspace& ws);
 cudaError_t launch_experts_prefill(const LaunchCfg& c, const DevTiles& gate_up, const DevTiles& down,
                                    const DevTiles& sh_gate_up, const DevTiles& sh_down,
                                    const Workspace& ws);

@@ -1,0 +1,322 @@
+// Grouped expert products for prefill-sized groups with BF16 weights on the 5th
+// generation tensor cores: tcgen05.mma kind::f16 (bf16 x bf16 -> f32) with the
+// accumulator in tensor memory.
+// Reference: dense_ffn (engine/src/model.rs:1119-1126) over the bf16 dot
+// (engine/src/quant.rs:509-521: bf16 weights widened to f32, times f32
+// activations, f32 accumulation), for experts whose token list is long
+// (model.rs:875-889).
+//
+// The reference multiplies bf16 weights by f32 activations.  The tensor core
+// takes bf16 on both sides, so an activation row is fed as two bf16 terms,
+// x = hi + lo (hi = bf16(x), lo = bf16(x - hi)), which represents x to 2^-17 |x|;
+// every weight K-step is multiplied by both and the products - exact in f32 -
+// accumulate in tensor memory.  That doubles the MMA count and keeps the result
+// within a few f32 roundings of the reference's, far inside the layer tolerance.
+//
+// Design.  One block per SM, five warps: warp 0 lane 0 issues the copies, lane 1
+// the MMAs; four epilogue warps own the 128 tensor-memory lanes.  A work item is
+// a tile of 128 tokens of one group times a chunk of 128 weight rows (64 gate
+// rows with their 64 up rows, or 128 down rows).  A pipeline stage is one
+// K-slice of 64 values: 128 rows x 128 bytes of weights and the tile's 16
+// activation records (hi and lo), both already in the tensor core's canonical
+// K-major layout (common.cuh), so a stage is two bulk copies.  Per stage the MMA
+// thread issues 2 terms x 4 K-steps (M = 128, N = 128, K = 16) accumulating into
+// one of two tensor-memory buffers; unlike the Q8_0 kernel nothing is scaled per
+// block, so the epilogue runs once per item, while the next item's MMAs fill the
+// other buffer.  Every wait is bounded; a wait that gives up records
+// BIVMOE_ERR_TIMEOUT, the block leaves its loops, frees its tensor memory and
+// returns.
+#include <cuda_bf16.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace bivmoe {
+
+constexpr int BF_NT = kPrefillTileBf16;                         // tokens per tile = MMA N
+constexpr int BF_EPI_WARPS = 4;
+constexpr int BF_THREADS = 32 * (1 + BF_EPI_WARPS);
+constexpr uint32_t BF_W_BYTES = kChunkRows * 128;               // 16384: one K-slice of a chunk
+constexpr uint32_t BF_X_BYTES = (BF_NT / 8) * kActBRec;         // 32768
+constexpr uint32_t BF_STAGE = BF_W_BYTES + BF_X_BYTES;          // 49152
+constexpr int BF_NSTAGE = 4;
+constexpr uint32_t BF_HEAD = 1024;
+constexpr uint32_t BF_XCHG = 64 * 32 * 4;                       // SwiGLU exchange of 32 tokens
+constexpr uint32_t BF_SMEM = BF_HEAD + BF_NSTAGE * BF_STAGE + BF_XCHG;   // 205824
+constexpr uint32_t BF_TMEM_COLS = 256;                          // two buffers of 128 columns
+
+enum { BF_GATEUP = 0, BF_DOWN = 1 };
+
+struct Bf16Args {
+    DevTiles w, sh;
+    const uint8_t* x_b;    // bf16 hi/lo records of the inputs by position, [K/64][R/8]
+    int act_rows;          // R
+    float* out;            // GATEUP: mid f32 slice-major; DOWN: pair_out [R][rows]
+    uint8_t* out_b;        // GATEUP: bf16 hi/lo records of mid
+    const int32_t* grp_expert;
+    const int32_t* grp_start;
+    const int32_t* grp_count;
+    const int32_t* ptile_group;
+    const int32_t* ptile_t0;
+    const int32_t* n_ptiles;
+    int32_t* status;
+    int n_expert;
+    int tiles_mode;        // 0: every tile, 1: skip the shared group's, 2: only the shared group's
+    int chunks;
+};
+
+struct BfItem {
+    int shared, expert, chunk, pos0, tc, nst;
+    const uint8_t* wsrc;   // stage 0 of the chunk's weights; stage s is s * BF_W_BYTES further
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(BF_THREADS, 1)
+experts_prefill_bf16_kernel(const Bf16Args A) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* full = (uint64_t*)smem;            // [4] copies landed
+    uint64_t* empty = full + 4;                  // [4] stage free: its MMAs are done
+    uint64_t* tfull = full + 8;                  // [2] an item's products are in tensor memory
+    uint64_t* tempty = full + 10;                // [2] drained by the epilogue warps
+    uint64_t* xbar = full + 12;                  // [1] meeting point of the epilogue warps
+    uint32_t* s_tmem = (uint32_t*)(smem + 256);
+    int* s_abort = (int*)(smem + 260);
+    uint8_t* stages = smem + BF_HEAD;
+    float* s_xchg = (float*)(smem + BF_HEAD + BF_NSTAGE * BF_STAGE);   // [32 tokens][64 rows]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int CH = MODE == BF_GATEUP ? 64 : 128;   // output rows per chunk
+
+    if (tid == 0) {
+        for (int i = 0; i < BF_NSTAGE; i++) {
+            pf_bar_init(&full[i], 1);
+            pf_bar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            pf_bar_init(&tfull[i], 1);
+            pf_bar_init(&tempty[i], BF_EPI_WARPS);
+        }
+        pf_bar_init(xbar, BF_EPI_WARPS);
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         pf_smem(s_tmem)),
+                     "r"(BF_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pf_fence_before();
+    __syncthreads();
+    pf_fence_after();
+    const uint32_t tmem = *s_tmem;
+
+    const int tiles_all = A.n_ptiles[0], tiles_sh = A.n_ptiles[1];
+    const int tile_lo = A.tiles_mode == 1 ? tiles_sh : 0;
+    const int tile_hi = A.tiles_mode == 2 ? tiles_sh : tiles_all;
+    const int total = (tile_hi - tile_lo) * A.chunks;
+
+    // Items are dealt round-robin, chunk-major: consecutive blocks take the same
+    // chunk of consecutive tiles... every role walks the same sequence on its own.
+    auto decode = [&](int idx) -> BfItem {
+        BfItem it;
+        const int tile = tile_lo + idx / A.chunks;
+        it.chunk = idx % A.chunks;
+        const int gi = A.ptile_group[tile], t0 = A.ptile_t0[tile];
+        it.expert = A.grp_expert[gi];
+        it.shared = it.expert == A.n_expert;
+        it.pos0 = A.grp_start[gi] + t0;
+        it.tc = min(BF_NT, A.grp_count[gi] - t0);
+        const DevTiles& m = it.shared ? A.sh : A.w;
+        it.nst = it.chunk < m.chunks ? m.nslices : 0;
+        it.wsrc = m.stage(it.shared ? 0 : it.expert, min(it.chunk, max(m.chunks - 1, 0)), 0);
+        return it;
+    };
+    auto give_up = [&]() {
+        atomicExch(A.status, BIVMOE_ERR_TIMEOUT);
+        atomicExch(s_abort, 1);
+    };
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- copy thread: two bulk copies per stage
+        uint32_t q = 0;
+        bool dead = false;
+        for (int idx = blockIdx.x; idx < total && !dead && !*(volatile int*)s_abort; idx += gridDim.x) {
+            const BfItem it = decode(idx);
+            for (int s = 0; s < it.nst && !dead; s++, q++) {
+                const uint32_t slot = q % BF_NSTAGE;
+                if (!pf_bar_wait(&empty[slot], ((q / BF_NSTAGE) & 1) ^ 1)) { give_up(); dead = true; break; }
+                uint8_t* dst = stages + slot * BF_STAGE;
+                pf_bar_expect_tx(&full[slot], BF_STAGE);
+                pf_bulk_g2s(dst, it.wsrc + (size_t)s * BF_W_BYTES, BF_W_BYTES, &full[slot]);
+                pf_bulk_g2s(dst + BF_W_BYTES,
+                            A.x_b + ((size_t)s * (A.act_rows / 8) + it.pos0 / 8) * kActBRec, BF_X_BYTES,
+                            &full[slot]);
+            }
+        }
+    } else if (warp == 0 && lane == 1) {
+        // ---------------- MMA thread: 2 terms x 4 K-steps per stage
+        const uint32_t idesc = pf_idesc_bf16(kChunkRows, BF_NT);
+        uint32_t q = 0, item = 0;
+        bool dead = false;
+        for (int idx = blockIdx.x; idx < total && !dead && !*(volatile int*)s_abort; idx += gridDim.x) {
+            const BfItem it = decode(idx);
+            if (it.nst == 0) continue;
+            const uint32_t buf = item & 1;
+            if (!pf_bar_wait(&tempty[buf], ((item >> 1) & 1) ^ 1)) { give_up(); break; }
+            pf_fence_after();
+            for (int s = 0; s < it.nst && !dead; s++, q++) {
+                const uint32_t slot = q % BF_NSTAGE;
+                if (!pf_bar_wait(&full[slot], (q / BF_NSTAGE) & 1)) { give_up(); dead = true; break; }
+                pf_fence_after();
+                const uint32_t wa = pf_smem(stages + slot * BF_STAGE);
+                const uint32_t xa = wa + BF_W_BYTES;
+#pragma unroll
+                for (int term = 0; term < 2; term++)
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) {
+                        // A: the chunk's rows, units 2ks and 2ks+1 (16 bf16 of K): 8-row groups
+                        //    128 B apart, the two units 2048 B apart.  B: the tokens' hi or lo
+                        //    term, the same units of each record: 8-token groups one record
+                        //    apart, the two units 128 B apart.
+                        const uint64_t ad = pf_desc(wa + 2 * ks * (kChunkRows * 16), kChunkRows * 16, 128);
+                        const uint64_t bd = pf_desc(xa + term * kActBLo + 2 * ks * 128, 128, kActBRec);
+                        pf_mma_bf16(tmem + buf * BF_NT, ad, bd, idesc, (s | term | ks) != 0);
+                    }
+                pf_commit(&empty[slot]);   // the stage's operands are no longer read
+            }
+            if (!dead) pf_commit(&tfull[buf]);
+            item++;
+        }
+    } else if (warp > 0) {
+        // ---------------- epilogue warps: once per item
+        const int quad = warp & 3;               // the tensor-memory lanes this warp may read
+        const int row = 32 * quad + lane;        // chunk row = tensor-memory lane
+        const uint32_t tlane = tmem + ((uint32_t)(32 * quad) << 16);
+        uint32_t item = 0, xphase = 0;
+        auto meet = [&]() -> bool {   // the epilogue warps meet (bounded): false when the wait gave up
+            __syncwarp();
+            if (lane == 0) pf_bar_arrive(xbar);
+            const bool ok = pf_bar_wait(xbar, xphase);
+            xphase ^= 1;
+            return ok;
+        };
+        bool ok = true;
+        for (int idx = blockIdx.x; idx < total && ok && !*(volatile int*)s_abort; idx += gridDim.x) {
+            const BfItem it = decode(idx);
+            if (it.nst == 0) continue;
+            const uint32_t buf = item & 1;
+            if (!pf_bar_wait(&tfull[buf], (item >> 1) & 1)) { ok = false; break; }
+            pf_fence_after();
+            const int rows = MODE == BF_DOWN ? (it.shared ? A.sh : A.w).rows : 0;
+#pragma unroll 1
+            for (int c = 0; c < BF_NT / 32 && ok; c++) {
+                int v[32];
+                pf_tmem_ld32(tlane + buf * BF_NT + c * 32, v);
+                pf_tmem_wait_ld();
+                if (c == BF_NT / 32 - 1) {      // the buffer is in registers: hand it back
+                    pf_fence_before();
+                    __syncwarp();
+                    if (lane == 0) pf_bar_arrive(&tempty[buf]);
+                }
+                const int tok0 = c * 32;
+                if (tok0 >= it.tc) continue;     // uniform; the loads above still ran for the hand-back
+                if (MODE == BF_GATEUP) {
+                    // Thread `row` of quadrants 0-1 holds gate row `row`, its partner in
+                    // quadrants 2-3 the up row of the same output.  Each finishes half of
+                    // the 32 tokens: the gate thread hands over tokens 16..31, the up thread
+                    // tokens 0..15.
+                    const int half = quad >> 1;
+                    const int orow = row & 63;
+#pragma unroll
+                    for (int i = 0; i < 16; i++)
+                        s_xchg[(half ? i : 16 + i) * 64 + orow] = __int_as_float(v[half ? i : 16 + i]);
+                    if (!meet()) { ok = false; break; }
+                    const int r = it.chunk * CH + orow;   // row of mid
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const int tl = 16 * half + i, tok = tok0 + tl;
+                        if (tok >= it.tc) break;          // uniform across the warp
+                        const float other = s_xchg[tl * 64 + orow];
+                        const float gt = half ? other : __int_as_float(v[i]);
+                        const float u = half ? __int_as_float(v[16 + i]) : other;
+                        // ops.rs:160-167: silu(x) = x * (1 / (1 + exp(-x)))
+                        const float y = (gt * __fdiv_rn(1.0f, 1.0f + expf(-gt))) * u;
+                        const size_t pos = (size_t)it.pos0 + tok;
+                        A.out[((size_t)(r / 64) * A.act_rows + pos) * 64 + r % 64] = y;
+                        const __nv_bfloat16 hi = __float2bfloat16_rn(y);
+                        const __nv_bfloat16 lo = __float2bfloat16_rn(y - __bfloat162float(hi));
+                        uint8_t* rec = A.out_b + ((size_t)(r / 64) * (A.act_rows / 8) + pos / 8) * kActBRec +
+                                       act_b_off((int)(pos % 8), r % 64);
+                        *(__nv_bfloat16*)rec = hi;
+                        *(__nv_bfloat16*)(rec + kActBLo) = lo;
+                    }
+                    if (!meet()) { ok = false; break; }   // the exchange tile is free again
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        const int tok = tok0 + i;
+                        if (tok >= it.tc) break;
+                        A.out[((size_t)it.pos0 + tok) * rows + it.chunk * CH + row] = __int_as_float(v[i]);
+                    }
+                }
+            }
+            item++;
+        }
+        if (!ok && lane == 0) give_up();
+    }
+    pf_fence_before();
+    __syncthreads();
+    pf_fence_after();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
+                     "r"(BF_TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+
+template <int MODE>
+static cudaError_t launch_bf16_one(const LaunchCfg& c, Bf16Args A) {
+    A.chunks = std::max(A.w.chunks, A.sh.chunks);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(experts_prefill_bf16_kernel<MODE>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, BF_SMEM);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    experts_prefill_bf16_kernel<MODE><<<c.sm_count, BF_THREADS, BF_SMEM, c.stream>>>(A);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// gate+up then down for the groups the sort put on the prefill tile list
+cudaError_t launch_experts_prefill_bf16(const LaunchCfg& c, const DevTiles& gate_up, const DevTiles& down,
+                                        const DevTiles& sh_gate_up, const DevTiles& sh_down,
+                                        const Workspace& ws) {
+    Bf16Args A{};
+    A.grp_expert = ws.grp_expert; A.grp_start = ws.grp_start; A.grp_count = ws.grp_count;
+    A.ptile_group = ws.ptile_group; A.ptile_t0 = ws.ptile_t0; A.n_ptiles = ws.n_ptiles;
+    A.status = ws.status;
+    A.n_expert = c.n_expert;
+    A.act_rows = ws.act_rows;
+    A.tiles_mode = c.only_shared ? 2 : 0;
+    Bf16Args G = A;
+    G.w = gate_up; G.sh = sh_gate_up;
+    G.x_b = ws.act_b; G.out = ws.mid; G.out_b = ws.mid_b;
+    cudaError_t err = launch_bf16_one<BF_GATEUP>(c, G);
+    if (err != cudaSuccess) return err;
+    Bf16Args D = A;
+    D.w = down; D.sh = sh_down;
+    D.x_b = ws.mid_b; D.out = ws.pair_out; D.out_b = nullptr;
+    return launch_bf16_one<BF_DOWN>(c, D);
+}
+
+}  // namespace bivmoe

@@ -260,7 +260,7 @@ __device__ void block_exclusive_scan(int (&v)[ITEMS], int* s_warp, int* total) {
 // everything; otherwise they are summed from the per-block counts.
 constexpr int SORT_EPT = 4;   // experts per thread in the scans (n_expert <= 1024)
 __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, int k,
-                          int has_shared, int prefill_min, const int* s_cnt, int* s_off) {
+                          int has_shared, int prefill_min, int ptile, const int* s_cnt, int* s_off) {
     __shared__ int s_warp[32];
     __shared__ int s_total[4];
     int cnt[SORT_EPT], off[SORT_EPT], act[SORT_EPT], til[SORT_EPT], ptl[SORT_EPT];
@@ -280,13 +280,13 @@ __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, in
                 }
             }
         }
-        // a group of at least prefill_min tokens is cut into tiles of 128 for the
+        // a group of at least prefill_min tokens is cut into tiles of `ptile` for the
         // tcgen05 kernels, a smaller one into tiles of 8 for the decode kernels
         const bool big = prefill_min > 0 && run >= prefill_min;
         cnt[i] = run;
         off[i] = (run + SORT_TILE - 1) / SORT_TILE * SORT_TILE;
         til[i] = big ? 0 : off[i] / SORT_TILE;
-        ptl[i] = big ? (run + kPrefillTile - 1) / kPrefillTile : 0;
+        ptl[i] = big ? (run + ptile - 1) / ptile : 0;
         act[i] = run > 0;
     }
     __syncthreads();   // s_cnt is read; s_off may alias it
@@ -298,7 +298,7 @@ __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, in
     const bool big_sh = has_shared && prefill_min > 0 && n >= prefill_min;
     const int p_sh = has_shared ? (n + SORT_TILE - 1) / SORT_TILE * SORT_TILE : 0;
     const int t_sh = has_shared && !big_sh ? p_sh / SORT_TILE : 0;
-    const int pt_sh = big_sh ? (n + kPrefillTile - 1) / kPrefillTile : 0;
+    const int pt_sh = big_sh ? (n + ptile - 1) / ptile : 0;
 #pragma unroll
     for (int i = 0; i < SORT_EPT; i++) {
         const int e = e0 + i;
@@ -318,10 +318,10 @@ __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, in
                 ws.tile_group[t_sh + til[i] + j] = g;
                 ws.tile_t0[t_sh + til[i] + j] = j * SORT_TILE;
             }
-            const int npt = big ? (cnt[i] + kPrefillTile - 1) / kPrefillTile : 0;
+            const int npt = big ? (cnt[i] + ptile - 1) / ptile : 0;
             for (int j = 0; j < npt; j++) {
                 ws.ptile_group[pt_sh + ptl[i] + j] = g;
-                ws.ptile_t0[pt_sh + ptl[i] + j] = j * kPrefillTile;
+                ws.ptile_t0[pt_sh + ptl[i] + j] = j * ptile;
             }
         }
     }
@@ -331,7 +331,7 @@ __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, in
     }
     for (int j = threadIdx.x; j < pt_sh; j += blockDim.x) {
         ws.ptile_group[j] = 0;
-        ws.ptile_t0[j] = j * kPrefillTile;
+        ws.ptile_t0[j] = j * ptile;
     }
     if (threadIdx.x == 0) {
         if (has_shared) {
@@ -376,7 +376,8 @@ __device__ void sort_scatter(const Workspace& ws, const uint16_t* s_ids, const u
 }
 
 __global__ void __launch_bounds__(SORT_THREADS)
-sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int prefill_min, int phase) {
+sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int prefill_min, int ptile,
+            int phase) {
     extern __shared__ uint8_t sort_smem[];
     uint16_t* s_ids = (uint16_t*)sort_smem;
     int* s_cnt = (int*)(sort_smem + (((size_t)SORT_TOKENS * k * 2 + 15) & ~(size_t)15));
@@ -390,7 +391,7 @@ sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int prefil
         __syncthreads();
         sort_hist(s_ids, npairs, n_expert, s_cnt);
         sort_build_masks(s_ids, npairs, k, n_expert, s_mask);
-        sort_scan(ws, n_expert, 1, n, k, has_shared, prefill_min, s_cnt, s_cnt);
+        sort_scan(ws, n_expert, 1, n, k, has_shared, prefill_min, ptile, s_cnt, s_cnt);
         sort_scatter(ws, s_ids, s_mask, pair0, npairs, k, n_expert, 0, s_cnt);
         return;
     }
@@ -401,7 +402,7 @@ sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int prefil
         for (int e = threadIdx.x; e < n_expert; e += blockDim.x)
             ws.blk_counts[(size_t)blk * n_expert + e] = s_cnt[e];
     }
-    if (phase == 2) sort_scan(ws, n_expert, nblk, n, k, has_shared, prefill_min, nullptr, nullptr);
+    if (phase == 2) sort_scan(ws, n_expert, nblk, n, k, has_shared, prefill_min, ptile, nullptr, nullptr);
     if (phase == 3) {
         sort_load_ids(ws.ids, pair0, npairs, s_ids);
         __syncthreads();
@@ -421,12 +422,12 @@ cudaError_t launch_sort(const LaunchCfg& c, const Workspace& ws) {
         attr_set = true;
     }
     if (nblk == 1) {
-        sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, 0);
+        sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, c.prefill_tile, 0);
         count_launch();
     } else {
-        sort_kernel<<<nblk, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, 1);
-        sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, 2);
-        sort_kernel<<<nblk, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, 3);
+        sort_kernel<<<nblk, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, c.prefill_tile, 1);
+        sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, c.prefill_tile, 2);
+        sort_kernel<<<nblk, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, c.prefill_tile, 3);
         count_launch(3);
     }
     return cudaGetLastError();

@@ -1,6 +1,8 @@
 // Row-wise helpers around the expert products: the Q8 activation quantiser,
 // rms_norm, the weighted gather-combine, and the upload-time repack of GGUF
 // rows into the device row layout.
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 #include "formats.cuh"
 
@@ -62,6 +64,17 @@ dispatch_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, 
                 const int sl = b / 2, off = (b % 2) * 32;
                 for (int j = 0; j <= k; j++)
                     ws.act_f[((size_t)sl * R + s_pos[j]) * 64 + off + lane] = v;
+                if (ws.act_b) {   // the two bf16 terms of the row, for the tensor-core kernel
+                    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+                    const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+                    for (int j = 0; j <= k; j++) {
+                        const int pos = s_pos[j];
+                        uint8_t* rec = ws.act_b + ((size_t)sl * (R / 8) + pos / 8) * kActBRec +
+                                       act_b_off(pos % 8, off + lane);
+                        *(__nv_bfloat16*)rec = hi;
+                        *(__nv_bfloat16*)(rec + kActBLo) = lo;
+                    }
+                }
             }
         }
     }

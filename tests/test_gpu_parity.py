@@ -242,3 +242,19 @@ def test_prefill_sized_groups_q8_0():
     counts = np.bincount(oracle.moe_forward(wl.layer, wl.h, taps=True)[1]["ids"].reshape(-1),
                          minlength=8)
     assert counts.max() >= 128 and counts.min() < counts.max()   # the shape exercises both paths
+
+
+def test_prefill_sized_groups_bf16():
+    # the same for BF16 weights: tcgen05 kind::f16 over bf16 hi/lo terms of the f32 rows
+    # (tiles of 128 tokens), shared expert included, beside decode-sized groups
+    wl = W.ep_bf16(n=700, n_embd=512, n_expert=8, k=2, ff=512, ff_sh=512)
+    got, ref = run_case(wl)
+    counts = np.bincount(oracle.moe_forward(wl.layer, wl.h, taps=True)[1]["ids"].reshape(-1),
+                         minlength=8)
+    assert counts.max() >= 128
+    # a skewed router as well, so that some groups stay below the threshold
+    wl2 = W.prefill_q8_0(n=600, n_embd=512, n_expert=8, k=2, ff=512, ff_sh=512)
+    rng = np.random.default_rng(7)
+    lay = W.make_layer(rng, gate_ty=W.BF16, n_embd=512, n_expert=8, k=2, ff=512, ff_sh=512)
+    lay.router = wl2.layer.router
+    run_case(W.Workload("bf16_skewed", 7, [lay], wl2.h))
