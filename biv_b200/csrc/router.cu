@@ -105,9 +105,125 @@ router_logits_kernel(const float* __restrict__ W, const float* __restrict__ h,
         }
 }
 
+// The same product for many tokens: a block of 8 warps computes 16 rows x 64
+// tokens, a warp 8 rows x 16 tokens (128 accumulators per lane, so 24 shared-
+// memory loads feed 128 multiply-adds), over K in chunks of 128 values that a
+// three-stage ring of 16-byte asynchronous copies keeps in flight (a chunk of
+// one row is 512 bytes: too small for bulk copies to pay).  The per-lane order of the
+// multiply-adds and the order of the final lane sums are those of the small
+// kernel above, so the logits are the same bits.
+constexpr int RL_ROWS = 8, RL_TOKS = 16;              // register tile of one warp
+constexpr int RL_BROWS = 16, RL_BTOKS = 64;           // rows and tokens of one block
+constexpr int RL_KC = 128, RL_STAGES = 3;
+constexpr int RL_STAGE_FLOATS = (RL_BROWS + RL_BTOKS) * RL_KC;
+constexpr int RL_SMEM = 128 + RL_STAGES * RL_STAGE_FLOATS * 4;   // 123008
+
+// one step of the lane sums: the lanes of a pair (lane ^ M) split the 2 * HALF values
+template <int HALF, int M>
+__device__ __forceinline__ void rl_reduce_step(float (&acc)[RL_ROWS * RL_TOKS], int lane, int& base) {
+    const bool up = (lane & M) != 0;
+#pragma unroll
+    for (int j = 0; j < HALF; j++) {
+        const float a = acc[j], b = acc[j + HALF];
+        const float send = up ? a : b, keep = up ? b : a;
+        acc[j] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, M));
+    }
+    if (up) base += HALF;
+}
+
+__global__ void __launch_bounds__(RT_THREADS, 1)
+router_logits_tiled_kernel(const float* __restrict__ W, const float* __restrict__ h,
+                           float* __restrict__ logits, int n, int e, int n_rows) {
+    extern __shared__ __align__(128) uint8_t rt_smem[];
+    float* ring = (float*)(rt_smem + 128);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int br0 = blockIdx.x * RL_BROWS, bt0 = blockIdx.y * RL_BTOKS;
+    const int nchunk = e / RL_KC;
+    // every thread copies ten 16-byte pieces of chunk c into stage `c % RL_STAGES`
+    auto fill = [&](int c) {
+        float* st = ring + (size_t)(c % RL_STAGES) * RL_STAGE_FLOATS;
+        for (int p = threadIdx.x; p < (RL_BROWS + RL_BTOKS) * (RL_KC / 4); p += RT_THREADS) {
+            const int r = p / (RL_KC / 4), q4 = p % (RL_KC / 4);   // rows past the end repeat the last one
+            const float* src = (r < RL_BROWS ? W + (size_t)min(br0 + r, n_rows - 1) * e
+                                             : h + (size_t)min(bt0 + r - RL_BROWS, n - 1) * e) +
+                               (size_t)c * RL_KC + q4 * 4;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                             rt_smem_u32(st + (size_t)r * RL_KC + q4 * 4)),
+                         "l"(src)
+                         : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (int c = 0; c < RL_STAGES - 1; c++) {
+        if (c < nchunk) fill(c);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    const int r0 = (warp & 1) * RL_ROWS, t0 = (warp >> 1) * RL_TOKS;   // inside the block
+    float acc[RL_ROWS * RL_TOKS];
+#pragma unroll
+    for (int i = 0; i < RL_ROWS * RL_TOKS; i++) acc[i] = 0.0f;
+    for (int c = 0; c < nchunk; c++) {
+        // chunk c has landed (one younger group may still be in flight); after the barrier
+        // everyone is also done with chunk c - 1, whose stage chunk c + RL_STAGES - 1 reuses
+        asm volatile("cp.async.wait_group %0;" ::"n"(RL_STAGES - 2) : "memory");
+        __syncthreads();
+        if (c + RL_STAGES - 1 < nchunk) fill(c + RL_STAGES - 1);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        const float* sw = ring + (size_t)(c % RL_STAGES) * RL_STAGE_FLOATS + (size_t)r0 * RL_KC;
+        const float* sx = ring + (size_t)(c % RL_STAGES) * RL_STAGE_FLOATS +
+                          (size_t)(RL_BROWS + t0) * RL_KC;
+#pragma unroll
+        for (int kk = 0; kk < RL_KC / 32; kk++) {
+            const int i = kk * 32 + lane;
+            float w[RL_ROWS], x[RL_TOKS];
+#pragma unroll
+            for (int r = 0; r < RL_ROWS; r++) w[r] = sw[r * RL_KC + i];
+#pragma unroll
+            for (int t = 0; t < RL_TOKS; t++) x[t] = sx[t * RL_KC + i];
+#pragma unroll
+            for (int r = 0; r < RL_ROWS; r++)
+#pragma unroll
+                for (int t = 0; t < RL_TOKS; t++)
+                    acc[r * RL_TOKS + t] = fmaf(w[r], x[t], acc[r * RL_TOKS + t]);
+        }
+    }
+    // Lane sums in the order 8, 16, 4, 2, 1.  Each step halves the values a lane
+    // carries: a lane keeps the half chosen by its bit of the step and gives the
+    // other half to its partner, which adds the same two numbers as a full
+    // butterfly would.  A lane ends with 4 of the warp's 128 outputs.
+    int base = 0;
+    rl_reduce_step<64, 8>(acc, lane, base);
+    rl_reduce_step<32, 16>(acc, lane, base);
+    rl_reduce_step<16, 4>(acc, lane, base);
+    rl_reduce_step<8, 2>(acc, lane, base);
+    rl_reduce_step<4, 1>(acc, lane, base);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int o = base + j;
+        const int row = br0 + r0 + o / RL_TOKS, tok = bt0 + t0 + o % RL_TOKS;
+        if (row < n_rows && tok < n) logits[(size_t)tok * n_rows + row] = acc[j];
+    }
+}
+
+constexpr int RL_MIN_TOKENS = 256;   // from here on the tiled kernel is the faster one
+
 cudaError_t launch_router(const LaunchCfg& c, const float* router_dev, const float* h,
                           const Workspace& ws) {
     int n_rows = c.n_expert + 1;
+    if (c.n >= RL_MIN_TOKENS && c.e % RL_KC == 0) {
+        static bool attr_set = false;
+        if (!attr_set) {
+            cudaError_t err = cudaFuncSetAttribute(router_logits_tiled_kernel,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, RL_SMEM);
+            if (err != cudaSuccess) return err;
+            attr_set = true;
+        }
+        dim3 grid((n_rows + RL_BROWS - 1) / RL_BROWS, (c.n + RL_BTOKS - 1) / RL_BTOKS);
+        router_logits_tiled_kernel<<<grid, RT_THREADS, RL_SMEM, c.stream>>>(router_dev, h, ws.logits, c.n,
+                                                                           c.e, n_rows);
+        count_launch();
+        return cudaGetLastError();
+    }
     const int smem = 128 + (RT_BROWS + RT_BTOKS) * c.e * 4;
     if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
     static bool attr_set = false;

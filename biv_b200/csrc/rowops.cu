@@ -18,17 +18,33 @@ namespace bivmoe {
 // function of the row alone.  One block per token, one warp per 32-value block.
 constexpr int DP_THREADS = 256, DP_MAX_K = 32;
 
+// s_pos[j]: the position of pair j (j < k) and, as entry k, the token's position in the
+// shared expert's group; s_big[j]: whether that position's group is large enough for
+// the tcgen05 kernels.  Without a shared expert entry k repeats the first pair.
+__device__ __forceinline__ void dispatch_positions(const Workspace& ws, int t, int n, int k, int n_expert,
+                                                   int has_shared, int prefill_min, int* s_pos,
+                                                   int* s_big) {
+    if (threadIdx.x < k) {
+        s_pos[threadIdx.x] = ws.pos_of[(size_t)t * k + threadIdx.x];
+        s_big[threadIdx.x] = prefill_min > 0 && ws.counts[ws.ids[(size_t)t * k + threadIdx.x]] >= prefill_min;
+    }
+    if (threadIdx.x == k) {
+        s_pos[k] = has_shared ? t : ws.pos_of[(size_t)t * k];
+        s_big[k] = has_shared ? (prefill_min > 0 && n >= prefill_min)
+                              : (prefill_min > 0 && ws.counts[ws.ids[(size_t)t * k]] >= prefill_min);
+    }
+    __syncthreads();
+}
+
+// Quantised rows.  One warp per 32-value block; the block's 32 int8 are gathered
+// into two 16-byte units by shuffles, so a position costs two 16-byte stores
+// instead of 32 single bytes.
 __global__ void __launch_bounds__(DP_THREADS)
-dispatch_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int quant, int f32,
-                int has_shared) {
-    __shared__ int s_pos[DP_MAX_K + 1];
+dispatch_q8_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int has_shared) {
+    __shared__ int s_pos[DP_MAX_K + 1], s_big[DP_MAX_K + 1];
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int R = ws.act_rows;
-    if (threadIdx.x < k) s_pos[threadIdx.x] = ws.pos_of[(size_t)t * k + threadIdx.x];
-    // the shared expert's group is positions 0..n; without one, position t belongs to
-    // a routed group and the extra copy is dropped (the first pair's position is repeated)
-    if (threadIdx.x == k) s_pos[k] = has_shared ? t : ws.pos_of[(size_t)t * k];
-    __syncthreads();
+    dispatch_positions(ws, t, n, k, 0, has_shared, 0, s_pos, s_big);
     const float* x = h + (size_t)t * e;
     constexpr int NW = DP_THREADS / 32, U = 4;   // U loads in flight per lane
     // blockIdx.y halves the row between two blocks
@@ -43,49 +59,164 @@ dispatch_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, 
         for (int u = 0; u < U; u++) {
             const int b = b0 + u * NW;
             if (b >= e / 32) break;
-            const float v = vv[u];
-            if (quant) {
-                float dd, ss;
-                const int q = q8_quantize_lane(v, dd, ss);
-                const int sl = b / 8, bb = b % 8;
-                float shi, slo;
-                split_tf32(ss, &shi, &slo);
-                for (int j = 0; j <= k; j++) {
-                    const int pos = s_pos[j];
-                    uint8_t* rec = ws.act_t + ((size_t)sl * (R / 8) + pos / 8) * kActTileBytes;
-                    rec[act_q_off(pos % 8, 32 * bb + lane)] = (uint8_t)(int8_t)q;
-                    if (lane < 4) {
-                        const float val = lane == 0 ? dd : lane == 1 ? shi : lane == 2 ? slo : ss;
-                        *(float*)(rec + kActOffDx + 256 * lane + (bb * 8 + pos % 8) * 4) = val;
-                    }
-                }
-            }
-            if (f32) {
-                const int sl = b / 2, off = (b % 2) * 32;
-                for (int j = 0; j <= k; j++)
-                    ws.act_f[((size_t)sl * R + s_pos[j]) * 64 + off + lane] = v;
-                if (ws.act_b) {   // the two bf16 terms of the row, for the tensor-core kernel
-                    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
-                    const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
-                    for (int j = 0; j <= k; j++) {
-                        const int pos = s_pos[j];
-                        uint8_t* rec = ws.act_b + ((size_t)sl * (R / 8) + pos / 8) * kActBRec +
-                                       act_b_off(pos % 8, off + lane);
-                        *(__nv_bfloat16*)rec = hi;
-                        *(__nv_bfloat16*)(rec + kActBLo) = lo;
-                    }
+            float dd, ss;
+            const int q = q8_quantize_lane(vv[u], dd, ss);
+            const int sl = b / 8, bb = b % 8;
+            float shi, slo;
+            split_tf32(ss, &shi, &slo);
+            // bytes of lanes l..l+3 in one word (lanes with l % 4 == 0), then four words
+            uint32_t w = (uint32_t)q & 0xffu;
+            w |= __shfl_down_sync(0xffffffffu, w, 1) << 8;
+            w |= __shfl_down_sync(0xffffffffu, w, 2) << 16;
+            uint4 unit;
+            unit.x = w;
+            unit.y = __shfl_down_sync(0xffffffffu, w, 4);
+            unit.z = __shfl_down_sync(0xffffffffu, w, 8);
+            unit.w = __shfl_down_sync(0xffffffffu, w, 12);
+            for (int j = 0; j <= k; j++) {
+                const int pos = s_pos[j];
+                uint8_t* rec = ws.act_t + ((size_t)sl * (R / 8) + pos / 8) * kActTileBytes;
+                if ((lane & 15) == 0)   // elements 32*bb + lane .. + 15: unit 2*bb + lane/16
+                    *(uint4*)(rec + act_q_off(pos % 8, 32 * bb + lane)) = unit;
+                if (lane < 4) {
+                    const float val = lane == 0 ? dd : lane == 1 ? shi : lane == 2 ? slo : ss;
+                    *(float*)(rec + kActOffDx + 256 * lane + (bb * 8 + pos % 8) * 4) = val;
                 }
             }
         }
     }
 }
 
+// Float rows (BF16 weights).  A thread owns 8 consecutive values: two float4 stores
+// per position of a decode-sized group (slice-major f32 rows), or one 16-byte unit
+// of each bf16 term per position of a group the tcgen05 kernel will take.
+__global__ void __launch_bounds__(DP_THREADS)
+dispatch_f32_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int has_shared,
+                    int prefill_min) {
+    __shared__ int s_pos[DP_MAX_K + 1], s_big[DP_MAX_K + 1];
+    const int t = blockIdx.x;
+    const int R = ws.act_rows;
+    dispatch_positions(ws, t, n, k, 0, has_shared, ws.act_b ? prefill_min : 0, s_pos, s_big);
+    const float* x = h + (size_t)t * e;
+    for (int i0 = threadIdx.x * 8; i0 < e; i0 += DP_THREADS * 8) {
+        const float4 a = *(const float4*)(x + i0), b = *(const float4*)(x + i0 + 4);
+        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            const __nv_bfloat16 h0 = __float2bfloat16_rn(v[2 * p]), h1 = __float2bfloat16_rn(v[2 * p + 1]);
+            const __nv_bfloat16 l0 = __float2bfloat16_rn(v[2 * p] - __bfloat162float(h0));
+            const __nv_bfloat16 l1 = __float2bfloat16_rn(v[2 * p + 1] - __bfloat162float(h1));
+            hi[p] = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+            lo[p] = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
+        }
+        const int sl = i0 / 64, off = i0 % 64;
+        for (int j = 0; j <= k; j++) {
+            const int pos = s_pos[j];
+            if (s_big[j]) {
+                uint8_t* rec = ws.act_b + ((size_t)sl * (R / 8) + pos / 8) * kActBRec + act_b_off(pos % 8, off);
+                *(uint4*)rec = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *(uint4*)(rec + kActBLo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            } else {
+                float* dst = ws.act_f + ((size_t)sl * R + pos) * 64 + off;
+                *(float4*)dst = a;
+                *(float4*)(dst + 4) = b;
+            }
+        }
+    }
+}
+
+// Float rows by position, for many tokens: one block per tile of 8 positions.  It
+// finds the tile's group, reads the 8 source rows (a row is read once per position
+// it occupies, mostly from L2) and writes whole records, so that the pieces of a
+// record - which interleave 8 tokens - are written together, 512 contiguous bytes
+// per warp.  (For quantised rows the same arrangement measured slower than the
+// by-token kernel: it quantises a row once per position.)
+constexpr int DP_MIN_TOKENS = 256;   // from here on the by-position kernel is the faster one
+
+__device__ __forceinline__ bool dispatch_tile(const Workspace& ws, int pos0, int n, int k, int n_expert,
+                                              int has_shared, int prefill_min, int* s_tok, int* s_big) {
+    if (pos0 >= ws.offsets[n_expert]) return false;   // past the last group (uniform: whole block)
+    if (threadIdx.x < 8) {
+        const int p = pos0 + threadIdx.x;
+        int start, count, tok = -1;
+        if (has_shared && pos0 < (n + 7) / 8 * 8) {
+            start = 0; count = n;
+            if (p < n) tok = p;
+        } else {
+            int lo = 0, hi = n_expert;   // the last expert whose first position is <= pos0
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (ws.offsets[mid] <= pos0) lo = mid; else hi = mid;
+            }
+            start = ws.offsets[lo]; count = ws.counts[lo];
+            if (p - start < count) tok = ws.order[p] / k;
+        }
+        s_tok[threadIdx.x] = tok;
+        if (threadIdx.x == 0) *s_big = prefill_min > 0 && count >= prefill_min;
+    }
+    __syncthreads();
+    return true;
+}
+
+__global__ void __launch_bounds__(DP_THREADS)
+dispatch_pos_f32_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int n_expert,
+                        int has_shared, int prefill_min) {
+    __shared__ int s_tok[8], s_big;
+    const int pos0 = blockIdx.x * 8;
+    if (!dispatch_tile(ws, pos0, n, k, n_expert, has_shared, ws.act_b ? prefill_min : 0, s_tok, &s_big))
+        return;
+    // thread (tk, u): 8 consecutive values of token tk; the 8 threads of a unit write
+    // 128 contiguous bytes of a record, a warp 512
+    const int tk = threadIdx.x & 7, u0 = threadIdx.x >> 3;
+    const int tok = s_tok[tk], big = s_big;
+    if (tok < 0) return;
+    const int R = ws.act_rows;
+    const float* x = h + (size_t)tok * e;
+    for (int i0 = u0 * 8; i0 < e; i0 += (DP_THREADS / 8) * 8) {
+        const float4 a = *(const float4*)(x + i0), b = *(const float4*)(x + i0 + 4);
+        const int sl = i0 / 64, off = i0 % 64;
+        if (big) {
+            const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int p = 0; p < 4; p++) {
+                const __nv_bfloat16 h0 = __float2bfloat16_rn(v[2 * p]), h1 = __float2bfloat16_rn(v[2 * p + 1]);
+                const __nv_bfloat16 l0 = __float2bfloat16_rn(v[2 * p] - __bfloat162float(h0));
+                const __nv_bfloat16 l1 = __float2bfloat16_rn(v[2 * p + 1] - __bfloat162float(h1));
+                hi[p] = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+                lo[p] = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
+            }
+            uint8_t* rec = ws.act_b + ((size_t)sl * (R / 8) + pos0 / 8) * kActBRec + act_b_off(tk, off);
+            *(uint4*)rec = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *(uint4*)(rec + kActBLo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        } else {
+            float* dst = ws.act_f + ((size_t)sl * R + pos0 + tk) * 64 + off;
+            *(float4*)dst = a;
+            *(float4*)(dst + 4) = b;
+        }
+    }
+}
+
 cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace& ws, bool quant,
                             bool f32) {
-    if (c.k > DP_MAX_K) return cudaErrorInvalidValue;
-    dispatch_kernel<<<dim3(c.n, 2), DP_THREADS, 0, c.stream>>>(h, ws, c.n, c.k, c.e, quant ? 1 : 0, f32 ? 1 : 0,
-                                                      c.has_shared);
-    count_launch();
+    if (c.k > DP_MAX_K || c.e % 256) return cudaErrorInvalidValue;
+    if (quant) {
+        dispatch_q8_kernel<<<dim3(c.n, 2), DP_THREADS, 0, c.stream>>>(h, ws, c.n, c.k, c.e, c.has_shared);
+        count_launch();
+    }
+    if (f32 && c.n >= DP_MIN_TOKENS) {
+        // an upper bound of the tiles in use; blocks past the last group return at once
+        const int shared_tiles = c.has_shared ? (c.n + 7) / 8 : 0;
+        const int tiles = c.k == 0 ? shared_tiles : shared_tiles + (c.n * c.k) / 8 + c.n_expert;
+        dispatch_pos_f32_kernel<<<tiles, DP_THREADS, 0, c.stream>>>(h, ws, c.n, max(c.k, 1), c.e, c.n_expert,
+                                                                    c.has_shared, c.prefill_min);
+        count_launch();
+    } else if (f32) {
+        dispatch_f32_kernel<<<c.n, DP_THREADS, 0, c.stream>>>(h, ws, c.n, c.k, c.e, c.has_shared,
+                                                             c.prefill_min);
+        count_launch();
+    }
     return cudaGetLastError();
 }
 
