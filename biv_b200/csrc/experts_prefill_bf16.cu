@@ -15,12 +15,15 @@
 //
 // Design.  One block per SM, five warps: warp 0 lane 0 issues the copies, lane 1
 // the MMAs; four epilogue warps own the 128 tensor-memory lanes.  A work item is
-// a tile of 128 tokens of one group times a chunk of 128 weight rows (64 gate
-// rows with their 64 up rows, or 128 down rows).  A pipeline stage is one
-// K-slice of 64 values: 128 rows x 128 bytes of weights and the tile's 16
-// activation records (hi and lo), both already in the tensor core's canonical
-// K-major layout (common.cuh), so a stage is two bulk copies.  Per stage the MMA
-// thread issues 2 terms x 4 K-steps (M = 128, N = 128, K = 16) accumulating into
+// a tile of 128 tokens of one group times TWO chunks of 128 weight rows (a chunk:
+// 64 gate rows with their 64 up rows, or 128 down rows).  A pipeline stage is one
+// K-slice of 64 values: 128 rows x 128 bytes of weights per chunk and the tile's
+// 16 activation records (hi and lo), all already in the tensor core's canonical
+// K-major layout (common.cuh), so a stage is three bulk copies.  The kernel is
+// bound by what an SM can pull from L2, and the activation records are two
+// thirds of a one-chunk stage: sharing them between two chunks cuts the bytes per
+// multiply-add by a third.  Per stage the MMA thread issues, per chunk, 2 terms x
+// 4 K-steps (M = 128, N = 128, K = 16) accumulating into that chunk's half of
 // one of two tensor-memory buffers; unlike the Q8_0 kernel nothing is scaled per
 // block, so the epilogue runs once per item, while the next item's MMAs fill the
 // other buffer.  Every wait is bounded; a wait that gives up records
@@ -40,12 +43,14 @@ constexpr int BF_EPI_WARPS = 4;
 constexpr int BF_THREADS = 32 * (1 + BF_EPI_WARPS);
 constexpr uint32_t BF_W_BYTES = kChunkRows * 128;               // 16384: one K-slice of a chunk
 constexpr uint32_t BF_X_BYTES = (BF_NT / 8) * kActBRec;         // 32768
-constexpr uint32_t BF_STAGE = BF_W_BYTES + BF_X_BYTES;          // 49152
-constexpr int BF_NSTAGE = 4;
+constexpr int BF_MC = 2;                                        // chunks per item
+constexpr uint32_t BF_STAGE = BF_MC * BF_W_BYTES + BF_X_BYTES;  // 65536
+constexpr int BF_NSTAGE = 3;
 constexpr uint32_t BF_HEAD = 1024;
 constexpr uint32_t BF_XCHG = 64 * 32 * 4;                       // SwiGLU exchange of 32 tokens
 constexpr uint32_t BF_SMEM = BF_HEAD + BF_NSTAGE * BF_STAGE + BF_XCHG;   // 205824
-constexpr uint32_t BF_TMEM_COLS = 256;                          // two buffers of 128 columns
+constexpr uint32_t BF_TMEM_COLS = 512;                          // two buffers of 2 x 128 columns
+constexpr uint32_t BF_TBUF = BF_MC * BF_NT;                     // columns of one buffer
 
 enum { BF_GATEUP = 0, BF_DOWN = 1 };
 
@@ -68,16 +73,17 @@ struct Bf16Args {
 };
 
 struct BfItem {
-    int shared, expert, chunk, pos0, tc, nst;
-    const uint8_t* wsrc;   // stage 0 of the chunk's weights; stage s is s * BF_W_BYTES further
+    int shared, expert, chunk, nch, pos0, tc, nst;   // chunks chunk .. chunk + nch - 1
+    const uint8_t* wsrc;   // stage 0 of the first chunk's weights; stage s is s * BF_W_BYTES
+    size_t wstep;          // further, the next chunk wstep further
 };
 
 template <int MODE>
 __global__ void __launch_bounds__(BF_THREADS, 1)
 experts_prefill_bf16_kernel(const Bf16Args A) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint64_t* full = (uint64_t*)smem;            // [4] copies landed
-    uint64_t* empty = full + 4;                  // [4] stage free: its MMAs are done
+    uint64_t* full = (uint64_t*)smem;            // [3] copies landed
+    uint64_t* empty = full + 4;                  // [3] stage free: its MMAs are done
     uint64_t* tfull = full + 8;                  // [2] an item's products are in tensor memory
     uint64_t* tempty = full + 10;                // [2] drained by the epilogue warps
     uint64_t* xbar = full + 12;                  // [1] meeting point of the epilogue warps
@@ -117,22 +123,24 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
     const int tiles_all = A.n_ptiles[0], tiles_sh = A.n_ptiles[1];
     const int tile_lo = A.tiles_mode == 1 ? tiles_sh : 0;
     const int tile_hi = A.tiles_mode == 2 ? tiles_sh : tiles_all;
-    const int total = (tile_hi - tile_lo) * A.chunks;
+    const int cpairs = (A.chunks + BF_MC - 1) / BF_MC;
+    const int total = (tile_hi - tile_lo) * cpairs;
 
-    // Items are dealt round-robin, chunk-major: consecutive blocks take the same
-    // chunk of consecutive tiles... every role walks the same sequence on its own.
+    // items are dealt round-robin; every role walks the same sequence on its own
     auto decode = [&](int idx) -> BfItem {
         BfItem it;
-        const int tile = tile_lo + idx / A.chunks;
-        it.chunk = idx % A.chunks;
+        const int tile = tile_lo + idx / cpairs;
+        it.chunk = (idx % cpairs) * BF_MC;
         const int gi = A.ptile_group[tile], t0 = A.ptile_t0[tile];
         it.expert = A.grp_expert[gi];
         it.shared = it.expert == A.n_expert;
         it.pos0 = A.grp_start[gi] + t0;
         it.tc = min(BF_NT, A.grp_count[gi] - t0);
         const DevTiles& m = it.shared ? A.sh : A.w;
-        it.nst = it.chunk < m.chunks ? m.nslices : 0;
+        it.nch = max(0, min(BF_MC, m.chunks - it.chunk));
+        it.nst = it.nch > 0 ? m.nslices : 0;
         it.wsrc = m.stage(it.shared ? 0 : it.expert, min(it.chunk, max(m.chunks - 1, 0)), 0);
+        it.wstep = (size_t)m.nslices * BF_W_BYTES;
         return it;
     };
     auto give_up = [&]() {
@@ -150,9 +158,11 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
                 const uint32_t slot = q % BF_NSTAGE;
                 if (!pf_bar_wait(&empty[slot], ((q / BF_NSTAGE) & 1) ^ 1)) { give_up(); dead = true; break; }
                 uint8_t* dst = stages + slot * BF_STAGE;
-                pf_bar_expect_tx(&full[slot], BF_STAGE);
-                pf_bulk_g2s(dst, it.wsrc + (size_t)s * BF_W_BYTES, BF_W_BYTES, &full[slot]);
-                pf_bulk_g2s(dst + BF_W_BYTES,
+                pf_bar_expect_tx(&full[slot], it.nch * BF_W_BYTES + BF_X_BYTES);
+                for (int ch = 0; ch < it.nch; ch++)
+                    pf_bulk_g2s(dst + ch * BF_W_BYTES, it.wsrc + ch * it.wstep + (size_t)s * BF_W_BYTES,
+                                BF_W_BYTES, &full[slot]);
+                pf_bulk_g2s(dst + BF_MC * BF_W_BYTES,
                             A.x_b + ((size_t)s * (A.act_rows / 8) + it.pos0 / 8) * kActBRec, BF_X_BYTES,
                             &full[slot]);
             }
@@ -173,19 +183,21 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
                 if (!pf_bar_wait(&full[slot], (q / BF_NSTAGE) & 1)) { give_up(); dead = true; break; }
                 pf_fence_after();
                 const uint32_t wa = pf_smem(stages + slot * BF_STAGE);
-                const uint32_t xa = wa + BF_W_BYTES;
+                const uint32_t xa = wa + BF_MC * BF_W_BYTES;
+                for (int ch = 0; ch < it.nch; ch++)
 #pragma unroll
-                for (int term = 0; term < 2; term++)
+                    for (int term = 0; term < 2; term++)
 #pragma unroll
-                    for (int ks = 0; ks < 4; ks++) {
-                        // A: the chunk's rows, units 2ks and 2ks+1 (16 bf16 of K): 8-row groups
-                        //    128 B apart, the two units 2048 B apart.  B: the tokens' hi or lo
-                        //    term, the same units of each record: 8-token groups one record
-                        //    apart, the two units 128 B apart.
-                        const uint64_t ad = pf_desc(wa + 2 * ks * (kChunkRows * 16), kChunkRows * 16, 128);
-                        const uint64_t bd = pf_desc(xa + term * kActBLo + 2 * ks * 128, 128, kActBRec);
-                        pf_mma_bf16(tmem + buf * BF_NT, ad, bd, idesc, (s | term | ks) != 0);
-                    }
+                        for (int ks = 0; ks < 4; ks++) {
+                            // A: the chunk's rows, units 2ks and 2ks+1 (16 bf16 of K): 8-row groups
+                            //    128 B apart, the two units 2048 B apart.  B: the tokens' hi or lo
+                            //    term, the same units of each record: 8-token groups one record
+                            //    apart, the two units 128 B apart.
+                            const uint64_t ad = pf_desc(wa + ch * BF_W_BYTES + 2 * ks * (kChunkRows * 16),
+                                                        kChunkRows * 16, 128);
+                            const uint64_t bd = pf_desc(xa + term * kActBLo + 2 * ks * 128, 128, kActBRec);
+                            pf_mma_bf16(tmem + buf * BF_TBUF + ch * BF_NT, ad, bd, idesc, (s | term | ks) != 0);
+                        }
                 pf_commit(&empty[slot]);   // the stage's operands are no longer read
             }
             if (!dead) pf_commit(&tfull[buf]);
@@ -212,12 +224,14 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
             if (!pf_bar_wait(&tfull[buf], (item >> 1) & 1)) { ok = false; break; }
             pf_fence_after();
             const int rows = MODE == BF_DOWN ? (it.shared ? A.sh : A.w).rows : 0;
+            const int ncol = it.nch * (BF_NT / 32);   // 32-column pieces: chunk cc / 4, tokens 32 * (cc % 4)
 #pragma unroll 1
-            for (int c = 0; c < BF_NT / 32 && ok; c++) {
+            for (int cc = 0; cc < ncol && ok; cc++) {
+                const int c = cc % (BF_NT / 32), chunk = it.chunk + cc / (BF_NT / 32);
                 int v[32];
-                pf_tmem_ld32(tlane + buf * BF_NT + c * 32, v);
+                pf_tmem_ld32(tlane + buf * BF_TBUF + cc * 32, v);
                 pf_tmem_wait_ld();
-                if (c == BF_NT / 32 - 1) {      // the buffer is in registers: hand it back
+                if (cc == ncol - 1) {           // the buffer is in registers: hand it back
                     pf_fence_before();
                     __syncwarp();
                     if (lane == 0) pf_bar_arrive(&tempty[buf]);
@@ -235,7 +249,7 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
                     for (int i = 0; i < 16; i++)
                         s_xchg[(half ? i : 16 + i) * 64 + orow] = __int_as_float(v[half ? i : 16 + i]);
                     if (!meet()) { ok = false; break; }
-                    const int r = it.chunk * CH + orow;   // row of mid
+                    const int r = chunk * CH + orow;      // row of mid
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
                         const int tl = 16 * half + i, tok = tok0 + tl;
@@ -260,7 +274,7 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
                     for (int i = 0; i < 32; i++) {
                         const int tok = tok0 + i;
                         if (tok >= it.tc) break;
-                        A.out[((size_t)it.pos0 + tok) * rows + it.chunk * CH + row] = __int_as_float(v[i]);
+                        A.out[((size_t)it.pos0 + tok) * rows + chunk * CH + row] = __int_as_float(v[i]);
                     }
                 }
             }
