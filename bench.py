@@ -372,7 +372,7 @@ def main():
             dist.destroy_process_group()
         return
 
-    hbm_peak, _, peak_kind = load_peaks()
+    hbm_peak, tf_peak, peak_kind = load_peaks()
     ms_step = ms / args.steps
     value = world * n * args.steps / (ms * 1e-3)
     kbytes = gateup_bytes(layer, n, experts_hit)
@@ -397,6 +397,34 @@ def main():
         "gpu_launches": launches,
         "clocks": sampler.summary(),
     }
+    if args.workload in ("prefill_q8_0", "ep_bf16") and stage_ms:
+        # prefill-sized groups: the expert products are the dense contraction; report the
+        # tensor-pipe roofline of the expert kernels (gate+up, SwiGLU, down) together
+        st = line["roofline"]["stage_ms"]
+        t_exp = (st["gateup"] + st["down"]) * 1e-3
+        k, e, ff = layer.n_expert_used, layer.n_embd, layer.n_ff_exp
+        ops = 2.0 * n * (k + (1 if layer.has_shared else 0)) * 3 * e * ff
+        int8 = args.workload == "prefill_q8_0"
+        peak = tf_peak * 2 if int8 else tf_peak
+        line["roofline"] = {
+            "bound": "tensor", "kernel": "experts_prefill_kernel (tcgen05 kind::i8)" if int8
+            else "experts_prefill_bf16_kernel (tcgen05 kind::f16)",
+            "achieved": ops / t_exp / 1e12, "peak": peak,
+            "peak_kind": f"2 x bf16 {peak_kind} (no int8 peak was measured)" if int8 else f"of {peak_kind}",
+            "unit": "TOP/s" if int8 else "TFLOP/s", "frac": ops / t_exp / 1e12 / peak, "traffic": None,
+            "kernel_ms": t_exp * 1e3, "stage_ms": st, "experts_hit": experts_hit,
+            "note": "achieved counts the reference's multiply-adds once; the BF16 kernel issues "
+                    "two MMAs per multiply-add (f32 rows as two bf16 terms)" if not int8 else
+                    "every 32-wide block dot is one MMA whose int32 result is scaled in f32 by the "
+                    "epilogue warps, which bound the kernel",
+        }
+        line["dtype"] = ("int8 x int8 -> int32 block dots, f32 scales" if int8
+                         else "bf16 weights x f32 activations (two bf16 terms), f32 accumulation")
+    if args.workload == "decode_q4k" and n == 64:
+        # dram__bytes_read.sum + dram__bytes_write.sum of this kernel on this workload
+        # (profiles/experts_kernel_decode_q4k.md)
+        line["roofline"]["traffic"] = 108.0e6
+        line["roofline"]["traffic_source"] = "ncu capture of the same command with one weight copy"
     if ep:
         line["ep"] = ep
     if not args.no_cpu:

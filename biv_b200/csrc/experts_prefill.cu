@@ -79,6 +79,7 @@ struct PrefillArgs {
 
 struct PfItem {
     int shared, expert, chunk, pos0, tc, nst;
+    int n_mma;             // tc rounded up to the MMA's N granularity of 16 (ragged last tiles)
     const uint8_t* wsrc;   // stage 0 of the chunk's weights; stage s is s * PF_W_BYTES further
 };
 
@@ -139,6 +140,7 @@ experts_prefill_kernel(const PrefillArgs A) {
         it.shared = it.expert == A.n_expert;
         it.pos0 = A.grp_start[gi] + t0;
         it.tc = min(PF_NT, A.grp_count[gi] - t0);
+        it.n_mma = (it.tc + 15) & ~15;
         const DevTiles& m = it.shared ? A.sh : A.w;
         it.nst = it.chunk < m.chunks ? m.nslices : 0;
         it.wsrc = m.stage(it.shared ? 0 : it.expert, min(it.chunk, max(m.chunks - 1, 0)), 0);
@@ -160,22 +162,23 @@ experts_prefill_kernel(const PrefillArgs A) {
                     const uint32_t slot = q & 1;
                     if (!pf_bar_wait(&empty[slot], ((q >> 1) & 1) ^ 1)) { give_up(); dead = true; break; }
                     uint8_t* dst = stages + slot * PF_STAGE;
-                    pf_bar_expect_tx(&full[slot], PF_STAGE);
+                    const uint32_t x_bytes = (uint32_t)(it.n_mma / 8) * kActTileBytes;
+                    pf_bar_expect_tx(&full[slot], PF_W_BYTES + x_bytes);
                     pf_bulk_g2s(dst, it.wsrc + (size_t)s * PF_W_BYTES, PF_W_BYTES, &full[slot]);
                     pf_bulk_g2s(dst + PF_W_BYTES,
                                 A.x_t + ((size_t)s * (A.act_rows / 8) + it.pos0 / 8) * kActTileBytes,
-                                PF_X_BYTES, &full[slot]);
+                                x_bytes, &full[slot]);
                 }
             }
         }
     } else if (warp == 0) {
         // ---------------- MMA thread: one MMA per 32-column block
         {
-            const uint32_t idesc = pf_idesc(kChunkRows, PF_NT);
             uint32_t q = 0, kb = 0;
             bool dead = false;
             for (int idx = blockIdx.x; idx < total && !dead && !*(volatile int*)s_abort; idx += gridDim.x) {
                 const PfItem it = decode(idx);
+                const uint32_t idesc = pf_idesc(kChunkRows, it.n_mma);
                 for (int s = 0; s < it.nst && !dead; s++, q++) {
                     const uint32_t slot = q & 1;
                     if (!pf_bar_wait(&full[slot], (q >> 1) & 1)) { give_up(); dead = true; break; }
@@ -229,7 +232,8 @@ experts_prefill_kernel(const PrefillArgs A) {
                     const uint32_t buf = kb % PF_TBUF;
                     if (!pf_bar_wait(&tfull[buf], (kb / PF_TBUF) & 1)) { ok = false; break; }
                     pf_fence_after();
-                    // drain this warp's 32 columns and hand the buffer back
+                    // drain this warp's 32 columns and hand the buffer back (a warp whose
+                    // columns lie past the end of a ragged tile only hands back)
                     int v[32];
                     pf_tmem_ld32(tlane + buf * PF_TSTRIDE, v);
                     pf_tmem_wait_ld();

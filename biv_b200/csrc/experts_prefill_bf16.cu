@@ -74,6 +74,8 @@ struct Bf16Args {
 
 struct BfItem {
     int shared, expert, chunk, nch, pos0, tc, nst;   // chunks chunk .. chunk + nch - 1
+    int n_mma;             // tc rounded up to the MMA's N granularity of 16: a ragged last
+                           // tile costs MMA time and activation bytes for its own tokens only
     const uint8_t* wsrc;   // stage 0 of the first chunk's weights; stage s is s * BF_W_BYTES
     size_t wstep;          // further, the next chunk wstep further
 };
@@ -136,6 +138,7 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
         it.shared = it.expert == A.n_expert;
         it.pos0 = A.grp_start[gi] + t0;
         it.tc = min(BF_NT, A.grp_count[gi] - t0);
+        it.n_mma = (it.tc + 15) & ~15;
         const DevTiles& m = it.shared ? A.sh : A.w;
         it.nch = max(0, min(BF_MC, m.chunks - it.chunk));
         it.nst = it.nch > 0 ? m.nslices : 0;
@@ -158,24 +161,25 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
                 const uint32_t slot = q % BF_NSTAGE;
                 if (!pf_bar_wait(&empty[slot], ((q / BF_NSTAGE) & 1) ^ 1)) { give_up(); dead = true; break; }
                 uint8_t* dst = stages + slot * BF_STAGE;
-                pf_bar_expect_tx(&full[slot], it.nch * BF_W_BYTES + BF_X_BYTES);
+                const uint32_t x_bytes = (uint32_t)(it.n_mma / 8) * kActBRec;
+                pf_bar_expect_tx(&full[slot], it.nch * BF_W_BYTES + x_bytes);
                 for (int ch = 0; ch < it.nch; ch++)
                     pf_bulk_g2s(dst + ch * BF_W_BYTES, it.wsrc + ch * it.wstep + (size_t)s * BF_W_BYTES,
                                 BF_W_BYTES, &full[slot]);
                 pf_bulk_g2s(dst + BF_MC * BF_W_BYTES,
-                            A.x_b + ((size_t)s * (A.act_rows / 8) + it.pos0 / 8) * kActBRec, BF_X_BYTES,
+                            A.x_b + ((size_t)s * (A.act_rows / 8) + it.pos0 / 8) * kActBRec, x_bytes,
                             &full[slot]);
             }
         }
     } else if (warp == 0 && lane == 1) {
         // ---------------- MMA thread: 2 terms x 4 K-steps per stage
-        const uint32_t idesc = pf_idesc_bf16(kChunkRows, BF_NT);
         uint32_t q = 0, item = 0;
         bool dead = false;
         for (int idx = blockIdx.x; idx < total && !dead && !*(volatile int*)s_abort; idx += gridDim.x) {
             const BfItem it = decode(idx);
             if (it.nst == 0) continue;
             const uint32_t buf = item & 1;
+            const uint32_t idesc = pf_idesc_bf16(kChunkRows, it.n_mma);
             if (!pf_bar_wait(&tempty[buf], ((item >> 1) & 1) ^ 1)) { give_up(); break; }
             pf_fence_after();
             for (int s = 0; s < it.nst && !dead; s++, q++) {
