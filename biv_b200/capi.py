@@ -77,7 +77,7 @@ def lib():
         L.bivmoe_tap_block_dots.argtypes = [vp, i32, i32, i32, i32, vp]
         L.bivmoe_route_noalloc.argtypes = [vp, vp, i32, vp, vp, vp]
         L.bivmoe_ep_create.argtypes = [C.POINTER(Desc), i32, i32, i32, C.POINTER(vp)]
-        L.bivmoe_ep_route.argtypes = [vp, vp, i32, vp, vp, vp]
+        L.bivmoe_ep_route.argtypes = [vp, vp, i32, vp, vp, vp, vp]
         L.bivmoe_ep_shared.argtypes = [vp, vp, vp]
         L.bivmoe_ep_experts.argtypes = [vp, vp, vp, i32, vp, vp]
         L.bivmoe_ep_combine.argtypes = [vp, vp, vp, i32, i32, vp]

@@ -77,8 +77,11 @@ struct bivmoe_layer {
     // experts, the shared expert), `ws_owner` the rows received for the local experts
     int ep_rank = 0, ep_world = 1, n_local = 0, max_recv = 0, ep_n = 0;
     Workspace ws_owner{};
-    int32_t* ep_compact_start = nullptr;   // [n_expert + 1]
-    int32_t* ep_compact_pos = nullptr;     // [max_tokens * k] pair -> slot among the sent rows
+    int32_t* ep_slot = nullptr;       // [max_tokens][world] a token's slot among a rank's rows, or -1
+    int32_t* ep_counts = nullptr;     // [world] rows for each rank
+    int32_t* ep_rank_ids = nullptr;   // [max_tokens][world] the rank, or -1: the home combine's "ids"
+    int32_t* ep_rank_pos = nullptr;   // [max_tokens][world] the row's index among the sent rows
+    float* ep_ones = nullptr;         // [max_tokens][world] the home combine's weights
     bool use_graph = true;
     int launches_per_forward = 0;
     std::string error, device_name;
@@ -138,9 +141,13 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
         return;
     }
     layout_one(L, a, L->ws, (size_t)L->max_tokens, (size_t)L->k, (size_t)L->n_expert, false);
-    layout_one(L, a, L->ws_owner, (size_t)L->max_recv, 1, (size_t)L->n_local, true);
-    L->ep_compact_start = a.take<int32_t>((size_t)L->n_expert + 1);
-    L->ep_compact_pos = a.take<int32_t>((size_t)L->max_tokens * L->k);
+    layout_one(L, a, L->ws_owner, (size_t)L->max_recv, (size_t)L->k, (size_t)L->n_local, true);
+    const size_t nw = (size_t)L->max_tokens * L->ep_world;
+    L->ep_slot = a.take<int32_t>(nw);
+    L->ep_counts = a.take<int32_t>((size_t)L->ep_world);
+    L->ep_rank_ids = a.take<int32_t>(nw);
+    L->ep_rank_pos = a.take<int32_t>(nw);
+    L->ep_ones = a.take<float>(nw);
 }
 
 #define CU(call)                                                                          \
@@ -249,9 +256,9 @@ static int create_impl(const bivmoe_desc* d, int ep_rank, int ep_world, int max_
     if (!d || !out) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null descriptor or output");
     if (ep_world < 1 || ep_rank < 0 || ep_rank >= ep_world)
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "rank %d outside 0..%d", ep_rank, ep_world);
-    if (ep_world > 1 && (d->n_expert % ep_world || max_recv <= 0))
+    if (ep_world > 1 && (d->n_expert % ep_world || max_recv <= 0 || ep_world > 32))
         return set_err(errp, BIVMOE_ERR_ARGUMENT,
-                       "%d experts do not split over %d ranks, or max_recv_rows %d is not positive",
+                       "%d experts do not split over %d ranks (at most 32), or max_recv_rows %d is not positive",
                        d->n_expert, ep_world, max_recv);
     const int n_local = d->n_expert / ep_world;
     if (d->n_embd <= 0 || d->n_expert <= 0 || d->n_ff_exp <= 0 || d->max_tokens <= 0 || !d->router)
@@ -341,8 +348,12 @@ static int create_impl(const bivmoe_desc* d, int ep_rank, int ep_world, int max_
     real.base = L->ws_mem;
     layout_workspace(L, real);
     if ((ce = cudaMemset(L->ws.status, 0, 16)) != cudaSuccess) return cu_fail(ce, "status");
-    if (ep_world > 1 && (ce = cudaMemset(L->ws_owner.status, 0, 16)) != cudaSuccess)
-        return cu_fail(ce, "status");
+    if (ep_world > 1) {
+        if ((ce = cudaMemset(L->ws_owner.status, 0, 16)) != cudaSuccess) return cu_fail(ce, "status");
+        std::vector<float> ones((size_t)L->max_tokens * ep_world, 1.0f);
+        if ((ce = cudaMemcpy(L->ep_ones, ones.data(), ones.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess)
+            return cu_fail(ce, "weights of one");
+    }
     if ((ce = cudaStreamCreateWithFlags(&L->own_stream, cudaStreamNonBlocking)) != cudaSuccess)
         return cu_fail(ce, "stream");
     if ((ce = cudaDeviceSynchronize()) != cudaSuccess) return cu_fail(ce, "upload");
@@ -400,7 +411,7 @@ static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int 
     if (c.prefill_min > 0)
         CU(launch_experts_prefill(c, L->gate_up, L->down, L->sh_gate_up, L->sh_down, L->ws));
     mark(c, EV_DOWN);
-    CU(launch_combine(c, L->ws, L->ws.pair_out, L->ws.pos_of, out, accumulate));
+    CU(launch_combine(c, combine_src(L->ws), out, accumulate));
     mark(c, EV_COMBINE);
     return BIVMOE_OK;
 }
@@ -478,10 +489,10 @@ static int ep_check(bivmoe_layer* L, const char* what) {
 }
 
 int bivmoe_ep_route(bivmoe_layer* L, const float* h_dev, int32_t n, float* send_rows_dev,
-                    int32_t* send_counts_dev, void* stream) {
+                    int32_t* send_tags_dev, int32_t* send_counts_dev, void* stream) {
     if (int rc = ep_check(L, "bivmoe_ep_route")) return rc;
     std::string* errp = &L->error;
-    if (!h_dev || !send_rows_dev || !send_counts_dev)
+    if (!h_dev || !send_rows_dev || !send_tags_dev || !send_counts_dev)
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "null pointer");
     if (n < 0 || n > L->max_tokens)
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens = %d", n, L->max_tokens);
@@ -489,18 +500,19 @@ int bivmoe_ep_route(bivmoe_layer* L, const float* h_dev, int32_t n, float* send_
     L->ep_n = n;
     L->last_n = n;
     if (n == 0) {
-        CU(cudaMemsetAsync(send_counts_dev, 0, (size_t)L->n_expert * 4, s));
+        CU(cudaMemsetAsync(send_counts_dev, 0, (size_t)L->ep_world * 4, s));
         return BIVMOE_OK;
     }
     LaunchCfg c{s, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh, L->has_shared ? 1 : 0, L->sm_count};
-    // the shared expert's group alone is computed here; its size decides its kernel
+    // the sort serves the shared expert's group, which is computed here; its size
+    // decides its kernel
     c.prefill_min = L->prefill_min;
     c.prefill_tile = L->prefill_tile;
     CU(launch_router(c, L->router, h_dev, L->ws));
     CU(launch_route_topk(c, L->ws));
-    CU(launch_sort(c, L->ws));
-    CU(launch_ep_gather(c, h_dev, L->ws, L->ep_compact_start, L->ep_compact_pos, send_rows_dev,
-                        send_counts_dev));
+    if (L->has_shared) CU(launch_sort(c, L->ws));
+    CU(launch_ep_gather(c, h_dev, L->ws, L->ep_world, L->n_local, L->ep_slot, L->ep_counts,
+                        L->ep_rank_ids, L->ep_rank_pos, send_rows_dev, send_tags_dev, send_counts_dev));
     return BIVMOE_OK;
 }
 
@@ -524,29 +536,30 @@ int bivmoe_ep_shared(bivmoe_layer* L, const float* h_dev, void* stream) {
     return BIVMOE_OK;
 }
 
-int bivmoe_ep_experts(bivmoe_layer* L, const float* recv_rows_dev, const int32_t* recv_counts_dev,
+int bivmoe_ep_experts(bivmoe_layer* L, const float* recv_rows_dev, const int32_t* recv_tags_dev,
                       int32_t m, float* out_rows_dev, void* stream) {
     if (int rc = ep_check(L, "bivmoe_ep_experts")) return rc;
     std::string* errp = &L->error;
     if (m < 0 || m > L->max_recv)
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "m = %d outside 0..max_recv_rows = %d", m, L->max_recv);
     if (m == 0) return BIVMOE_OK;
-    if (!recv_rows_dev || !recv_counts_dev || !out_rows_dev)
+    if (!recv_rows_dev || !recv_tags_dev || !out_rows_dev)
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "null pointer");
     cudaStream_t s = (cudaStream_t)stream;
-    // the received rows are a k = 1 routing result over the local experts, no shared expert
-    LaunchCfg c{s, m, 1, L->e, L->n_local, L->ff, 0, 0, L->sm_count};
+    // the received rows with their tags are a routing result over the local experts with
+    // empty slots for the experts other ranks own; no shared expert here
+    LaunchCfg c{s, m, L->k, L->e, L->n_local, L->ff, 0, 0, L->sm_count};
     c.prefill_min = L->prefill_min;
     c.prefill_tile = L->prefill_tile;
     const Workspace& w = L->ws_owner;
     const DevTiles none{};
-    CU(launch_ep_expand(c, recv_counts_dev, L->ep_world, w));
+    CU(launch_ep_localize(c, recv_tags_dev, L->ep_rank * L->n_local, w));
     CU(launch_sort(c, w));
     CU(launch_dispatch(c, recv_rows_dev, w, w.act_t != nullptr && !type_uses_f32_act(L->gate_up.ty),
                        w.act_f != nullptr && type_uses_f32_act(L->gate_up.ty)));
     CU(launch_experts(c, L->gate_up, L->down, none, none, w));
     if (c.prefill_min > 0) CU(launch_experts_prefill(c, L->gate_up, L->down, none, none, w));
-    CU(launch_combine(c, w, w.pair_out, w.pos_of, out_rows_dev, 0));   // weight 1: rows in arrival order
+    CU(launch_combine(c, combine_src(w), out_rows_dev, 0));   // the weighted sum over the local experts
     return BIVMOE_OK;
 }
 
@@ -558,9 +571,12 @@ int bivmoe_ep_combine(bivmoe_layer* L, const float* returned_rows_dev, float* ou
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d, but bivmoe_ep_route ran on %d rows", n, L->ep_n);
     if (n == 0) return BIVMOE_OK;
     if (!returned_rows_dev || !out_dev) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null pointer");
-    LaunchCfg c{(cudaStream_t)stream, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh,
+    // the ranks take the experts' place: weight one, ascending rank = ascending expert id
+    LaunchCfg c{(cudaStream_t)stream, n, L->ep_world, L->e, L->n_expert, L->ff, L->ff_sh,
                 L->has_shared ? 1 : 0, L->sm_count};
-    CU(launch_combine(c, L->ws, returned_rows_dev, L->ep_compact_pos, out_dev, accumulate));
+    const CombineSrc src{L->ep_rank_ids, L->ep_ones, returned_rows_dev, L->ep_rank_pos, L->ws.pair_out,
+                         L->ws.logits};
+    CU(launch_combine(c, src, out_dev, accumulate));
     return BIVMOE_OK;
 }
 
@@ -576,9 +592,7 @@ int bivmoe_ep_status(bivmoe_layer* L, void* stream) {
         cudaMemsetAsync(L->ws.status, 0, 16, s);
         cudaMemsetAsync(L->ws_owner.status, 0, 16, s);
         const int code = st[0] ? st[0] : st[1];
-        return set_err(errp, code, code == BIVMOE_ERR_TIMEOUT
-                                       ? "a device-side bounded wait gave up"
-                                       : "the received-row count differs from the sum of the count matrix");
+        return set_err(errp, code, "a device-side bounded wait gave up (status %d)", code);
     }
     return BIVMOE_OK;
 }

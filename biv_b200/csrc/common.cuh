@@ -170,15 +170,28 @@ cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace&
                             bool f32);
 cudaError_t launch_experts(const LaunchCfg& c, const DevTiles& gate_up, const DevTiles& down,
                            const DevTiles& sh_gate_up, const DevTiles& sh_down, const Workspace& ws);
-// `routed_rows` [.][e] indexed by `routed_pos[pair]`: the workspace's pair_out and pos_of,
-// or under expert parallelism the rows the owners returned and their compact slots
-cudaError_t launch_combine(const LaunchCfg& c, const Workspace& ws, const float* routed_rows,
-                           const int32_t* routed_pos, float* out, int accumulate);
-cudaError_t launch_ep_gather(const LaunchCfg& c, const float* h, const Workspace& ws,
-                             int32_t* compact_start, int32_t* compact_pos, float* send_rows,
+// What the combine sums for token t: for each of its k slots j with ids[t*k+j] >= 0, in
+// ascending id, weights[t*k+j] * routed_rows[routed_pos[t*k+j]]; then, with a shared
+// expert, sigmoid(logits[t][n_expert]) * shared_rows[t].  One layer: the workspace's
+// routing result, pair_out and pos_of.  Expert parallelism: the ranks as "experts" and
+// the partial sums they returned as the routed rows.
+struct CombineSrc {
+    const int32_t* ids;
+    const float* weights;
+    const float* routed_rows;
+    const int32_t* routed_pos;
+    const float* shared_rows;
+    const float* logits;
+};
+inline CombineSrc combine_src(const Workspace& ws) {
+    return CombineSrc{ws.ids, ws.weights, ws.pair_out, ws.pos_of, ws.pair_out, ws.logits};
+}
+cudaError_t launch_combine(const LaunchCfg& c, const CombineSrc& src, float* out, int accumulate);
+cudaError_t launch_ep_gather(const LaunchCfg& c, const float* h, const Workspace& ws, int world,
+                             int n_local, int32_t* slot, int32_t* counts, int32_t* rank_ids,
+                             int32_t* rank_pos, float* send_rows, int32_t* send_tags,
                              int32_t* counts_out);
-cudaError_t launch_ep_expand(const LaunchCfg& c, const int32_t* recv_counts, int world,
-                             const Workspace& ws);
+cudaError_t launch_ep_localize(const LaunchCfg& c, const int32_t* tags, int first, const Workspace& ws);
 cudaError_t launch_rms_norm(const LaunchCfg& c, const float* x, const float* w, float eps,
                             float* out);
 cudaError_t launch_repack(const DevTiles& dst, const uint8_t* gguf_rows, int tile_base,

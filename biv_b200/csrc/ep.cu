@@ -1,19 +1,22 @@
-// Expert parallelism: the two small kernels either side of the all-to-all
-// exchanges.  The reference has no multi-device path (one MTLDevice,
+// Expert parallelism: the small kernels either side of the all-to-all exchanges.
+// The reference has no multi-device path (one MTLDevice,
 // engine/src/metal/mod.rs:450-462; one thread pool on the CPU), so these have no
 // counterpart there.  Rank r of W owns experts [r * n_expert / W, (r + 1) *
 // n_expert / W) - a contiguous byte range of each ffn_*_exps tensor, experts
 // being outermost (engine/src/model.rs:353) - and is the home rank of its own
 // tokens.
 //
-//   home rank    route + sort by expert (router.cu)  ->  ep_gather: the token
-//                rows in expert order, compact, which is also destination-rank
-//                order since a rank's experts are contiguous
-//   exchange 1   rows to the owners (the caller's all-to-all)
-//   owner rank   ep_expand: the local expert id of every received row from the
-//                count matrix, then the ordinary sort / dispatch / expert kernels
-//   exchange 2   the rows' outputs back, same layout
-//   home rank    combine (rowops.cu) with the returned rows as the routed source
+//   home rank    route (router.cu), then ep_rank_slots / ep_rank_gather: a token's
+//                row goes ONCE to every rank that owns at least one of its experts,
+//                with the token's k expert ids and weights as a tag
+//   exchange 1   rows and tags to the owners (the caller's all-to-all)
+//   owner rank   ep_localize: the tag becomes a routing result over the local
+//                experts with empty slots for the others; then the ordinary sort /
+//                dispatch / expert kernels, and the ordinary combine, which leaves
+//                per row the weighted sum over the local experts
+//   exchange 2   one partial sum per row back, same layout
+//   home rank    combine (rowops.cu) with the ranks as "experts" of weight one and
+//                the partial sums as the routed rows, then the shared expert
 #include <algorithm>
 
 #include "common.cuh"
@@ -21,121 +24,121 @@
 namespace bivmoe {
 
 // ---------------------------------------------------------------------------
-// compact_start[x] = number of pairs of experts below x; also hands the counts
-// to the caller.  One block of 1024 threads (n_expert <= 1024).
+// Block d: which tokens have an expert on rank d, and the rank-d slot of each (its
+// index among them, in token order).  slot[t * world + d] = slot or -1;
+// counts[d] = rows for rank d.
 __global__ void __launch_bounds__(1024)
-ep_compact_starts_kernel(const int32_t* __restrict__ counts, int n_expert,
-                         int32_t* __restrict__ compact_start, int32_t* __restrict__ counts_out) {
+ep_rank_slots_kernel(const int32_t* __restrict__ ids, int n, int k, int n_local, int world,
+                     int32_t* __restrict__ slot, int32_t* __restrict__ counts,
+                     int32_t* __restrict__ counts_out) {
     __shared__ int s_warp[32];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int c = threadIdx.x < n_expert ? counts[threadIdx.x] : 0;
-    int inc = c;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += t;
-    }
-    if (lane == 31) s_warp[warp] = inc;
+    __shared__ int s_base;
+    const int d = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) s_base = 0;
     __syncthreads();
-    if (warp == 0) {
-        int w = s_warp[lane], winc = w;
+    for (int t0 = 0; t0 < n; t0 += 1024) {
+        const int t = t0 + threadIdx.x;
+        int flag = 0;
+        if (t < n)
+            for (int j = 0; j < k; j++) {
+                const int id = ids[(size_t)t * k + j];
+                flag |= id >= 0 && id / n_local == d;
+            }
+        int inc = flag;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            const int t = __shfl_up_sync(0xffffffffu, winc, o);
-            if (lane >= o) winc += t;
+            const int v = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += v;
         }
-        s_warp[lane] = winc - w;
+        if (lane == 31) s_warp[warp] = inc;
+        __syncthreads();
+        if (warp == 0) {
+            int w = s_warp[lane], winc = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, winc, o);
+                if (lane >= o) winc += v;
+            }
+            s_warp[lane] = winc - w;
+        }
+        __syncthreads();
+        const int base = s_base;
+        if (t < n) slot[(size_t)t * world + d] = flag ? base + s_warp[warp] + inc - flag : -1;
+        __syncthreads();
+        if (threadIdx.x == 1023) s_base = base + s_warp[31] + inc;
+        __syncthreads();
     }
-    __syncthreads();
-    if (threadIdx.x < n_expert) {
-        compact_start[threadIdx.x] = s_warp[warp] + inc - c;
-        if (counts_out) counts_out[threadIdx.x] = c;
-        if (threadIdx.x == n_expert - 1) compact_start[n_expert] = s_warp[warp] + inc;
+    if (threadIdx.x == 0) {
+        counts[d] = s_base;
+        counts_out[d] = s_base;
     }
 }
 
-// One block per pair: its token's row goes to the pair's compact slot.
+// One block per token: its row, ids and weights go to the slot of every rank it uses;
+// also the home combine's view of the pass: rank_ids[t][d] = d or -1, rank_pos[t][d] =
+// the row's index in the send (= return) buffer.
 constexpr int EPG_THREADS = 256;
 __global__ void __launch_bounds__(EPG_THREADS)
-ep_gather_kernel(const float* __restrict__ h, Workspace ws, const int32_t* __restrict__ compact_start,
-                 int k, int e, float* __restrict__ send_rows, int32_t* __restrict__ compact_pos) {
-    const int p = blockIdx.x;
-    const int x = ws.ids[p];
-    const int slot = compact_start[x] + (ws.pos_of[p] - ws.offsets[x]);
-    if (threadIdx.x == 0) compact_pos[p] = slot;
-    const float4* src = (const float4*)(h + (size_t)(p / k) * e);
-    float4* dst = (float4*)(send_rows + (size_t)slot * e);
-    for (int i = threadIdx.x; i < e / 4; i += EPG_THREADS) dst[i] = src[i];
+ep_rank_gather_kernel(const float* __restrict__ h, const int32_t* __restrict__ ids,
+                      const float* __restrict__ weights, const int32_t* __restrict__ slot,
+                      const int32_t* __restrict__ counts, int k, int e, int world,
+                      float* __restrict__ send_rows, int32_t* __restrict__ send_tags,
+                      int32_t* __restrict__ rank_ids, int32_t* __restrict__ rank_pos) {
+    __shared__ int s_dst[32];
+    const int t = blockIdx.x;
+    if (threadIdx.x < world) {
+        const int d = threadIdx.x, sl = slot[(size_t)t * world + d];
+        int base = 0;
+        for (int x = 0; x < d; x++) base += counts[x];
+        s_dst[d] = sl < 0 ? -1 : base + sl;
+        rank_ids[(size_t)t * world + d] = sl < 0 ? -1 : d;
+        rank_pos[(size_t)t * world + d] = sl < 0 ? 0 : base + sl;
+    }
+    __syncthreads();
+    const float4* src = (const float4*)(h + (size_t)t * e);
+    for (int d = 0; d < world; d++) {
+        const int dst = s_dst[d];
+        if (dst < 0) continue;
+        float4* drow = (float4*)(send_rows + (size_t)dst * e);
+        for (int i = threadIdx.x; i < e / 4; i += EPG_THREADS) drow[i] = src[i];
+        if (threadIdx.x < k) {   // the tag: k ids, then the k weights' bits
+            send_tags[(size_t)dst * 2 * k + threadIdx.x] = ids[(size_t)t * k + threadIdx.x];
+            send_tags[(size_t)dst * 2 * k + k + threadIdx.x] =
+                __float_as_int(weights[(size_t)t * k + threadIdx.x]);
+        }
+    }
 }
 
-cudaError_t launch_ep_gather(const LaunchCfg& c, const float* h, const Workspace& ws,
-                             int32_t* compact_start, int32_t* compact_pos, float* send_rows,
+cudaError_t launch_ep_gather(const LaunchCfg& c, const float* h, const Workspace& ws, int world,
+                             int n_local, int32_t* slot, int32_t* counts, int32_t* rank_ids,
+                             int32_t* rank_pos, float* send_rows, int32_t* send_tags,
                              int32_t* counts_out) {
-    if (c.n_expert > 1024 || c.e % 4) return cudaErrorInvalidValue;
-    ep_compact_starts_kernel<<<1, 1024, 0, c.stream>>>(ws.counts, c.n_expert, compact_start, counts_out);
-    ep_gather_kernel<<<c.n * c.k, EPG_THREADS, 0, c.stream>>>(h, ws, compact_start, c.k, c.e, send_rows,
-                                                            compact_pos);
+    if (world > 32 || c.k > 32 || c.e % 4) return cudaErrorInvalidValue;
+    ep_rank_slots_kernel<<<world, 1024, 0, c.stream>>>(ws.ids, c.n, c.k, n_local, world, slot, counts,
+                                                      counts_out);
+    ep_rank_gather_kernel<<<c.n, EPG_THREADS, 0, c.stream>>>(h, ws.ids, ws.weights, slot, counts, c.k, c.e,
+                                                           world, send_rows, send_tags, rank_ids, rank_pos);
     count_launch(2);
     return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------
-// The owner's view of what it received: rows ordered by source rank, then by
-// expert, `recv_counts[s][x]` of them for local expert x from source s.  Writes
-// the local expert id of every row (and a weight of one) as a k = 1 routing
-// result, which the ordinary sort then groups.  Every block redoes the small
-// scan and fills a slice of the rows.
-__global__ void __launch_bounds__(1024)
-ep_expand_kernel(const int32_t* __restrict__ recv_counts, int cells /* world * n_local */,
-                 int n_local, int m, int32_t* __restrict__ ids, float* __restrict__ weights,
-                 int32_t* __restrict__ status) {
-    __shared__ int s_warp[32];
-    __shared__ int s_start[1025];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int c = threadIdx.x < cells ? recv_counts[threadIdx.x] : 0;
-    int inc = c;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += t;
-    }
-    if (lane == 31) s_warp[warp] = inc;
-    __syncthreads();
-    if (warp == 0) {
-        int w = s_warp[lane], winc = w;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int t = __shfl_up_sync(0xffffffffu, winc, o);
-            if (lane >= o) winc += t;
-        }
-        s_warp[lane] = winc - w;
-    }
-    __syncthreads();
-    s_start[threadIdx.x] = threadIdx.x < cells ? s_warp[warp] + inc - c : 0x7fffffff;
-    if (threadIdx.x == cells - 1) {
-        s_start[cells] = s_warp[warp] + inc;
-        // the caller's row count must be the sum of the matrix
-        if (blockIdx.x == 0 && s_warp[warp] + inc != m) atomicExch(status, BIVMOE_ERR_ARGUMENT);
-    }
-    __syncthreads();
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < m; i += gridDim.x * blockDim.x) {
-        int lo = 0, hi = cells;   // the last cell whose start is <= i (empty cells share a start)
-        while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (s_start[mid] <= i) lo = mid; else hi = mid;
-        }
-        ids[i] = lo % n_local;
-        weights[i] = 1.0f;
-    }
+// The owner's routing result from the received tags: the ids this rank owns, made
+// local; every other slot empty.
+__global__ void ep_localize_kernel(const int32_t* __restrict__ tags, int m, int k, int first, int n_local,
+                                   int32_t* __restrict__ ids, float* __restrict__ weights) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= m * k) return;
+    const int row = i / k, j = i % k;
+    const int id = tags[(size_t)row * 2 * k + j];
+    ids[i] = id >= first && id < first + n_local ? id - first : -1;
+    weights[i] = __int_as_float(tags[(size_t)row * 2 * k + k + j]);
 }
 
-cudaError_t launch_ep_expand(const LaunchCfg& c, const int32_t* recv_counts, int world,
-                             const Workspace& ws) {
-    const int cells = world * c.n_expert;   // c.n_expert: the rank's local experts
-    if (cells > 1024 || cells <= 0) return cudaErrorInvalidValue;
-    const int blocks = std::max(1, std::min(c.sm_count, (c.n + 1023) / 1024));
-    ep_expand_kernel<<<blocks, 1024, 0, c.stream>>>(recv_counts, cells, c.n_expert, c.n, ws.ids, ws.weights,
-                                                    ws.status);
+cudaError_t launch_ep_localize(const LaunchCfg& c, const int32_t* tags, int first, const Workspace& ws) {
+    const int total = c.n * c.k;
+    ep_localize_kernel<<<(total + 255) / 256, 256, 0, c.stream>>>(tags, c.n, c.k, first, c.n_expert, ws.ids,
+                                                                ws.weights);
     count_launch();
     return cudaGetLastError();
 }

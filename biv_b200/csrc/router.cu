@@ -324,15 +324,21 @@ cudaError_t launch_route_topk(const LaunchCfg& c, const Workspace& ws) {
 // thread per expert walk its block's pairs in order.  With one block the three
 // phases run in a single launch.
 constexpr int SORT_TOKENS = 256, SORT_THREADS = 256;
+constexpr uint16_t kNoExpert = 0xFFFF;
 constexpr int SORT_TILE = 8;   // tokens per tile of the expert kernels
 
 __device__ void sort_load_ids(const int32_t* ids, int pair0, int npairs, uint16_t* s_ids) {
-    for (int i = threadIdx.x; i < npairs; i += blockDim.x) s_ids[i] = (uint16_t)ids[pair0 + i];
+    // a negative id marks an empty slot (a row with fewer than k experts: expert parallelism)
+    for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+        const int id = ids[pair0 + i];
+        s_ids[i] = id < 0 ? kNoExpert : (uint16_t)id;
+    }
 }
 __device__ void sort_hist(const uint16_t* s_ids, int npairs, int n_expert, int* s_cnt) {
     for (int e = threadIdx.x; e < n_expert; e += blockDim.x) s_cnt[e] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < npairs; i += blockDim.x) atomicAdd(&s_cnt[s_ids[i]], 1);
+    for (int i = threadIdx.x; i < npairs; i += blockDim.x)
+        if (s_ids[i] != kNoExpert) atomicAdd(&s_cnt[s_ids[i]], 1);
     __syncthreads();
 }
 // exclusive scan over the block of one int per thread slot; `n_items` slots,
@@ -474,6 +480,7 @@ __device__ void sort_build_masks(const uint16_t* s_ids, int npairs, int k, int n
     __syncthreads();
     for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
         const int t = i / k;
+        if (s_ids[i] == kNoExpert) continue;
         atomicOr(&s_mask[s_ids[i] * (SORT_TOKENS / 32) + (t >> 5)], 1u << (t & 31));
     }
     __syncthreads();
@@ -482,6 +489,10 @@ __device__ void sort_scatter(const Workspace& ws, const uint16_t* s_ids, const u
                              int pair0, int npairs, int k, int n_expert, int blk, const int* s_off) {
     for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
         const int e = s_ids[i], t = i / k;
+        if (e == kNoExpert) {
+            ws.pos_of[pair0 + i] = -1;
+            continue;
+        }
         const uint32_t* m = s_mask + e * (SORT_TOKENS / 32);
         int rank = __popc(m[t >> 5] & ((1u << (t & 31)) - 1u));
         for (int w = 0; w < (t >> 5); w++) rank += __popc(m[w]);

@@ -24,14 +24,14 @@ constexpr int DP_THREADS = 256, DP_MAX_K = 32;
 __device__ __forceinline__ void dispatch_positions(const Workspace& ws, int t, int n, int k, int n_expert,
                                                    int has_shared, int prefill_min, int* s_pos,
                                                    int* s_big) {
-    if (threadIdx.x < k) {
-        s_pos[threadIdx.x] = ws.pos_of[(size_t)t * k + threadIdx.x];
-        s_big[threadIdx.x] = prefill_min > 0 && ws.counts[ws.ids[(size_t)t * k + threadIdx.x]] >= prefill_min;
+    if (threadIdx.x < k) {   // a negative position: an empty slot, nothing is written for it
+        const int id = ws.ids[(size_t)t * k + threadIdx.x];
+        s_pos[threadIdx.x] = id < 0 ? -1 : ws.pos_of[(size_t)t * k + threadIdx.x];
+        s_big[threadIdx.x] = id >= 0 && prefill_min > 0 && ws.counts[id] >= prefill_min;
     }
     if (threadIdx.x == k) {
-        s_pos[k] = has_shared ? t : ws.pos_of[(size_t)t * k];
-        s_big[k] = has_shared ? (prefill_min > 0 && n >= prefill_min)
-                              : (prefill_min > 0 && ws.counts[ws.ids[(size_t)t * k]] >= prefill_min);
+        s_pos[k] = has_shared ? t : -1;
+        s_big[k] = has_shared && prefill_min > 0 && n >= prefill_min;
     }
     __syncthreads();
 }
@@ -75,6 +75,7 @@ dispatch_q8_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int 
             unit.w = __shfl_down_sync(0xffffffffu, w, 12);
             for (int j = 0; j <= k; j++) {
                 const int pos = s_pos[j];
+                if (pos < 0) continue;
                 uint8_t* rec = ws.act_t + ((size_t)sl * (R / 8) + pos / 8) * kActTileBytes;
                 if ((lane & 15) == 0)   // elements 32*bb + lane .. + 15: unit 2*bb + lane/16
                     *(uint4*)(rec + act_q_off(pos % 8, 32 * bb + lane)) = unit;
@@ -113,6 +114,7 @@ dispatch_f32_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int
         const int sl = i0 / 64, off = i0 % 64;
         for (int j = 0; j <= k; j++) {
             const int pos = s_pos[j];
+            if (pos < 0) continue;
             if (s_big[j]) {
                 uint8_t* rec = ws.act_b + ((size_t)sl * (R / 8) + pos / 8) * kActBRec + act_b_off(pos % 8, off);
                 *(uint4*)rec = make_uint4(hi[0], hi[1], hi[2], hi[3]);
@@ -258,37 +260,49 @@ cudaError_t launch_rms_norm(const LaunchCfg& c, const float* x, const float* w, 
 constexpr int CB_THREADS = 256, CB_MAX_K = 32;
 
 __global__ void __launch_bounds__(CB_THREADS)
-combine_kernel(Workspace ws, const float* __restrict__ routed_rows,
-               const int32_t* __restrict__ routed_pos, float* __restrict__ out, int n, int k, int e,
-               int n_expert, int has_shared, int accumulate) {
+combine_kernel(const int32_t* __restrict__ ids, const float* __restrict__ weights,
+               const float* __restrict__ routed_rows, const int32_t* __restrict__ routed_pos,
+               const float* __restrict__ shared_rows, const float* __restrict__ logits,
+               float* __restrict__ out, int n, int k, int e, int n_expert, int has_shared, int accumulate) {
     __shared__ int s_pos[CB_MAX_K];
     __shared__ float s_w[CB_MAX_K];
     __shared__ float s_gate;
+    __shared__ int s_valid;
     const int t = blockIdx.x;
+    if (threadIdx.x == 0) s_valid = 0;
+    __syncthreads();
     if (threadIdx.x < k) {
-        // rank of this pair among the token's pairs by expert id (ids are distinct)
-        const int my = ws.ids[(size_t)t * k + threadIdx.x];
-        int rank = 0;
-        for (int j = 0; j < k; j++) rank += ws.ids[(size_t)t * k + j] < my;
-        s_pos[rank] = routed_pos[(size_t)t * k + threadIdx.x];
-        s_w[rank] = ws.weights[(size_t)t * k + threadIdx.x];
+        // rank of this pair among the token's pairs by expert id (ids are distinct; a
+        // negative id is an empty slot and takes no rank)
+        const int my = ids[(size_t)t * k + threadIdx.x];
+        if (my >= 0) {
+            int rank = 0;
+            for (int j = 0; j < k; j++) {
+                const int o = ids[(size_t)t * k + j];
+                rank += o >= 0 && o < my;
+            }
+            s_pos[rank] = routed_pos[(size_t)t * k + threadIdx.x];
+            s_w[rank] = weights[(size_t)t * k + threadIdx.x];
+            atomicAdd(&s_valid, 1);
+        }
     }
     if (threadIdx.x == 32 && has_shared) {
-        const float g = ws.logits[(size_t)t * (n_expert + 1) + n_expert];
+        const float g = logits[(size_t)t * (n_expert + 1) + n_expert];
         s_gate = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g)));   // ops.rs:160-162
     }
     __syncthreads();
+    const int kv = s_valid;
     const int c4 = blockIdx.y * CB_THREADS + threadIdx.x;     // float4 column
     if (c4 * 4 >= e) return;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int j = 0; j < k; j++) {
+    for (int j = 0; j < kv; j++) {
         const float4 y = *(const float4*)(routed_rows + (size_t)s_pos[j] * e + c4 * 4);
         const float w = s_w[j];
         acc.x = fmaf(w, y.x, acc.x); acc.y = fmaf(w, y.y, acc.y);
         acc.z = fmaf(w, y.z, acc.z); acc.w = fmaf(w, y.w, acc.w);
     }
     if (has_shared) {
-        const float4 y = *(const float4*)(ws.pair_out + (size_t)t * e + c4 * 4);
+        const float4 y = *(const float4*)(shared_rows + (size_t)t * e + c4 * 4);
         const float w = s_gate;
         acc.x = fmaf(w, y.x, acc.x); acc.y = fmaf(w, y.y, acc.y);
         acc.z = fmaf(w, y.z, acc.z); acc.w = fmaf(w, y.w, acc.w);
@@ -301,11 +315,11 @@ combine_kernel(Workspace ws, const float* __restrict__ routed_rows,
     *o = acc;
 }
 
-cudaError_t launch_combine(const LaunchCfg& c, const Workspace& ws, const float* routed_rows,
-                           const int32_t* routed_pos, float* out, int accumulate) {
+cudaError_t launch_combine(const LaunchCfg& c, const CombineSrc& src, float* out, int accumulate) {
     if (c.k > CB_MAX_K || c.e % 4) return cudaErrorInvalidValue;
     dim3 grid(c.n, (c.e / 4 + CB_THREADS - 1) / CB_THREADS);
-    combine_kernel<<<grid, CB_THREADS, 0, c.stream>>>(ws, routed_rows, routed_pos, out, c.n, c.k, c.e,
+    combine_kernel<<<grid, CB_THREADS, 0, c.stream>>>(src.ids, src.weights, src.routed_rows, src.routed_pos,
+                                                      src.shared_rows, src.logits, out, c.n, c.k, c.e,
                                                       c.n_expert, c.has_shared, accumulate);
     count_launch();
     return cudaGetLastError();

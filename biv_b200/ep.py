@@ -1,6 +1,7 @@
 """Expert parallelism: one process per GPU, experts sharded ``n_expert / W`` per
-rank, token rows exchanged with two all-to-alls (``torch.distributed``: NCCL
-over NVLink between GPUs; gloo between CPU processes in the tests).
+rank.  A token's row travels once to every rank that owns one of its experts and
+one partial sum per row comes back (``torch.distributed`` all-to-alls: NCCL over
+NVLink between GPUs; gloo between CPU processes in the tests).
 
 The reference has no multi-device path (one ``MTLDevice``,
 engine/src/metal/mod.rs:450-462; the CPU backend loops over the experts in one
@@ -28,23 +29,19 @@ from .workloads import ExpertStack, MoeLayer
 
 @dataclass
 class EpPlan:
-    """What one rank sends and receives, from everyone's per-expert row counts."""
-    send_splits: List[int]      # rows this rank sends to each rank (its rows are in expert order)
+    """What one rank sends and receives, from everyone's per-destination row counts."""
+    send_splits: List[int]      # rows this rank sends to each rank (grouped by destination)
     recv_splits: List[int]      # rows it receives from each rank
-    recv_counts: np.ndarray     # int32 [W][n_local]: rows from source s for local expert x
     m: int                      # rows received in all
 
 
 def ep_plan(counts_all: np.ndarray, rank: int) -> EpPlan:
-    """``counts_all`` [W][n_expert]: row s = how many rows rank s has for every
-    expert (global id).  Rank r owns experts ``[r * n_local, (r + 1) * n_local)``."""
-    W, E = counts_all.shape
-    assert E % W == 0 and 0 <= rank < W
-    nl = E // W
-    per_dest = counts_all.reshape(W, W, nl).sum(axis=2)         # [source][dest]
-    recv_counts = np.ascontiguousarray(counts_all[:, rank * nl:(rank + 1) * nl], dtype=np.int32)
-    return EpPlan([int(v) for v in per_dest[rank]], [int(v) for v in per_dest[:, rank]],
-                  recv_counts, int(recv_counts.sum()))
+    """``counts_all`` [W][W]: entry [s][d] = rows rank s has for rank d (a token's row
+    goes once to every rank that owns at least one of its experts)."""
+    W = counts_all.shape[0]
+    assert counts_all.shape == (W, W) and 0 <= rank < W
+    recv = [int(v) for v in counts_all[:, rank]]
+    return EpPlan([int(v) for v in counts_all[rank]], recv, sum(recv))
 
 
 def local_experts(layer: MoeLayer, rank: int, world: int) -> MoeLayer:
@@ -79,28 +76,28 @@ class TorchComm:
 def ep_pass(steps, h, out, accumulate: bool, comm=None):
     """One pass of the layer over this rank's rows ``h`` [n, n_embd] into ``out``.
 
-    ``steps`` supplies ``rank``, ``world``, ``n_expert``, ``k`` and
-    ``route(h) -> (send_rows, send_counts)``, ``shared(h)``,
-    ``rows(count) -> tensor [count, n_embd]`` (scratch, two distinct buffers in turn),
-    ``experts(recv_rows, recv_counts, m) -> out_rows`` and
+    ``steps`` supplies ``rank``, ``world``, ``k`` and
+    ``route(h) -> (send_rows, send_tags, send_counts)``, ``shared(h)``,
+    ``rows(count)`` / ``tags(count)`` (scratch tensors [count, n_embd] f32 and
+    [count, 2k] i32; ``rows`` hands out two distinct buffers in turn),
+    ``experts(recv_rows, recv_tags, m) -> out_rows`` and
     ``combine(returned_rows, out, accumulate)``; ``comm`` the two collectives
     (``TorchComm`` over the default process group when None)."""
     import torch
     comm = comm or TorchComm()
     W, rank = steps.world, steps.rank
-    send_rows, send_counts = steps.route(h)
-    flat = torch.empty((W * steps.n_expert,), dtype=torch.int32, device=send_counts.device)
+    send_rows, send_tags, send_counts = steps.route(h)
+    flat = torch.empty((W * W,), dtype=torch.int32, device=send_counts.device)
     comm.all_gather(flat, send_counts)
-    counts_all = flat.view(W, steps.n_expert)
-    counts_host = counts_all.cpu().numpy()          # the one host synchronisation of the pass
+    counts_host = flat.view(W, W).cpu().numpy()     # the one host synchronisation of the pass
     plan = ep_plan(counts_host, rank)
     steps.shared(h)                                  # overlaps the exchange where it can
-    recv_rows = steps.rows(plan.m)
-    comm.all_to_all(recv_rows, send_rows, plan.recv_splits, plan.send_splits)
-    nl = steps.n_expert // W
-    recv_counts = counts_all[:, rank * nl:(rank + 1) * nl].contiguous()
-    out_rows = steps.experts(recv_rows, recv_counts, plan.m)
-    returned = steps.rows(send_rows.shape[0])
+    n_send = sum(plan.send_splits)
+    recv_rows, recv_tags = steps.rows(plan.m), steps.tags(plan.m)
+    comm.all_to_all(recv_rows, send_rows[:n_send], plan.recv_splits, plan.send_splits)
+    comm.all_to_all(recv_tags, send_tags[:n_send], plan.recv_splits, plan.send_splits)
+    out_rows = steps.experts(recv_rows, recv_tags, plan.m)
+    returned = steps.rows(n_send)
     comm.all_to_all(returned, out_rows, plan.send_splits, plan.recv_splits)
     steps.combine(returned, out, accumulate)
     return plan
@@ -118,7 +115,7 @@ class DeviceSteps:
         self.n_embd, self.n_expert, self.k = layer.n_embd, layer.n_expert, layer.n_expert_used
         self.max_tokens = max_tokens
         nl = layer.n_expert // world
-        self.max_recv = max_recv_rows or world * max_tokens * min(self.k, nl)
+        self.max_recv = max_recv_rows or world * max_tokens
         local = local_experts(layer, rank, world)
         d, self._keep = fill_desc(local, max_tokens, device)
         d.n_expert = layer.n_expert
@@ -126,10 +123,13 @@ class DeviceSteps:
         capi.check(capi.lib().bivmoe_ep_create(C.byref(d), rank, world, self.max_recv, C.byref(h)))
         self._h = h
         dev = torch.device("cuda", device)
-        self._send = torch.empty((max_tokens * self.k, self.n_embd), dtype=torch.float32, device=dev)
-        self._counts = torch.empty((self.n_expert,), dtype=torch.int32, device=dev)
-        self._bufs = [torch.empty((max(self.max_recv, max_tokens * self.k), self.n_embd),
+        max_send = max_tokens * min(world, self.k)
+        self._send = torch.empty((max_send, self.n_embd), dtype=torch.float32, device=dev)
+        self._send_tags = torch.empty((max_send, 2 * self.k), dtype=torch.int32, device=dev)
+        self._counts = torch.empty((world,), dtype=torch.int32, device=dev)
+        self._bufs = [torch.empty((max(self.max_recv, max_send), self.n_embd),
                                   dtype=torch.float32, device=dev) for _ in range(2)]
+        self._recv_tags = torch.empty((self.max_recv, 2 * self.k), dtype=torch.int32, device=dev)
         self._out_rows = torch.empty((self.max_recv, self.n_embd), dtype=torch.float32, device=dev)
         self._turn = 0
         self._side = torch.cuda.Stream(device=dev)
@@ -158,9 +158,10 @@ class DeviceSteps:
         self._n = n
         capi.check(capi.lib().bivmoe_ep_route(self._h, C.c_void_p(h.data_ptr()), n,
                                               C.c_void_p(self._send.data_ptr()),
+                                              C.c_void_p(self._send_tags.data_ptr()),
                                               C.c_void_p(self._counts.data_ptr()), self._stream()),
                    self._h)
-        return self._send[:n * self.k], self._counts
+        return self._send, self._send_tags, self._counts
 
     def shared(self, h):
         import torch
@@ -173,9 +174,12 @@ class DeviceSteps:
         self._turn ^= 1
         return self._bufs[self._turn][:count]
 
-    def experts(self, recv_rows, recv_counts, m: int):
+    def tags(self, count: int):
+        return self._recv_tags[:count]
+
+    def experts(self, recv_rows, recv_tags, m: int):
         capi.check(capi.lib().bivmoe_ep_experts(self._h, C.c_void_p(recv_rows.data_ptr()),
-                                                C.c_void_p(recv_counts.data_ptr()), m,
+                                                C.c_void_p(recv_tags.data_ptr()), m,
                                                 C.c_void_p(self._out_rows.data_ptr()),
                                                 self._stream()), self._h)
         return self._out_rows[:m]

@@ -199,43 +199,48 @@ BIVMOE_API int bivmoe_route_noalloc(bivmoe_layer* layer, const float* h_dev, int
  * a GGUF tensor: the same `data` and `stride_bytes`, `offset_bytes` advanced to
  * the rank's first expert, `n` = n_expert / W); `n_expert`, the router, the
  * shared expert and its gate vector are the whole layer's, on every rank.  Each
- * rank is the home of its own token rows.  One pass:
+ * rank is the home of its own token rows.  A token's row travels once to every
+ * rank that owns at least one of its k experts, and one partial sum per row
+ * comes back.  One pass:
  *
- *   1. bivmoe_ep_route    home: router, top-k, sort; writes the token rows in
- *                         expert order (so: destination-rank order) to
- *                         `send_rows_dev` [n * k][n_embd] and the number of rows
- *                         per expert to `send_counts_dev` [n_expert].
- *   2. caller             exchanges the counts (every rank needs row r of every
- *                         rank's counts: an all-gather), then the rows: rank d
- *                         receives, from every source in rank order, that
- *                         source's rows for d's experts.
+ *   1. bivmoe_ep_route    home: router and top-k; writes, grouped by destination
+ *                         rank and in token order inside a rank, the rows to
+ *                         `send_rows_dev` [.][n_embd], their tags - the token's k
+ *                         expert ids (i32) followed by its k weights (f32 bits) -
+ *                         to `send_tags_dev` [.][2 * k], and the number of rows
+ *                         for each rank to `send_counts_dev` [W].  At most
+ *                         n * min(W, k) rows.
+ *   2. caller             exchanges the counts (an all-gather), then rows and
+ *                         tags: rank d receives, from every source in rank order,
+ *                         that source's rows for d.
  *      bivmoe_ep_shared   home, any time after step 1 (e.g. on a second stream,
  *                         during the exchange): the shared expert over the rank's
  *                         own rows.
- *   3. bivmoe_ep_experts  owner: `recv_rows_dev` [m][n_embd] ordered by source,
- *                         then expert; `recv_counts_dev` [W][n_expert / W] = how
- *                         many rows each source sent for each local expert (m is
- *                         their sum).  Writes silu(gate x) * (up x) -> down for
- *                         every row to `out_rows_dev` [m][n_embd], in the same
- *                         order, unweighted.
- *   4. caller             sends every row's output back where the row came from.
- *   5. bivmoe_ep_combine  home: out[t] (+)= sum_j w[t,j] * returned row of pair
- *                         (t, j), in ascending expert id, + sigmoid(gate) *
- *                         shared[t] - the arithmetic and order of bivmoe_forward.
+ *   3. bivmoe_ep_experts  owner: m received rows with their tags.  Writes to
+ *                         `out_rows_dev` [m][n_embd], row for row, the weighted sum
+ *                         over the experts THIS rank owns among the row's k:
+ *                         sum_j w_j * down_j(silu(gate_j x) * (up_j x)), in
+ *                         ascending expert id.
+ *   4. caller             sends every row's partial sum back where the row came
+ *                         from (the exchange of step 2 reversed).
+ *   5. bivmoe_ep_combine  home: out[t] (+)= the partial sums of token t in ascending
+ *                         rank (= ascending expert id), + sigmoid(gate) * shared[t].
  *
- * All steps are asynchronous on `stream`; the caller orders them against its
- * exchanges.  `max_tokens` bounds n (a rank's own rows), `max_recv_rows` bounds m
- * (a safe value is W * max_tokens * min(n_expert_used, n_expert / W)).
- * bivmoe_ep_status synchronises the stream and reports device-side failures
- * (a bounded wait that gave up; an m that is not the sum of the count matrix).
- * With W = 1 bivmoe_ep_create is bivmoe_create and bivmoe_forward applies. */
+ * The result differs from bivmoe_forward on the same rows only in the association
+ * of the f32 sum over a token's experts (by rank first).  All steps are
+ * asynchronous on `stream`; the caller orders them against its exchanges.
+ * `max_tokens` bounds n (a rank's own rows), `max_recv_rows` bounds m (W *
+ * max_tokens is always enough).  bivmoe_ep_status synchronises the stream and
+ * reports device-side failures (a bounded wait that gave up).  With W = 1
+ * bivmoe_ep_create is bivmoe_create and bivmoe_forward applies. */
 BIVMOE_API int bivmoe_ep_create(const bivmoe_desc* desc, int32_t ep_rank, int32_t ep_world,
                                 int32_t max_recv_rows, bivmoe_layer** out);
 BIVMOE_API int bivmoe_ep_route(bivmoe_layer* layer, const float* h_dev, int32_t n,
-                               float* send_rows_dev, int32_t* send_counts_dev, void* stream);
+                               float* send_rows_dev, int32_t* send_tags_dev,
+                               int32_t* send_counts_dev, void* stream);
 BIVMOE_API int bivmoe_ep_shared(bivmoe_layer* layer, const float* h_dev, void* stream);
 BIVMOE_API int bivmoe_ep_experts(bivmoe_layer* layer, const float* recv_rows_dev,
-                                 const int32_t* recv_counts_dev, int32_t m, float* out_rows_dev,
+                                 const int32_t* recv_tags_dev, int32_t m, float* out_rows_dev,
                                  void* stream);
 BIVMOE_API int bivmoe_ep_combine(bivmoe_layer* layer, const float* returned_rows_dev, float* out_dev,
                                  int32_t n, int32_t accumulate, void* stream);

@@ -1,7 +1,8 @@
 """Expert parallelism, host side: two gloo ranks on the CPU run ``ep_pass`` (the
 count exchange, the split sizes, the two all-to-alls, the order in which rows
 travel and return) with the oracle standing in for the device steps, and must
-reproduce the single-process oracle on each rank's rows bit for bit."""
+reproduce the single-process oracle on each rank's rows up to the association of
+the f32 sum over a token's experts (by rank first)."""
 import os
 import socket
 
@@ -16,7 +17,7 @@ torch = pytest.importorskip("torch")
 
 
 class OracleSteps:
-    """The five steps of ``ep_pass`` restated on numpy rows with the CPU oracle."""
+    """The steps of ``ep_pass`` restated on numpy rows with the CPU oracle."""
 
     def __init__(self, layer, rank, world):
         self.layer, self.rank, self.world = layer, rank, world
@@ -28,8 +29,20 @@ class OracleSteps:
         hn = h.numpy()
         _, tap = oracle.moe_forward(self.layer, hn, taps=True)
         self.tap, self.n = tap, hn.shape[0]
-        send = hn[tap["order"] // self.k]
-        return torch.from_numpy(np.ascontiguousarray(send)), torch.from_numpy(tap["counts"].copy())
+        nl = self.n_expert // self.world
+        dest = tap["ids"] // nl                                   # [n][k]
+        rows, tags, counts, self.where = [], [], [], {}
+        for d in range(self.world):                               # grouped by rank, token order inside
+            toks = np.nonzero((dest == d).any(axis=1))[0]
+            for t in toks:
+                self.where[(int(t), d)] = len(rows)
+                rows.append(hn[t])
+                tags.append(np.concatenate([tap["ids"][t].astype(np.int32),
+                                            tap["weights"][t].view(np.int32)]))
+            counts.append(len(toks))
+        rows = np.array(rows, np.float32).reshape(-1, self.n_embd)
+        tags = np.array(tags, np.int32).reshape(-1, 2 * self.k)
+        return torch.from_numpy(rows), torch.from_numpy(tags), torch.tensor(counts, dtype=torch.int32)
 
     def shared(self, h):
         pass   # the tap of route() already holds the shared expert's rows
@@ -37,18 +50,19 @@ class OracleSteps:
     def rows(self, count):
         return torch.empty((count, self.n_embd), dtype=torch.float32)
 
-    def experts(self, recv_rows, recv_counts, m):
-        rows, cnt = recv_rows.numpy(), recv_counts.numpy()
+    def tags(self, count):
+        return torch.empty((count, 2 * self.k), dtype=torch.int32)
+
+    def experts(self, recv_rows, recv_tags, m):
+        rows, tags = recv_rows.numpy(), recv_tags.numpy()
         nl = self.n_expert // self.world
-        out = np.empty_like(rows)
-        at = 0
-        for s in range(self.world):
-            for x in range(nl):
-                c = int(cnt[s, x])
-                if c:
-                    out[at:at + c] = self._ffn(x, rows[at:at + c])
-                    at += c
-        assert at == m
+        out = np.zeros_like(rows)
+        for i in range(m):
+            ids, wts = tags[i, :self.k], tags[i, self.k:].view(np.float32)
+            mine = [(int(e), float(w)) for e, w in zip(ids, wts) if e // nl == self.rank]
+            assert mine, "a row arrived that has no expert here"
+            for e, w in sorted(mine):                              # ascending expert id
+                out[i] = oracle.axpy(self.level, out[i], w, self._ffn(e - self.rank * nl, rows[i:i + 1])[0])
         return torch.from_numpy(out)
 
     def _ffn(self, x, rows):
@@ -71,13 +85,12 @@ class OracleSteps:
         return f(float(g))
 
     def combine(self, returned, out, accumulate):
-        ret, tap, k = returned.numpy(), self.tap, self.k
-        slot = np.empty(self.n * k, np.int64)
-        slot[tap["order"]] = np.arange(self.n * k)          # pair -> where its row travelled
+        ret, tap = returned.numpy(), self.tap
         res = np.zeros((self.n, self.n_embd), np.float32)
         for t in range(self.n):
-            for j in np.argsort(tap["ids"][t], kind="stable"):   # ascending expert id
-                res[t] = oracle.axpy(self.level, res[t], float(tap["weights"][t, j]), ret[slot[t * k + j]])
+            for d in range(self.world):                            # ascending rank
+                if (t, d) in self.where:
+                    res[t] = oracle.axpy(self.level, res[t], 1.0, ret[self.where[(t, d)]])
             if self.layer.has_shared:
                 res[t] = oracle.axpy(self.level, res[t], float(self._sigmoid(tap["shared_gate"][t])),
                                      tap["shared_out"][t])
@@ -97,12 +110,14 @@ def _worker(rank, world, port, cfg, n_per_rank):
         out = torch.zeros((n_per_rank, layer.n_embd), dtype=torch.float32)
         plan = ep_pass(steps, torch.from_numpy(h), out, False)
         want = oracle.moe_forward(layer, h)
-        assert plan.m == int(plan.recv_counts.sum()) and sum(plan.send_splits) == n_per_rank * layer.n_expert_used
-        np.testing.assert_array_equal(out.numpy(), want)
-        # every rank's received rows, summed, are every pair
-        total = torch.tensor([plan.m])
+        assert plan.m == sum(plan.recv_splits)
+        assert n_per_rank <= sum(plan.send_splits) <= n_per_rank * min(world, layer.n_expert_used)
+        # the sum over a token's experts is associated by rank first: f32 rounding apart
+        np.testing.assert_allclose(out.numpy(), want, rtol=0, atol=4e-7 * float(np.abs(want).max()))
+        # every row sent is a row received
+        total = torch.tensor([plan.m - sum(plan.send_splits)])
         dist.all_reduce(total)
-        assert int(total) == world * n_per_rank * layer.n_expert_used
+        assert int(total) == 0
     finally:
         dist.destroy_process_group()
 
@@ -121,16 +136,16 @@ def test_two_gloo_ranks_reproduce_the_single_process_oracle(cfg):
 
 def test_plan_is_consistent_across_ranks():
     rng = np.random.default_rng(0)
-    W, E = 4, 32
-    counts = rng.integers(0, 9, size=(W, E)).astype(np.int32)
-    counts[1, 8:16] = 0                                      # a rank that sends nothing to rank 1
+    W = 4
+    counts = rng.integers(0, 9, size=(W, W)).astype(np.int32)
+    counts[1, 2] = 0                                         # rank 1 sends nothing to rank 2
     plans = [ep_plan(counts, r) for r in range(W)]
     for r in range(W):
         assert sum(plans[r].send_splits) == counts[r].sum()
         for d in range(W):
             assert plans[r].send_splits[d] == plans[d].recv_splits[r]
-            assert plans[d].recv_counts[r].sum() == plans[r].send_splits[d]
-    assert plans[1].recv_splits[1] == 0
+        assert plans[r].m == counts[:, r].sum()
+    assert plans[2].recv_splits[1] == 0
 
 
 def test_local_experts_are_a_byte_range_of_the_same_tensor():

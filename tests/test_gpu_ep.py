@@ -6,8 +6,8 @@ This runs the device steps exactly as W processes would, without a second GPU.
 Two or more GPUs: the same pass as real processes over NCCL.
 
 Gates: every rank's output equals the single-GPU layer's output on the same rows
-bit for bit when both take the decode kernels (small row counts), and is within
-the layer tolerance of the CPU oracle always.
+up to the association of the f32 sum over a token's experts (the ranks return
+partial sums), and is within the layer tolerance of the CPU oracle.
 """
 import os
 import socket
@@ -131,10 +131,12 @@ def test_ranks_as_threads_match_the_single_gpu_layer(cfg, world, n):
     n_per = n // world
     want = np.concatenate([_single_gpu(layer, np.ascontiguousarray(h[r * n_per:(r + 1) * n_per]))
                            for r in range(world)])
-    np.testing.assert_array_equal(got, want)
+    np.testing.assert_allclose(got, want, rtol=0, atol=1e-6 * float(np.abs(want).max()))
     ref = oracle.moe_forward(layer, h)
     assert rel_err(got, ref) < TOL
-    assert sum(p.m for p in plans) == n * layer.n_expert_used
+    # a token's row goes once to every rank that owns one of its experts
+    k = layer.n_expert_used
+    assert n <= sum(p.m for p in plans) <= n * min(world, k)
 
 
 def test_full_size_layer_two_ranks_as_threads():
@@ -168,14 +170,11 @@ def test_steps_reject_a_plain_layer_and_bad_sizes():
         with pytest.raises(capi.BivMoeError):       # a whole-layer call on a sharded layer
             capi.check(capi.lib().bivmoe_forward(st._h, C.c_void_p(h.data_ptr()),
                                                  C.c_void_p(h.data_ptr()), 8, 0, None), st._h)
-        # a received-row count that is not the sum of the count matrix is reported
-        st.route(h)
-        counts = torch.zeros((2, 8), dtype=torch.int32, device="cuda")
-        counts[0, 0] = 3
-        st.experts(st.rows(4), counts, 4)
-        with pytest.raises(capi.BivMoeError) as ei:
-            st.status()
-        assert ei.value.code == capi.ERR_ARGUMENT
+        with pytest.raises(capi.BivMoeError):       # more received rows than max_recv_rows
+            capi.check(capi.lib().bivmoe_ep_experts(st._h, C.c_void_p(h.data_ptr()),
+                                                    C.c_void_p(h.data_ptr()), st.max_recv + 1,
+                                                    C.c_void_p(h.data_ptr()), None), st._h)
+        st.status()                                 # nothing failed on the device
     finally:
         st.close()
 
