@@ -229,7 +229,8 @@ def run_ep_workload(args, wl, rank, world, local):
                          "frac": flops / (ms * 1e-3) / 1e12 / world / tf_peak if tf_peak else None,
                          "traffic": None, "scope": "whole pass per GPU, exchanges included"},
             "exchange": {"rows_received_rank0": recv, "bytes_each_way_rank0": recv * row_bytes,
-                         "transport": "NCCL all_to_all_single over NVLink, f32 rows"},
+                         "transport": "NCCL all_to_all_single over NVLink; an f32 row once per owning "
+                                      "rank out, one f32 partial sum per row back"},
             "gpu_launches": None, "clocks": sampler.summary(),
         }
         print(json.dumps(line))
@@ -365,8 +366,9 @@ def main():
         ep = {"value": world * n / (ep_ms * 1e-3), "unit": UNIT, "ms_per_step": ep_ms,
               "parallelism": f"ep{world}", "experts_per_gpu": layer.n_expert // world,
               "tokens_per_gpu": n, "rows_received_rank0": ep_recv,
-              "note": "experts sharded, two NCCL all-to-alls and one host-read count exchange "
-                      "per pass; `value` above is the replicated (no-exchange) arrangement"}
+              "note": "experts sharded; per pass one count all-gather read by the host, rows and "
+                      "tags out and partial sums back as NCCL all-to-alls; `value` above is the "
+                      "replicated (no-exchange) arrangement"}
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
