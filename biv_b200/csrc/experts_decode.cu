@@ -25,6 +25,7 @@
 
 #include "common.cuh"
 #include "formats.cuh"
+#include "tcgen05.cuh"
 
 namespace bivmoe {
 
@@ -120,6 +121,18 @@ __device__ __forceinline__ void mma_u8s8_k32_f(float (&f)[4], const int (&a)[4],
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0x4B400000));
 #pragma unroll
     for (int i = 0; i < 4; i++) f[i] = __fsub_rn(__int_as_float(d[i]), 12582912.0f);
+}
+// The same, returning the results two tokens at a time (f32x2): lo = row g, hi = row g+8.
+__device__ __forceinline__ void mma_u8s8_k32_f2(f32x2& lo, f32x2& hi, const int (&a)[4], int b0, int b1) {
+    int d[4];
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0x4B400000));
+    const f32x2 neg = pk(-12582912.0f, -12582912.0f);
+    lo = add2(pk(__int_as_float(d[0]), __int_as_float(d[1])), neg);
+    hi = add2(pk(__int_as_float(d[2]), __int_as_float(d[3])), neg);
 }
 // the k = 16 form: a0 (row g, k 4c..4c+3), a1 (row g+8), b0 (k 4c..4c+3, column g)
 __device__ __forceinline__ void mma_s8_k16(int (&d)[4], int a0, int a1, int b0) {
@@ -250,12 +263,12 @@ template <int TY> struct FmtK45 {
                 mma_tf32_k8(tM[mt], a, bl0, bl1);
             }
         }
-        float tS[2][4] = {};
+        f32x2 tS[2][2] = {};   // [mt][r]: tokens 2c, 2c+1 of row g + 8r
         const uint8_t* xlane = act + g * 16 + 4 * c;
 #pragma unroll
         for (int j = 0; j < 4; j++) {       // sub-blocks 2j (low nibbles) and 2j+1 (high nibbles)
-            const float2 xa = *(const float2*)(dxp + (2 * j) * 8 + 2 * c);       // d of tokens 2c, 2c+1
-            const float2 xb = *(const float2*)(dxp + (2 * j + 1) * 8 + 2 * c);
+            const f32x2 xa = *(const f32x2*)(dxp + (2 * j) * 8 + 2 * c);         // d of tokens 2c, 2c+1
+            const f32x2 xb = *(const f32x2*)(dxp + (2 * j + 1) * 8 + 2 * c);
             const int blo0 = XQ(xlane, 4 * j), blo1 = XQ(xlane, 4 * j + 1);
             const int bhi0 = XQ(xlane, 4 * j + 2), bhi1 = XQ(xlane, 4 * j + 3);
 #pragma unroll
@@ -266,7 +279,7 @@ template <int TY> struct FmtK45 {
                 w[2] = LDS32(WU(rowp[mt][0], QOFF + 32 * j + 16) + 4 * c);
                 w[3] = LDS32(WU(rowp[mt][1], QOFF + 32 * j + 16) + 4 * c);
                 int alo[4], ahi[4];
-                float I[4];   // the int32 block dots, exactly, as floats
+                f32x2 I[2];   // the int32 block dots, exactly, as floats: [r] tokens 2c, 2c+1
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     alo[i] = (int)(w[i] & 0x0F0F0F0Fu);
@@ -281,27 +294,27 @@ template <int TY> struct FmtK45 {
                         ahi[i] |= (int)(((hb >> (2 * j + 1)) & 0x01010101u) << 4);
                     }
                 }
-                mma_u8s8_k32_f(I, alo, blo0, blo1);
+                mma_u8s8_k32_f2(I[0], I[1], alo, blo0, blo1);
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
                     const float scf = (float)k4_scale(sc[mt][r], 2 * j);
-                    tS[mt][2 * r] = fmaf(scf, xa.x * I[2 * r], tS[mt][2 * r]);
-                    tS[mt][2 * r + 1] = fmaf(scf, xa.y * I[2 * r + 1], tS[mt][2 * r + 1]);
+                    tS[mt][r] = fma2(pk(scf, scf), mul2(xa, I[r]), tS[mt][r]);
                 }
-                mma_u8s8_k32_f(I, ahi, bhi0, bhi1);
+                mma_u8s8_k32_f2(I[0], I[1], ahi, bhi0, bhi1);
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
                     const float scf = (float)k4_scale(sc[mt][r], 2 * j + 1) * (TY == BIVMOE_Q4_K ? 0.0625f : 1.0f);
-                    tS[mt][2 * r] = fmaf(scf, xb.x * I[2 * r], tS[mt][2 * r]);
-                    tS[mt][2 * r + 1] = fmaf(scf, xb.y * I[2 * r + 1], tS[mt][2 * r + 1]);
+                    tS[mt][r] = fma2(pk(scf, scf), mul2(xb, I[r]), tS[mt][r]);
                 }
             }
         }
 #pragma unroll
         for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-            for (int i = 0; i < 4; i++)
-                acc[mt][i] += d[mt][i >> 1] * tS[mt][i] - dmin[mt][i >> 1] * tM[mt][i];
+            for (int i = 0; i < 4; i++) {
+                const float ts = (i & 1) ? hi_of(tS[mt][i >> 1]) : lo_of(tS[mt][i >> 1]);
+                acc[mt][i] += d[mt][i >> 1] * ts - dmin[mt][i >> 1] * tM[mt][i];
+            }
     }
 };
 template <> struct Fmt<BIVMOE_Q4_K> : FmtK45<BIVMOE_Q4_K> {};

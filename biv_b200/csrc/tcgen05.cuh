@@ -105,7 +105,7 @@ __device__ __forceinline__ void pf_tmem_ld32(uint32_t taddr, int (&v)[32]) {
 __device__ __forceinline__ void pf_tmem_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-// two f32 lanes per instruction (sm_100): d = a * b + c, d = a * b
+// two f32 lanes per instruction (sm_100): d = a * b + c, d = a + b, d = a * b
 typedef unsigned long long f32x2;
 __device__ __forceinline__ f32x2 pk(float lo, float hi) {
     return (f32x2)__float_as_uint(lo) | ((f32x2)__float_as_uint(hi) << 32);
@@ -115,6 +115,13 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
 }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float lo_of(f32x2 v) { return __uint_as_float((uint32_t)v); }
+__device__ __forceinline__ float hi_of(f32x2 v) { return __uint_as_float((uint32_t)(v >> 32)); }
 __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
     f32x2 d;
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
