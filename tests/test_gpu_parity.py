@@ -344,3 +344,28 @@ def test_config5_bf16_full_size_kernel_families_agree(monkeypatch):
         m.close()
     assert np.isfinite(a).all() and rel_err(a, b) < 1e-4
     assert np.bincount(ids.reshape(-1), minlength=256).min() > 300   # balanced routing: all large groups
+
+
+def test_host_call_with_page_locked_buffers_replays_one_graph():
+    # with page-locked buffers the copies, the launches and the status read of the
+    # host-buffer call become one graph on its second identical call
+    import torch
+    from biv_b200.moe import Moe
+    wl = W.decode_q4k(n=40, **W.SMALL)
+    m = Moe(wl.layer, wl.n)
+    try:
+        want = m.moe_host(wl.h)                                  # pageable: plain path
+        h_pin = torch.from_numpy(wl.h).pin_memory()
+        out_pin = torch.empty_like(h_pin).pin_memory()
+        for _ in range(4):
+            out_pin.zero_()
+            m.moe_host(h_pin, out_pin)
+            assert np.array_equal(out_pin.numpy(), want)
+        h2 = W.decode_q4k(n=40, seed=9, **W.SMALL).h
+        h_pin.copy_(torch.from_numpy(h2))                        # same buffers, new rows
+        m.moe_host(h_pin, out_pin)
+        assert np.array_equal(out_pin.numpy(), m.moe_host(h2))
+        m.moe_host(h_pin[:8], out_pin[:8])                       # another n: a new graph
+        assert np.array_equal(out_pin[:8].numpy(), m.moe_host(h2[:8]))
+    finally:
+        m.close()
