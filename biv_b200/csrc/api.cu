@@ -397,9 +397,9 @@ int bivmoe_set_post_norm(bivmoe_layer* L, const float* w, float eps) {
 static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int accumulate,
                         cudaStream_t stream, cudaEvent_t* ev = nullptr) {
     std::string* errp = &L->error;
-    if (!h || !out) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null activation pointer");
     if (n < 0 || n > L->max_tokens)
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens = %d", n, L->max_tokens);
+    if (n > 0 && (!h || !out)) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null activation pointer");
     if (L->ep_world > 1)
         return set_err(errp, BIVMOE_ERR_ARGUMENT,
                        "the layer holds 1/%d of the experts: use the bivmoe_ep_* steps", L->ep_world);
@@ -481,10 +481,14 @@ static int forward_graphed(bivmoe_layer* L, const float* h, float* out, int n, i
 int bivmoe_forward(bivmoe_layer* L, const float* h_dev, float* out_dev, int32_t n,
                    int32_t accumulate, void* stream) {
     if (!L) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer");
-    if (!h_dev || !out_dev) return set_err(&L->error, BIVMOE_ERR_ARGUMENT, "null activation pointer");
     if (n < 0 || n > L->max_tokens)
         return set_err(&L->error, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens = %d", n,
                        L->max_tokens);
+    if (n == 0) {   // no rows (their pointers may be null): nothing to do
+        L->last_n = 0;
+        return BIVMOE_OK;
+    }
+    if (!h_dev || !out_dev) return set_err(&L->error, BIVMOE_ERR_ARGUMENT, "null activation pointer");
     return forward_graphed(L, h_dev, out_dev, n, accumulate, (cudaStream_t)stream);
 }
 
@@ -649,9 +653,13 @@ static int forward_host_enqueue(bivmoe_layer* L, const float* h_host, float* out
 int bivmoe_forward_host(bivmoe_layer* L, const float* h_host, float* out_host, int32_t n) {
     if (!L) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer");
     std::string* errp = &L->error;
-    if (!h_host || !out_host) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null host pointer");
     if (n < 0 || n > L->max_tokens)
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens = %d", n, L->max_tokens);
+    if (n == 0) {
+        L->last_n = 0;
+        return BIVMOE_OK;
+    }
+    if (!h_host || !out_host) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null host pointer");
     CU(cudaSetDevice(L->device));
     if (!L->host_in) {
         const size_t bytes = (size_t)L->max_tokens * L->e * 4;
@@ -662,7 +670,6 @@ int bivmoe_forward_host(bivmoe_layer* L, const float* h_host, float* out_host, i
         L->ws_bytes += 2 * bytes;
         CU(cudaHostAlloc((void**)&L->status_host, 16, cudaHostAllocDefault));
     }
-    if (n == 0) return BIVMOE_OK;
     cudaStream_t s = L->own_stream;
     auto& G = L->host_graph;
     const bool same = G.h == h_host && G.out == out_host && G.n == n;

@@ -604,6 +604,7 @@ experts_kernel(const ExpertArgs A) {
             nxt_claimed = 1;
             pump();
         }
+        int ks = 0, chunk = cur.chunk0;   // the stage's K-slice inside its chunk, and the chunk
         for (int s = 0; s < cur.nst; s++) {
             const bool claim = !nxt_claimed && cur.nst - s <= EX_LEAD;
             if (claim && tid == 0) pf = (int)atomicAdd(A.work_ctr, 1u);
@@ -641,9 +642,8 @@ experts_kernel(const ExpertArgs A) {
                 nxt_claimed = 1;
             }
             pump();
-            if ((s + 1) % cur.nsl) continue;
+            if (++ks < cur.nsl) continue;
             // ---- epilogue of the chunk that just ended
-            const int chunk = cur.chunk0 + s / cur.nsl;
             const int rows = (cur.shared ? A.sh : A.w).rows;
             if (MODE == MODE_GATEUP) {
                 // SwiGLU into the staging tile [token][64 rows of the chunk]
@@ -712,6 +712,8 @@ experts_kernel(const ExpertArgs A) {
                 for (int i = 0; i < 4; i++) acc[mt][i] = 0.0f;
 #pragma unroll
             for (int t = 0; t < EX_TT; t++) accf[t] = 0.0f;
+            ks = 0;
+            chunk++;
         }
         if (!nxt.valid) break;
         // the stream may already run inside `nxt`: it becomes the current item

@@ -369,3 +369,22 @@ def test_host_call_with_page_locked_buffers_replays_one_graph():
         assert np.array_equal(out_pin[:8].numpy(), m.moe_host(h2[:8]))
     finally:
         m.close()
+
+
+def test_edges_empty_input_every_expert_and_the_expert_limit():
+    import torch
+    from biv_b200.moe import Moe
+    # no rows: a successful no-op that leaves the output alone
+    wl = W.parity_q8_0(n=4, **W.SMALL)
+    m = Moe(wl.layer, 4)
+    try:
+        h = torch.empty((0, wl.layer.n_embd), device="cuda")
+        assert m.moe(h).shape == (0, wl.layer.n_embd)
+        assert m.moe_host(np.empty((0, wl.layer.n_embd), np.float32)).shape == (0, wl.layer.n_embd)
+    finally:
+        m.close()
+    # k = n_expert (every token selects every expert), one expert with k = 1, and the
+    # largest expert count the library accepts with the narrowest matrices it accepts
+    run_case(W.decode_q4k(n=13, **dict(W.SMALL, n_expert=8, k=8)))
+    run_case(W.parity_q8_0(n=10, **dict(W.SMALL, n_expert=1, k=1)))
+    run_case(W.parity_q8_0(n=70, **dict(W.SMALL, n_expert=1024, k=32)), check_dots=False)
