@@ -163,9 +163,27 @@ __device__ __forceinline__ void mma_tf32_k8(float (&d)[4], const float (&a)[4], 
 //                then dx, s_hi, s_lo as [8 blocks][8 tokens] f32
 //   XQ(act,u)    this lane's B-fragment word of unit u: token g, bytes 4c..4c+3
 //   acc[mt][i]   i = 2*r + tt: row g+8r, token 2c+tt
+// All of these take 32-bit shared-memory addresses and load with ld.shared: no
+// generic-address arithmetic, constant offsets fold into the instruction.
 #define WU(w, off) ((w) + ((((off)) >> 4) << 11) + ((off) & 15))
-#define LDS32(p) (*(const uint32_t*)(p))
-#define XQ(xlane, u) ((int)LDS32((xlane) + (u) * 128))
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float ldsf(uint32_t a) { return __uint_as_float(lds32(a)); }
+__device__ __forceinline__ f32x2 lds64(uint32_t a) {
+    f32x2 v;
+    asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+#define LDS32(a) lds32(a)
+#define XQ(xlane, u) ((int)lds32((xlane) + (u) * 128))
 
 struct NoSide {};
 
@@ -176,23 +194,23 @@ template <> struct Fmt<BIVMOE_Q8_0> {
     static constexpr int ELEMS = 256, SL = 272, MINB = 2;   // 2 x 37.7 KB stages per block
     static constexpr bool F32ACT = false;
     using Side = NoSide;
-    __device__ static void compute(const uint8_t* const (&rowp)[2][2], Side, const uint8_t* act,
+    __device__ static void compute(const uint32_t (&rowp)[2][2], Side, uint32_t act,
                                    float (&acc)[2][4], int g, int c) {
-        const float* dxp = (const float*)(act + kActOffDx);
+        const uint32_t dxp = act + kActOffDx;
         uint4 dwv[2][2];   // the 8 f16 scales of each row's slice (unit 16)
 #pragma unroll
         for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-            for (int r = 0; r < 2; r++) dwv[mt][r] = *(const uint4*)WU(rowp[mt][r], 256);
-        const uint8_t* xlane = act + g * 16 + 4 * c;
+            for (int r = 0; r < 2; r++) dwv[mt][r] = lds128(WU(rowp[mt][r], 256));
+        const uint32_t xlane = act + g * 16 + 4 * c;
 #pragma unroll
         for (int j = 0; j < 4; j++) {       // blocks 2j and 2j+1
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 const int b = 2 * j + h;
                 const int b0 = XQ(xlane, 2 * b), b1 = XQ(xlane, 2 * b + 1);
-                const float2 dxv = *(const float2*)(dxp + b * 8 + 2 * c);   // tokens 2c, 2c+1
-                const float dx[2] = {dxv.x, dxv.y};
+                const f32x2 dxv = lds64(dxp + 4 * (b * 8 + 2 * c));   // tokens 2c, 2c+1
+                const float dx[2] = {lo_of(dxv), hi_of(dxv)};
 #pragma unroll
                 for (int mt = 0; mt < 2; mt++) {
                     int a[4], I[4];
@@ -223,11 +241,9 @@ template <int TY> struct FmtK45 {
     static constexpr int ELEMS = 256, SL = TY == BIVMOE_Q4_K ? 144 : 176, MINB = 4;
     static constexpr bool F32ACT = false;
     using Side = NoSide;
-    __device__ static void compute(const uint8_t* const (&rowp)[2][2], Side, const uint8_t* act,
+    __device__ static void compute(const uint32_t (&rowp)[2][2], Side, uint32_t act,
                                    float (&acc)[2][4], int g, int c) {
-        const float* dxp = (const float*)(act + kActOffDx);
-        const float* shi = (const float*)(act + kActOffSHi);
-        const float* slo = (const float*)(act + kActOffSLo);
+        const uint32_t dxp = act + kActOffDx, shi = act + kActOffSHi, slo = act + kActOffSLo;
         float d[2][2], dmin[2][2];
         K4Scales sc[2][2];
         uint32_t qh[2][2][2];
@@ -235,7 +251,7 @@ template <int TY> struct FmtK45 {
         for (int mt = 0; mt < 2; mt++)
 #pragma unroll
             for (int r = 0; r < 2; r++) {
-                const uint4 v = *(const uint4*)rowp[mt][r];
+                const uint4 v = lds128(rowp[mt][r]);
                 const __half2 dd = *(const __half2*)&v.x;
                 d[mt][r] = __low2float(dd);
                 dmin[mt][r] = __high2float(dd);
@@ -250,8 +266,8 @@ template <int TY> struct FmtK45 {
         // two tf32-exact parts.  Lane (g, c) supplies m of blocks c, c+4 and s of token g.
         float tM[2][4] = {};
         {
-            const float bh0 = shi[c * 8 + g], bh1 = shi[(c + 4) * 8 + g];
-            const float bl0 = slo[c * 8 + g], bl1 = slo[(c + 4) * 8 + g];
+            const float bh0 = ldsf(shi + 4 * (c * 8 + g)), bh1 = ldsf(shi + 4 * ((c + 4) * 8 + g));
+            const float bl0 = ldsf(slo + 4 * (c * 8 + g)), bl1 = ldsf(slo + 4 * ((c + 4) * 8 + g));
 #pragma unroll
             for (int mt = 0; mt < 2; mt++) {
                 float a[4];
@@ -264,11 +280,11 @@ template <int TY> struct FmtK45 {
             }
         }
         f32x2 tS[2][2] = {};   // [mt][r]: tokens 2c, 2c+1 of row g + 8r
-        const uint8_t* xlane = act + g * 16 + 4 * c;
+        const uint32_t xlane = act + g * 16 + 4 * c;
 #pragma unroll
         for (int j = 0; j < 4; j++) {       // sub-blocks 2j (low nibbles) and 2j+1 (high nibbles)
-            const f32x2 xa = *(const f32x2*)(dxp + (2 * j) * 8 + 2 * c);         // d of tokens 2c, 2c+1
-            const f32x2 xb = *(const f32x2*)(dxp + (2 * j + 1) * 8 + 2 * c);
+            const f32x2 xa = lds64(dxp + 4 * ((2 * j) * 8 + 2 * c));             // d of tokens 2c, 2c+1
+            const f32x2 xb = lds64(dxp + 4 * ((2 * j + 1) * 8 + 2 * c));
             const int blo0 = XQ(xlane, 4 * j), blo1 = XQ(xlane, 4 * j + 1);
             const int bhi0 = XQ(xlane, 4 * j + 2), bhi1 = XQ(xlane, 4 * j + 3);
 #pragma unroll
@@ -333,15 +349,15 @@ template <> struct Fmt<BIVMOE_Q6_K> {
         const uint32_t t = v ^ 0x20202020u;
         return (int)(t | ((t & 0x20202020u) * 7u));
     }
-    __device__ static void compute(const uint8_t* const (&rowp)[2][2], Side sd, const uint8_t* act,
+    __device__ static void compute(const uint32_t (&rowp)[2][2], Side sd, uint32_t act,
                                    float (&acc)[2][4], int g, int c) {
-        const float* dxp = (const float*)(act + kActOffDx);
+        const uint32_t dxp = act + kActOffDx;
         uint4 scv[2][2];   // the 16 int8 scales of each row's super-block (unit 12)
 #pragma unroll
         for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-            for (int r = 0; r < 2; r++) scv[mt][r] = *(const uint4*)WU(rowp[mt][r], 192);
-        const uint8_t* xlane = act + g * 16 + 4 * c;
+            for (int r = 0; r < 2; r++) scv[mt][r] = lds128(WU(rowp[mt][r], 192));
+        const uint32_t xlane = act + g * 16 + 4 * c;
 #pragma unroll
         for (int n = 0; n < 2; n++) {
             uint32_t qh[2][2][2];   // [mt][r][lhalf]
@@ -365,8 +381,8 @@ template <> struct Fmt<BIVMOE_Q6_K> {
 #pragma unroll
                 for (int hi = 0; hi < 2; hi++) {
                     const int kq = par + 2 * hi, xb = 4 * n + kq;
-                    const float2 dxv = *(const float2*)(dxp + xb * 8 + 2 * c);
-                    const float dx0 = dxv.x, dx1 = dxv.y;
+                    const f32x2 dxv = lds64(dxp + 4 * (xb * 8 + 2 * c));
+                    const float dx0 = lo_of(dxv), dx1 = hi_of(dxv);
                     const int b0 = XQ(xlane, 2 * xb), b1 = XQ(xlane, 2 * xb + 1);
 #pragma unroll
                     for (int mt = 0; mt < 2; mt++) {
@@ -475,6 +491,7 @@ experts_kernel(const ExpertArgs A) {
     int* s_item = (int*)(smem + 16);           // [2]
     float* s_mid = (float*)(smem + 64);        // [EX_TT][64]
     uint8_t* ring = smem + EX_SMEM_HEAD;
+    const uint32_t ring_a = smem_u32(ring);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c = lane & 3;
 
@@ -626,13 +643,14 @@ experts_kernel(const ExpertArgs A) {
                 else wrow = st + (32 * warp + lane) * 16;
                 F::compute_f32(wrow, (const float*)act, cur.tc, accf);
             } else {
-                const uint8_t* rowp[2][2];
+                uint32_t rowp[2][2];
+                const uint32_t sta = ring_a + (uint32_t)slot * SB;
 #pragma unroll
                 for (int mt = 0; mt < 2; mt++)
 #pragma unroll
                     for (int r = 0; r < 2; r++)
-                        rowp[mt][r] = st + (row_of[mt] + g + 8 * r) * 16;
-                F::compute(rowp, slot ? side1 : side0, act, acc, g, c);
+                        rowp[mt][r] = sta + (row_of[mt] + g + 8 * r) * 16;
+                F::compute(rowp, slot ? side1 : side0, sta + W_BYTES, acc, g, c);
             }
             if (claim && tid == 0) s_item[n_fetch & 1] = pf;
             __syncthreads();   // every warp is done with the slot; the claimed value is visible
