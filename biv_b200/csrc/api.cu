@@ -117,8 +117,7 @@ static void layout_one(bivmoe_layer* L, Arena& a, Workspace& w, size_t N, size_t
     w.grp_count = a.take<int32_t>(ne + 1);
     w.n_groups = a.take<int32_t>(1);
     const size_t tiles = P / 8 + N / 8 + ne + 2;
-    w.tile_group = a.take<int32_t>(tiles);
-    w.tile_t0 = a.take<int32_t>(tiles);
+    w.tile_desc = a.take<int4>(tiles);
     w.n_tiles = a.take<int32_t>(2);
     const size_t ptiles = (P + N) / kPrefillTile + ne + 2;
     w.ptile_group = a.take<int32_t>(ptiles);

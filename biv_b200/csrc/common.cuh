@@ -128,8 +128,8 @@ struct Workspace {
     int32_t* grp_start;  // [n_expert + 1] first position
     int32_t* grp_count;  // [n_expert + 1]
     int32_t* n_groups;   // [1]
-    int32_t* tile_group; // [tiles] tile -> group; a tile is <= 8 consecutive positions of a group
-    int32_t* tile_t0;    // [tiles] first token of the tile inside its group
+    int4* tile_desc;     // [tiles] a tile is <= 8 consecutive positions of a group:
+                         // {expert id (n_expert = shared), first position, tokens, 0}
     int32_t* n_tiles;    // [2] all tiles; the shared group's tiles (they come first)
     int32_t* ptile_group;// [ptiles] tiles of 128 positions of the prefill-sized groups
     int32_t* ptile_t0;

@@ -46,8 +46,7 @@ struct ExpertArgs {
     const int32_t* grp_expert;
     const int32_t* grp_start;
     const int32_t* grp_count;
-    const int32_t* tile_group;
-    const int32_t* tile_t0;
+    const int4* tile_desc;    // {expert (n_expert: shared), first position, tokens, 0}
     const int32_t* n_tiles;   // [0] all tiles, [1] tiles of the shared group (they come first)
     uint32_t* work_ctr;
     int32_t* status;
@@ -522,11 +521,11 @@ experts_kernel(const ExpertArgs A) {
         if (!it.valid) return it;
         const int tile = tile_lo + idx / groups_of_chunks;
         it.chunk0 = (idx % groups_of_chunks) * CG;
-        const int gi = A.tile_group[tile], t0 = A.tile_t0[tile];
-        it.expert = A.grp_expert[gi];
+        const int4 td = A.tile_desc[tile];   // one load: no chain of dependent lookups
+        it.expert = td.x;
         it.shared = it.expert == A.n_expert;
-        it.pos0 = A.grp_start[gi] + t0;
-        it.tc = min(EX_TT, A.grp_count[gi] - t0);
+        it.pos0 = td.y;
+        it.tc = td.z;
         const DevTiles& m = it.shared ? A.sh : A.w;
         it.nsl = m.nslices;
         it.nst = max(0, min(CG, m.chunks - it.chunk0)) * m.nslices;
@@ -575,7 +574,8 @@ experts_kernel(const ExpertArgs A) {
         }
     };
 
-    if (tid == 0) s_item[0] = (int)atomicAdd(A.work_ctr, 1u);
+    // the first item needs no counter: block b starts with item b, later claims follow the grid
+    if (tid == 0) s_item[0] = (int)blockIdx.x;
     __syncthreads();
     Item cur = fetch();
     if (!cur.valid) return;
@@ -615,7 +615,7 @@ experts_kernel(const ExpertArgs A) {
 #pragma unroll
         for (int t = 0; t < EX_TT; t++) accf[t] = 0.0f;
         if (cur.nst == 0 && !nxt_claimed) {   // nothing to do for this group: claim the next right away
-            if (tid == 0) s_item[n_fetch & 1] = (int)atomicAdd(A.work_ctr, 1u);
+            if (tid == 0) s_item[n_fetch & 1] = (int)(gridDim.x + atomicAdd(A.work_ctr, 1u));
             __syncthreads();
             nxt = fetch();
             nxt_claimed = 1;
@@ -624,7 +624,7 @@ experts_kernel(const ExpertArgs A) {
         int ks = 0, chunk = cur.chunk0;   // the stage's K-slice inside its chunk, and the chunk
         for (int s = 0; s < cur.nst; s++) {
             const bool claim = !nxt_claimed && cur.nst - s <= EX_LEAD;
-            if (claim && tid == 0) pf = (int)atomicAdd(A.work_ctr, 1u);
+            if (claim && tid == 0) pf = (int)(gridDim.x + atomicAdd(A.work_ctr, 1u));
             const int slot = consumed & 1;
             if (!mbar_wait_bounded(&mbar[slot], (consumed >> 1) & 1, A.wait_hint_ns)) {
                 // every thread waits on the same barrier, so all give up together: flag
@@ -791,7 +791,7 @@ cudaError_t launch_experts(const LaunchCfg& c, const DevTiles& gate_up, const De
                            const DevTiles& sh_gate_up, const DevTiles& sh_down, const Workspace& ws) {
     ExpertArgs A{};
     A.grp_expert = ws.grp_expert; A.grp_start = ws.grp_start; A.grp_count = ws.grp_count;
-    A.tile_group = ws.tile_group; A.tile_t0 = ws.tile_t0; A.n_tiles = ws.n_tiles;
+    A.tile_desc = ws.tile_desc; A.n_tiles = ws.n_tiles;
     A.status = ws.status;
     A.n = c.n; A.k = c.k; A.n_expert = c.n_expert;
     A.act_rows = ws.act_rows;

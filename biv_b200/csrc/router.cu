@@ -437,8 +437,8 @@ __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, in
             const bool big = prefill_min > 0 && cnt[i] >= prefill_min;
             const int nt = big ? 0 : (cnt[i] + SORT_TILE - 1) / SORT_TILE;
             for (int j = 0; j < nt; j++) {
-                ws.tile_group[t_sh + til[i] + j] = g;
-                ws.tile_t0[t_sh + til[i] + j] = j * SORT_TILE;
+                ws.tile_desc[t_sh + til[i] + j] =
+                    make_int4(e, start + j * SORT_TILE, min(SORT_TILE, cnt[i] - j * SORT_TILE), 0);
             }
             const int npt = big ? (cnt[i] + ptile - 1) / ptile : 0;
             for (int j = 0; j < npt; j++) {
@@ -448,8 +448,7 @@ __device__ void sort_scan(const Workspace& ws, int n_expert, int nblk, int n, in
         }
     }
     for (int j = threadIdx.x; j < t_sh; j += blockDim.x) {
-        ws.tile_group[j] = 0;
-        ws.tile_t0[j] = j * SORT_TILE;
+        ws.tile_desc[j] = make_int4(n_expert, j * SORT_TILE, min(SORT_TILE, n - j * SORT_TILE), 0);
     }
     for (int j = threadIdx.x; j < pt_sh; j += blockDim.x) {
         ws.ptile_group[j] = 0;
