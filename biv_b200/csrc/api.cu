@@ -167,6 +167,22 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
                            "%s: %s", #call, cudaGetErrorString(e_));                      \
     } while (0)
 
+// Makes the layer's device current for the duration of an entry point and puts the
+// caller's back afterwards (a caller with several GPUs in one process need not switch).
+struct DeviceScope {
+    int prev = -1;
+    bool switched = false;
+    explicit DeviceScope(int device) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != device)
+            switched = cudaSetDevice(device) == cudaSuccess;
+    }
+    ~DeviceScope() {
+        if (switched) cudaSetDevice(prev);
+    }
+    DeviceScope(const DeviceScope&) = delete;
+    DeviceScope& operator=(const DeviceScope&) = delete;
+};
+
 static int check_stack(std::string* errp, const char* name, const bivmoe_experts& s, int64_t cols,
                        int64_t rows, int64_t n, bool is_down) {
     if (!s.data) return set_err(errp, BIVMOE_ERR_ARGUMENT, "%s: null data", name);
@@ -480,6 +496,7 @@ static int forward_graphed(bivmoe_layer* L, const float* h, float* out, int n, i
 int bivmoe_forward(bivmoe_layer* L, const float* h_dev, float* out_dev, int32_t n,
                    int32_t accumulate, void* stream) {
     if (!L) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer");
+    DeviceScope on_device(L->device);
     if (n < 0 || n > L->max_tokens)
         return set_err(&L->error, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens = %d", n,
                        L->max_tokens);
@@ -505,6 +522,7 @@ static int ep_check(bivmoe_layer* L, const char* what) {
 int bivmoe_ep_route(bivmoe_layer* L, const float* h_dev, int32_t n, float* send_rows_dev,
                     int32_t* send_tags_dev, int32_t* send_counts_dev, void* stream) {
     if (int rc = ep_check(L, "bivmoe_ep_route")) return rc;
+    DeviceScope on_device(L->device);
     std::string* errp = &L->error;
     if (!h_dev || !send_rows_dev || !send_tags_dev || !send_counts_dev)
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "null pointer");
@@ -532,6 +550,7 @@ int bivmoe_ep_route(bivmoe_layer* L, const float* h_dev, int32_t n, float* send_
 
 int bivmoe_ep_shared(bivmoe_layer* L, const float* h_dev, void* stream) {
     if (int rc = ep_check(L, "bivmoe_ep_shared")) return rc;
+    DeviceScope on_device(L->device);
     std::string* errp = &L->error;
     const int n = L->ep_n;
     if (!L->has_shared || n == 0) return BIVMOE_OK;
@@ -553,6 +572,7 @@ int bivmoe_ep_shared(bivmoe_layer* L, const float* h_dev, void* stream) {
 int bivmoe_ep_experts(bivmoe_layer* L, const float* recv_rows_dev, const int32_t* recv_tags_dev,
                       int32_t m, float* out_rows_dev, void* stream) {
     if (int rc = ep_check(L, "bivmoe_ep_experts")) return rc;
+    DeviceScope on_device(L->device);
     std::string* errp = &L->error;
     if (m < 0 || m > L->max_recv)
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "m = %d outside 0..max_recv_rows = %d", m, L->max_recv);
@@ -580,6 +600,7 @@ int bivmoe_ep_experts(bivmoe_layer* L, const float* recv_rows_dev, const int32_t
 int bivmoe_ep_combine(bivmoe_layer* L, const float* returned_rows_dev, float* out_dev, int32_t n,
                       int32_t accumulate, void* stream) {
     if (int rc = ep_check(L, "bivmoe_ep_combine")) return rc;
+    DeviceScope on_device(L->device);
     std::string* errp = &L->error;
     if (n != L->ep_n)
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d, but bivmoe_ep_route ran on %d rows", n, L->ep_n);
@@ -596,6 +617,7 @@ int bivmoe_ep_combine(bivmoe_layer* L, const float* returned_rows_dev, float* ou
 
 int bivmoe_ep_status(bivmoe_layer* L, void* stream) {
     if (int rc = ep_check(L, "bivmoe_ep_status")) return rc;
+    DeviceScope on_device(L->device);
     std::string* errp = &L->error;
     cudaStream_t s = (cudaStream_t)stream;
     int32_t st[2] = {0, 0};
@@ -614,6 +636,7 @@ int bivmoe_ep_status(bivmoe_layer* L, void* stream) {
 int bivmoe_forward_profile(bivmoe_layer* L, const float* h_dev, float* out_dev, int32_t n,
                            void* stream, float* ms) {
     if (!L || !ms) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or buffer");
+    DeviceScope on_device(L->device);
     std::string* errp = &L->error;
     cudaEvent_t ev[EV_COUNT];
     for (int i = 0; i < EV_COUNT; i++) CU(cudaEventCreate(&ev[i]));
@@ -659,7 +682,7 @@ int bivmoe_forward_host(bivmoe_layer* L, const float* h_host, float* out_host, i
         return BIVMOE_OK;
     }
     if (!h_host || !out_host) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null host pointer");
-    CU(cudaSetDevice(L->device));
+    DeviceScope on_device(L->device);
     if (!L->host_in) {
         const size_t bytes = (size_t)L->max_tokens * L->e * 4;
         CU(cudaMalloc((void**)&L->host_in, bytes));
@@ -727,6 +750,7 @@ int bivmoe_forward_stack(bivmoe_layer* const* layers, int32_t n_layers, float* x
         if (n < 0 || n > L->max_tokens)
             return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens", n);
         if (n == 0) continue;
+        DeviceScope on_device(L->device);
         LaunchCfg c{(cudaStream_t)stream, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh,
                     L->has_shared ? 1 : 0, L->sm_count};
         CU(launch_rms_norm(c, x_dev, L->post_norm, L->norm_eps, L->ws.h_norm));

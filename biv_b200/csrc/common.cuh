@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/bivmoe.h"
 
 namespace bivmoe {
@@ -159,6 +161,20 @@ struct LaunchCfg {
 enum { EV_START = 0, EV_ROUTER, EV_TOPK, EV_SORT, EV_QUANT, EV_GATEUP, EV_DOWN, EV_COMBINE, EV_COUNT };
 inline void mark(const LaunchCfg& c, int which) {
     if (c.ev) cudaEventRecord(c.ev[which], c.stream);
+}
+
+// Raises a kernel's dynamic shared-memory limit once per device (the attribute is per
+// device; `done` is the caller's static bit mask, one bit per device ordinal).
+template <class K>
+inline cudaError_t ensure_dynamic_smem(K kernel, int bytes, std::atomic<uint64_t>& done) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const uint64_t bit = 1ull << (dev & 63);
+    if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) done.fetch_or(bit, std::memory_order_release);
+    return e;
 }
 
 // kernels (one translation unit each)

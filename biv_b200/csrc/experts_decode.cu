@@ -760,13 +760,8 @@ static cudaError_t launch_one(const LaunchCfg& c, ExpertArgs A) {
     A.chunks = std::max(A.w.chunks, A.sh.chunks);
     constexpr int smem = smem_bytes<TY>();
     static_assert(smem * Fmt<TY>::MINB <= 227 * 1024, "the blocks of one SM must fit in shared memory");
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(experts_kernel<TY, MODE>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    static std::atomic<uint64_t> attr_set{0};
+    if (cudaError_t e = ensure_dynamic_smem(experts_kernel<TY, MODE>, smem, attr_set)) return e;
     experts_kernel<TY, MODE><<<c.sm_count * Fmt<TY>::MINB, EX_THREADS, smem, c.stream>>>(A);
     count_launch();
     return cudaGetLastError();

@@ -340,13 +340,8 @@ bool prefill_supported(int gate_up_ty, int down_ty) {
 template <int MODE>
 static cudaError_t launch_prefill_one(const LaunchCfg& c, PrefillArgs A) {
     A.chunks = std::max(A.w.chunks, A.sh.chunks);
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(experts_prefill_kernel<MODE>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    static std::atomic<uint64_t> attr_set{0};
+    if (cudaError_t e = ensure_dynamic_smem(experts_prefill_kernel<MODE>, (int)PF_SMEM, attr_set)) return e;
     experts_prefill_kernel<MODE><<<c.sm_count, PF_THREADS, PF_SMEM, c.stream>>>(A);
     count_launch();
     return cudaGetLastError();

@@ -303,13 +303,8 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
 template <int MODE>
 static cudaError_t launch_bf16_one(const LaunchCfg& c, Bf16Args A) {
     A.chunks = std::max(A.w.chunks, A.sh.chunks);
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(experts_prefill_bf16_kernel<MODE>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, BF_SMEM);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    static std::atomic<uint64_t> attr_set{0};
+    if (cudaError_t e = ensure_dynamic_smem(experts_prefill_bf16_kernel<MODE>, (int)BF_SMEM, attr_set)) return e;
     experts_prefill_bf16_kernel<MODE><<<c.sm_count, BF_THREADS, BF_SMEM, c.stream>>>(A);
     count_launch();
     return cudaGetLastError();

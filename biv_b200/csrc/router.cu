@@ -211,13 +211,8 @@ cudaError_t launch_router(const LaunchCfg& c, const float* router_dev, const flo
                           const Workspace& ws) {
     int n_rows = c.n_expert + 1;
     if (c.n >= RL_MIN_TOKENS && c.e % RL_KC == 0) {
-        static bool attr_set = false;
-        if (!attr_set) {
-            cudaError_t err = cudaFuncSetAttribute(router_logits_tiled_kernel,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, RL_SMEM);
-            if (err != cudaSuccess) return err;
-            attr_set = true;
-        }
+        static std::atomic<uint64_t> attr_set{0};
+        if (cudaError_t err = ensure_dynamic_smem(router_logits_tiled_kernel, RL_SMEM, attr_set)) return err;
         dim3 grid((n_rows + RL_BROWS - 1) / RL_BROWS, (c.n + RL_BTOKS - 1) / RL_BTOKS);
         router_logits_tiled_kernel<<<grid, RT_THREADS, RL_SMEM, c.stream>>>(router_dev, h, ws.logits, c.n,
                                                                            c.e, n_rows);
@@ -226,13 +221,8 @@ cudaError_t launch_router(const LaunchCfg& c, const float* router_dev, const flo
     }
     const int smem = 128 + (RT_BROWS + RT_BTOKS) * c.e * 4;
     if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t err = cudaFuncSetAttribute(router_logits_kernel,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (err != cudaSuccess) return err;
-        attr_set = true;
-    }
+    static std::atomic<uint64_t> attr_set{0};
+    if (cudaError_t err = ensure_dynamic_smem(router_logits_kernel, 227 * 1024, attr_set)) return err;
     dim3 grid((n_rows + RT_BROWS - 1) / RT_BROWS, (c.n + RT_BTOKS - 1) / RT_BTOKS);
     router_logits_kernel<<<grid, RT_THREADS, smem, c.stream>>>(router_dev, h, ws.logits, c.n, c.e,
                                                                n_rows, ws.status);
@@ -541,12 +531,8 @@ cudaError_t launch_sort(const LaunchCfg& c, const Workspace& ws) {
     const int nblk = (c.n + SORT_TOKENS - 1) / SORT_TOKENS;
     size_t smem = (((size_t)SORT_TOKENS * c.k * 2 + 15) & ~(size_t)15) + (size_t)c.n_expert * 4 +
                   (size_t)c.n_expert * (SORT_TOKENS / 32) * 4;   // <= 16 + 4 + 32 KiB
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t err = cudaFuncSetAttribute(sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-        if (err != cudaSuccess) return err;
-        attr_set = true;
-    }
+    static std::atomic<uint64_t> attr_set{0};
+    if (cudaError_t err = ensure_dynamic_smem(sort_kernel, 64 * 1024, attr_set)) return err;
     if (nblk == 1) {
         sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, c.prefill_tile, 0);
         count_launch();

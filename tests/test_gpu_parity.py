@@ -388,3 +388,26 @@ def test_edges_empty_input_every_expert_and_the_expert_limit():
     run_case(W.decode_q4k(n=13, **dict(W.SMALL, n_expert=8, k=8)))
     run_case(W.parity_q8_0(n=10, **dict(W.SMALL, n_expert=1, k=1)))
     run_case(W.parity_q8_0(n=70, **dict(W.SMALL, n_expert=1024, k=32)), check_dots=False)
+
+
+def test_a_layer_on_a_second_device_of_the_same_process():
+    # kernel attributes are per device and the entry points make the layer's device
+    # current themselves: a process may hold layers on several GPUs
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from biv_b200.moe import Moe
+    wl = W.decode_q4k(n=24, **W.SMALL)
+    ref = oracle.moe_forward(wl.layer, wl.h)
+    outs = []
+    for dev in (0, 1, 0):
+        m = Moe(wl.layer, wl.n, device=dev)
+        try:
+            torch.cuda.set_device(0)                       # not the layer's device
+            h = torch.from_numpy(wl.h).to(f"cuda:{dev}")
+            outs.append(m.moe(h).cpu().numpy())
+            assert torch.cuda.current_device() == 0        # and it is left as it was
+        finally:
+            m.close()
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    assert rel_err(outs[1], ref) < TOL
