@@ -244,7 +244,9 @@ def config_of(wl, args, world):
                         f"gate/up {W.TYPE_NAMES[l.gate.ty]} down {W.TYPE_NAMES[l.down.ty]}, seed {wl.seed}",
             "tokens_per_gpu": wl.n, "parallelism": "replicas" if world > 1 else "single",
             "l2": f"steps rotate over {max(1, args.copies)} resident copies of the layer's weights "
-                  "(working set > 126 MB L2), no flush"}
+                  "(working set > 126 MB L2), no flush",
+            "streams": "passes alternate on two streams, two in flight" if getattr(args, "streams", 2) != 1
+            else "one stream, one pass at a time"}
 
 
 def main():
@@ -258,6 +260,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--copies", type=int, default=WEIGHT_COPIES,
                     help="resident copies of the layer the timed loop rotates over")
+    ap.add_argument("--streams", type=int, default=2, help="streams the timed passes alternate on (1 or 2)")
     ap.add_argument("--quick", action="store_true",
                     help="warm-up and timed loop only (the command profilers wrap)")
     args = ap.parse_args()
@@ -295,12 +298,20 @@ def main():
 
     # a side stream: the library replays its launch sequence as a CUDA graph, which the
     # legacy default stream cannot capture
-    side = torch.cuda.Stream()
+    # Passes alternate on two streams (layer object j on stream j % 2): the ramp and tail
+    # of one pass's kernels overlap another's, as with a host that keeps two micro-batches
+    # in flight.  `--quick` (the command profilers wrap) keeps one stream.
+    nstreams = 2 if (ncopies % 2 == 0 and not args.quick and args.streams != 1) else 1
+    streams = [torch.cuda.Stream() for _ in range(nstreams)]
+    outs = [out] + [torch.empty_like(h) for _ in range(nstreams - 1)]
+    side = streams[0]
     torch.cuda.synchronize()
     torch.cuda.set_stream(side)
 
     def step(i):
-        copies[i % ncopies].moe_(h, out, accumulate=False)
+        j = i % ncopies
+        with torch.cuda.stream(streams[j % nstreams]):
+            copies[j].moe_(h, outs[j % nstreams], accumulate=False)
 
     for i in range(warmup):
         step(i)
@@ -313,10 +324,14 @@ def main():
     barrier()
     l0 = launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
+    e0.record(streams[0])
     for i in range(args.steps):
         step(i)
-    e1.record()
+    for st in streams[1:]:      # the second event closes after both streams' work
+        joined = torch.cuda.Event()
+        joined.record(st)
+        streams[0].wait_event(joined)
+    e1.record(streams[0])
     barrier()
     launches = launch_count() - l0
     ms = e0.elapsed_time(e1)
@@ -324,13 +339,37 @@ def main():
         if rank == 0:
             print(json.dumps({"quick": True, "ms_per_step": ms / args.steps, "steps": args.steps}))
         return
-    # ---- end to end: host rows in, host delta out, through the host-buffer call
+    # ---- end to end: host rows in, host delta out, through the host-buffer call.  Every
+    #      step copies its rows in from page-locked memory and its result out.  First one
+    #      pass at a time; then with two passes in flight on different layer objects
+    #      (bivmoe_forward_host_async / bivmoe_host_wait), which lets the copies of one
+    #      pass overlap the kernels of another - how a host with several micro-batches
+    #      drives the layers.
     for i in range(3):
         copies[i % ncopies].moe_host(h_pin, out_pin)
     barrier()
     t0 = time.perf_counter()
     for i in range(args.steps):
         copies[i % ncopies].moe_host(h_pin, out_pin)
+    torch.cuda.synchronize()
+    e2e_sync_s = time.perf_counter() - t0
+    depth = 2 if ncopies % 2 == 0 else 1
+    h_pins = [h_pin] + [torch.from_numpy(wl.h).pin_memory() for _ in range(depth - 1)]
+    out_pins = [out_pin] + [torch.empty_like(h_pin).pin_memory() for _ in range(depth - 1)]
+
+    def pipelined(count):
+        for i in range(count):
+            j = i % ncopies
+            if i >= depth:
+                copies[(i - depth) % ncopies].wait()
+            copies[j].moe_host_async(h_pins[j % depth], out_pins[j % depth])
+        for i in range(max(0, count - depth), count):
+            copies[i % ncopies].wait()
+
+    pipelined(3 * ncopies)      # each layer object sees its buffers twice: the graphs exist
+    barrier()
+    t0 = time.perf_counter()
+    pipelined(args.steps)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     # ---- the dominant kernel alone, events around each launch (separate loop so
@@ -352,10 +391,10 @@ def main():
     sampler.stop_flag = True
     sampler.join()
 
-    t = torch.tensor([ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
+    t = torch.tensor([ms, e2e_s * 1e3, e2e_sync_s * 1e3], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(t[0]), float(t[1])
+    ms, e2e_ms, e2e_sync_ms = float(t[0]), float(t[1]), float(t[2])
     # ---- the same shape with the experts sharded over the GPUs instead of replicated:
     #      every rank passes its own n rows, rows travel to the experts' owners and back
     ep = None
@@ -395,7 +434,11 @@ def main():
                      "layer_bytes": lbytes,
                      "layer_frac": lbytes / (ms_step * 1e-3) / 1e9 / hbm_peak},
         "e2e": {"value": world * n * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
-                "h2d_bytes_per_step": n * layer.n_embd * 4, "d2h_bytes_per_step": n * layer.n_embd * 4},
+                "h2d_bytes_per_step": n * layer.n_embd * 4, "d2h_bytes_per_step": n * layer.n_embd * 4,
+                "passes_in_flight": depth,
+                "one_pass_at_a_time": world * n * args.steps / (e2e_sync_ms * 1e-3),
+                "call": "bivmoe_forward_host_async + bivmoe_host_wait on page-locked buffers; every "
+                        "step copies its rows in and its result out"},
         "gpu_launches": launches,
         "clocks": sampler.summary(),
     }

@@ -25,7 +25,8 @@ SYMBOLS = ["bivmoe_create", "bivmoe_destroy", "bivmoe_forward", "bivmoe_forward_
            "bivmoe_set_post_norm", "bivmoe_forward_stack", "bivmoe_tap", "bivmoe_tap_block_dots",
            "bivmoe_route_noalloc", "bivmoe_numerics", "bivmoe_memory", "bivmoe_launch_count", "bivmoe_last_error",
            "bivmoe_global_error", "bivmoe_ep_create", "bivmoe_ep_route", "bivmoe_ep_shared",
-           "bivmoe_ep_experts", "bivmoe_ep_combine", "bivmoe_ep_status"]
+           "bivmoe_ep_experts", "bivmoe_ep_combine", "bivmoe_ep_status", "bivmoe_forward_host_async",
+           "bivmoe_host_wait"]
 
 
 class BivMoeError(RuntimeError):
@@ -70,6 +71,8 @@ def lib():
         L.bivmoe_destroy.restype = None
         L.bivmoe_forward.argtypes = [vp, vp, vp, i32, i32, vp]
         L.bivmoe_forward_host.argtypes = [vp, vp, vp, i32]
+        L.bivmoe_forward_host_async.argtypes = [vp, vp, vp, i32]
+        L.bivmoe_host_wait.argtypes = [vp]
         L.bivmoe_forward_profile.argtypes = [vp, vp, vp, i32, vp, C.POINTER(C.c_float)]
         L.bivmoe_set_post_norm.argtypes = [vp, vp, C.c_float]
         L.bivmoe_forward_stack.argtypes = [C.POINTER(vp), i32, vp, i32, vp]

@@ -672,7 +672,7 @@ static int forward_host_enqueue(bivmoe_layer* L, const float* h_host, float* out
     return BIVMOE_OK;
 }
 
-int bivmoe_forward_host(bivmoe_layer* L, const float* h_host, float* out_host, int32_t n) {
+int bivmoe_forward_host_async(bivmoe_layer* L, const float* h_host, float* out_host, int32_t n) {
     if (!L) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer");
     std::string* errp = &L->error;
     if (n < 0 || n > L->max_tokens)
@@ -729,6 +729,15 @@ int bivmoe_forward_host(bivmoe_layer* L, const float* h_host, float* out_host, i
         if (rc) return rc;
     }
     L->last_n = n;
+    return BIVMOE_OK;
+}
+
+int bivmoe_host_wait(bivmoe_layer* L) {
+    if (!L) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer");
+    std::string* errp = &L->error;
+    if (!L->status_host) return BIVMOE_OK;   // no host-buffer call was ever made
+    DeviceScope on_device(L->device);
+    cudaStream_t s = L->own_stream;
     CU(cudaStreamSynchronize(s));
     if (L->status_host[0]) {
         const int code = L->status_host[0];
@@ -736,6 +745,11 @@ int bivmoe_forward_host(bivmoe_layer* L, const float* h_host, float* out_host, i
         return set_err(errp, code, "a device-side bounded wait gave up (status %d)", code);
     }
     return BIVMOE_OK;
+}
+
+int bivmoe_forward_host(bivmoe_layer* L, const float* h_host, float* out_host, int32_t n) {
+    if (int rc = bivmoe_forward_host_async(L, h_host, out_host, n)) return rc;
+    return n > 0 ? bivmoe_host_wait(L) : BIVMOE_OK;
 }
 
 int bivmoe_forward_stack(bivmoe_layer* const* layers, int32_t n_layers, float* x_dev, int32_t n,

@@ -113,6 +113,18 @@ class Moe:
         self.last_n = n
         return out_host
 
+    def moe_host_async(self, h_host, out_host):
+        """The first half of ``moe_host``: enqueue and return.  ``out_host`` is valid
+        after ``wait()``; one pass per layer object may be outstanding."""
+        hp, n = _host_ptr(h_host, self.n_embd)
+        op, n2 = _host_ptr(out_host, self.n_embd)
+        assert n == n2
+        capi.check(capi.lib().bivmoe_forward_host_async(self._h, hp, op, n), self._h)
+        self.last_n = n
+
+    def wait(self):
+        capi.check(capi.lib().bivmoe_host_wait(self._h), self._h)
+
     STAGES = ("router", "topk", "sort", "quantize", "gateup", "down", "combine")
 
     def profile(self, h, out) -> dict:

@@ -114,6 +114,17 @@ BIVMOE_API int bivmoe_forward(bivmoe_layer* layer, const float* h_dev, float* ou
  * waits for it.  Pinned host buffers make the copies asynchronous. */
 BIVMOE_API int bivmoe_forward_host(bivmoe_layer* layer, const float* h_host, float* out_host, int32_t n);
 
+/* The same in two halves, for a host that keeps several passes in flight (layers
+ * of different micro-batches, each layer object with its own buffers): the first
+ * enqueues copy-in, the layer, copy-out on the layer's own stream and returns;
+ * the second waits for it and reports a device-side failure.  `out_host` is
+ * complete, and `h_host` reusable, only after bivmoe_host_wait.  One pass per layer
+ * object may be outstanding; page-locked buffers are needed for the copies to
+ * overlap anything. */
+BIVMOE_API int bivmoe_forward_host_async(bivmoe_layer* layer, const float* h_host, float* out_host,
+                                         int32_t n);
+BIVMOE_API int bivmoe_host_wait(bivmoe_layer* layer);
+
 /* `bivmoe_forward` (accumulate 0) with CUDA events between its stages, for
  * benchmarks: waits for the pass and writes the device time of each stage in
  * milliseconds to ms[7] = {router product, softmax/top-k, sort, activation

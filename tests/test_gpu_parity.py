@@ -411,3 +411,27 @@ def test_a_layer_on_a_second_device_of_the_same_process():
             m.close()
     assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
     assert rel_err(outs[1], ref) < TOL
+
+
+def test_two_host_passes_in_flight_on_two_layer_objects():
+    import torch
+    from biv_b200.moe import Moe
+    wl = W.decode_q4k(n=40, **W.SMALL)
+    a, b = Moe(wl.layer, wl.n), Moe(wl.layer, wl.n)
+    try:
+        want = a.moe_host(wl.h)
+        h2 = W.decode_q4k(n=40, seed=11, **W.SMALL).h
+        want2 = a.moe_host(h2)
+        hp = [torch.from_numpy(wl.h).pin_memory(), torch.from_numpy(h2).pin_memory()]
+        op = [torch.empty_like(hp[0]).pin_memory(), torch.empty_like(hp[1]).pin_memory()]
+        for _ in range(4):
+            for o in op:
+                o.zero_()
+            a.moe_host_async(hp[0], op[0])
+            b.moe_host_async(hp[1], op[1])
+            a.wait()
+            b.wait()
+            assert np.array_equal(op[0].numpy(), want) and np.array_equal(op[1].numpy(), want2)
+    finally:
+        a.close()
+        b.close()
