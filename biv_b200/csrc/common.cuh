@@ -31,7 +31,7 @@ namespace bivmoe {
 //   BF16   64        128  64 values
 constexpr int kRepackVersion = 4;
 constexpr int kChunkRows = 128;
-constexpr int kPrefillTile = 96;    // tokens per tile of the tcgen05 kernel for Q8_0
+constexpr int kPrefillTile = 128;   // tokens per tile of the tcgen05 kernel for Q8_0
 constexpr int kPrefillTileBf16 = 128;   // and for BF16
 constexpr int kPrefillPad = 128;    // positions a tile's copy may run past the last group
 

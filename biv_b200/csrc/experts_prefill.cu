@@ -5,18 +5,19 @@
 // engine/src/model.rs:1119-1126, over the Q8_0 dot, engine/src/quant.rs:599-607),
 // for experts whose token list is long (model.rs:875-889).
 //
-// Design.  One block per SM, thirteen warps: one warp whose lane 0 issues the
-// copies and whose lane 1 issues the MMAs, and twelve epilogue warps (three per
-// tensor-memory lane quadrant, 32 token columns each, which keeps a thread's
-// accumulators and one drained block within 128 registers).  A work item is a
-// tile of 96 tokens of one group times a chunk of 128 weight rows (64 gate rows with their 64 up rows, or 128 down
-// rows).  The device layouts of common.cuh are already the tensor core's
+// Design.  One block per SM, seventeen warps: one warp whose lane 0 issues the
+// copies and whose lane 1 issues the MMAs, and sixteen epilogue warps (four per
+// tensor-memory lane quadrant, 32 token columns each: a thread's accumulators and
+// one drained block fit in the 96 registers that 544 threads leave each, and four
+// warps per scheduler hide the tensor-memory load latency better than three).  A
+// work item is a tile of 128 tokens of one group times a chunk of 128 weight rows
+// (64 gate rows with their 64 up rows, or 128 down rows).  The device layouts of common.cuh are already the tensor core's
 // canonical K-major operand layouts, so a stage - one K-slice of 256 columns:
-// 128 rows x 272 bytes of weights and the 12 activation records of the tile -
+// 128 rows x 272 bytes of weights and the 16 activation records of the tile -
 // is two bulk copies (cp.async.bulk) and no shuffling.  The reference scales
 // every 32-element block dot by its own pair of scales, so the products cannot
 // accumulate across blocks inside the tensor core: each block is one MMA
-// (M = 128 rows, N = 96 tokens, K = 32) into one of four tensor-memory buffers,
+// (M = 128 rows, N = 128 tokens, K = 32) into one of four tensor-memory buffers,
 // which the epilogue warps drain (tcgen05.ld), scale by d_w * d_x and add to f32
 // accumulators in registers while the next MMA runs.  The int32 values in tensor
 // memory are the reference's block dots exactly.  The epilogue is the bottleneck
@@ -42,17 +43,17 @@
 namespace bivmoe {
 
 constexpr int PF_NT = kPrefillTile;                  // tokens per tile = MMA N
-constexpr int PF_EPI_WARPS = 12;                     // three per tensor-memory lane quadrant
+constexpr int PF_EPI_WARPS = 16;                     // four per tensor-memory lane quadrant
 constexpr int PF_COLS = PF_NT / (PF_EPI_WARPS / 4);  // token columns per epilogue thread
 static_assert(PF_COLS == 32, "an epilogue thread drains one 32-column load per block dot");
 constexpr int PF_THREADS = 32 * (1 + PF_EPI_WARPS);  // warp 0: lane 0 copies, lane 1 issues MMAs
 constexpr int PF_SL = 272;                           // Q8_0: bytes per row per K-slice
 constexpr uint32_t PF_W_BYTES = kChunkRows * PF_SL;                // 34816
-constexpr uint32_t PF_X_BYTES = (PF_NT / 8) * kActTileBytes;       // 36864
-constexpr uint32_t PF_STAGE = PF_W_BYTES + PF_X_BYTES;             // 71680
+constexpr uint32_t PF_X_BYTES = (PF_NT / 8) * kActTileBytes;       // 49152
+constexpr uint32_t PF_STAGE = PF_W_BYTES + PF_X_BYTES;             // 83968
 constexpr uint32_t PF_HEAD = 1024;
-constexpr uint32_t PF_XCHG = 64 * PF_NT * 4;                        // SwiGLU exchange, 24 KiB
-constexpr uint32_t PF_SMEM = PF_HEAD + 2 * PF_STAGE + PF_XCHG;      // 168960
+constexpr uint32_t PF_XCHG = 64 * PF_NT * 4;                        // SwiGLU exchange, 32 KiB
+constexpr uint32_t PF_SMEM = PF_HEAD + 2 * PF_STAGE + PF_XCHG;      // 201728
 constexpr uint32_t PF_TMEM_COLS = 512;                              // four buffers, 128 columns apart
 constexpr uint32_t PF_TBUF = 4;
 constexpr uint32_t PF_TSTRIDE = PF_TMEM_COLS / PF_TBUF;
@@ -95,7 +96,7 @@ experts_prefill_kernel(const PrefillArgs A) {
     uint32_t* s_tmem = (uint32_t*)(smem + 256);
     int* s_abort = (int*)(smem + 260);
     uint8_t* stages = smem + PF_HEAD;
-    float* s_xchg = (float*)(smem + PF_HEAD + 2 * PF_STAGE);   // [96 tokens][64 rows]
+    float* s_xchg = (float*)(smem + PF_HEAD + 2 * PF_STAGE);   // [128 tokens][64 rows]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int CH = MODE == PF_GATEUP ? 64 : 128;   // output rows per chunk
 
@@ -204,7 +205,7 @@ experts_prefill_kernel(const PrefillArgs A) {
         // ---------------- epilogue warps
         const int ew = warp - 1;                 // 0..11
         const int quad = warp & 3;               // the tensor-memory lanes this warp may read
-        const int cg = ew >> 2;                  // which 32 of the 96 token columns
+        const int cg = ew >> 2;                  // which 32 of the 128 token columns
         const int row = 32 * quad + lane;        // chunk row = tensor-memory lane
         const uint32_t tlane = tmem + ((uint32_t)(32 * quad) << 16) + cg * PF_COLS;
         uint32_t q = 0, kb = 0, xphase = 0;
