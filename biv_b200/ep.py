@@ -83,12 +83,26 @@ def ep_pass(steps, h, out, accumulate: bool, comm=None):
     ``experts(recv_rows, recv_tags, m) -> out_rows`` and
     ``combine(returned_rows, out, accumulate)``; ``comm`` the two collectives
     (``TorchComm`` over the default process group when None)."""
-    import torch
     comm = comm or TorchComm()
-    W, rank = steps.world, steps.rank
+    return ep_pass_finish(steps, h, out, accumulate, comm, ep_pass_begin(steps, h, comm))
+
+
+def ep_pass_begin(steps, h, comm):
+    """The part of a pass before its host synchronisation: routing and the exchange of
+    the row counts, enqueued and not waited for.  A host that keeps two passes in flight
+    (two micro-batches, each with its own ``steps`` and stream) begins both before it
+    finishes either, so that one pass's exchanges overlap the other's kernels."""
+    import torch
+    W = steps.world
     send_rows, send_tags, send_counts = steps.route(h)
     flat = torch.empty((W * W,), dtype=torch.int32, device=send_counts.device)
     comm.all_gather(flat, send_counts)
+    return send_rows, send_tags, flat
+
+
+def ep_pass_finish(steps, h, out, accumulate: bool, comm, begun):
+    W, rank = steps.world, steps.rank
+    send_rows, send_tags, flat = begun
     counts_host = flat.view(W, W).cpu().numpy()     # the one host synchronisation of the pass
     plan = ep_plan(counts_host, rank)
     steps.shared(h)                                  # overlaps the exchange where it can
@@ -208,6 +222,15 @@ class EpMoe:
 
     def moe_(self, h, out, accumulate: bool = True):
         self.last_plan = ep_pass(self.steps, h, out, accumulate, self.comm)
+        return out
+
+    def begin(self, h):
+        """``moe_`` in two halves (see ``ep_pass_begin``): enqueue the routing."""
+        self._begun = (h, ep_pass_begin(self.steps, h, self.comm))
+
+    def finish(self, out, accumulate: bool = True):
+        h, begun = self._begun
+        self.last_plan = ep_pass_finish(self.steps, h, out, accumulate, self.comm, begun)
         return out
 
     def moe(self, h):

@@ -192,9 +192,28 @@ def _nccl_worker(rank, world, port, cfg, n, tmp):
         layer, n_per = wl.layers[0], n // world
         h = np.ascontiguousarray(wl.h[rank * n_per:(rank + 1) * n_per])
         m = EpMoe(layer, n_per, rank, world, rank)
-        out = m.moe(torch.from_numpy(h).cuda(rank))
+        hd = torch.from_numpy(h).cuda(rank)
+        out = m.moe(hd)
         m.status()
         np.save(os.path.join(tmp, f"out{rank}.npy"), out.cpu().numpy())
+        # the same rows as two micro-batches in flight, each with its own layer object and stream
+        half = n_per // 2
+        parts = [EpMoe(layer, half, rank, world, rank) for _ in range(2)]
+        streams = [torch.cuda.Stream() for _ in range(2)]
+        out2 = torch.empty_like(hd)
+        torch.cuda.synchronize()
+        for _ in range(2):
+            for i in range(2):
+                with torch.cuda.stream(streams[i]):
+                    parts[i].begin(hd[i * half:(i + 1) * half])
+            for i in range(2):
+                with torch.cuda.stream(streams[i]):
+                    parts[i].finish(out2[i * half:(i + 1) * half], accumulate=False)
+        torch.cuda.synchronize()
+        for p_ in parts:
+            p_.status()
+            p_.close()
+        assert torch.equal(out2, out)
         m.close()
     finally:
         dist.destroy_process_group()
