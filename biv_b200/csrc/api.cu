@@ -788,6 +788,8 @@ static int copy_out(bivmoe_layer* L, void* dst, const void* src, size_t want, si
 int bivmoe_tap(bivmoe_layer* L, int32_t which, void* dst, size_t bytes) {
     if (!L || !dst) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or buffer");
     std::string* errp = &L->error;
+    if (L->ep_world > 1)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "taps read a whole layer's workspace; this layer is sharded");
     CU(cudaSetDevice(L->device));
     CU(cudaDeviceSynchronize());
     const size_t n = (size_t)L->last_n, k = L->k, ne = L->n_expert, e = L->e, P = n * k;
@@ -885,6 +887,8 @@ int bivmoe_tap_block_dots(bivmoe_layer* L, int32_t matrix, int32_t expert, int32
                           int32_t act_row, int32_t* out) {
     if (!L || !out) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or buffer");
     std::string* errp = &L->error;
+    if (L->ep_world > 1)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "taps read a whole layer's workspace; this layer is sharded");
     CU(cudaSetDevice(L->device));
     CU(cudaDeviceSynchronize());
     if (matrix < 0 || matrix > 5 || (matrix >= 3 && !L->has_shared))
