@@ -273,8 +273,8 @@ def config_of(wl, args, world):
             "tokens_per_gpu": wl.n, "parallelism": "replicas" if world > 1 else "single",
             "l2": f"steps rotate over {max(1, args.copies)} resident copies of the layer's weights "
                   "(working set > 126 MB L2), no flush",
-            "streams": "passes alternate on two streams, two in flight" if getattr(args, "streams", 2) != 1
-            else "one stream, one pass at a time"}
+            "streams": f"passes rotate over {args.streams} streams, {args.streams} in flight"
+            if getattr(args, "streams", 2) != 1 else "one stream, one pass at a time"}
 
 
 def main():
@@ -288,7 +288,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--copies", type=int, default=WEIGHT_COPIES,
                     help="resident copies of the layer the timed loop rotates over")
-    ap.add_argument("--streams", type=int, default=2, help="streams the timed passes alternate on (1 or 2)")
+    ap.add_argument("--streams", type=int, default=WEIGHT_COPIES,
+                    help="passes in flight: the timed passes rotate over this many streams, layer object "
+                         "j on stream j mod streams (must divide --copies; 1: one pass at a time)")
     ap.add_argument("--ep-in-flight", type=int, default=1,
                     help="micro-batches a rank keeps in flight in the expert-parallel workload (two "
                          "measured slower than one at 2 GPUs: 2.65 against 2.50 ms)")
@@ -329,10 +331,12 @@ def main():
 
     # a side stream: the library replays its launch sequence as a CUDA graph, which the
     # legacy default stream cannot capture
-    # Passes alternate on two streams (layer object j on stream j % 2): the ramp and tail
-    # of one pass's kernels overlap another's, as with a host that keeps two micro-batches
-    # in flight.  `--quick` (the command profilers wrap) keeps one stream.
-    nstreams = 2 if (ncopies % 2 == 0 and not args.quick and args.streams != 1) else 1
+    # Passes rotate over `--streams` streams (layer object j on stream j mod streams): the
+    # latency-bound routing kernels and the ramp and tail of one pass's expert kernels
+    # overlap another's, as with a host that keeps several micro-batches in flight.
+    # Measured at the decode shape: 94 us per pass alone, 77 with two in flight, 57 with
+    # four.  `--quick` (the command profilers wrap) keeps one stream.
+    nstreams = args.streams if (args.streams >= 1 and ncopies % max(1, args.streams) == 0 and not args.quick) else 1
     streams = [torch.cuda.Stream() for _ in range(nstreams)]
     outs = [out] + [torch.empty_like(h) for _ in range(nstreams - 1)]
     side = streams[0]
@@ -370,6 +374,21 @@ def main():
         if rank == 0:
             print(json.dumps({"quick": True, "ms_per_step": ms / args.steps, "steps": args.steps}))
         return
+    # ---- the same K steps one pass at a time on one stream (the latency figure)
+    def step_alone(i):
+        with torch.cuda.stream(streams[0]):
+            copies[i % ncopies].moe_(h, outs[0], accumulate=False)
+
+    for i in range(3 * ncopies):     # the layers' graphs are rebuilt for the new stream
+        step_alone(i)
+    barrier()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record(streams[0])
+    for i in range(args.steps):
+        step_alone(i)
+    a1.record(streams[0])
+    barrier()
+    ms_alone = a0.elapsed_time(a1)
     # ---- end to end: host rows in, host delta out, through the host-buffer call.  Every
     #      step copies its rows in from page-locked memory and its result out.  First one
     #      pass at a time; then with two passes in flight on different layer objects
@@ -384,7 +403,7 @@ def main():
         copies[i % ncopies].moe_host(h_pin, out_pin)
     torch.cuda.synchronize()
     e2e_sync_s = time.perf_counter() - t0
-    depth = 2 if ncopies % 2 == 0 else 1
+    depth = nstreams
     h_pins = [h_pin] + [torch.from_numpy(wl.h).pin_memory() for _ in range(depth - 1)]
     out_pins = [out_pin] + [torch.empty_like(h_pin).pin_memory() for _ in range(depth - 1)]
 
@@ -422,10 +441,10 @@ def main():
     sampler.stop_flag = True
     sampler.join()
 
-    t = torch.tensor([ms, e2e_s * 1e3, e2e_sync_s * 1e3], device="cuda", dtype=torch.float64)
+    t = torch.tensor([ms, e2e_s * 1e3, e2e_sync_s * 1e3, ms_alone], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, e2e_sync_ms = float(t[0]), float(t[1]), float(t[2])
+    ms, e2e_ms, e2e_sync_ms, ms_alone = float(t[0]), float(t[1]), float(t[2]), float(t[3])
     # ---- the same shape with the experts sharded over the GPUs instead of replicated:
     #      every rank passes its own n rows, rows travel to the experts' owners and back
     ep = None
@@ -456,6 +475,9 @@ def main():
         "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8 x int8 -> int32 block dots, f32 scales",
         "data": "synthetic", "config": config_of(wl, args, world),
+        "one_pass_at_a_time": {"value": world * n * args.steps / (ms_alone * 1e-3), "unit": UNIT,
+                               "ms_per_step": ms_alone / args.steps,
+                               "note": "the same steps on one stream, each pass after the previous"},
         "roofline": {"bound": "hbm", "kernel": "experts_kernel<gate+up>", "achieved": achieved,
                      "peak": hbm_peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
                      "frac": achieved / hbm_peak if achieved else None, "traffic": None,
