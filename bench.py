@@ -265,6 +265,71 @@ def run_ep_workload(args, wl, rank, world, local):
     dist.destroy_process_group()
 
 
+def run_stack_workload(args, rank, world, local):
+    """`--workload mtp_stack` (BASELINE.json configs[3]): the 40-layer MoE FFN stack over
+    32 sequences x 5 tokens, gate/up Q5_K and down Q6_K, rms_norm before each layer and
+    the residual carried; a step is one pass of the whole stack (`--layers` of it)."""
+    import torch
+    from biv_b200.moe import Moe, MoeStack, launch_count
+    wl = W.mtp_stack(n_layers=args.layers)
+    n, nl = wl.n, len(wl.layers)
+    layers = [Moe(l, n, device=local) for l in wl.layers]
+    for m, nw in zip(layers, wl.norm_w):
+        m.set_post_norm(nw, wl.eps)
+    stack = MoeStack(layers)
+    x0 = torch.from_numpy(wl.h).cuda()
+    x = x0.clone()
+    stream = torch.cuda.Stream()
+    torch.cuda.synchronize()
+
+    def step():
+        with torch.cuda.stream(stream):
+            x.copy_(x0)                 # the residual of a fresh pass
+            stack.forward_(x)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    l0 = launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    launches = launch_count() - l0
+    sampler.stop_flag = True
+    sampler.join()
+    ms = e0.elapsed_time(e1) / args.steps
+    hits = [int((m.tap(3) > 0).sum()) for m in layers]          # TAP_COUNTS of the last pass
+    hbm_peak, _, peak_kind = load_peaks()
+    bytes_pass = sum(algorithmic_bytes(l, n, h_) for l, h_ in zip(wl.layers, hits))
+    l = wl.layers[0]
+    line = {
+        "metric": METRIC, "value": world * n / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int8 -> int32 block dots, f32 scales",
+        "data": "synthetic",
+        "config": {"workload": f"mtp_stack: {nl} MoE FFN layers, {n} tokens (32 sequences x 5), hidden "
+                               f"{l.n_embd}, {l.n_expert} experts top-{l.n_expert_used} + shared expert, ff "
+                               f"{l.n_ff_exp}, gate/up Q5_K down Q6_K, rms_norm + residual per layer, seed {wl.seed}",
+                   "tokens_per_gpu": n, "layers": nl, "parallelism": "single" if world == 1 else "replicas",
+                   "l2": f"{nl} layers of weights ({sum(x_.weight_bytes() for x_ in wl.layers) / 1e9:.1f} GB) "
+                         "stream through the 126 MB L2 once per pass, no flush"},
+        "roofline": {"bound": "hbm", "kernel": "whole stack", "achieved": bytes_pass / (ms * 1e-3) / 1e9,
+                     "peak": hbm_peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+                     "frac": bytes_pass / (ms * 1e-3) / 1e9 / hbm_peak, "traffic": None,
+                     "bytes_per_pass": bytes_pass, "experts_hit_per_layer": hits},
+        "gpu_launches": launches, "clocks": sampler.summary(),
+    }
+    for m in layers:
+        m.close()
+    if rank == 0:
+        print(json.dumps(line))
+
+
 def config_of(wl, args, world):
     l = wl.layer
     return {"workload": f"{wl.name}: {wl.n} tokens per GPU, hidden {l.n_embd}, {l.n_expert} experts "
@@ -291,6 +356,7 @@ def main():
     ap.add_argument("--streams", type=int, default=WEIGHT_COPIES,
                     help="passes in flight: the timed passes rotate over this many streams, layer object "
                          "j on stream j mod streams (must divide --copies; 1: one pass at a time)")
+    ap.add_argument("--layers", type=int, default=40, help="layers of the mtp_stack workload")
     ap.add_argument("--ep-in-flight", type=int, default=1,
                     help="micro-batches a rank keeps in flight in the expert-parallel workload (two "
                          "measured slower than one at 2 GPUs: 2.65 against 2.50 ms)")
@@ -313,6 +379,8 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     warmup = max(args.warmup, 3)
 
+    if args.workload == "mtp_stack":
+        return run_stack_workload(args, rank, world, local)
     wl = make_workload(args.workload, args)
     if world > 1 and args.workload == "ep_bf16":
         return run_ep_workload(args, wl, rank, world, local)
