@@ -266,7 +266,7 @@ def run_ep_workload(args, wl, rank, world, local):
 
 
 def run_stack_workload(args, rank, world, local):
-    """`--workload mtp_stack` (BASELINE.json configs[3]): the 40-layer MoE FFN stack over
+    """`--workload mtp_stack` (the MTP-verify shape): the 40-layer MoE FFN stack over
     32 sequences x 5 tokens, gate/up Q5_K and down Q6_K, rms_norm before each layer and
     the residual carried; a step is one pass of the whole stack (`--layers` of it)."""
     import torch
