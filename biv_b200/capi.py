@@ -26,7 +26,7 @@ SYMBOLS = ["bivmoe_create", "bivmoe_destroy", "bivmoe_forward", "bivmoe_forward_
            "bivmoe_route_noalloc", "bivmoe_numerics", "bivmoe_memory", "bivmoe_launch_count", "bivmoe_last_error",
            "bivmoe_global_error", "bivmoe_ep_create", "bivmoe_ep_route", "bivmoe_ep_shared",
            "bivmoe_ep_experts", "bivmoe_ep_combine", "bivmoe_ep_status", "bivmoe_forward_host_async",
-           "bivmoe_host_wait"]
+           "bivmoe_host_wait", "bivmoe_int8_peak"]
 
 
 class BivMoeError(RuntimeError):
@@ -73,6 +73,7 @@ def lib():
         L.bivmoe_forward_host.argtypes = [vp, vp, vp, i32]
         L.bivmoe_forward_host_async.argtypes = [vp, vp, vp, i32]
         L.bivmoe_host_wait.argtypes = [vp]
+        L.bivmoe_int8_peak.argtypes = [vp, C.POINTER(C.c_double)]
         L.bivmoe_forward_profile.argtypes = [vp, vp, vp, i32, vp, C.POINTER(C.c_float)]
         L.bivmoe_set_post_norm.argtypes = [vp, vp, C.c_float]
         L.bivmoe_forward_stack.argtypes = [C.POINTER(vp), i32, vp, i32, vp]

@@ -921,6 +921,20 @@ int bivmoe_tap_block_dots(bivmoe_layer* L, int32_t matrix, int32_t expert, int32
     return BIVMOE_OK;
 }
 
+int bivmoe_int8_peak(bivmoe_layer* L, double* tops) {
+    if (!L || !tops) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or result");
+    std::string* errp = &L->error;
+    DeviceScope on_device(L->device);
+    CU(measure_int8_peak(L->sm_count, L->ws.status + 1, L->own_stream, tops));
+    int32_t st = 0;
+    CU(cudaMemcpy(&st, L->ws.status + 1, 4, cudaMemcpyDeviceToHost));
+    if (st) {
+        cudaMemset(L->ws.status + 1, 0, 4);
+        return set_err(errp, st, "the probe's bounded wait gave up");
+    }
+    return BIVMOE_OK;
+}
+
 int bivmoe_numerics(const bivmoe_layer* L, char* buf, size_t len) {
     if (!L || !buf || !len) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or buffer");
     snprintf(buf, len,

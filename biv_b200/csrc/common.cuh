@@ -217,6 +217,7 @@ cudaError_t launch_block_dots(const DevTiles& t, int tile_base, int expert, int 
                               cudaStream_t stream);
 bool experts_supported(int ty, int cols, int rows, bool is_down);
 bool prefill_supported(int gate_up_ty, int down_ty);
+cudaError_t measure_int8_peak(int sm_count, int32_t* status_dev, cudaStream_t stream, double* tops);
 cudaError_t launch_experts_prefill_bf16(const LaunchCfg& c, const DevTiles& gate_up, const DevTiles& down,
                                         const DevTiles& sh_gate_up, const DevTiles& sh_down,
                                         const Workspace& ws);

@@ -373,3 +373,82 @@ cudaError_t launch_experts_prefill(const LaunchCfg& c, const DevTiles& gate_up, 
 }
 
 }  // namespace bivmoe
+
+// ---------------------------------------------------------------------------
+// The int8 tensor-pipe peak of this GPU, measured: no int8 figure comes with the
+// machine's measured peaks, so the Q8_0 kernel's roofline denominator is taken here.
+// One block per SM issues back-to-back tcgen05.mma kind::i8 (M 128, N 256, K 32) from
+// one thread, alternating between two tensor-memory accumulators, on operands that stay
+// in shared memory; nothing is loaded or drained, so this is the pipe alone.
+namespace bivmoe {
+
+constexpr uint32_t PEAK_SMEM = 1024 + 128 * 32 + 256 * 32;   // descriptors' operands: A 4 KiB, B 8 KiB
+
+__global__ void __launch_bounds__(128, 1) int8_peak_kernel(int mmas, int32_t* status) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* done = (uint64_t*)smem;
+    uint32_t* s_tmem = (uint32_t*)(smem + 64);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    for (uint32_t i = tid; i < (PEAK_SMEM - 1024) / 4; i += blockDim.x) ((uint32_t*)(smem + 1024))[i] = 0x01010101u;
+    if (tid == 0) {
+        pf_bar_init(done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the operands, for the tensor core
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         pf_smem(s_tmem)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pf_fence_before();
+    __syncthreads();
+    pf_fence_after();
+    const uint32_t tmem = *s_tmem;
+    if (tid == 0) {
+        const uint32_t a = pf_smem(smem + 1024), b = a + 128 * 32;
+        // K-major, two 16-byte K units: rows 16 bytes apart inside an 8-row group
+        const uint64_t ad = pf_desc(a, 128 * 16, 128), bd = pf_desc(b, 256 * 16, 128);
+        const uint32_t idesc = pf_idesc(128, 256);
+        for (int i = 0; i < mmas; i++) pf_mma_i8(tmem + (i & 1) * 256, ad, bd, idesc);
+        pf_commit(done);
+        if (!pf_bar_wait(done, 0)) atomicExch(status, BIVMOE_ERR_TIMEOUT);
+    }
+    pf_fence_before();
+    __syncthreads();
+    pf_fence_after();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u)
+                     : "memory");
+    }
+}
+
+// tera-operations per second (2 per multiply-add) over all SMs; `status_dev`: a device
+// word that a bounded wait flags
+cudaError_t measure_int8_peak(int sm_count, int32_t* status_dev, cudaStream_t stream, double* tops) {
+    static std::atomic<uint64_t> attr_set{0};
+    if (cudaError_t e = ensure_dynamic_smem(int8_peak_kernel, (int)PEAK_SMEM, attr_set)) return e;
+    const int mmas = 1 << 15;
+    cudaEvent_t e0, e1;
+    cudaError_t err = cudaEventCreate(&e0);
+    if (err != cudaSuccess) return err;
+    err = cudaEventCreate(&e1);
+    if (err != cudaSuccess) { cudaEventDestroy(e0); return err; }
+    int8_peak_kernel<<<sm_count, 128, PEAK_SMEM, stream>>>(1 << 10, status_dev);   // warm-up
+    cudaEventRecord(e0, stream);
+    int8_peak_kernel<<<sm_count, 128, PEAK_SMEM, stream>>>(mmas, status_dev);
+    cudaEventRecord(e1, stream);
+    err = cudaEventSynchronize(e1);
+    float ms = 0.0f;
+    if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (err != cudaSuccess) return err;
+    *tops = 2.0 * 128 * 256 * 32 * (double)mmas * sm_count / (ms * 1e-3) / 1e12;
+    return cudaGetLastError();
+}
+
+}  // namespace bivmoe

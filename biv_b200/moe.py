@@ -159,6 +159,12 @@ class Moe:
         capi.check(capi.lib().bivmoe_set_post_norm(self._h, w.ctypes.data, eps), self._h)
 
     # ---- observability ---------------------------------------------------
+    def int8_peak(self) -> float:
+        """Measured int8 tensor-pipe peak of this GPU, tera-operations per second."""
+        v = C.c_double()
+        capi.check(capi.lib().bivmoe_int8_peak(self._h, C.byref(v)), self._h)
+        return v.value
+
     def numerics(self) -> str:
         buf = C.create_string_buffer(512)
         capi.check(capi.lib().bivmoe_numerics(self._h, buf, 512), self._h)

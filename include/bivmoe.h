@@ -257,6 +257,12 @@ BIVMOE_API int bivmoe_ep_combine(bivmoe_layer* layer, const float* returned_rows
                                  int32_t n, int32_t accumulate, void* stream);
 BIVMOE_API int bivmoe_ep_status(bivmoe_layer* layer, void* stream);
 
+/* The int8 tensor-pipe peak of the layer's GPU in tera-operations per second (two per
+ * multiply-add), measured with back-to-back tcgen05.mma kind::i8 on resident operands
+ * (about 10 ms).  A benchmark hook with no reference counterpart: the roofline
+ * denominator of the Q8_0 tensor-core kernel. */
+BIVMOE_API int bivmoe_int8_peak(bivmoe_layer* layer, double* tops);
+
 /* What decides the numbers besides code and weights, as `Engine::numerics`
  * reports (engine.rs:42-46): device, kernel variants, repack version. */
 BIVMOE_API int bivmoe_numerics(const bivmoe_layer* layer, char* buf, size_t len);

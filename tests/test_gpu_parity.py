@@ -435,3 +435,16 @@ def test_two_host_passes_in_flight_on_two_layer_objects():
     finally:
         a.close()
         b.close()
+
+
+def test_int8_peak_probe_is_plausible():
+    from biv_b200.moe import Moe
+    wl = W.parity_q8_0(n=4, **W.SMALL)
+    m = Moe(wl.layer, 4)
+    try:
+        tops = m.int8_peak()
+        # a B200's dense int8 rate is a few thousand TOP/s; the probe must neither time out
+        # nor report a figure that the MMAs cannot have run at
+        assert 1000.0 < tops < 6000.0, tops
+    finally:
+        m.close()
