@@ -29,6 +29,10 @@ namespace bivmoe {
 //   Q5_K   256       176  the 176-byte super-block {d, dmin, scales[12], qh[32], qs[128]}
 //   Q6_K   256       208  ql[128], qh[64], scales[16]; the f16 d goes to a side plane
 //   BF16   64        128  64 values
+//   F16    64        128  64 values
+//   F32    64        256  64 values
+//   Q4_0   256       144  8 blocks' nibbles (8 x 16 bytes) then their 8 f16 scales (16)
+//   Q4_1   256       160  8 blocks' nibbles, their 8 f16 scales, their 8 f16 minimums
 constexpr int kRepackVersion = 4;
 constexpr int kChunkRows = 128;
 constexpr int kPrefillTile = 128;   // tokens per tile of the tcgen05 kernel for Q8_0
@@ -43,13 +47,19 @@ __host__ __device__ inline SliceGeom slice_geom(int ty) {
         case BIVMOE_Q5_K: return {256, 176};
         case BIVMOE_Q6_K: return {256, 208};
         case BIVMOE_BF16: return {64, 128};
+        case BIVMOE_F16: return {64, 128};
+        case BIVMOE_F32: return {64, 256};
+        case BIVMOE_Q4_0: return {256, 144};
+        case BIVMOE_Q4_1: return {256, 160};
         default: return {0, 0};
     }
 }
 __host__ __device__ inline int64_t gguf_row_bytes(int ty, int64_t cols) {
     switch (ty) {
         case BIVMOE_F32: return cols * 4;
-        case BIVMOE_BF16: return cols * 2;
+        case BIVMOE_BF16: case BIVMOE_F16: return cols * 2;
+        case BIVMOE_Q4_0: return cols / 32 * 18;
+        case BIVMOE_Q4_1: return cols / 32 * 20;
         case BIVMOE_Q8_0: return cols / 32 * 34;
         case BIVMOE_Q4_K: return cols / 256 * 144;
         case BIVMOE_Q5_K: return cols / 256 * 176;
@@ -58,7 +68,7 @@ __host__ __device__ inline int64_t gguf_row_bytes(int ty, int64_t cols) {
     }
 }
 __host__ __device__ inline bool type_uses_f32_act(int ty) {  // quant.rs:75-77
-    return ty == BIVMOE_F32 || ty == BIVMOE_BF16;
+    return ty == BIVMOE_F32 || ty == BIVMOE_F16 || ty == BIVMOE_BF16;
 }
 
 struct DevTiles {          // the tiles of one product (gate+up, or down) of a stack of experts

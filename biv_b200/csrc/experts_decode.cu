@@ -232,6 +232,106 @@ template <> struct Fmt<BIVMOE_Q8_0> {
     }
 };
 
+// ---- Q4_0 / Q4_1 (quant.rs:570-597): per 32-element block
+//      Q4_0: d * d_x * sum((q - 8) * q_x)        Q4_1: d * d_x * sum(q * q_x) + m * s_x
+//      A block's 16 bytes hold element j in the low half of byte j and element j + 16
+//      in the high half: one word per row and block gives both halves of the MMA's K.
+//      The nibbles go to the high half of their byte - Q4_0 with bit 3 flipped, which
+//      makes the byte the int8 value 16 * (q - 8); Q4_1 as unsigned 16 * q - and the
+//      exact factor 1/16 goes into the scale.
+template <int TY> struct FmtQ4 {
+    static constexpr int ELEMS = 256, SL = TY == BIVMOE_Q4_0 ? 144 : 160, MINB = 4;
+    static constexpr bool F32ACT = false;
+    using Side = NoSide;
+    __device__ static void mma_f2(f32x2& lo, f32x2& hi, const int (&a)[4], int b0, int b1) {
+        if (TY == BIVMOE_Q4_1) {
+            mma_u8s8_k32_f2(lo, hi, a, b0, b1);
+        } else {
+            int d[4];
+            asm volatile(
+                "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                "{%10,%10,%10,%10};"
+                : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0x4B400000));
+            const f32x2 neg = pk(-12582912.0f, -12582912.0f);
+            lo = add2(pk(__int_as_float(d[0]), __int_as_float(d[1])), neg);
+            hi = add2(pk(__int_as_float(d[2]), __int_as_float(d[3])), neg);
+        }
+    }
+    __device__ static float half_at(const uint4& v, int b) {
+        const uint32_t w = (&v.x)[b >> 1];
+        return __half2float(__ushort_as_half((unsigned short)(w >> (16 * (b & 1)))));
+    }
+    // half i (0..3, not known at compile time) of the four in the words w0, w1
+    __device__ static float half_sel(uint32_t w0, uint32_t w1, int i) {
+        const uint32_t w = (i & 2) ? w1 : w0;
+        return __half2float(__ushort_as_half((unsigned short)((i & 1) ? w >> 16 : w)));
+    }
+    __device__ static void compute(const uint32_t (&rowp)[2][2], Side, uint32_t act,
+                                   float (&acc)[2][4], int g, int c) {
+        const uint32_t dxp = act + kActOffDx, shi = act + kActOffSHi, slo = act + kActOffSLo;
+        uint4 dwv[2][2], mv[2][2];   // the 8 f16 scales (unit 8) and minimums (unit 9) of each row's slice
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                dwv[mt][r] = lds128(WU(rowp[mt][r], 128));
+                if (TY == BIVMOE_Q4_1) mv[mt][r] = lds128(WU(rowp[mt][r], 144));
+            }
+        // Q4_1's term sum_b m[r][b] * s[t][b] is a 16x8x8 product: tf32 on the tensor core,
+        // exact products because m is an f16 and s comes split in two tf32-exact parts.
+        float tM[2][4] = {};
+        if (TY == BIVMOE_Q4_1) {
+            const float bh0 = ldsf(shi + 4 * (c * 8 + g)), bh1 = ldsf(shi + 4 * ((c + 4) * 8 + g));
+            const float bl0 = ldsf(slo + 4 * (c * 8 + g)), bl1 = ldsf(slo + 4 * ((c + 4) * 8 + g));
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                float a[4];
+                a[0] = half_sel(mv[mt][0].x, mv[mt][0].y, c);
+                a[1] = half_sel(mv[mt][1].x, mv[mt][1].y, c);
+                a[2] = half_sel(mv[mt][0].z, mv[mt][0].w, c);
+                a[3] = half_sel(mv[mt][1].z, mv[mt][1].w, c);
+                mma_tf32_k8(tM[mt], a, bh0, bh1);
+                mma_tf32_k8(tM[mt], a, bl0, bl1);
+            }
+        }
+        f32x2 tS[2][2] = {};   // [mt][r]: tokens 2c, 2c+1 of row g + 8r
+        const uint32_t xlane = act + g * 16 + 4 * c;
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+            const int b0 = XQ(xlane, 2 * b), b1 = XQ(xlane, 2 * b + 1);
+            const f32x2 dxv = lds64(dxp + 4 * (b * 8 + 2 * c));   // d of tokens 2c, 2c+1
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                const uint32_t w0 = LDS32(WU(rowp[mt][0], 16 * b) + 4 * c);
+                const uint32_t w1 = LDS32(WU(rowp[mt][1], 16 * b) + 4 * c);
+                const uint32_t flip = TY == BIVMOE_Q4_0 ? 0x80808080u : 0u;
+                int a[4];
+                a[0] = (int)(((w0 << 4) & 0xF0F0F0F0u) ^ flip);
+                a[1] = (int)(((w1 << 4) & 0xF0F0F0F0u) ^ flip);
+                a[2] = (int)((w0 & 0xF0F0F0F0u) ^ flip);
+                a[3] = (int)((w1 & 0xF0F0F0F0u) ^ flip);
+                f32x2 I[2];   // 16 x the int32 block dots, exactly, as floats
+                mma_f2(I[0], I[1], a, b0, b1);
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    const float dw = half_at(dwv[mt][r], b) * 0.0625f;
+                    tS[mt][r] = fma2(pk(dw, dw), mul2(dxv, I[r]), tS[mt][r]);
+                }
+            }
+        }
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float ts = (i & 1) ? hi_of(tS[mt][i >> 1]) : lo_of(tS[mt][i >> 1]);
+                acc[mt][i] += ts + tM[mt][i];
+            }
+    }
+};
+template <> struct Fmt<BIVMOE_Q4_0> : FmtQ4<BIVMOE_Q4_0> {};
+template <> struct Fmt<BIVMOE_Q4_1> : FmtQ4<BIVMOE_Q4_1> {};
+
 // ---- Q4_K / Q5_K (quant.rs:609-649): per sub-block
 //      d*sc*d_x*sum(q*q_x) - dmin*m*s_x ; Q5_K adds bit sb of qh[l] as value bit 4.
 //      A stage is one super-block, so d and dmin are applied once per stage.
@@ -415,40 +515,62 @@ template <> struct Fmt<BIVMOE_Q6_K> {
     }
 };
 
-// ---- BF16 weights meet f32 activations (quant.rs:509-521, 1229-1256): f32
-//      multiply-adds, a lane per weight row, activations read as broadcasts ----
-template <> struct Fmt<BIVMOE_BF16> {
-    static constexpr int ELEMS = 64, SL = 128, MINB = 4;
+// ---- BF16, F16 and F32 weights meet f32 activations (quant.rs:483-521, 1229-1281):
+//      f32 multiply-adds, a lane per weight row, activations read as broadcasts ----
+template <int TY> struct FmtFloat {
+    static constexpr int ELEMS = 64, SL = TY == BIVMOE_F32 ? 256 : 128, MINB = TY == BIVMOE_F32 ? 3 : 4;
     static constexpr bool F32ACT = true;
+    static constexpr int PER_UNIT = TY == BIVMOE_F32 ? 4 : 8;   // values in a 16-byte unit
     using Side = NoSide;
     __device__ static void widen(const uint4& v, float (&w)[8]) {
-        w[0] = __uint_as_float(v.x << 16); w[1] = __uint_as_float(v.x & 0xFFFF0000u);
-        w[2] = __uint_as_float(v.y << 16); w[3] = __uint_as_float(v.y & 0xFFFF0000u);
-        w[4] = __uint_as_float(v.z << 16); w[5] = __uint_as_float(v.z & 0xFFFF0000u);
-        w[6] = __uint_as_float(v.w << 16); w[7] = __uint_as_float(v.w & 0xFFFF0000u);
+        if (TY == BIVMOE_BF16) {
+            w[0] = __uint_as_float(v.x << 16); w[1] = __uint_as_float(v.x & 0xFFFF0000u);
+            w[2] = __uint_as_float(v.y << 16); w[3] = __uint_as_float(v.y & 0xFFFF0000u);
+            w[4] = __uint_as_float(v.z << 16); w[5] = __uint_as_float(v.z & 0xFFFF0000u);
+            w[6] = __uint_as_float(v.w << 16); w[7] = __uint_as_float(v.w & 0xFFFF0000u);
+        } else if (TY == BIVMOE_F16) {
+            const uint32_t p[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 f = __half22float2(*(const __half2*)&p[i]);
+                w[2 * i] = f.x;
+                w[2 * i + 1] = f.y;
+            }
+        } else {
+            w[0] = __uint_as_float(v.x); w[1] = __uint_as_float(v.y);
+            w[2] = __uint_as_float(v.z); w[3] = __uint_as_float(v.w);
+            w[4] = w[5] = w[6] = w[7] = 0.0f;
+        }
     }
     // `wrow`: this lane's row (tile + row*16); acc[t] += dot(row slice, token t)
     __device__ static void compute_f32(const uint8_t* wrow, const float* xf, int cnt,
                                        float (&acc)[EX_TT]) {
 #pragma unroll 2
-        for (int u = 0; u < 8; u++) {
+        for (int u = 0; u < SL / 16; u++) {
             float w[8];
             widen(*(const uint4*)(wrow + 2048 * u), w);
 #pragma unroll
             for (int t = 0; t < EX_TT; t++) {
                 if (t < cnt) {
-                    const float4* xp = (const float4*)(xf + t * ELEMS + 8 * u);
-                    const float4 x0 = xp[0], x1 = xp[1];
+                    const float4* xp = (const float4*)(xf + t * ELEMS + PER_UNIT * u);
+                    const float4 x0 = xp[0];
                     float s = acc[t];
                     s = fmaf(w[0], x0.x, s); s = fmaf(w[1], x0.y, s); s = fmaf(w[2], x0.z, s);
-                    s = fmaf(w[3], x0.w, s); s = fmaf(w[4], x1.x, s); s = fmaf(w[5], x1.y, s);
-                    s = fmaf(w[6], x1.z, s); s = fmaf(w[7], x1.w, s);
+                    s = fmaf(w[3], x0.w, s);
+                    if (PER_UNIT == 8) {
+                        const float4 x1 = xp[1];
+                        s = fmaf(w[4], x1.x, s); s = fmaf(w[5], x1.y, s);
+                        s = fmaf(w[6], x1.z, s); s = fmaf(w[7], x1.w, s);
+                    }
                     acc[t] = s;
                 }
             }
         }
     }
 };
+template <> struct Fmt<BIVMOE_BF16> : FmtFloat<BIVMOE_BF16> {};
+template <> struct Fmt<BIVMOE_F16> : FmtFloat<BIVMOE_F16> {};
+template <> struct Fmt<BIVMOE_F32> : FmtFloat<BIVMOE_F32> {};
 
 // ---------------------------------------------------------------------------
 template <int TY>
@@ -749,8 +871,10 @@ experts_kernel(const ExpertArgs A) {
 // host side
 
 bool experts_supported(int ty, int cols, int rows, bool is_down) {
+    // every type the reference has a dot kernel for (quant.rs:80-93)
     if (ty != BIVMOE_Q8_0 && ty != BIVMOE_Q4_K && ty != BIVMOE_Q5_K && ty != BIVMOE_Q6_K &&
-        ty != BIVMOE_BF16)
+        ty != BIVMOE_BF16 && ty != BIVMOE_F16 && ty != BIVMOE_F32 && ty != BIVMOE_Q4_0 &&
+        ty != BIVMOE_Q4_1)
         return false;
     return cols > 0 && cols % 256 == 0 && rows > 0 && rows % (is_down ? 128 : 64) == 0;
 }
@@ -775,6 +899,10 @@ static cudaError_t launch_typed(int ty, const LaunchCfg& c, const ExpertArgs& A)
         case BIVMOE_Q5_K: return launch_one<BIVMOE_Q5_K, MODE>(c, A);
         case BIVMOE_Q6_K: return launch_one<BIVMOE_Q6_K, MODE>(c, A);
         case BIVMOE_BF16: return launch_one<BIVMOE_BF16, MODE>(c, A);
+        case BIVMOE_F16: return launch_one<BIVMOE_F16, MODE>(c, A);
+        case BIVMOE_F32: return launch_one<BIVMOE_F32, MODE>(c, A);
+        case BIVMOE_Q4_0: return launch_one<BIVMOE_Q4_0, MODE>(c, A);
+        case BIVMOE_Q4_1: return launch_one<BIVMOE_Q4_1, MODE>(c, A);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -351,7 +351,15 @@ __global__ void repack_kernel(DevTiles dt, const uint8_t* __restrict__ src, int 
         switch (dt.ty) {
             case BIVMOE_Q4_K: from = row + 144 * (int64_t)s + 16 * u; break;
             case BIVMOE_Q5_K: from = row + 176 * (int64_t)s + 16 * u; break;
-            case BIVMOE_BF16: from = row + 128 * (int64_t)s + 16 * u; break;
+            case BIVMOE_BF16:
+            case BIVMOE_F16: from = row + 128 * (int64_t)s + 16 * u; break;
+            case BIVMOE_F32: from = row + 256 * (int64_t)s + 16 * u; break;
+            case BIVMOE_Q4_0:
+                if (u < 8) from = row + 18 * (int64_t)(8 * s + u) + 2;
+                break;
+            case BIVMOE_Q4_1:
+                if (u < 8) from = row + 20 * (int64_t)(8 * s + u) + 4;
+                break;
             case BIVMOE_Q6_K: from = row + 210 * (int64_t)s + 16 * u; break;   // ql, qh, scales in order
             case BIVMOE_Q8_0:
                 if (u < 16) from = row + 34 * (int64_t)(8 * s + u / 2) + 2 + 16 * (u % 2);
@@ -359,10 +367,12 @@ __global__ void repack_kernel(DevTiles dt, const uint8_t* __restrict__ src, int 
         }
         if (from) {
             for (int j = 0; j < 16; j++) dst[j] = from[j];
-        } else {   // Q8_0 unit 16: the eight f16 scales of the slice
+        } else {   // the eight f16 scales of the slice (Q4_1 unit 9: its eight f16 minimums)
+            const int bb = dt.ty == BIVMOE_Q8_0 ? 34 : dt.ty == BIVMOE_Q4_0 ? 18 : 20;
+            const int at = dt.ty == BIVMOE_Q4_1 && u == 9 ? 2 : 0;
             for (int b = 0; b < 8; b++) {
-                dst[2 * b] = row[34 * (int64_t)(8 * s + b)];
-                dst[2 * b + 1] = row[34 * (int64_t)(8 * s + b) + 1];
+                dst[2 * b] = row[bb * (int64_t)(8 * s + b) + at];
+                dst[2 * b + 1] = row[bb * (int64_t)(8 * s + b) + at + 1];
             }
         }
         if (dt.ty == BIVMOE_Q6_K && u == 0) {
@@ -403,6 +413,12 @@ __global__ void block_dots_kernel(DevTiles t, int tile_base, int expert, int row
     int32_t sum = 0;
     if (t.ty == BIVMOE_Q8_0) {
         for (int l = 0; l < 32; l++) sum += (int)(int8_t)tile_byte(t, t0, rr, s, 32 * sb + l) * x[l];
+    } else if (t.ty == BIVMOE_Q4_0 || t.ty == BIVMOE_Q4_1) {
+        // quant.rs:574-577, 589-592: byte j = element j (low half) and j + 16 (high half)
+        for (int l = 0; l < 32; l++) {
+            const int q = (tile_byte(t, t0, rr, s, 16 * sb + (l & 15)) >> (4 * (l >> 4))) & 0xF;
+            sum += (t.ty == BIVMOE_Q4_0 ? q - 8 : q) * x[l];
+        }
     } else if (t.ty == BIVMOE_Q4_K || t.ty == BIVMOE_Q5_K) {
         const int qoff = (t.ty == BIVMOE_Q4_K ? 16 : 48) + 32 * (sb / 2);
         for (int l = 0; l < 32; l++) {

@@ -25,11 +25,11 @@ from typing import Optional
 import numpy as np
 
 # ggml type ids (engine/src/quant.rs:30-48)
-F32, F16, Q8_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 8, 12, 13, 14, 30
-TYPE_NAMES = {F32: "F32", F16: "F16", Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K",
-              BF16: "BF16"}
-_BLOCK = {F32: (1, 4), F16: (1, 2), BF16: (1, 2), Q8_0: (32, 34), Q4_K: (256, 144),
-          Q5_K: (256, 176), Q6_K: (256, 210)}
+F32, F16, Q4_0, Q4_1, Q8_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 2, 3, 8, 12, 13, 14, 30
+TYPE_NAMES = {F32: "F32", F16: "F16", Q4_0: "Q4_0", Q4_1: "Q4_1", Q8_0: "Q8_0", Q4_K: "Q4_K",
+              Q5_K: "Q5_K", Q6_K: "Q6_K", BF16: "BF16"}
+_BLOCK = {F32: (1, 4), F16: (1, 2), BF16: (1, 2), Q4_0: (32, 18), Q4_1: (32, 20), Q8_0: (32, 34),
+          Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}
 
 
 def row_size(ty: int, n: int) -> int:
@@ -153,6 +153,36 @@ def quantize_q8_0(x: np.ndarray) -> np.ndarray:
     return out.reshape(lead + (cols // 32 * 34,))
 
 
+def quantize_q4(w: np.ndarray, with_min: bool) -> np.ndarray:
+    """Rows of f32 as Q4_0 (``with_min`` false: ``d = amax/7``, nibble = ``round(x/d) + 8``)
+    or Q4_1 (``d = (max - min)/15``, ``m = min``, nibble = ``round((x - m)/d)``) blocks; byte
+    j of a block holds element j in its low half and element j + 16 in its high half
+    (engine/src/quant.rs:174-192).  The reference only reads these formats: the
+    quantiser is this module's own."""
+    w = np.asarray(w, dtype=np.float32)
+    lead, cols = w.shape[:-1], w.shape[-1]
+    xb = w.reshape(-1, cols // 32, 32)
+    if with_min:
+        lo, hi = xb.min(axis=-1, keepdims=True), xb.max(axis=-1, keepdims=True)
+        d32 = (hi - lo) / np.float32(15.0)
+        off = lo
+    else:
+        d32 = np.abs(xb).max(axis=-1, keepdims=True) / np.float32(7.0)
+        off = np.float32(-8.0) * d32
+    with np.errstate(divide="ignore", invalid="ignore"):
+        q = np.where(d32 > 0, np.rint((xb - off) / d32), 0.0)
+    q = np.clip(q, 0, 15).astype(np.uint8)
+    head = 4 if with_min else 2
+    out = np.empty(xb.shape[:2] + (head + 16,), dtype=np.uint8)
+    out[..., 0:2] = f32_to_f16_bits(d32[..., 0])[..., None].view(np.uint8).reshape(
+        xb.shape[0], xb.shape[1], 2)
+    if with_min:
+        out[..., 2:4] = f32_to_f16_bits(off[..., 0])[..., None].view(np.uint8).reshape(
+            xb.shape[0], xb.shape[1], 2)
+    out[..., head:] = q[..., :16] | (q[..., 16:] << 4)
+    return out.reshape(lead + (cols // 32 * (head + 16),))
+
+
 def _random_bytes(rng: np.random.Generator, n: int) -> np.ndarray:
     return np.frombuffer(rng.bytes(n), dtype=np.uint8).copy()
 
@@ -181,8 +211,8 @@ def _stack(ty, cols, rows, n, data) -> ExpertStack:
 
 
 def make_weights(rng, ty: int, n: int, rows: int, cols: int, sigma: float = 0.02) -> ExpertStack:
-    """``n`` matrices [rows, cols] of type ``ty``: N(0, sigma) values for Q8_0,
-    BF16 and F32; random blocks for the k-quants."""
+    """``n`` matrices [rows, cols] of type ``ty``: N(0, sigma) values for Q8_0, Q4_0,
+    Q4_1, BF16, F16 and F32; random blocks for the k-quants."""
     if ty in (Q4_K, Q5_K, Q6_K):
         return _stack(ty, cols, rows, n, random_kquant(rng, ty, n * rows, cols))
     rb = row_size(ty, cols)
@@ -191,8 +221,12 @@ def make_weights(rng, ty: int, n: int, rows: int, cols: int, sigma: float = 0.02
         w = rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(sigma)
         if ty == Q8_0:
             out[e] = quantize_q8_0(w).reshape(-1)
+        elif ty in (Q4_0, Q4_1):
+            out[e] = quantize_q4(w, ty == Q4_1).reshape(-1)
         elif ty == BF16:
             out[e] = f32_to_bf16_bits(w).view(np.uint8).reshape(-1)
+        elif ty == F16:
+            out[e] = w.astype(np.float16).view(np.uint8).reshape(-1)
         elif ty == F32:
             out[e] = w.view(np.uint8).reshape(-1)
         else:
@@ -289,6 +323,16 @@ def ep_bf16(n=16384, seed=4, **shape) -> Workload:
     layer = make_layer(rng, gate_ty=BF16, router_dist="uniform", **shape)
     h = rng.standard_normal((n, layer.n_embd), dtype=np.float32)
     return Workload("ep_bf16", seed, [layer], h)
+
+
+def typed_layer(gate_ty, down_ty=None, n=16, seed=5, **shape) -> Workload:
+    """One layer of any weight types the reference has dot kernels for
+    (engine/src/quant.rs:80-93), N(0, 1) rows normalised like configuration 1."""
+    rng = np.random.default_rng(seed)
+    layer = make_layer(rng, gate_ty=gate_ty, down_ty=down_ty, **shape)
+    h = rms_normalise(rng.standard_normal((n, layer.n_embd), dtype=np.float32))
+    name = f"typed_{TYPE_NAMES[gate_ty]}_{TYPE_NAMES[layer.down.ty]}"
+    return Workload(name, seed, [layer], h)
 
 
 CONFIGS = {"parity_q8_0": parity_q8_0, "decode_q4k": decode_q4k, "prefill_q8_0": prefill_q8_0,

@@ -49,6 +49,9 @@ enum {
 /* ggml type ids as stored in GGUF files (engine/src/quant.rs:30-48). */
 enum {
     BIVMOE_F32 = 0,
+    BIVMOE_F16 = 1,
+    BIVMOE_Q4_0 = 2,
+    BIVMOE_Q4_1 = 3,
     BIVMOE_Q8_0 = 8,
     BIVMOE_Q4_K = 12,
     BIVMOE_Q5_K = 13,

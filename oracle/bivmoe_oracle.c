@@ -39,7 +39,7 @@
 #define ORC_API __attribute__((visibility("default")))
 
 /* ggml type ids, quant.rs:30-48 */
-enum { T_F32 = 0, T_F16 = 1, T_Q8_0 = 8, T_Q4K = 12, T_Q5K = 13, T_Q6K = 14, T_BF16 = 30 };
+enum { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q8_0 = 8, T_Q4K = 12, T_Q5K = 13, T_Q6K = 14, T_BF16 = 30 };
 
 /* ------------------------------------------------------------------------ */
 /* scalars                                                                   */
@@ -72,6 +72,8 @@ ORC_API long orc_row_size(int ty, long n) {
     switch (ty) {
         case T_F32: return n * 4;
         case T_F16: case T_BF16: return n * 2;
+        case T_Q4_0: return n % 32 ? -1 : n / 32 * 18;
+        case T_Q4_1: return n % 32 ? -1 : n / 32 * 20;
         case T_Q8_0: return n % 32 ? -1 : n / 32 * 34;
         case T_Q4K: return n % 256 ? -1 : n / 256 * 144;
         case T_Q5K: return n % 256 ? -1 : n / 256 * 176;
@@ -105,6 +107,26 @@ ORC_API int orc_dequantize_row(int ty, const uint8_t* src, float* dst, long n) {
             return 0;
         case T_BF16:
             for (long i = 0; i < n; i++) dst[i] = orc_bf16_to_f32(rd16(src, 2 * i));
+            return 0;
+        case T_Q4_0: /* quant.rs:174-182 */
+            for (long b = 0; b < n / 32; b++) {
+                const uint8_t* blk = src + 18 * b;
+                float d = orc_f16_to_f32(rd16(blk, 0));
+                for (int j = 0; j < 16; j++) {
+                    dst[32 * b + j] = (float)((int)(blk[2 + j] & 0xF) - 8) * d;
+                    dst[32 * b + j + 16] = (float)((int)(blk[2 + j] >> 4) - 8) * d;
+                }
+            }
+            return 0;
+        case T_Q4_1: /* quant.rs:183-192 */
+            for (long b = 0; b < n / 32; b++) {
+                const uint8_t* blk = src + 20 * b;
+                float d = orc_f16_to_f32(rd16(blk, 0)), m = orc_f16_to_f32(rd16(blk, 2));
+                for (int j = 0; j < 16; j++) {
+                    dst[32 * b + j] = (float)(blk[4 + j] & 0xF) * d + m;
+                    dst[32 * b + j + 16] = (float)(blk[4 + j] >> 4) * d + m;
+                }
+            }
             return 0;
         case T_Q8_0:
             for (long b = 0; b < n / 32; b++) {
@@ -212,6 +234,16 @@ ORC_API void orc_q8_quantize(const float* x, long n, int8_t* qs, float* d, float
  * scalar dots and the int32 block-dot tap.  For k-quants `sb` is the
  * sub-block (0..8) of super-block `i`.                                      */
 
+/* quant.rs:574-577 (Q4_0: nibble - 8) and 589-592 (Q4_1: the nibble): byte j holds
+ * element j in its low half and element j + 16 in its high half */
+static void unpack_q4_01(int ty, const uint8_t* blk, int32_t* q) {
+    const uint8_t* qs = blk + (ty == T_Q4_0 ? 2 : 4);
+    const int off = ty == T_Q4_0 ? 8 : 0;
+    for (int j = 0; j < 16; j++) {
+        q[j] = (int32_t)(qs[j] & 0xF) - off;
+        q[j + 16] = (int32_t)(qs[j] >> 4) - off;
+    }
+}
 static void unpack_q4k(const uint8_t* blk, int sb, int32_t* q) { /* quant.rs:616-620 */
     const uint8_t* q4 = blk + 16 + 32 * (sb / 2);
     for (int l = 0; l < 32; l++) q[l] = (q4[l] >> (4 * (sb % 2))) & 0xF;
@@ -248,6 +280,13 @@ static int32_t idot(const int32_t* a, const int8_t* b, int n) { /* quant.rs:566-
 ORC_API int orc_block_dots(int ty, const uint8_t* w, const int8_t* xq, long n, int32_t* out) {
     int32_t q[256], sc16[16];
     switch (ty) {
+        case T_Q4_0:
+        case T_Q4_1:
+            for (long i = 0; i < n / 32; i++) {
+                unpack_q4_01(ty, w + (ty == T_Q4_0 ? 18 : 20) * i, q);
+                out[i] = idot(q, xq + 32 * i, 32);
+            }
+            return 0;
         case T_Q8_0:
             for (long i = 0; i < n / 32; i++) {
                 const uint8_t* b = w + 34 * i;
@@ -303,6 +342,29 @@ static float dot_f16_seq(const uint8_t* w, const float* x, long n) { /* quant.rs
     return s;
 }
 
+static float sc_dot_q4_0(const uint8_t* w, const int8_t* qs, const float* xd, long nb) {
+    float sum = 0.0f; /* quant.rs:570-582 */
+    int32_t q[32];
+    for (long i = 0; i < nb; i++) {
+        const uint8_t* b = w + 18 * i;
+        float d = orc_f16_to_f32(rd16(b, 0));
+        unpack_q4_01(T_Q4_0, b, q);
+        sum += d * xd[i] * (float)idot(q, qs + 32 * i, 32);
+    }
+    return sum;
+}
+static float sc_dot_q4_1(const uint8_t* w, const int8_t* qs, const float* xd, const float* xs,
+                         long nb) {
+    float sum = 0.0f; /* quant.rs:584-597 */
+    int32_t q[32];
+    for (long i = 0; i < nb; i++) {
+        const uint8_t* b = w + 20 * i;
+        float d = orc_f16_to_f32(rd16(b, 0)), m = orc_f16_to_f32(rd16(b, 2));
+        unpack_q4_01(T_Q4_1, b, q);
+        sum += d * xd[i] * (float)idot(q, qs + 32 * i, 32) + m * xs[i];
+    }
+    return sum;
+}
 static float sc_dot_q8_0(const uint8_t* w, const int8_t* qs, const float* xd, long nb) {
     float sum = 0.0f; /* quant.rs:599-607 */
     int32_t q[32];
@@ -389,6 +451,12 @@ AVX2 static inline __m256 fma_i32(__m256 acc, __m256i p, float d) { /* quant.rs:
     return _mm256_fmadd_ps(_mm256_cvtepi32_ps(p), _mm256_set1_ps(d), acc);
 }
 AVX2 static inline __m256i ld256(const void* p) { return _mm256_loadu_si256((const __m256i*)p); }
+/* quant.rs:1165-1175: 16 bytes of nibbles as 32 bytes, the low halves in the low lane */
+AVX2 static inline __m256i q4_nibbles(const uint8_t* p) {
+    __m128i v = _mm_loadu_si128((const __m128i*)p);
+    __m128i m4 = _mm_set1_epi8(0x0F);
+    return _mm256_set_m128i(_mm_and_si128(_mm_srli_epi16(v, 4), m4), _mm_and_si128(v, m4));
+}
 
 /* quant.rs:1177-1206 */
 AVX2 static float dot_f32_avx2(const float* a, const float* b, long n) {
@@ -456,6 +524,32 @@ AVX2 static float dot_f16_avx2(const uint8_t* w, const float* x, long n) {
     ATTR static inline __m256i dot_u8_i8_##SUF(__m256i u, __m256i s) { return DOT_U8_I8; }      \
     ATTR static inline __m256i dot_i8_i8_##SUF(__m256i a, __m256i s) {                          \
         return dot_u8_i8_##SUF(_mm256_sign_epi8(a, a), _mm256_sign_epi8(s, a));                 \
+    }                                                                                           \
+    /* quant.rs:1302-1321: nibbles of 16 bytes as 32 bytes (low halves first), minus 8 */       \
+    ATTR static float dot_q4_0_##SUF(const uint8_t* w, const int8_t* xq, const float* xd,       \
+                                     long nb) {                                                 \
+        const __m256i s8 = _mm256_set1_epi8(8);                                                 \
+        __m256 acc[2] = {_mm256_setzero_ps(), _mm256_setzero_ps()};                             \
+        for (long i = 0; i < nb; i++) {                                                         \
+            const uint8_t* b = w + 18 * i;                                                      \
+            __m256i q = _mm256_sub_epi8(q4_nibbles(b + 2), s8);                                 \
+            acc[i & 1] = fma_i32(acc[i & 1], dot_i8_i8_##SUF(q, ld256(xq + 32 * i)),            \
+                                 f16_hw(b) * xd[i]);                                            \
+        }                                                                                       \
+        return hsum8(_mm256_add_ps(acc[0], acc[1]));                                            \
+    }                                                                                           \
+    /* quant.rs:1323-1339: the min terms are summed apart, in block order */                    \
+    ATTR static float dot_q4_1_##SUF(const uint8_t* w, const int8_t* xq, const float* xd,       \
+                                     const float* xs, long nb) {                                \
+        __m256 acc[2] = {_mm256_setzero_ps(), _mm256_setzero_ps()};                             \
+        float summs = 0.0f;                                                                     \
+        for (long i = 0; i < nb; i++) {                                                         \
+            const uint8_t* b = w + 20 * i;                                                      \
+            __m256i p = dot_u8_i8_##SUF(q4_nibbles(b + 4), ld256(xq + 32 * i));                 \
+            acc[i & 1] = fma_i32(acc[i & 1], p, f16_hw(b) * xd[i]);                             \
+            summs += f16_hw(b + 2) * xs[i];                                                     \
+        }                                                                                       \
+        return hsum8(_mm256_add_ps(acc[0], acc[1])) + summs;                                    \
     }                                                                                           \
     /* quant.rs:1369-1382 */                                                                    \
     ATTR static float dot_q8_0_##SUF(const uint8_t* w, const int8_t* xq, const float* xd,       \
@@ -580,6 +674,11 @@ static float dot_level(int level, int ty, const uint8_t* w, act_row x, long n) {
             case T_F32: return dot_f32_avx2((const float*)w, x.xf, n);
             case T_F16: return dot_f16_avx2(w, x.xf, n);
             case T_BF16: return dot_bf16_avx2(w, x.xf, n);
+            case T_Q4_0:
+                return level == 2 ? dot_q4_0_vnni(w, x.qs, x.d, nb) : dot_q4_0_avx2(w, x.qs, x.d, nb);
+            case T_Q4_1:
+                return level == 2 ? dot_q4_1_vnni(w, x.qs, x.d, x.s, nb)
+                                  : dot_q4_1_avx2(w, x.qs, x.d, x.s, nb);
             case T_Q8_0:
                 return level == 2 ? dot_q8_0_vnni(w, x.qs, x.d, nb) : dot_q8_0_avx2(w, x.qs, x.d, nb);
             case T_Q4K: case T_Q5K:
@@ -593,6 +692,8 @@ static float dot_level(int level, int ty, const uint8_t* w, act_row x, long n) {
         case T_F32: return dot_f32_seq((const float*)w, x.xf, n);
         case T_F16: return dot_f16_seq(w, x.xf, n);
         case T_BF16: return dot_bf16_seq(w, x.xf, n);
+        case T_Q4_0: return sc_dot_q4_0(w, x.qs, x.d, nb);
+        case T_Q4_1: return sc_dot_q4_1(w, x.qs, x.d, x.s, nb);
         case T_Q8_0: return sc_dot_q8_0(w, x.qs, x.d, nb);
         case T_Q4K: case T_Q5K: return sc_dot_q45k(ty, w, x.qs, x.d, x.s, nb);
         case T_Q6K: return sc_dot_q6k(w, x.qs, x.d, nb);

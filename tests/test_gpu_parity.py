@@ -10,7 +10,7 @@ import pytest
 
 import oracle
 from biv_b200 import capi, workloads as W
-from helpers import loose_err, rel_err, routing_mismatches
+from helpers import FLOAT_TYPES, loose_err, rel_err, routing_mismatches
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-3        # the gate
@@ -52,7 +52,7 @@ def run_case(wl, max_tokens=None, check_dots=True):
             seg = order[bounds[e]:bounds[e + 1]]
             assert (flat[seg] == e).all() and (np.diff(seg) > 0).all()
         # --- quantiser: bit-exact
-        quant = layer.gate.ty not in (W.F32, W.BF16)
+        quant = layer.gate.ty not in FLOAT_TYPES
         if quant:
             assert np.array_equal(m.tap(capi.TAP_ACT_Q), tap["act_q"])
             assert np.array_equal(m.tap(capi.TAP_ACT_D), tap["act_d"])
@@ -68,7 +68,7 @@ def run_case(wl, max_tokens=None, check_dots=True):
                     row = st.expert(e)[r * rb:(r + 1) * rb]
                     want = oracle.block_dots(st.ty, row, tap["act_q"][t])
                     assert np.array_equal(m.tap_block_dots(mat, e, r, t), want)
-            if layer.down.ty not in (W.F32, W.BF16):
+            if layer.down.ty not in FLOAT_TYPES:
                 rbd = W.row_size(layer.down.ty, layer.n_ff_exp)
                 mid = m.tap(capi.TAP_MID)
                 for _ in range(6):
@@ -149,6 +149,18 @@ def test_small_mixed_kquants(n):
     run_case(wl)
 
 
+# the other weight types the reference has dot kernels for (engine/src/quant.rs:80-93)
+@pytest.mark.parametrize("gate_ty,down_ty,n", [
+    (W.Q4_0, W.Q4_0, 5), (W.Q4_0, W.Q4_1, 37), (W.Q4_1, W.Q4_1, 12), (W.Q4_1, W.Q8_0, 70),
+    (W.F16, W.F16, 9), (W.F16, W.BF16, 33), (W.F32, W.F32, 7), (W.Q8_0, W.F16, 19)])
+def test_other_weight_types(gate_ty, down_ty, n):
+    run_case(W.typed_layer(gate_ty, down_ty, n=n, **W.SMALL))
+
+
+def test_q4_0_and_q4_1_at_the_model_shape():
+    run_case(W.typed_layer(W.Q4_0, W.Q4_1, n=64, n_expert=32))
+
+
 def test_one_token_and_ragged_tiles():
     # 1 token; a token count that leaves a ragged last activation tile; k = 1
     run_case(W.parity_q8_0(n=1, **W.SMALL))
@@ -191,7 +203,7 @@ def test_errors_are_statuses_not_crashes():
     from biv_b200.moe import Moe
     wl = W.parity_q8_0(n=4, **W.SMALL)
     bad = W.parity_q8_0(n=4, **W.SMALL).layer
-    bad.gate.ty = 2     # Q4_0: no kernel on this path
+    bad.gate.ty = 6     # Q5_0: the reference can only dequantise it (quant.rs:80-93)
     with pytest.raises(capi.BivMoeError) as ei:
         Moe(bad, 4)
     assert ei.value.code in (capi.ERR_UNSUPPORTED, capi.ERR_ARGUMENT)

@@ -28,22 +28,17 @@ def rand_bytes(n, seed):
     return np.frombuffer(bytes(out), dtype=np.uint8).copy(), seed
 
 
-# bytes of the Q4_0 and Q4_1 rows the reference tests draw before the types on
-# this path (18 and 20 bytes per 32 elements)
-def _skip_q4(n, seed):
-    _, seed = rand_bytes(n // 32 * 18, seed)
-    _, seed = rand_bytes(n // 32 * 20, seed)
-    return seed
-
-
 def rand_row(ty, n, seed):
     """engine/src/quant.rs:1628-1649: random blocks with f16 scales 0x2E66 (~0.1)."""
     be, bb = W._BLOCK[ty]
     b, seed = rand_bytes(W.row_size(ty, n), seed)
     blk = b.reshape(-1, bb)
     half = np.array([0x66, 0x2E], dtype=np.uint8)
-    if ty == W.Q8_0:
+    if ty in (W.Q8_0, W.Q4_0):
         blk[:, 0:2] = half
+    elif ty == W.Q4_1:
+        blk[:, 0:2] = half
+        blk[:, 2:4] = np.array([0x66, 0xAE], dtype=np.uint8)   # ~-0.1
     elif ty in (W.Q4_K, W.Q5_K):
         blk[:, 0:2] = half
         blk[:, 2:4] = half
@@ -65,8 +60,8 @@ def test_kernels_match_dequantized_dot():
     x = probe_x(n)
     qs, d, s = oracle.q8_quantize(x)
     xd = (qs.astype(np.float32) * np.repeat(d, 32)).astype(np.float32)
-    seed = _skip_q4(n, 0x123456789ABCDEF1)
-    for ty in (W.Q8_0, W.Q4_K, W.Q5_K, W.Q6_K):
+    seed = 0x123456789ABCDEF1
+    for ty in (W.Q4_0, W.Q4_1, W.Q8_0, W.Q4_K, W.Q5_K, W.Q6_K):
         w, seed = rand_row(ty, n, seed)
         wd = oracle.dequantize_row(ty, w, n)
         ref = np.float32(0)
@@ -94,8 +89,8 @@ def test_vnni_matches_avx2():
         idx = np.arange(n) % 5 == t
         v = np.where(idx, np.float32(1e3) * np.sign(x), v).astype(np.float32)
         xs.append(v)
-    seed = _skip_q4(n, 0x0BADCAFEDEADBEEF)
-    for ty in (W.Q8_0, W.Q4_K, W.Q5_K, W.Q6_K):
+    seed = 0x0BADCAFEDEADBEEF
+    for ty in (W.Q4_0, W.Q4_1, W.Q8_0, W.Q4_K, W.Q5_K, W.Q6_K):
         w, seed = rand_row(ty, n, seed)
         if ty == W.Q8_0:
             w[2] = 0x80      # -128, the weight the sign trick cannot negate
@@ -113,9 +108,12 @@ def test_bf16_and_f16():
     want = float(np.sum(x.astype(np.float64) ** 2))
     w_bf16 = (x.view(np.uint32) >> 16).astype(np.uint16).view(np.uint8)
     w_f32 = x.view(np.uint8)
+    w_f16 = x.astype(np.float16).view(np.uint8)     # multiples of 1/4 below 512: exact in f16
     for level in LEVELS:
         lib = oracle.lib()
         got = lib.orc_dot(level, W.BF16, oracle._p(w_bf16), oracle._p(x), None, None, None, 37)
+        assert abs(got - want) < 1e-3
+        got = lib.orc_dot(level, W.F16, oracle._p(w_f16), oracle._p(x), None, None, None, 37)
         assert abs(got - want) < 1e-3
         got = lib.orc_dot(level, W.F32, oracle._p(w_f32), oracle._p(x), None, None, None, 37)
         assert abs(got - want) < 1e-3

@@ -25,6 +25,18 @@ def test_layer_matches_float64(name, kw):
     assert rel_err(out, ref) < 2e-5
 
 
+@pytest.mark.parametrize("gate_ty,down_ty", [(W.Q4_0, W.Q4_1), (W.Q4_1, W.Q4_0), (W.F16, W.F32)])
+def test_other_types_match_float64_and_levels_agree(gate_ty, down_ty):
+    wl = W.typed_layer(gate_ty, down_ty, n=6, **W.SMALL)
+    out, tap = oracle.moe_forward(wl.layer, wl.h, level=0, taps=True)
+    ref = layer_float64(wl.layer, wl.h, tap["ids"], tap["weights"])
+    assert rel_err(out, ref) < 2e-5
+    for level in LEVELS[1:]:
+        got, tapl = oracle.moe_forward(wl.layer, wl.h, level=level, taps=True)
+        if np.array_equal(tapl["ids"], tap["ids"]):
+            assert rel_err(got, out) < 1e-4
+
+
 def test_mixed_kquants_match_float64():
     wl = W.mtp_stack(n_seq=3, n_tok=2, n_layers=1, **W.SMALL)
     out, tap = oracle.moe_forward(wl.layer, wl.h, level=0, taps=True)
