@@ -26,7 +26,7 @@ SYMBOLS = ["bivmoe_create", "bivmoe_destroy", "bivmoe_forward", "bivmoe_forward_
            "bivmoe_route_noalloc", "bivmoe_numerics", "bivmoe_memory", "bivmoe_launch_count", "bivmoe_last_error",
            "bivmoe_global_error", "bivmoe_ep_create", "bivmoe_ep_route", "bivmoe_ep_shared",
            "bivmoe_ep_experts", "bivmoe_ep_combine", "bivmoe_ep_status", "bivmoe_forward_host_async",
-           "bivmoe_host_wait", "bivmoe_int8_peak"]
+           "bivmoe_host_wait", "bivmoe_int8_peak", "bivmoe_dense_create"]
 
 
 class BivMoeError(RuntimeError):
@@ -67,6 +67,8 @@ def lib():
         L = C.CDLL(LIB_PATH)
         vp, i32 = C.c_void_p, C.c_int32
         L.bivmoe_create.argtypes = [C.POINTER(Desc), C.POINTER(vp)]
+        L.bivmoe_dense_create.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(Experts),
+                                          C.POINTER(Experts), C.POINTER(Experts), C.POINTER(vp)]
         L.bivmoe_destroy.argtypes = [vp]
         L.bivmoe_destroy.restype = None
         L.bivmoe_forward.argtypes = [vp, vp, vp, i32, i32, vp]

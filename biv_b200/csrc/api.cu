@@ -389,6 +389,24 @@ static int create_impl(const bivmoe_desc* d, int ep_rank, int ep_world, int max_
 
 int bivmoe_create(const bivmoe_desc* d, bivmoe_layer** out) { return create_impl(d, 0, 1, 0, out); }
 
+int bivmoe_dense_create(int32_t device, int32_t n_embd, int32_t n_ff, int32_t max_tokens,
+                        const bivmoe_experts* gate, const bivmoe_experts* up,
+                        const bivmoe_experts* down, bivmoe_layer** out) {
+    if (out) *out = nullptr;
+    if (!gate || !up || !down || !out || n_embd <= 0)
+        return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null pointer or non-positive n_embd");
+    // one expert behind a router of zeros: softmax of one logit is 1, so is the
+    // renormalised weight, and the combine's w * y is y
+    std::vector<float> router((size_t)n_embd, 0.0f);
+    bivmoe_desc d{};
+    d.n_embd = n_embd; d.n_expert = 1; d.n_expert_used = 1;
+    d.n_ff_exp = n_ff; d.n_ff_shexp = 0;
+    d.max_tokens = max_tokens; d.device = device;
+    d.router = router.data();
+    d.gate = *gate; d.up = *up; d.down = *down;
+    return create_impl(&d, 0, 1, 0, out);
+}
+
 int bivmoe_ep_create(const bivmoe_desc* d, int32_t ep_rank, int32_t ep_world, int32_t max_recv_rows,
                      bivmoe_layer** out) {
     if (ep_world == 1) return create_impl(d, 0, 1, 0, out);

@@ -57,6 +57,25 @@ class Moe:
         d, self._keep = fill_desc(layer, max_tokens, device)
         h = C.c_void_p()
         capi.check(L.bivmoe_create(C.byref(d), C.byref(h)))
+        self._adopt(h, layer, max_tokens, device)
+
+    @classmethod
+    def dense(cls, gate: ExpertStack, up: ExpertStack, down: ExpertStack, max_tokens: int,
+              device: int = 0) -> "Moe":
+        """``Ffn::Dense`` (engine/src/model.rs:853-858): ``down(silu(gate h) * up h)`` with
+        single matrices; ``moe`` / ``moe_`` / ``moe_host`` then compute the dense block."""
+        self = cls.__new__(cls)
+        self._h = None
+        g, u, dn = _experts(gate), _experts(up), _experts(down)
+        h = C.c_void_p()
+        capi.check(capi.lib().bivmoe_dense_create(device, gate.cols, gate.rows, max_tokens,
+                                                  C.byref(g), C.byref(u), C.byref(dn), C.byref(h)))
+        layer = MoeLayer(gate.cols, 1, 1, gate.rows, 0, np.zeros((1, gate.cols), np.float32),
+                         gate=gate, up=up, down=down)
+        self._adopt(h, layer, max_tokens, device)
+        return self
+
+    def _adopt(self, h, layer, max_tokens, device):
         self._h = h
         self.n_embd, self.n_expert, self.k = layer.n_embd, layer.n_expert, layer.n_expert_used
         self.n_ff_exp, self.has_shared = layer.n_ff_exp, layer.has_shared

@@ -103,6 +103,17 @@ typedef struct bivmoe_layer bivmoe_layer;
 BIVMOE_API int bivmoe_create(const bivmoe_desc* desc, bivmoe_layer** out);
 BIVMOE_API void bivmoe_destroy(bivmoe_layer* layer);
 
+/* The dense feed-forward block of the qwen35 layers, `Ffn::Dense` (engine/src/model.rs:
+ * 853-858; `dense_ffn`, 1119-1126): out = down(silu(gate h) * up h), the step the
+ * mixture-of-experts layer replaces in the same place of the graph.  `gate` and `up` are
+ * [n_ff x n_embd], `down` is [n_embd x n_ff], each with n = 1.  The layer object is a
+ * mixture with one expert that every row selects with weight exactly 1 (a softmax over
+ * one logit), so every other call of this header - forward, host forms, stack, taps -
+ * takes it unchanged. */
+BIVMOE_API int bivmoe_dense_create(int32_t device, int32_t n_embd, int32_t n_ff, int32_t max_tokens,
+                                   const bivmoe_experts* gate, const bivmoe_experts* up,
+                                   const bivmoe_experts* down, bivmoe_layer** out);
+
 /* The layer on device rows: out[n][n_embd] = (accumulate ? out : 0) + moe(h).
  * `accumulate` 0 is `Model::moe`'s return value (model.rs:861-898);
  * 1 is Metal's `moe_combine`, which adds into the residual

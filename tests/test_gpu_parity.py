@@ -17,13 +17,13 @@ TOL = 1e-3        # the gate
 FLIP_TOL = 1e-2   # tokens touched by a re-quantisation flip (see run_case)
 
 
-def run_case(wl, max_tokens=None, check_dots=True):
+def run_case(wl, max_tokens=None, check_dots=True, make=None):
     import torch
     from biv_b200.moe import Moe
     layer = wl.layer
     level = oracle.host_level()
     ref, tap = oracle.moe_forward(layer, wl.h, level=level, threads=oracle.max_threads(), taps=True)
-    m = Moe(layer, max_tokens or wl.n)
+    m = (make or Moe)(layer, max_tokens or wl.n)
     try:
         h = torch.from_numpy(wl.h).cuda()
         out = m.moe(h)
@@ -159,6 +159,27 @@ def test_other_weight_types(gate_ty, down_ty, n):
 
 def test_q4_0_and_q4_1_at_the_model_shape():
     run_case(W.typed_layer(W.Q4_0, W.Q4_1, n=64, n_expert=32))
+
+
+# Ffn::Dense (engine/src/model.rs:853-858, 1119-1126): the oracle's statement of it is its
+# layer with one expert of weight 1 and no shared expert
+@pytest.mark.parametrize("ty,n", [(W.Q8_0, 5), (W.Q4_K, 33), (W.BF16, 9), (W.Q6_K, 70), (W.Q8_0, 300)])
+def test_dense_ffn(ty, n):
+    from biv_b200.moe import Moe
+    rng = np.random.default_rng(7)
+    layer = W.make_layer(rng, gate_ty=ty, n_embd=256, n_expert=1, k=1, ff=512, ff_sh=0)
+    layer.router[:] = 0
+    h = W.rms_normalise(rng.standard_normal((n, 256), dtype=np.float32))
+    wl = W.Workload("dense", 7, [layer], h)
+    got, ref = run_case(wl, make=lambda l, cap: Moe.dense(l.gate, l.up, l.down, cap))
+    # and it is dense_ffn: down(silu(gate h) * up h) from the oracle's matmuls
+    lv = oracle.host_level()
+    g = oracle.matmul(lv, ty, layer.gate.expert(0), 512, 256, h)
+    u = oracle.matmul(lv, ty, layer.up.expert(0), 512, 256, h)
+    with np.errstate(over="ignore"):   # exp(-g) may be inf: silu is then 0, as in f32
+        mid = (g * (np.float32(1) / (np.float32(1) + np.exp(-g))) * u).astype(np.float32)
+    want = oracle.matmul(lv, ty, layer.down.expert(0), 256, 512, mid)
+    assert rel_err(ref, want) < 1e-2 and rel_err(got, want) < 1e-2
 
 
 def test_one_token_and_ragged_tiles():
