@@ -163,20 +163,22 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def time_ep(layer, h_rank, steps, warmup, rank, world, local, in_flight=1):
+def time_ep(layer, h_rank, steps, warmup, rank, world, local, in_flight=1, exchange="all_to_all"):
     """Expert-parallel passes of the layer: this rank's rows in, experts sharded
     n_expert / world per GPU, rows exchanged over NCCL.  Device time of `steps`
     passes, max over ranks; also this rank's output of the last pass.  With
     `in_flight` = 2 the rank's rows are two micro-batches, each with its own layer
     object and stream, begun together so that one's exchanges overlap the other's
-    kernels; a step is still all of the rank's rows."""
+    kernels; a step is still all of the rank's rows.  `exchange` "peer": the rows move by
+    the library's own kernels (stores into the peers' memory), one pass at a time."""
     import torch
     import torch.distributed as dist
     from biv_b200.ep import EpMoe
     n = h_rank.shape[0]
-    parts = in_flight if (in_flight > 1 and n % in_flight == 0) else 1
+    peer = exchange == "peer"
+    parts = in_flight if (in_flight > 1 and n % in_flight == 0 and not peer) else 1
     n_part = n // parts
-    ms_ = [EpMoe(layer, n_part, rank, world, local) for _ in range(parts)]
+    ms_ = [EpMoe(layer, n_part, rank, world, local, exchange=exchange) for _ in range(parts)]
     streams = [torch.cuda.Stream() for _ in range(parts)]
     h = torch.from_numpy(h_rank).cuda()
     out = torch.empty_like(h)
@@ -185,6 +187,10 @@ def time_ep(layer, h_rank, steps, warmup, rank, world, local, in_flight=1):
     torch.cuda.synchronize()
 
     def one_step():
+        if peer:
+            with torch.cuda.stream(streams[0]):
+                ms_[0].moe_(hs[0], outs[0], accumulate=False)
+            return
         for i in range(parts):
             with torch.cuda.stream(streams[i]):
                 ms_[i].begin(hs[i])
@@ -213,7 +219,7 @@ def time_ep(layer, h_rank, steps, warmup, rank, world, local, in_flight=1):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     for m in ms_:
         m.status()
-    recv = sum(m.last_plan.m for m in ms_)
+    recv = sum(m.last_plan.m for m in ms_) if not peer else 0
     res = out.cpu().numpy()
     for m in ms_:
         m.close()
@@ -231,7 +237,7 @@ def run_ep_workload(args, wl, rank, world, local):
     sampler = ClockSampler(local)
     sampler.start()
     ms, recv, _ = time_ep(layer, h_rank, args.steps, args.warmup, rank, world, local,
-                          in_flight=args.ep_in_flight)
+                          in_flight=args.ep_in_flight, exchange=args.ep_exchange)
     sampler.stop_flag = True
     sampler.join()
     if rank == 0:
@@ -257,8 +263,12 @@ def run_ep_workload(args, wl, rank, world, local):
                          "frac": flops / (ms * 1e-3) / 1e12 / world / tf_peak if tf_peak else None,
                          "traffic": None, "scope": "whole pass per GPU, exchanges included"},
             "exchange": {"rows_received_rank0": recv, "bytes_each_way_rank0": recv * row_bytes,
-                         "transport": "NCCL all_to_all_single over NVLink; an f32 row once per owning "
-                                      "rank out, one f32 partial sum per row back"},
+                         "transport": ("the library's kernels store into the peers' memory over NVLink "
+                                       "(CUDA IPC mappings), two one-element all-reduces per pass as "
+                                       "barriers" if args.ep_exchange == "peer" else
+                                       "NCCL all_to_all_single over NVLink") +
+                                      "; an f32 row once per owning rank out, one f32 partial sum per "
+                                      "row back"},
             "gpu_launches": None, "clocks": sampler.summary(),
         }
         print(json.dumps(line))
@@ -357,6 +367,9 @@ def main():
                     help="passes in flight: the timed passes rotate over this many streams, layer object "
                          "j on stream j mod streams (must divide --copies; 1: one pass at a time)")
     ap.add_argument("--layers", type=int, default=40, help="layers of the mtp_stack workload")
+    ap.add_argument("--ep-exchange", default="all_to_all", choices=["all_to_all", "peer"],
+                    help="expert parallelism: rows moved by NCCL all-to-alls, or by the library's "
+                         "kernels storing into the peers' memory")
     ap.add_argument("--ep-in-flight", type=int, default=1,
                     help="micro-batches a rank keeps in flight in the expert-parallel workload (two "
                          "measured slower than one at 2 GPUs: 2.65 against 2.50 ms)")

@@ -26,7 +26,9 @@ SYMBOLS = ["bivmoe_create", "bivmoe_destroy", "bivmoe_forward", "bivmoe_forward_
            "bivmoe_route_noalloc", "bivmoe_numerics", "bivmoe_memory", "bivmoe_launch_count", "bivmoe_last_error",
            "bivmoe_global_error", "bivmoe_ep_create", "bivmoe_ep_route", "bivmoe_ep_shared",
            "bivmoe_ep_experts", "bivmoe_ep_combine", "bivmoe_ep_status", "bivmoe_forward_host_async",
-           "bivmoe_host_wait", "bivmoe_int8_peak", "bivmoe_dense_create"]
+           "bivmoe_host_wait", "bivmoe_int8_peak", "bivmoe_dense_create", "bivmoe_ep_peer_info",
+           "bivmoe_ep_peer_attach", "bivmoe_ep_peer_dispatch", "bivmoe_ep_peer_experts",
+           "bivmoe_ep_peer_combine"]
 
 
 class BivMoeError(RuntimeError):
@@ -55,6 +57,12 @@ class Desc(C.Structure):
 
 
 _lib = None
+
+
+class PeerInfo(C.Structure):
+    """``bivmoe_peer_info``: how another rank reaches this rank's exchange block."""
+    _fields_ = [("ipc_handle", C.c_uint8 * 64), ("base", C.c_void_p), ("pid", C.c_int64),
+                ("bytes", C.c_int64), ("device", C.c_int32), ("reserved", C.c_int32)]
 
 
 def lib():
@@ -88,6 +96,11 @@ def lib():
         L.bivmoe_ep_experts.argtypes = [vp, vp, vp, i32, vp, vp]
         L.bivmoe_ep_combine.argtypes = [vp, vp, vp, i32, i32, vp]
         L.bivmoe_ep_status.argtypes = [vp, vp]
+        L.bivmoe_ep_peer_info.argtypes = [vp, C.POINTER(PeerInfo)]
+        L.bivmoe_ep_peer_attach.argtypes = [vp, C.POINTER(PeerInfo)]
+        L.bivmoe_ep_peer_dispatch.argtypes = [vp, vp, i32, vp]
+        L.bivmoe_ep_peer_experts.argtypes = [vp, vp]
+        L.bivmoe_ep_peer_combine.argtypes = [vp, vp, i32, i32, vp]
         L.bivmoe_numerics.argtypes = [vp, C.c_char_p, C.c_size_t]
         L.bivmoe_memory.argtypes = [vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
         L.bivmoe_launch_count.restype = C.c_uint64

@@ -4,6 +4,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <unistd.h>
 
 #include <algorithm>
 #include <atomic>
@@ -91,6 +92,14 @@ struct bivmoe_layer {
     int32_t* ep_rank_ids = nullptr;   // [max_tokens][world] the rank, or -1: the home combine's "ids"
     int32_t* ep_rank_pos = nullptr;   // [max_tokens][world] the row's index among the sent rows
     float* ep_ones = nullptr;         // [max_tokens][world] the home combine's weights
+    // the peer-store exchange (bivmoe_ep_peer_*): this rank's block, the ranks' blocks as
+    // mapped into this process, the owner's partial sums before they are returned
+    uint8_t* peer_block = nullptr;
+    PeerLayout peer_lay{};
+    PeerTable peers{};
+    bool peers_attached = false;
+    std::vector<void*> ipc_opened;
+    float* peer_out_rows = nullptr;   // [world * cap][e]
     bool use_graph = true;
     int launches_per_forward = 0;
     std::string error, device_name;
@@ -270,6 +279,7 @@ void bivmoe_destroy(bivmoe_layer* L) {
     if (L->graph.exec) cudaGraphExecDestroy(L->graph.exec);
     if (L->host_graph.exec) cudaGraphExecDestroy(L->host_graph.exec);
     if (L->status_host) cudaFreeHost(L->status_host);
+    for (void* p : L->ipc_opened) cudaIpcCloseMemHandle(p);
     for (void* p : L->allocs) cudaFree(p);
     if (L->own_stream) cudaStreamDestroy(L->own_stream);
     delete L;
@@ -631,6 +641,147 @@ int bivmoe_ep_combine(bivmoe_layer* L, const float* returned_rows_dev, float* ou
                          L->ws.logits};
     CU(launch_combine(c, src, out_dev, accumulate));
     return BIVMOE_OK;
+}
+
+// ---- the peer-store exchange ------------------------------------------------------
+
+static int peer_check(bivmoe_layer* L, const char* what, bool attached) {
+    if (int rc = ep_check(L, what)) return rc;
+    if (attached && !L->peers_attached)
+        return set_err(&L->error, BIVMOE_ERR_ARGUMENT, "%s before bivmoe_ep_peer_attach", what);
+    return BIVMOE_OK;
+}
+
+int bivmoe_ep_peer_info(bivmoe_layer* L, bivmoe_peer_info* info) {
+    if (int rc = peer_check(L, "bivmoe_ep_peer_info", false)) return rc;
+    std::string* errp = &L->error;
+    if (!info) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null pointer");
+    DeviceScope on_device(L->device);
+    if (!L->peer_block) {
+        const size_t W = (size_t)L->ep_world, cap = (size_t)L->max_tokens, e = (size_t)L->e;
+        if ((size_t)L->max_recv < W * cap)
+            return set_err(errp, BIVMOE_ERR_ARGUMENT,
+                           "max_recv_rows %d is below world * max_tokens = %zu, the rows of the regions",
+                           L->max_recv, W * cap);
+        PeerLayout lay{};
+        lay.cap = (int)cap;
+        lay.rows = 0;
+        lay.returned = W * cap * e * 4;
+        lay.tags = 2 * lay.returned;
+        lay.counts = lay.tags + ((W * cap * 2 * (size_t)L->k * 4 + 255) & ~(size_t)255);
+        lay.bytes = lay.counts + 256;
+        void* p = nullptr;
+        CU(cudaMalloc(&p, lay.bytes));
+        L->allocs.push_back(p);
+        CU(cudaMemset(p, 0, lay.bytes));
+        L->peer_block = (uint8_t*)p;
+        L->peer_lay = lay;
+        CU(cudaMalloc(&p, W * cap * e * 4));
+        L->allocs.push_back(p);
+        L->peer_out_rows = (float*)p;
+        L->ws_bytes += lay.bytes + W * cap * e * 4;
+    }
+    memset(info, 0, sizeof(*info));
+    cudaIpcMemHandle_t hnd;
+    CU(cudaIpcGetMemHandle(&hnd, L->peer_block));
+    static_assert(sizeof(hnd) == sizeof(info->ipc_handle), "cudaIpcMemHandle_t is 64 bytes");
+    memcpy(info->ipc_handle, &hnd, sizeof(hnd));
+    info->base = L->peer_block;
+    info->pid = (int64_t)getpid();
+    info->device = L->device;
+    info->bytes = (int64_t)L->peer_lay.bytes;
+    return BIVMOE_OK;
+}
+
+int bivmoe_ep_peer_attach(bivmoe_layer* L, const bivmoe_peer_info* all) {
+    if (int rc = peer_check(L, "bivmoe_ep_peer_attach", false)) return rc;
+    std::string* errp = &L->error;
+    if (!all) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null pointer");
+    if (!L->peer_block) return set_err(errp, BIVMOE_ERR_ARGUMENT, "bivmoe_ep_peer_info comes first");
+    if (L->peers_attached) return set_err(errp, BIVMOE_ERR_ARGUMENT, "already attached");
+    DeviceScope on_device(L->device);
+    for (int r = 0; r < L->ep_world; r++) {
+        const bivmoe_peer_info& pi = all[r];
+        if (pi.bytes != (int64_t)L->peer_lay.bytes)
+            return set_err(errp, BIVMOE_ERR_ARGUMENT,
+                           "rank %d's block has %lld bytes, this rank's %zu: the ranks' shapes differ", r,
+                           (long long)pi.bytes, L->peer_lay.bytes);
+        if (r == L->ep_rank) {
+            L->peers.base[r] = L->peer_block;
+        } else if (pi.pid == (int64_t)getpid()) {   // a rank of this process: its pointer as it is
+            if (pi.device != L->device) {
+                int can = 0;
+                CU(cudaDeviceCanAccessPeer(&can, L->device, pi.device));
+                if (!can)
+                    return set_err(errp, BIVMOE_ERR_UNSUPPORTED, "device %d cannot map device %d's memory",
+                                   L->device, pi.device);
+                const cudaError_t pe = cudaDeviceEnablePeerAccess(pi.device, 0);
+                if (pe != cudaSuccess && pe != cudaErrorPeerAccessAlreadyEnabled) CU(pe);
+                cudaGetLastError();
+            }
+            L->peers.base[r] = (uint8_t*)pi.base;
+        } else {
+            cudaIpcMemHandle_t hnd;
+            memcpy(&hnd, pi.ipc_handle, sizeof(hnd));
+            void* p = nullptr;
+            CU(cudaIpcOpenMemHandle(&p, hnd, cudaIpcMemLazyEnablePeerAccess));
+            L->ipc_opened.push_back(p);
+            L->peers.base[r] = (uint8_t*)p;
+        }
+    }
+    L->peers_attached = true;
+    return BIVMOE_OK;
+}
+
+int bivmoe_ep_peer_dispatch(bivmoe_layer* L, const float* h_dev, int32_t n, void* stream) {
+    if (int rc = peer_check(L, "bivmoe_ep_peer_dispatch", true)) return rc;
+    DeviceScope on_device(L->device);
+    std::string* errp = &L->error;
+    if (n < 0 || n > L->max_tokens)
+        return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens = %d", n, L->max_tokens);
+    if (n > 0 && !h_dev) return set_err(errp, BIVMOE_ERR_ARGUMENT, "null pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    L->ep_n = n;
+    LaunchCfg c{s, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh, L->has_shared ? 1 : 0, L->sm_count};
+    c.prefill_min = L->prefill_min;
+    c.prefill_tile = L->prefill_tile;
+    if (n > 0) {
+        CU(launch_router(c, L->router, h_dev, L->ws));
+        CU(launch_route_topk(c, L->ws));
+        if (L->has_shared) CU(launch_sort(c, L->ws));
+    }
+    CU(launch_ep_peer_scatter(c, h_dev, L->ws, L->ep_world, L->ep_rank, L->n_local, L->ep_slot, L->ep_counts,
+                              L->ep_rank_ids, L->ep_rank_pos, L->peers, L->peer_lay));
+    return BIVMOE_OK;
+}
+
+int bivmoe_ep_peer_experts(bivmoe_layer* L, void* stream) {
+    if (int rc = peer_check(L, "bivmoe_ep_peer_experts", true)) return rc;
+    DeviceScope on_device(L->device);
+    std::string* errp = &L->error;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int m = L->ep_world * L->peer_lay.cap;
+    LaunchCfg c{s, m, L->k, L->e, L->n_local, L->ff, 0, 0, L->sm_count};
+    c.prefill_min = L->prefill_min;
+    c.prefill_tile = L->prefill_tile;
+    const Workspace& w = L->ws_owner;
+    const DevTiles none{};
+    const float* rows = (const float*)(L->peer_block + L->peer_lay.rows);
+    CU(launch_ep_peer_localize(c, L->peer_block, L->peer_lay, L->ep_rank * L->n_local, w));
+    CU(launch_sort(c, w));
+    CU(launch_dispatch(c, rows, w, w.act_t != nullptr && !type_uses_f32_act(L->gate_up.ty),
+                       w.act_f != nullptr && type_uses_f32_act(L->gate_up.ty)));
+    CU(launch_experts(c, L->gate_up, L->down, none, none, w));
+    if (c.prefill_min > 0) CU(launch_experts_prefill(c, L->gate_up, L->down, none, none, w));
+    CU(launch_combine(c, combine_src(w), L->peer_out_rows, 0));
+    CU(launch_ep_peer_return(c, L->peer_out_rows, L->peer_block, L->ep_rank, L->peers, L->peer_lay));
+    return BIVMOE_OK;
+}
+
+int bivmoe_ep_peer_combine(bivmoe_layer* L, float* out_dev, int32_t n, int32_t accumulate, void* stream) {
+    if (int rc = peer_check(L, "bivmoe_ep_peer_combine", true)) return rc;
+    return bivmoe_ep_combine(L, (const float*)(L->peer_block + L->peer_lay.returned), out_dev, n, accumulate,
+                             stream);
 }
 
 int bivmoe_ep_status(bivmoe_layer* L, void* stream) {

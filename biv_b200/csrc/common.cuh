@@ -218,6 +218,22 @@ cudaError_t launch_ep_gather(const LaunchCfg& c, const float* h, const Workspace
                              int32_t* rank_pos, float* send_rows, int32_t* send_tags,
                              int32_t* counts_out);
 cudaError_t launch_ep_localize(const LaunchCfg& c, const int32_t* tags, int first, const Workspace& ws);
+// Peer-store exchange (ep.cu): every rank owns one block of this layout and maps the others'.
+struct PeerTable { uint8_t* base[32]; };          // rank -> its block, as seen from this device
+struct PeerLayout {
+    int cap;                                       // rows per region = the layer's max_tokens
+    size_t rows, returned, tags, counts, bytes;   // byte offsets: [W][cap][e] f32 received rows,
+                                                   // [W][cap][e] f32 returned sums, [W][cap][2k] i32
+                                                   // tags, [W] i32 counts; the block's size
+};
+cudaError_t launch_ep_peer_scatter(const LaunchCfg& c, const float* h, const Workspace& ws, int world,
+                                   int me, int n_local, int32_t* slot, int32_t* counts,
+                                   int32_t* rank_ids, int32_t* rank_pos, const PeerTable& peers,
+                                   const PeerLayout& lay);
+cudaError_t launch_ep_peer_localize(const LaunchCfg& c, const uint8_t* block, const PeerLayout& lay,
+                                    int first, const Workspace& ws);
+cudaError_t launch_ep_peer_return(const LaunchCfg& c, const float* out_rows, const uint8_t* block, int me,
+                                  const PeerTable& peers, const PeerLayout& lay);
 cudaError_t launch_rms_norm(const LaunchCfg& c, const float* x, const float* w, float eps,
                             float* out);
 cudaError_t launch_repack(const DevTiles& dst, const uint8_t* gguf_rows, int tile_base,

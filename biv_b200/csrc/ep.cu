@@ -17,6 +17,18 @@
 //   exchange 2   one partial sum per row back, same layout
 //   home rank    combine (rowops.cu) with the ranks as "experts" of weight one and
 //                the partial sums as the routed rows, then the shared expert
+//
+// The exchanges come in two forms.  With the caller's all-to-all the rows are packed
+// by destination and the row counts cross the host.  With peer stores (the ep_peer_*
+// kernels) every rank maps one block of every other rank's memory (NVLink peer access)
+// and the kernels write where the rows are needed: the home rank's scatter kernel puts
+// a row straight into region [home rank] of the owner's receive buffer, the owner's
+// return kernel puts the partial sum straight into region [owner] of the home rank's
+// return buffer.  A region holds `cap` rows (the most a rank can send to one peer), so
+// no offsets depend on other ranks' counts, the counts travel as peer stores too, and
+// the host never waits; the owner treats a region's unused rows as rows without experts.
+// Two stream-ordered barriers of the caller's communicator per pass order the stores
+// against their readers.  Plain stores only: no multicast, no waiting inside a kernel.
 #include <algorithm>
 
 #include "common.cuh"
@@ -139,6 +151,110 @@ cudaError_t launch_ep_localize(const LaunchCfg& c, const int32_t* tags, int firs
     const int total = c.n * c.k;
     ep_localize_kernel<<<(total + 255) / 256, 256, 0, c.stream>>>(tags, c.n, c.k, first, c.n_expert, ws.ids,
                                                                 ws.weights);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Peer stores.  PeerLayout::rows etc. are byte offsets into every rank's block.
+
+// Block d: the count of rows for rank d goes to rank d's recv_counts[me].
+__global__ void ep_peer_counts_kernel(const int32_t* __restrict__ counts, PeerTable peers,
+                                      PeerLayout lay, int me, int world) {
+    const int d = threadIdx.x;
+    if (d < world) ((int32_t*)(peers.base[d] + lay.counts))[me] = counts[d];
+}
+
+// One block per token, as ep_rank_gather_kernel, but the row and its tag go into region
+// `me` of each owner's receive buffer; rank_pos is the row's index in this rank's own
+// return buffer (region d, same slot).
+__global__ void __launch_bounds__(EPG_THREADS)
+ep_peer_scatter_kernel(const float* __restrict__ h, const int32_t* __restrict__ ids,
+                       const float* __restrict__ weights, const int32_t* __restrict__ slot, int k, int e,
+                       int world, int me, PeerTable peers, PeerLayout lay,
+                       int32_t* __restrict__ rank_ids, int32_t* __restrict__ rank_pos) {
+    __shared__ int s_slot[32];
+    const int t = blockIdx.x;
+    if (threadIdx.x < world) {
+        const int d = threadIdx.x, sl = slot[(size_t)t * world + d];
+        s_slot[d] = sl;
+        rank_ids[(size_t)t * world + d] = sl < 0 ? -1 : d;
+        rank_pos[(size_t)t * world + d] = sl < 0 ? 0 : d * lay.cap + sl;
+    }
+    __syncthreads();
+    const float4* src = (const float4*)(h + (size_t)t * e);
+    for (int d = 0; d < world; d++) {
+        const int sl = s_slot[d];
+        if (sl < 0) continue;
+        const size_t row = (size_t)me * lay.cap + sl;
+        float4* drow = (float4*)(peers.base[d] + lay.rows) + row * (e / 4);
+        for (int i = threadIdx.x; i < e / 4; i += EPG_THREADS) drow[i] = src[i];
+        if (threadIdx.x < k) {
+            int32_t* tag = (int32_t*)(peers.base[d] + lay.tags) + row * 2 * k;
+            tag[threadIdx.x] = ids[(size_t)t * k + threadIdx.x];
+            tag[k + threadIdx.x] = __float_as_int(weights[(size_t)t * k + threadIdx.x]);
+        }
+    }
+}
+
+cudaError_t launch_ep_peer_scatter(const LaunchCfg& c, const float* h, const Workspace& ws, int world,
+                                   int me, int n_local, int32_t* slot, int32_t* counts,
+                                   int32_t* rank_ids, int32_t* rank_pos, const PeerTable& peers,
+                                   const PeerLayout& lay) {
+    if (world > 32 || c.k > 32 || c.e % 4) return cudaErrorInvalidValue;
+    // c.n = 0 still publishes the (zero) counts: the owners read them every pass
+    ep_rank_slots_kernel<<<world, 1024, 0, c.stream>>>(ws.ids, c.n, c.k, n_local, world, slot, counts,
+                                                      counts);
+    ep_peer_counts_kernel<<<1, 32, 0, c.stream>>>(counts, peers, lay, me, world);
+    count_launch(2);
+    if (c.n > 0) {
+        ep_peer_scatter_kernel<<<c.n, EPG_THREADS, 0, c.stream>>>(h, ws.ids, ws.weights, slot, c.k, c.e,
+                                                                world, me, peers, lay, rank_ids, rank_pos);
+        count_launch();
+    }
+    return cudaGetLastError();
+}
+
+// The owner's routing result from its receive buffer: row r = region r / cap, slot
+// r % cap; slots past the region's count are rows without experts.
+__global__ void ep_peer_localize_kernel(const int32_t* __restrict__ tags, const int32_t* __restrict__ counts,
+                                        int cap, int m, int k, int first, int n_local,
+                                        int32_t* __restrict__ ids, float* __restrict__ weights) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= m * k) return;
+    const int row = i / k, j = i % k;
+    const bool used = row % cap < counts[row / cap];
+    const int id = used ? tags[(size_t)row * 2 * k + j] : -1;
+    ids[i] = id >= first && id < first + n_local ? id - first : -1;
+    weights[i] = used ? __int_as_float(tags[(size_t)row * 2 * k + k + j]) : 0.0f;
+}
+
+cudaError_t launch_ep_peer_localize(const LaunchCfg& c, const uint8_t* block, const PeerLayout& lay,
+                                    int first, const Workspace& ws) {
+    const int total = c.n * c.k;
+    ep_peer_localize_kernel<<<(total + 255) / 256, 256, 0, c.stream>>>(
+        (const int32_t*)(block + lay.tags), (const int32_t*)(block + lay.counts), lay.cap, c.n, c.k, first,
+        c.n_expert, ws.ids, ws.weights);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// One block per received row: the row's partial sum goes to region `me`, same slot, of
+// the return buffer of the rank it came from.
+__global__ void __launch_bounds__(EPG_THREADS)
+ep_peer_return_kernel(const float* __restrict__ out_rows, const int32_t* __restrict__ counts, int e, int me,
+                      PeerTable peers, PeerLayout lay) {
+    const int r = blockIdx.x, src = r / lay.cap, sl = r % lay.cap;
+    if (sl >= counts[src]) return;
+    const float4* from = (const float4*)(out_rows + (size_t)r * e);
+    float4* to = (float4*)(peers.base[src] + lay.returned) + ((size_t)me * lay.cap + sl) * (e / 4);
+    for (int i = threadIdx.x; i < e / 4; i += EPG_THREADS) to[i] = from[i];
+}
+
+cudaError_t launch_ep_peer_return(const LaunchCfg& c, const float* out_rows, const uint8_t* block, int me,
+                                  const PeerTable& peers, const PeerLayout& lay) {
+    ep_peer_return_kernel<<<c.n, EPG_THREADS, 0, c.stream>>>(out_rows, (const int32_t*)(block + lay.counts),
+                                                           c.e, me, peers, lay);
     count_launch();
     return cudaGetLastError();
 }

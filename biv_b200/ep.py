@@ -72,6 +72,25 @@ class TorchComm:
         import torch.distributed as dist
         dist.all_to_all_single(recv, send, recv_splits, send_splits, group=self.group)
 
+    def barrier(self, device):
+        """Stream-ordered on the current stream: a one-element all-reduce."""
+        import torch
+        import torch.distributed as dist
+        if getattr(self, "_one", None) is None or self._one.device != device:
+            self._one = torch.zeros(1, dtype=torch.int32, device=device)
+        dist.all_reduce(self._one, group=self.group)
+
+    def all_gather_bytes(self, blob: bytes, device):
+        """Every rank's ``blob`` (same length everywhere), in rank order."""
+        import torch
+        import torch.distributed as dist
+        W = dist.get_world_size(self.group)
+        mine = torch.frombuffer(bytearray(blob), dtype=torch.uint8).to(device)
+        out = torch.empty(W * len(blob), dtype=torch.uint8, device=device)
+        dist.all_gather_into_tensor(out, mine, group=self.group)
+        raw = out.cpu().numpy().tobytes()
+        return [raw[r * len(blob):(r + 1) * len(blob)] for r in range(W)]
+
 
 def ep_pass(steps, h, out, accumulate: bool, comm=None):
     """One pass of the layer over this rank's rows ``h`` [n, n_embd] into ``out``.
@@ -115,6 +134,18 @@ def ep_pass_finish(steps, h, out, accumulate: bool, comm, begun):
     comm.all_to_all(returned, out_rows, plan.send_splits, plan.recv_splits)
     steps.combine(returned, out, accumulate)
     return plan
+
+
+def ep_pass_peer(steps, h, out, accumulate: bool, comm):
+    """The pass with the library's own exchange kernels (stores into the peers' memory over
+    NVLink, ``bivmoe_ep_peer_*``): no packing by destination, no counts on the host, no
+    host wait; ``comm`` supplies the two stream-ordered barriers."""
+    steps.peer_dispatch(h)
+    comm.barrier(h.device)          # every rank's rows are where their owners read them
+    steps.shared(h)                 # beside the owners' work, on the side stream
+    steps.peer_experts()
+    comm.barrier(h.device)          # the partial sums are back; the receive buffers are free
+    steps.peer_combine(out, accumulate)
 
 
 class DeviceSteps:
@@ -208,20 +239,59 @@ class DeviceSteps:
     def status(self):
         capi.check(capi.lib().bivmoe_ep_status(self._h, self._stream()), self._h)
 
+    # ---- the peer-store exchange --------------------------------------------
+    def peer_info(self) -> bytes:
+        info = capi.PeerInfo()
+        capi.check(capi.lib().bivmoe_ep_peer_info(self._h, C.byref(info)), self._h)
+        return bytes(info)
+
+    def peer_attach(self, infos):
+        arr = (capi.PeerInfo * self.world)(*[capi.PeerInfo.from_buffer_copy(b) for b in infos])
+        capi.check(capi.lib().bivmoe_ep_peer_attach(self._h, arr), self._h)
+
+    def peer_dispatch(self, h):
+        import torch
+        assert h.is_cuda and h.dtype == torch.float32 and h.is_contiguous()
+        n = h.numel() // self.n_embd
+        self._n = n
+        capi.check(capi.lib().bivmoe_ep_peer_dispatch(self._h, C.c_void_p(h.data_ptr()), n,
+                                                      self._stream()), self._h)
+
+    def peer_experts(self):
+        capi.check(capi.lib().bivmoe_ep_peer_experts(self._h, self._stream()), self._h)
+
+    def peer_combine(self, out, accumulate: bool):
+        import torch
+        torch.cuda.current_stream(self.device).wait_stream(self._side)   # the shared expert is done
+        capi.check(capi.lib().bivmoe_ep_peer_combine(self._h, C.c_void_p(out.data_ptr()), self._n,
+                                                     int(accumulate), self._stream()), self._h)
+
 
 class EpMoe:
     """``Moe`` (moe.py) for a layer whose experts are spread over the ranks of a
     process group; every rank passes its own rows."""
 
     def __init__(self, layer: MoeLayer, max_tokens: int, rank: int, world: int, device: int = 0,
-                 comm=None, max_recv_rows: Optional[int] = None):
+                 comm=None, max_recv_rows: Optional[int] = None, exchange: str = "all_to_all"):
+        """``exchange``: "all_to_all" (the communicator's collectives move the rows) or
+        "peer" (the library's kernels store them into the peers' memory; the ranks are on
+        the GPUs of one node; all ranks construct the object together)."""
+        import torch
+        assert exchange in ("all_to_all", "peer")
         self.steps = DeviceSteps(layer, max_tokens, rank, world, device, max_recv_rows)
         self.comm = comm or TorchComm()
         self.n_embd = layer.n_embd
         self.last_plan: Optional[EpPlan] = None
+        self.exchange = exchange
+        if exchange == "peer" and world > 1:
+            infos = self.comm.all_gather_bytes(self.steps.peer_info(), torch.device("cuda", device))
+            self.steps.peer_attach(infos)
 
     def moe_(self, h, out, accumulate: bool = True):
-        self.last_plan = ep_pass(self.steps, h, out, accumulate, self.comm)
+        if self.exchange == "peer" and self.steps.world > 1:
+            ep_pass_peer(self.steps, h, out, accumulate, self.comm)
+        else:
+            self.last_plan = ep_pass(self.steps, h, out, accumulate, self.comm)
         return out
 
     def begin(self, h):

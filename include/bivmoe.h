@@ -271,6 +271,47 @@ BIVMOE_API int bivmoe_ep_combine(bivmoe_layer* layer, const float* returned_rows
                                  int32_t n, int32_t accumulate, void* stream);
 BIVMOE_API int bivmoe_ep_status(bivmoe_layer* layer, void* stream);
 
+/* The same pass with the exchanges done by the library's own kernels as stores into
+ * the other ranks' memory (NVLink peer access), for ranks on the GPUs of one node.
+ * Every rank owns one block holding a receive buffer, a return buffer, the tags and
+ * the counts, each split in W regions of `max_tokens` rows, one per peer; a rank maps
+ * the blocks of all ranks.  Steps 1-2 become one call whose kernels write each row
+ * into region [home rank] of its owner's receive buffer; steps 3-4 one call whose last
+ * kernel writes each partial sum into region [owner] of the home rank's return
+ * buffer; a region's unused rows count as rows without experts.  No size depends on
+ * another rank's counts, so the host never waits.  The caller's part is two barriers:
+ *
+ *   setup   bivmoe_ep_peer_info on every rank, the W results gathered to every rank (any
+ *           transport), bivmoe_ep_peer_attach.  Ranks may be processes (the block is
+ *           opened through its CUDA IPC handle) or threads of one process (the pointer
+ *           is used as it is, peer access enabled between distinct devices).
+ *   pass    bivmoe_ep_peer_dispatch(h, n)                    home: route, stores to owners
+ *           barrier A (stream-ordered, e.g. a one-element all-reduce)
+ *           bivmoe_ep_shared(h)            [may run beside the next call on another stream]
+ *           bivmoe_ep_peer_experts()                         owner: experts, stores to homes
+ *           barrier B
+ *           bivmoe_ep_peer_combine(out, n, accumulate)       home
+ *
+ * Barrier A orders every rank's stores before the owners' reads; barrier B orders the
+ * returned sums before the combine, and - every rank having finished its experts step -
+ * the receive buffers against the next pass's stores.  All ranks pass the same
+ * max_tokens, and max_recv_rows >= W * max_tokens.  The kernels only store to peers:
+ * none waits on another GPU. */
+typedef struct bivmoe_peer_info {
+    uint8_t ipc_handle[64];   /* cudaIpcMemHandle_t of the rank's block */
+    void* base;               /* the block in the owning process */
+    int64_t pid;              /* the owning process */
+    int64_t bytes;            /* the block's size: equal on all ranks */
+    int32_t device;           /* the owning process's device ordinal */
+    int32_t reserved;
+} bivmoe_peer_info;
+BIVMOE_API int bivmoe_ep_peer_info(bivmoe_layer* layer, bivmoe_peer_info* info);
+BIVMOE_API int bivmoe_ep_peer_attach(bivmoe_layer* layer, const bivmoe_peer_info* all_ranks);
+BIVMOE_API int bivmoe_ep_peer_dispatch(bivmoe_layer* layer, const float* h_dev, int32_t n, void* stream);
+BIVMOE_API int bivmoe_ep_peer_experts(bivmoe_layer* layer, void* stream);
+BIVMOE_API int bivmoe_ep_peer_combine(bivmoe_layer* layer, float* out_dev, int32_t n, int32_t accumulate,
+                                      void* stream);
+
 /* The int8 tensor-pipe peak of the layer's GPU in tera-operations per second (two per
  * multiply-add), measured with back-to-back tcgen05.mma kind::i8 on resident operands
  * (about 10 ms).  A benchmark hook with no reference counterpart: the roofline

@@ -62,8 +62,15 @@ class ThreadComm:
             at += c
         self.sh.barrier.wait()
 
+    def barrier(self, device):
+        # the ranks launch on one stream: the order of the launches is the order of the work
+        self.sh.barrier.wait()
 
-def _run_threads(world, layer, h, max_tokens):
+    def all_gather_bytes(self, blob, device):
+        return self._publish(blob)
+
+
+def _run_threads(world, layer, h, max_tokens, exchange="all_to_all"):
     import torch
     from biv_b200.ep import EpMoe
     n_per = h.shape[0] // world
@@ -74,7 +81,7 @@ def _run_threads(world, layer, h, max_tokens):
     def rank_main(r):
         try:
             torch.cuda.set_device(0)
-            m = EpMoe(layer, max_tokens, r, world, 0, comm=ThreadComm(shared, r))
+            m = EpMoe(layer, max_tokens, r, world, 0, comm=ThreadComm(shared, r), exchange=exchange)
             try:
                 hr = torch.from_numpy(np.ascontiguousarray(h[r * n_per:(r + 1) * n_per])).cuda()
                 for _ in range(2):       # twice: the scratch buffers are reused
@@ -139,6 +146,58 @@ def test_ranks_as_threads_match_the_single_gpu_layer(cfg, world, n):
     assert n <= sum(p.m for p in plans) <= n * min(world, k)
 
 
+@pytest.mark.parametrize("cfg,world,n", [("parity_q8_0", 2, 16), ("decode_q4k", 4, 24),
+                                         ("mtp_stack", 2, 10), ("ep_bf16", 4, 12)])
+def test_peer_store_exchange_ranks_as_threads(cfg, world, n):
+    """The exchange by the library's own kernels (stores into the ranks' blocks): the same
+    result as the all-to-all form, bit for bit - the rows, their order per owner up to the
+    regions' padding, and the order of every sum are the same."""
+    wl = _small(cfg, n)
+    layer, h = wl.layers[0], np.ascontiguousarray(wl.h)
+    got, _ = _run_threads(world, layer, h, max_tokens=n // world, exchange="peer")
+    want, _ = _run_threads(world, layer, h, max_tokens=n // world)
+    assert np.array_equal(got, want)
+    assert rel_err(got, oracle.moe_forward(layer, h)) < TOL
+
+
+def test_peer_store_exchange_with_room_to_spare_and_ragged_ranks():
+    """max_tokens above the rows in use (regions mostly padding), and a rank without rows."""
+    import torch
+    from biv_b200.ep import EpMoe
+    wl = _small("decode_q4k", 12)
+    layer, h = wl.layers[0], np.ascontiguousarray(wl.h)
+    world, cap = 2, 16
+    rows = [h[:12], h[:0]]
+    shared = ThreadComm.Shared(world)
+    outs, errs = [None] * world, [None] * world
+
+    def rank_main(r):
+        try:
+            m = EpMoe(layer, cap, r, world, 0, comm=ThreadComm(shared, r), exchange="peer")
+            try:
+                hr = torch.from_numpy(np.ascontiguousarray(rows[r])).cuda()
+                for _ in range(2):
+                    out = m.moe(hr)
+                m.status()
+                outs[r] = out.cpu().numpy()
+            finally:
+                m.close()
+        except BaseException as e:      # noqa: BLE001
+            errs[r] = e
+            shared.barrier.abort()
+
+    ts = [threading.Thread(target=rank_main, args=(r,)) for r in range(world)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    for e in errs:
+        if e is not None:
+            raise e
+    assert outs[1].shape == (0, layer.n_embd)
+    assert rel_err(outs[0], oracle.moe_forward(layer, h)) < TOL
+
+
 def test_full_size_layer_two_ranks_as_threads():
     """The BF16 configuration at its real shape, 512 rows: groups large and small."""
     wl = W.ep_bf16(n=512)
@@ -195,6 +254,14 @@ def _nccl_worker(rank, world, port, cfg, n, tmp):
         hd = torch.from_numpy(h).cuda(rank)
         out = m.moe(hd)
         m.status()
+        # the exchange by peer stores (blocks opened through CUDA IPC handles): same bits
+        mp_ = EpMoe(layer, n_per, rank, world, rank, exchange="peer")
+        for _ in range(2):
+            outp = mp_.moe(hd)
+        mp_.status()
+        assert torch.equal(outp, out)
+        dist.barrier()      # nobody unmaps a block a peer may still write to
+        mp_.close()
         np.save(os.path.join(tmp, f"out{rank}.npy"), out.cpu().numpy())
         # the same rows as two micro-batches in flight, each with its own layer object and stream
         half = n_per // 2
