@@ -163,7 +163,8 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def time_ep(layer, h_rank, steps, warmup, rank, world, local, in_flight=1, exchange="all_to_all"):
+def time_ep(layer, h_rank, steps, warmup, rank, world, local, in_flight=1, exchange="all_to_all",
+            graph=False):
     """Expert-parallel passes of the layer: this rank's rows in, experts sharded
     n_expert / world per GPU, rows exchanged over NCCL.  Device time of `steps`
     passes, max over ranks; also this rank's output of the last pass.  With
@@ -204,6 +205,17 @@ def time_ep(layer, h_rank, steps, warmup, rank, world, local, in_flight=1, excha
         m.status()
     dist.barrier()
     torch.cuda.synchronize()
+    if peer and graph:      # the pass has no host step: replay it as one graph launch
+        with torch.cuda.stream(streams[0]):
+            g = ms_[0].capture(hs[0], outs[0], accumulate=False)
+
+            def one_step():     # noqa: F811
+                with torch.cuda.stream(streams[0]):
+                    g.replay()
+            for _ in range(3):
+                one_step()
+        dist.barrier()
+        torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(streams[0])
     for _ in range(steps):
@@ -237,7 +249,7 @@ def run_ep_workload(args, wl, rank, world, local):
     sampler = ClockSampler(local)
     sampler.start()
     ms, recv, _ = time_ep(layer, h_rank, args.steps, args.warmup, rank, world, local,
-                          in_flight=args.ep_in_flight, exchange=args.ep_exchange)
+                          in_flight=args.ep_in_flight, exchange=args.ep_exchange, graph=args.ep_graph)
     sampler.stop_flag = True
     sampler.join()
     if rank == 0:
@@ -254,8 +266,11 @@ def run_ep_workload(args, wl, rank, world, local):
                                    f"{layer.n_expert} experts top-{k} + shared expert, ff {ff}, "
                                    f"BF16, seed {wl.seed}",
                        "tokens_per_gpu": n_per, "parallelism": f"ep{world}",
-                       "in_flight": f"{args.ep_in_flight} micro-batch(es) of "
-                                    f"{n_per // max(1, args.ep_in_flight)} rows per GPU",
+                       "exchange": args.ep_exchange,
+                       "graph_replay": bool(args.ep_graph and args.ep_exchange == "peer"),
+                       "in_flight": ("1 pass" if args.ep_exchange == "peer" else
+                                     f"{args.ep_in_flight} micro-batch(es) of "
+                                     f"{n_per // max(1, args.ep_in_flight)} rows per GPU"),
                        "experts_per_gpu": layer.n_expert // world,
                        "l2": "weights and rows of one pass exceed the 126 MB L2, no flush"},
             "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12 / world,
@@ -367,9 +382,12 @@ def main():
                     help="passes in flight: the timed passes rotate over this many streams, layer object "
                          "j on stream j mod streams (must divide --copies; 1: one pass at a time)")
     ap.add_argument("--layers", type=int, default=40, help="layers of the mtp_stack workload")
-    ap.add_argument("--ep-exchange", default="all_to_all", choices=["all_to_all", "peer"],
+    ap.add_argument("--ep-exchange", default="peer", choices=["all_to_all", "peer"],
                     help="expert parallelism: rows moved by NCCL all-to-alls, or by the library's "
                          "kernels storing into the peers' memory")
+    ap.add_argument("--no-ep-graph", dest="ep_graph", action="store_false",
+                    help="with --ep-exchange peer: launch every pass kernel by kernel instead of "
+                         "replaying it as one CUDA graph")
     ap.add_argument("--ep-in-flight", type=int, default=1,
                     help="micro-batches a rank keeps in flight in the expert-parallel workload (two "
                          "measured slower than one at 2 GPUs: 2.65 against 2.50 ms)")
@@ -534,13 +552,18 @@ def main():
     if world > 1 and layer.n_expert % world == 0:
         torch.cuda.set_stream(torch.cuda.default_stream())
         h_rank = np.random.default_rng(1000 + rank).standard_normal((n, layer.n_embd), dtype=np.float32)
-        ep_ms, ep_recv, _ = time_ep(layer, h_rank, min(args.steps, 100), 5, rank, world, local)
+        ep_ms, ep_recv, _ = time_ep(layer, h_rank, min(args.steps, 100), 5, rank, world, local,
+                                    exchange=args.ep_exchange, graph=args.ep_graph)
         ep = {"value": world * n / (ep_ms * 1e-3), "unit": UNIT, "ms_per_step": ep_ms,
               "parallelism": f"ep{world}", "experts_per_gpu": layer.n_expert // world,
-              "tokens_per_gpu": n, "rows_received_rank0": ep_recv,
-              "note": "experts sharded; per pass one count all-gather read by the host, rows and "
-                      "tags out and partial sums back as NCCL all-to-alls; `value` above is the "
-                      "replicated (no-exchange) arrangement"}
+              "tokens_per_gpu": n, "exchange": args.ep_exchange,
+              "graph_replay": bool(args.ep_graph and args.ep_exchange == "peer"),
+              "note": ("experts sharded; rows and tags out and partial sums back as stores of the "
+                       "library's kernels into the peers' memory, two one-element all-reduces per "
+                       "pass as barriers" if args.ep_exchange == "peer" else
+                       "experts sharded; per pass one count all-gather read by the host, rows and "
+                       "tags out and partial sums back as NCCL all-to-alls") +
+                      "; `value` above is the replicated (no-exchange) arrangement"}
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()

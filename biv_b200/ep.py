@@ -294,6 +294,18 @@ class EpMoe:
             self.last_plan = ep_pass(self.steps, h, out, accumulate, self.comm)
         return out
 
+    def capture(self, h, out, accumulate: bool = False):
+        """One pass over fixed tensors as a CUDA graph (``.replay()`` runs it): the peer
+        exchange has no host step, so the whole pass - this rank's kernels, its stores into
+        the peers and the two barrier all-reduces - is one graph launch.  Run the pass
+        eagerly a few times first; all ranks capture and replay together."""
+        import torch
+        assert self.exchange == "peer", "the all-to-all form reads the row counts on the host"
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.moe_(h, out, accumulate)
+        return g
+
     def begin(self, h):
         """``moe_`` in two halves (see ``ep_pass_begin``): enqueue the routing."""
         self._begun = (h, ep_pass_begin(self.steps, h, self.comm))
