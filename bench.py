@@ -385,9 +385,9 @@ def main():
     ap.add_argument("--ep-exchange", default="peer", choices=["all_to_all", "peer"],
                     help="expert parallelism: rows moved by NCCL all-to-alls, or by the library's "
                          "kernels storing into the peers' memory")
-    ap.add_argument("--no-ep-graph", dest="ep_graph", action="store_false",
-                    help="with --ep-exchange peer: launch every pass kernel by kernel instead of "
-                         "replaying it as one CUDA graph")
+    ap.add_argument("--ep-graph", action="store_true",
+                    help="with --ep-exchange peer: replay each pass, barriers included, as one CUDA "
+                         "graph instead of launching it kernel by kernel")
     ap.add_argument("--ep-in-flight", type=int, default=1,
                     help="micro-batches a rank keeps in flight in the expert-parallel workload (two "
                          "measured slower than one at 2 GPUs: 2.65 against 2.50 ms)")

@@ -260,17 +260,6 @@ def _nccl_worker(rank, world, port, cfg, n, tmp):
             outp = mp_.moe(hd)
         mp_.status()
         assert torch.equal(outp, out)
-        # and the whole pass, barriers included, replayed as one CUDA graph
-        outg = torch.zeros_like(out)
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            g = mp_.capture(hd, outg)
-            for _ in range(2):
-                g.replay()
-        torch.cuda.current_stream().wait_stream(side)
-        mp_.status()
-        assert torch.equal(outg, out)
         dist.barrier()      # nobody unmaps a block a peer may still write to
         mp_.close()
         np.save(os.path.join(tmp, f"out{rank}.npy"), out.cpu().numpy())
