@@ -298,7 +298,9 @@ class EpMoe:
         """One pass over fixed tensors as a CUDA graph (``.replay()`` runs it): the peer
         exchange has no host step, so the whole pass - this rank's kernels, its stores into
         the peers and the two barrier all-reduces - is one graph launch.  Run the pass
-        eagerly a few times first; all ranks capture and replay together."""
+        eagerly a few times first, then bring all ranks to the same point (a process-group
+        barrier and a device synchronize) before any of them captures; all ranks capture
+        and replay together."""
         import torch
         assert self.exchange == "peer", "the all-to-all form reads the row counts on the host"
         g = torch.cuda.CUDAGraph()
