@@ -11,7 +11,7 @@ import pytest
 
 import oracle
 from biv_b200 import workloads as wl
-from biv_b200.ep import ep_pass, ep_plan, local_experts
+from biv_b200.ep import TorchComm, ep_pass, ep_pass_peer, ep_plan, local_experts
 
 torch = pytest.importorskip("torch")
 
@@ -96,6 +96,82 @@ class OracleSteps:
                                      tap["shared_out"][t])
         o = out.numpy()
         o[...] = o + res if accumulate else res
+
+
+class OraclePeerSteps(OracleSteps):
+    """The steps of ``ep_pass_peer`` on the CPU: every rank's exchange block is a set of
+    shared-memory tensors that the other rank's process writes into, split in regions of
+    ``cap`` rows per source rank exactly as the library's device blocks are."""
+
+    def __init__(self, layer, rank, world, blocks, cap):
+        super().__init__(layer, rank, world)
+        self.blocks, self.cap = blocks, cap
+
+    def peer_dispatch(self, h):
+        rows, tags, counts = self.route(h)              # grouped by rank, token order inside
+        at = 0
+        for d in range(self.world):
+            c = int(counts[d])
+            assert c <= self.cap
+            blk = self.blocks[d]                        # stores into rank d's block, region [me]
+            blk["rows"][self.rank, :c] = rows[at:at + c]
+            blk["tags"][self.rank, :c] = tags[at:at + c]
+            blk["counts"][self.rank] = c
+            at += c
+        self.base = np.concatenate([[0], np.cumsum(counts.numpy())])
+
+    def peer_experts(self):
+        mine = self.blocks[self.rank]
+        for src in range(self.world):
+            c = int(mine["counts"][src])                # rows past the count have no experts
+            if c:
+                out = self.experts(mine["rows"][src, :c], mine["tags"][src, :c], c)
+                self.blocks[src]["returned"][self.rank, :c] = out   # region [me] of the home's block
+
+    def peer_combine(self, out, accumulate):
+        ret = self.blocks[self.rank]["returned"]
+        packed = torch.cat([ret[d, :int(self.base[d + 1] - self.base[d])] for d in range(self.world)])
+        self.combine(packed, out, accumulate)
+
+
+class GlooComm(TorchComm):
+    def barrier(self, device):
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def _peer_worker(rank, world, port, cfg, rows_per_rank, cap, blocks):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        n_all = sum(rows_per_rank)
+        w = getattr(wl, cfg)(n=n_all, **wl.SMALL)
+        layer = w.layers[0]
+        lo = sum(rows_per_rank[:rank])
+        h = np.ascontiguousarray(w.h[lo:lo + rows_per_rank[rank]])
+        steps = OraclePeerSteps(layer, rank, world, blocks, cap)
+        out = torch.zeros((h.shape[0], layer.n_embd), dtype=torch.float32)
+        for _ in range(2):      # twice: the regions are reused, the second barrier frees them
+            ep_pass_peer(steps, torch.from_numpy(h), out, False, GlooComm())
+        want = oracle.moe_forward(layer, h)
+        np.testing.assert_allclose(out.numpy(), want, rtol=0, atol=4e-7 * float(np.abs(want).max()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("cfg,rows_per_rank", [("parity_q8_0", (12, 12)), ("ep_bf16", (9, 3))])
+def test_two_gloo_ranks_exchange_through_each_others_blocks(cfg, rows_per_rank):
+    import torch.multiprocessing as mp
+    world, cap = 2, 16      # regions larger than any rank's rows: the rest is padding
+    layer = getattr(wl, cfg)(n=4, **wl.SMALL).layers[0]
+    e, k = layer.n_embd, layer.n_expert_used
+    blocks = [{"rows": torch.zeros((world, cap, e)).share_memory_(),
+               "returned": torch.zeros((world, cap, e)).share_memory_(),
+               "tags": torch.zeros((world, cap, 2 * k), dtype=torch.int32).share_memory_(),
+               "counts": torch.zeros((world,), dtype=torch.int32).share_memory_()} for _ in range(world)]
+    mp.spawn(_peer_worker, args=(world, _free_port(), cfg, rows_per_rank, cap, blocks), nprocs=world,
+             join=True)
 
 
 def _worker(rank, world, port, cfg, n_per_rank):
