@@ -670,15 +670,15 @@ int bivmoe_ep_peer_info(bivmoe_layer* L, bivmoe_peer_info* info) {
         lay.tags = 2 * lay.returned;
         lay.counts = lay.tags + ((W * cap * 2 * (size_t)L->k * 4 + 255) & ~(size_t)255);
         lay.bytes = lay.counts + 256;
-        void* p = nullptr;
+        void *p = nullptr, *q = nullptr;
         CU(cudaMalloc(&p, lay.bytes));
         L->allocs.push_back(p);
         CU(cudaMemset(p, 0, lay.bytes));
+        CU(cudaMalloc(&q, W * cap * e * 4));
+        L->allocs.push_back(q);
+        L->peer_out_rows = (float*)q;   // both are there before the block counts as made
         L->peer_block = (uint8_t*)p;
         L->peer_lay = lay;
-        CU(cudaMalloc(&p, W * cap * e * 4));
-        L->allocs.push_back(p);
-        L->peer_out_rows = (float*)p;
         L->ws_bytes += lay.bytes + W * cap * e * 4;
     }
     memset(info, 0, sizeof(*info));
