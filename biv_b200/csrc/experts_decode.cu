@@ -31,7 +31,7 @@ namespace bivmoe {
 
 constexpr int EX_TT = 8;                       // tokens per tile
 constexpr int EX_THREADS = 128;                // four warps
-constexpr uint32_t EX_WAIT_LIMIT = 1u << 16;   // bounded mbarrier wait: tries of up to 20 us each
+constexpr uint32_t EX_WAIT_LIMIT = 1u << 16;   // bounded mbarrier wait: tries that may sleep wait_hint_ns each
 
 enum { MODE_GATEUP = 0, MODE_DOWN = 1 };
 
@@ -919,8 +919,8 @@ cudaError_t launch_experts(const LaunchCfg& c, const DevTiles& gate_up, const De
     A.n = c.n; A.k = c.k; A.n_expert = c.n_expert;
     A.act_rows = ws.act_rows;
     {
-        static int hint = -1;
-        if (hint < 0) { const char* e = getenv("BIVMOE_WAIT_HINT"); hint = e ? atoi(e) : 1000; }
+        // read once; the initialisation of a function-local static is safe between host threads
+        static const int hint = [] { const char* e = getenv("BIVMOE_WAIT_HINT"); return e ? atoi(e) : 1000; }();
         A.wait_hint_ns = (uint32_t)hint;
     }
     const bool fused = c.has_shared && sh_gate_up.ty == gate_up.ty && sh_down.ty == down.ty;
