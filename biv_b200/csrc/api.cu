@@ -93,13 +93,12 @@ struct bivmoe_layer {
     int32_t* ep_rank_pos = nullptr;   // [max_tokens][world] the row's index among the sent rows
     float* ep_ones = nullptr;         // [max_tokens][world] the home combine's weights
     // the peer-store exchange (bivmoe_ep_peer_*): this rank's block, the ranks' blocks as
-    // mapped into this process, the owner's partial sums before they are returned
+    // mapped into this process
     uint8_t* peer_block = nullptr;
     PeerLayout peer_lay{};
     PeerTable peers{};
     bool peers_attached = false;
     std::vector<void*> ipc_opened;
-    float* peer_out_rows = nullptr;   // [world * cap][e]
     bool use_graph = true;
     int launches_per_forward = 0;
     std::string error, device_name;
@@ -670,16 +669,13 @@ int bivmoe_ep_peer_info(bivmoe_layer* L, bivmoe_peer_info* info) {
         lay.tags = 2 * lay.returned;
         lay.counts = lay.tags + ((W * cap * 2 * (size_t)L->k * 4 + 255) & ~(size_t)255);
         lay.bytes = lay.counts + 256;
-        void *p = nullptr, *q = nullptr;
+        void* p = nullptr;
         CU(cudaMalloc(&p, lay.bytes));
         L->allocs.push_back(p);
         CU(cudaMemset(p, 0, lay.bytes));
-        CU(cudaMalloc(&q, W * cap * e * 4));
-        L->allocs.push_back(q);
-        L->peer_out_rows = (float*)q;   // both are there before the block counts as made
         L->peer_block = (uint8_t*)p;
         L->peer_lay = lay;
-        L->ws_bytes += lay.bytes + W * cap * e * 4;
+        L->ws_bytes += lay.bytes;
     }
     memset(info, 0, sizeof(*info));
     cudaIpcMemHandle_t hnd;
@@ -773,8 +769,8 @@ int bivmoe_ep_peer_experts(bivmoe_layer* L, void* stream) {
                        w.act_f != nullptr && type_uses_f32_act(L->gate_up.ty)));
     CU(launch_experts(c, L->gate_up, L->down, none, none, w));
     if (c.prefill_min > 0) CU(launch_experts_prefill(c, L->gate_up, L->down, none, none, w));
-    CU(launch_combine(c, combine_src(w), L->peer_out_rows, 0));
-    CU(launch_ep_peer_return(c, L->peer_out_rows, L->peer_block, L->ep_rank, L->peers, L->peer_lay));
+    // the weighted sum over the local experts, stored where its home rank reads it
+    CU(launch_combine_to_peers(c, combine_src(w), L->peer_block, L->ep_rank, L->peers, L->peer_lay));
     return BIVMOE_OK;
 }
 

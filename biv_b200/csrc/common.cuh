@@ -232,8 +232,10 @@ cudaError_t launch_ep_peer_scatter(const LaunchCfg& c, const float* h, const Wor
                                    const PeerLayout& lay);
 cudaError_t launch_ep_peer_localize(const LaunchCfg& c, const uint8_t* block, const PeerLayout& lay,
                                     int first, const Workspace& ws);
-cudaError_t launch_ep_peer_return(const LaunchCfg& c, const float* out_rows, const uint8_t* block, int me,
-                                  const PeerTable& peers, const PeerLayout& lay);
+// the combine over an owner's receive regions, each row's sum stored into the return
+// buffer of the rank it came from (rowops.cu)
+cudaError_t launch_combine_to_peers(const LaunchCfg& c, const CombineSrc& src, const uint8_t* block, int me,
+                                    const PeerTable& peers, const PeerLayout& lay);
 cudaError_t launch_rms_norm(const LaunchCfg& c, const float* x, const float* w, float eps,
                             float* out);
 cudaError_t launch_repack(const DevTiles& dst, const uint8_t* gguf_rows, int tile_base,

@@ -23,8 +23,9 @@
 // kernels) every rank maps one block of every other rank's memory (NVLink peer access)
 // and the kernels write where the rows are needed: the home rank's scatter kernel puts
 // a row straight into region [home rank] of the owner's receive buffer, the owner's
-// return kernel puts the partial sum straight into region [owner] of the home rank's
-// return buffer.  A region holds `cap` rows (the most a rank can send to one peer), so
+// combine kernel puts the partial sum straight into region [owner] of the home rank's
+// return buffer (that kernel is the owner's combine itself, rowops.cu: the weighted sum
+// over the local experts is stored where the home rank reads it).  A region holds `cap` rows (the most a rank can send to one peer), so
 // no offsets depend on other ranks' counts, the counts travel as peer stores too, and
 // the host never waits; the owner treats a region's unused rows as rows without experts.
 // Two stream-ordered barriers of the caller's communicator per pass order the stores
@@ -235,26 +236,6 @@ cudaError_t launch_ep_peer_localize(const LaunchCfg& c, const uint8_t* block, co
     ep_peer_localize_kernel<<<(total + 255) / 256, 256, 0, c.stream>>>(
         (const int32_t*)(block + lay.tags), (const int32_t*)(block + lay.counts), lay.cap, c.n, c.k, first,
         c.n_expert, ws.ids, ws.weights);
-    count_launch();
-    return cudaGetLastError();
-}
-
-// One block per received row: the row's partial sum goes to region `me`, same slot, of
-// the return buffer of the rank it came from.
-__global__ void __launch_bounds__(EPG_THREADS)
-ep_peer_return_kernel(const float* __restrict__ out_rows, const int32_t* __restrict__ counts, int e, int me,
-                      PeerTable peers, PeerLayout lay) {
-    const int r = blockIdx.x, src = r / lay.cap, sl = r % lay.cap;
-    if (sl >= counts[src]) return;
-    const float4* from = (const float4*)(out_rows + (size_t)r * e);
-    float4* to = (float4*)(peers.base[src] + lay.returned) + ((size_t)me * lay.cap + sl) * (e / 4);
-    for (int i = threadIdx.x; i < e / 4; i += EPG_THREADS) to[i] = from[i];
-}
-
-cudaError_t launch_ep_peer_return(const LaunchCfg& c, const float* out_rows, const uint8_t* block, int me,
-                                  const PeerTable& peers, const PeerLayout& lay) {
-    ep_peer_return_kernel<<<c.n, EPG_THREADS, 0, c.stream>>>(out_rows, (const int32_t*)(block + lay.counts),
-                                                           c.e, me, peers, lay);
     count_launch();
     return cudaGetLastError();
 }

@@ -259,16 +259,30 @@ cudaError_t launch_rms_norm(const LaunchCfg& c, const float* x, const float* w, 
 // fused multiply-add as the reference's axpy.  No atomics: run-to-run identical.
 constexpr int CB_THREADS = 256, CB_MAX_K = 32;
 
+// PEER: the rows are an owner rank's receive regions (expert parallelism by peer stores,
+// ep.cu); row t = region t / cap, slot t % cap; a slot past the region's count has no row,
+// and the sum of a row goes straight into region `me`, same slot, of the return buffer of
+// the rank the row came from - the weighted sum and its way home are one kernel.
+struct PeerDest {
+    PeerTable peers;
+    PeerLayout lay;
+    const int32_t* counts;
+    int me;
+};
+
+template <bool PEER>
 __global__ void __launch_bounds__(CB_THREADS)
 combine_kernel(const int32_t* __restrict__ ids, const float* __restrict__ weights,
                const float* __restrict__ routed_rows, const int32_t* __restrict__ routed_pos,
                const float* __restrict__ shared_rows, const float* __restrict__ logits,
-               float* __restrict__ out, int n, int k, int e, int n_expert, int has_shared, int accumulate) {
+               float* __restrict__ out, int n, int k, int e, int n_expert, int has_shared, int accumulate,
+               PeerDest pd) {
     __shared__ int s_pos[CB_MAX_K];
     __shared__ float s_w[CB_MAX_K];
     __shared__ float s_gate;
     __shared__ int s_valid;
     const int t = blockIdx.x;
+    if (PEER && t % pd.lay.cap >= pd.counts[t / pd.lay.cap]) return;   // the whole block
     if (threadIdx.x == 0) s_valid = 0;
     __syncthreads();
     if (threadIdx.x < k) {
@@ -308,6 +322,9 @@ combine_kernel(const int32_t* __restrict__ ids, const float* __restrict__ weight
         acc.z = fmaf(w, y.z, acc.z); acc.w = fmaf(w, y.w, acc.w);
     }
     float4* o = (float4*)(out + (size_t)t * e + c4 * 4);
+    if (PEER)
+        o = (float4*)(pd.peers.base[t / pd.lay.cap] + pd.lay.returned) +
+            ((size_t)pd.me * pd.lay.cap + t % pd.lay.cap) * (e / 4) + c4;
     if (accumulate) {
         float4 r = *o;
         acc.x += r.x; acc.y += r.y; acc.z += r.z; acc.w += r.w;
@@ -318,9 +335,22 @@ combine_kernel(const int32_t* __restrict__ ids, const float* __restrict__ weight
 cudaError_t launch_combine(const LaunchCfg& c, const CombineSrc& src, float* out, int accumulate) {
     if (c.k > CB_MAX_K || c.e % 4) return cudaErrorInvalidValue;
     dim3 grid(c.n, (c.e / 4 + CB_THREADS - 1) / CB_THREADS);
-    combine_kernel<<<grid, CB_THREADS, 0, c.stream>>>(src.ids, src.weights, src.routed_rows, src.routed_pos,
-                                                      src.shared_rows, src.logits, out, c.n, c.k, c.e,
-                                                      c.n_expert, c.has_shared, accumulate);
+    combine_kernel<false><<<grid, CB_THREADS, 0, c.stream>>>(src.ids, src.weights, src.routed_rows,
+                                                             src.routed_pos, src.shared_rows, src.logits, out,
+                                                             c.n, c.k, c.e, c.n_expert, c.has_shared,
+                                                             accumulate, PeerDest{});
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_combine_to_peers(const LaunchCfg& c, const CombineSrc& src, const uint8_t* block, int me,
+                                    const PeerTable& peers, const PeerLayout& lay) {
+    if (c.k > CB_MAX_K || c.e % 4) return cudaErrorInvalidValue;
+    dim3 grid(c.n, (c.e / 4 + CB_THREADS - 1) / CB_THREADS);
+    const PeerDest pd{peers, lay, (const int32_t*)(block + lay.counts), me};
+    combine_kernel<true><<<grid, CB_THREADS, 0, c.stream>>>(src.ids, src.weights, src.routed_rows,
+                                                            src.routed_pos, src.shared_rows, src.logits, nullptr,
+                                                            c.n, c.k, c.e, c.n_expert, c.has_shared, 0, pd);
     count_launch();
     return cudaGetLastError();
 }
