@@ -1009,9 +1009,11 @@ ORC_API int orc_moe_stack(const orc_moe* layers, int n_layers, const float* cons
     return rc;
 }
 
+/* the host's usable cores; every parallel loop here names its thread count, so this
+ * holds under a launcher that sets OMP_NUM_THREADS=1 for its workers */
 ORC_API int orc_max_threads(void) {
 #ifdef _OPENMP
-    return omp_get_max_threads();
+    return omp_get_num_procs();
 #else
     return 1;
 #endif
