@@ -1,7 +1,10 @@
 """Expert parallelism: one process per GPU, experts sharded ``n_expert / W`` per
 rank.  A token's row travels once to every rank that owns one of its experts and
-one partial sum per row comes back (``torch.distributed`` all-to-alls: NCCL over
-NVLink between GPUs; gloo between CPU processes in the tests).
+one partial sum per row comes back.  The rows move either through
+``torch.distributed`` all-to-alls (NCCL over NVLink between GPUs; gloo between CPU
+processes in the tests) or, between the GPUs of one node, as stores of the library's
+own kernels into the other ranks' memory (``EpMoe(exchange="peer")``,
+``ep_pass_peer``): no packing, no counts on the host, no host wait.
 
 The reference has no multi-device path (one ``MTLDevice``,
 engine/src/metal/mod.rs:450-462; the CPU backend loops over the experts in one
