@@ -95,6 +95,21 @@ def test_layer_read_back_from_a_file(tmp_path, cfg, fused):
         g.close()
 
 
+@pytest.mark.parametrize("gate_ty,down_ty", [(W.Q4_0, W.Q4_1), (W.F16, W.F32)])
+def test_the_other_tensor_types_read_back(tmp_path, gate_ty, down_ty):
+    wl = W.typed_layer(gate_ty, down_ty, n=4, **W.SMALL)
+    layer = wl.layers[0]
+    path = tmp_path / "m.gguf"
+    write_gguf(path, layer, block=1, fused=True)
+    g = GgufFile(str(path))
+    try:
+        got = g.moe_layer(1)
+        assert (got.gate.ty, got.down.ty) == (gate_ty, down_ty)
+        np.testing.assert_array_equal(oracle.moe_forward(got, wl.h), oracle.moe_forward(layer, wl.h))
+    finally:
+        g.close()
+
+
 def test_broken_files_are_refused(tmp_path):
     wl = W.parity_q8_0(n=2, **W.SMALL)
     path = tmp_path / "m.gguf"

@@ -142,3 +142,24 @@ def test_route_picks_and_weighs():
         assert abs(float(wi) - p / total) < 1e-6
     ids, w = oracle.route(l, 1)
     assert ids.tolist() == [0] and w.tolist() == [1.0]
+
+
+def test_q4_generators_round_trip_through_the_reference_layouts():
+    """The build's own Q4_0 / Q4_1 / F16 weight generators against the oracle's statement of
+    the reference's dequantisation (engine/src/quant.rs:174-192): a value comes back within
+    half a quantisation step of what went in."""
+    rng = np.random.default_rng(11)
+    w = (rng.standard_normal((3, 256), dtype=np.float32) * np.float32(0.02))
+    for ty, with_min in ((W.Q4_0, False), (W.Q4_1, True)):
+        rows = W.quantize_q4(w, with_min)
+        assert rows.shape == (3, W.row_size(ty, 256))
+        for r in range(3):
+            back = oracle.dequantize_row(ty, rows[r], 256)
+            blk = w[r].reshape(-1, 32)
+            step = ((blk.max(1) - blk.min(1)) / 15 if with_min else np.abs(blk).max(1) / 7)
+            err = np.abs(back.reshape(-1, 32) - blk).max(1)
+            # Q4_0 has no code for +8 steps: the block's positive extreme may clip by one step
+            assert (err <= step * (0.51 if with_min else 1.01) + 1e-4 * step).all(), (ty, err / step)
+    st = W.make_weights(rng, W.F16, 1, 2, 256)
+    back = oracle.dequantize_row(W.F16, st.expert(0)[:512], 256)
+    assert np.array_equal(back, st.expert(0)[:512].view(np.float16).astype(np.float32))
