@@ -28,7 +28,8 @@ SYMBOLS = ["bivmoe_create", "bivmoe_destroy", "bivmoe_forward", "bivmoe_forward_
            "bivmoe_ep_experts", "bivmoe_ep_combine", "bivmoe_ep_status", "bivmoe_forward_host_async",
            "bivmoe_host_wait", "bivmoe_int8_peak", "bivmoe_dense_create", "bivmoe_ep_peer_info",
            "bivmoe_ep_peer_attach", "bivmoe_ep_peer_dispatch", "bivmoe_ep_peer_experts",
-           "bivmoe_ep_peer_combine"]
+           "bivmoe_ep_peer_combine", "bivmoe_status", "bivmoe_last_oom_bytes", "bivmoe_ep_peer_signal",
+           "bivmoe_ep_peer_wait", "bivmoe_ep_peer_barrier", "bivmoe_ep_peer_wait_limit"]
 
 
 class BivMoeError(RuntimeError):
@@ -101,6 +102,12 @@ def lib():
         L.bivmoe_ep_peer_dispatch.argtypes = [vp, vp, i32, vp]
         L.bivmoe_ep_peer_experts.argtypes = [vp, vp]
         L.bivmoe_ep_peer_combine.argtypes = [vp, vp, i32, i32, vp]
+        L.bivmoe_status.argtypes = [vp, vp]
+        L.bivmoe_last_oom_bytes.restype = C.c_uint64
+        L.bivmoe_ep_peer_signal.argtypes = [vp, vp]
+        L.bivmoe_ep_peer_wait.argtypes = [vp, vp]
+        L.bivmoe_ep_peer_barrier.argtypes = [vp, vp]
+        L.bivmoe_ep_peer_wait_limit.argtypes = [vp, C.c_uint64]
         L.bivmoe_numerics.argtypes = [vp, C.c_char_p, C.c_size_t]
         L.bivmoe_memory.argtypes = [vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
         L.bivmoe_launch_count.restype = C.c_uint64

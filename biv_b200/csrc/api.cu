@@ -20,6 +20,14 @@ static std::atomic<uint64_t> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
 static thread_local std::string g_error;
+static thread_local uint64_t g_oom_bytes = 0;   // size of the device allocation that failed last
+
+// cudaMalloc that remembers the size of a failed request (Error::OutOfMemory{bytes})
+static cudaError_t dev_alloc(void** p, size_t bytes) {
+    const cudaError_t e = cudaMalloc(p, bytes);
+    if (e == cudaErrorMemoryAllocation) g_oom_bytes = bytes;
+    return e;
+}
 
 static int set_err(std::string* dst, int code, const char* fmt, ...) {
     char buf[512];
@@ -98,6 +106,7 @@ struct bivmoe_layer {
     PeerLayout peer_lay{};
     PeerTable peers{};
     bool peers_attached = false;
+    unsigned long long barrier_limit_ns = 2000000000ull;   // how long bivmoe_ep_peer_wait waits
     std::vector<void*> ipc_opened;
     bool use_graph = true;
     int launches_per_forward = 0;
@@ -149,6 +158,7 @@ static void layout_one(bivmoe_layer* L, Arena& a, Workspace& w, size_t N, size_t
     w.mid_t = a.take<uint8_t>(qmid ? (mid / 256) * (R / 8) * kActTileBytes : 0);
     w.pair_out = a.take<float>(R * e);
     w.h_norm = a.take<float>(N * e);
+    w.row_scale = a.take<float>(N);
 }
 
 static void layout_workspace(bivmoe_layer* L, Arena& a) {
@@ -174,22 +184,6 @@ static void layout_workspace(bivmoe_layer* L, Arena& a) {
                                                                  : BIVMOE_ERR_CUDA,       \
                            "%s: %s", #call, cudaGetErrorString(e_));                      \
     } while (0)
-
-// Makes the layer's device current for the duration of an entry point and puts the
-// caller's back afterwards (a caller with several GPUs in one process need not switch).
-struct DeviceScope {
-    int prev = -1;
-    bool switched = false;
-    explicit DeviceScope(int device) {
-        if (cudaGetDevice(&prev) == cudaSuccess && prev != device)
-            switched = cudaSetDevice(device) == cudaSuccess;
-    }
-    ~DeviceScope() {
-        if (switched) cudaSetDevice(prev);
-    }
-    DeviceScope(const DeviceScope&) = delete;
-    DeviceScope& operator=(const DeviceScope&) = delete;
-};
 
 static int check_stack(std::string* errp, const char* name, const bivmoe_experts& s, int64_t cols,
                        int64_t rows, int64_t n, bool is_down) {
@@ -220,13 +214,13 @@ static int upload_tiles(bivmoe_layer* L, std::string* errp, const bivmoe_experts
     out->expert_bytes = (int64_t)out->chunks * out->nslices * kChunkRows * g.sl;
     const size_t dev_bytes = (size_t)(a->n * out->expert_bytes);
     void* p = nullptr;
-    CU(cudaMalloc(&p, dev_bytes));
+    CU(dev_alloc(&p, dev_bytes));
     L->allocs.push_back(p);
     L->weight_bytes += dev_bytes;
     out->data = (uint8_t*)p;
     if (a->ggml_type == BIVMOE_Q6_K) {
         const size_t sb = (size_t)a->n * out->chunks * kChunkRows * out->nslices * 2;
-        CU(cudaMalloc(&p, sb));
+        CU(dev_alloc(&p, sb));
         L->allocs.push_back(p);
         L->weight_bytes += sb;
         out->side = (uint16_t*)p;
@@ -238,7 +232,7 @@ static int upload_tiles(bivmoe_layer* L, std::string* errp, const bivmoe_experts
         const int64_t mat = s->rows * gguf_row_bytes(s->ggml_type, s->cols);
         const int64_t stride = s->stride_bytes ? s->stride_bytes : mat;
         void* staging = nullptr;
-        CU(cudaMalloc(&staging, (size_t)(s->n * mat)));
+        CU(dev_alloc(&staging, (size_t)(s->n * mat)));
         cudaError_t e1 = cudaMemcpy2D(staging, (size_t)mat, (const uint8_t*)s->data + s->offset_bytes,
                                       (size_t)stride, (size_t)mat, (size_t)s->n, cudaMemcpyHostToDevice);
         if (e1 == cudaSuccess) e1 = launch_repack(*out, (const uint8_t*)staging, 2 * i, 0);
@@ -271,10 +265,11 @@ const char* bivmoe_last_error(const bivmoe_layer* layer) {
     return layer ? layer->error.c_str() : g_error.c_str();
 }
 uint64_t bivmoe_launch_count(void) { return g_launches.load(); }
+uint64_t bivmoe_last_oom_bytes(void) { return g_oom_bytes; }
 
 void bivmoe_destroy(bivmoe_layer* L) {
     if (!L) return;
-    cudaSetDevice(L->device);
+    DeviceScope on_device(L->device);
     if (L->graph.exec) cudaGraphExecDestroy(L->graph.exec);
     if (L->host_graph.exec) cudaGraphExecDestroy(L->host_graph.exec);
     if (L->status_host) cudaFreeHost(L->status_host);
@@ -323,7 +318,12 @@ static int create_impl(const bivmoe_desc* d, int ep_rank, int ep_world, int max_
         if (d->sh_gate.ggml_type != d->sh_up.ggml_type)
             return set_err(errp, BIVMOE_ERR_UNSUPPORTED, "shared gate and up of different types");
     }
-    CU(cudaSetDevice(d->device));
+    DeviceScope on_device(d->device);   // the caller's device is current again on return
+    {
+        int cur = -1;
+        CU(cudaGetDevice(&cur));
+        if (cur != d->device) CU(cudaSetDevice(d->device));   // reports an invalid ordinal
+    }
     cudaDeviceProp prop;
     CU(cudaGetDeviceProperties(&prop, d->device));
     if (prop.major != 10)
@@ -353,7 +353,7 @@ static int create_impl(const bivmoe_desc* d, int ep_rank, int ep_world, int max_
     };
     cudaError_t ce;
     const size_t rbytes = (size_t)(L->n_expert + 1) * L->e * sizeof(float);
-    if ((ce = cudaMalloc((void**)&L->router, rbytes)) != cudaSuccess) return cu_fail(ce, "router");
+    if ((ce = dev_alloc((void**)&L->router, rbytes)) != cudaSuccess) return cu_fail(ce, "router");
     L->allocs.push_back(L->router);
     L->weight_bytes += rbytes;
     if ((ce = cudaMemset(L->router, 0, rbytes)) != cudaSuccess) return cu_fail(ce, "router");
@@ -374,7 +374,7 @@ static int create_impl(const bivmoe_desc* d, int ep_rank, int ep_world, int max_
     Arena probe;
     layout_workspace(L, probe);
     L->ws_bytes = probe.off;
-    if ((ce = cudaMalloc((void**)&L->ws_mem, L->ws_bytes)) != cudaSuccess) {
+    if ((ce = dev_alloc((void**)&L->ws_mem, L->ws_bytes)) != cudaSuccess) {
         set_err(errp, BIVMOE_ERR_OOM, "workspace of %zu bytes: %s", L->ws_bytes, cudaGetErrorString(ce));
         return fail(BIVMOE_ERR_OOM);
     }
@@ -425,9 +425,9 @@ int bivmoe_ep_create(const bivmoe_desc* d, int32_t ep_rank, int32_t ep_world, in
 int bivmoe_set_post_norm(bivmoe_layer* L, const float* w, float eps) {
     if (!L || !w) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or weights");
     std::string* errp = &L->error;
-    CU(cudaSetDevice(L->device));
+    DeviceScope on_device(L->device);
     if (!L->post_norm) {
-        CU(cudaMalloc((void**)&L->post_norm, (size_t)L->e * 4));
+        CU(dev_alloc((void**)&L->post_norm, (size_t)L->e * 4));
         L->allocs.push_back(L->post_norm);
         L->weight_bytes += (size_t)L->e * 4;
     }
@@ -436,8 +436,10 @@ int bivmoe_set_post_norm(bivmoe_layer* L, const float* w, float eps) {
     return BIVMOE_OK;
 }
 
+// `norm`: `h` holds the residual rows and the router and dispatch kernels apply the
+// layer's rms_norm themselves (bivmoe_forward_stack)
 static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int accumulate,
-                        cudaStream_t stream, cudaEvent_t* ev = nullptr) {
+                        cudaStream_t stream, cudaEvent_t* ev = nullptr, const RowNorm* norm = nullptr) {
     std::string* errp = &L->error;
     if (n < 0 || n > L->max_tokens)
         return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens = %d", n, L->max_tokens);
@@ -452,13 +454,13 @@ static int forward_impl(bivmoe_layer* L, const float* h, float* out, int n, int 
     c.prefill_min = L->prefill_min;
     c.prefill_tile = L->prefill_tile;
     mark(c, EV_START);
-    CU(launch_router(c, L->router, h, L->ws));
+    CU(launch_router(c, L->router, h, L->ws, norm));
     mark(c, EV_ROUTER);
     CU(launch_route_topk(c, L->ws));
     mark(c, EV_TOPK);
     CU(launch_sort(c, L->ws));
     mark(c, EV_SORT);
-    CU(launch_dispatch(c, h, L->ws, L->ws.act_t != nullptr, L->ws.act_f != nullptr));
+    CU(launch_dispatch(c, h, L->ws, L->ws.act_t != nullptr, L->ws.act_f != nullptr, norm));
     mark(c, EV_QUANT);
     CU(launch_experts(c, L->gate_up, L->down, L->sh_gate_up, L->sh_down, L->ws));
     if (c.prefill_min > 0)
@@ -668,9 +670,10 @@ int bivmoe_ep_peer_info(bivmoe_layer* L, bivmoe_peer_info* info) {
         lay.returned = W * cap * e * 4;
         lay.tags = 2 * lay.returned;
         lay.counts = lay.tags + ((W * cap * 2 * (size_t)L->k * 4 + 255) & ~(size_t)255);
-        lay.bytes = lay.counts + 256;
+        lay.flags = lay.counts + 256;
+        lay.bytes = lay.flags + 1024;
         void* p = nullptr;
-        CU(cudaMalloc(&p, lay.bytes));
+        CU(dev_alloc(&p, lay.bytes));
         L->allocs.push_back(p);
         CU(cudaMemset(p, 0, lay.bytes));
         L->peer_block = (uint8_t*)p;
@@ -780,22 +783,60 @@ int bivmoe_ep_peer_combine(bivmoe_layer* L, float* out_dev, int32_t n, int32_t a
                              stream);
 }
 
-int bivmoe_ep_status(bivmoe_layer* L, void* stream) {
-    if (int rc = ep_check(L, "bivmoe_ep_status")) return rc;
+int bivmoe_ep_peer_signal(bivmoe_layer* L, void* stream) {
+    if (int rc = peer_check(L, "bivmoe_ep_peer_signal", true)) return rc;
+    DeviceScope on_device(L->device);
+    std::string* errp = &L->error;
+    CU(launch_ep_peer_signal((cudaStream_t)stream, L->peer_block, L->ep_rank, L->ep_world, L->peers,
+                             L->peer_lay));
+    return BIVMOE_OK;
+}
+
+int bivmoe_ep_peer_wait(bivmoe_layer* L, void* stream) {
+    if (int rc = peer_check(L, "bivmoe_ep_peer_wait", true)) return rc;
+    DeviceScope on_device(L->device);
+    std::string* errp = &L->error;
+    CU(launch_ep_peer_wait((cudaStream_t)stream, L->peer_block, L->ep_world, L->peer_lay,
+                           L->barrier_limit_ns, L->ws.status));
+    return BIVMOE_OK;
+}
+
+int bivmoe_ep_peer_barrier(bivmoe_layer* L, void* stream) {
+    if (int rc = bivmoe_ep_peer_signal(L, stream)) return rc;
+    return bivmoe_ep_peer_wait(L, stream);
+}
+
+int bivmoe_ep_peer_wait_limit(bivmoe_layer* L, uint64_t microseconds) {
+    if (int rc = ep_check(L, "bivmoe_ep_peer_wait_limit")) return rc;
+    if (microseconds == 0 || microseconds > 60000000ull)
+        return set_err(&L->error, BIVMOE_ERR_ARGUMENT, "a wait limit of %llu us is outside 1 us .. 60 s",
+                       (unsigned long long)microseconds);
+    L->barrier_limit_ns = microseconds * 1000ull;
+    return BIVMOE_OK;
+}
+
+int bivmoe_status(bivmoe_layer* L, void* stream) {
+    if (!L) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer");
     DeviceScope on_device(L->device);
     std::string* errp = &L->error;
     cudaStream_t s = (cudaStream_t)stream;
+    const bool ep = L->ep_world > 1;
     int32_t st[2] = {0, 0};
     CU(cudaMemcpyAsync(&st[0], L->ws.status, 4, cudaMemcpyDeviceToHost, s));
-    CU(cudaMemcpyAsync(&st[1], L->ws_owner.status, 4, cudaMemcpyDeviceToHost, s));
+    if (ep) CU(cudaMemcpyAsync(&st[1], L->ws_owner.status, 4, cudaMemcpyDeviceToHost, s));
     CU(cudaStreamSynchronize(s));
     if (st[0] || st[1]) {
         cudaMemsetAsync(L->ws.status, 0, 16, s);
-        cudaMemsetAsync(L->ws_owner.status, 0, 16, s);
+        if (ep) cudaMemsetAsync(L->ws_owner.status, 0, 16, s);
         const int code = st[0] ? st[0] : st[1];
         return set_err(errp, code, "a device-side bounded wait gave up (status %d)", code);
     }
     return BIVMOE_OK;
+}
+
+int bivmoe_ep_status(bivmoe_layer* L, void* stream) {
+    if (int rc = ep_check(L, "bivmoe_ep_status")) return rc;
+    return bivmoe_status(L, stream);
 }
 
 int bivmoe_forward_profile(bivmoe_layer* L, const float* h_dev, float* out_dev, int32_t n,
@@ -850,9 +891,9 @@ int bivmoe_forward_host_async(bivmoe_layer* L, const float* h_host, float* out_h
     DeviceScope on_device(L->device);
     if (!L->host_in) {
         const size_t bytes = (size_t)L->max_tokens * L->e * 4;
-        CU(cudaMalloc((void**)&L->host_in, bytes));
+        CU(dev_alloc((void**)&L->host_in, bytes));
         L->allocs.push_back(L->host_in);
-        CU(cudaMalloc((void**)&L->host_out, bytes));
+        CU(dev_alloc((void**)&L->host_out, bytes));
         L->allocs.push_back(L->host_out);
         L->ws_bytes += 2 * bytes;
         CU(cudaHostAlloc((void**)&L->status_host, 16, cudaHostAllocDefault));
@@ -932,8 +973,16 @@ int bivmoe_forward_stack(bivmoe_layer* const* layers, int32_t n_layers, float* x
         DeviceScope on_device(L->device);
         LaunchCfg c{(cudaStream_t)stream, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh,
                     L->has_shared ? 1 : 0, L->sm_count};
-        CU(launch_rms_norm(c, x_dev, L->post_norm, L->norm_eps, L->ws.h_norm));
-        int rc = forward_impl(L, L->ws.h_norm, x_dev, n, 1, (cudaStream_t)stream);
+        int rc;
+        if (router_fuses_norm(n, L->e)) {
+            // the router kernel normalises the rows it stages and publishes the scales; the
+            // dispatch kernel applies them on the fly: the normed rows never reach HBM
+            const RowNorm norm{L->post_norm, L->norm_eps, L->ws.row_scale};
+            rc = forward_impl(L, x_dev, x_dev, n, 1, (cudaStream_t)stream, nullptr, &norm);
+        } else {
+            CU(launch_rms_norm(c, x_dev, L->post_norm, L->norm_eps, L->ws.h_norm));
+            rc = forward_impl(L, L->ws.h_norm, x_dev, n, 1, (cudaStream_t)stream);
+        }
         if (rc) return rc;
     }
     return BIVMOE_OK;

@@ -156,7 +156,16 @@ struct Workspace {
     float* mid;          // silu(gate)*up by position, slice-major f32 [ff/64][R][64]
     uint8_t* mid_t;      // its Q8 records, [ff/256][R/8] tiles (quantised down types)
     float* pair_out;     // [P + n][e], by position
-    float* h_norm;       // [n][e] rms-normed rows (forward_stack)
+    float* h_norm;       // [n][e] rms-normed rows (forward_stack with many tokens)
+    float* row_scale;    // [n] rms_norm scales of the rows (forward_stack, norm fused into the router)
+};
+
+// The rms_norm that precedes the layer (ops.rs:136-149), applied on the fly by the
+// kernels that read the rows: h[t][i] = x[t][i] * (scale[t] * w[i]).
+struct RowNorm {
+    const float* w;       // [e] post_norm weights
+    float eps;
+    const float* scale;   // [n] written by the router kernel, read by the dispatch kernels
 };
 
 struct LaunchCfg {
@@ -188,12 +197,15 @@ inline cudaError_t ensure_dynamic_smem(K kernel, int bytes, std::atomic<uint64_t
 }
 
 // kernels (one translation unit each)
+// `norm`: the rows are the residual x and the router kernel normalises them itself
+// (only where router_fuses_norm says so; it also fills ws.row_scale)
 cudaError_t launch_router(const LaunchCfg& c, const float* router_dev /*[n_expert+1][e]*/,
-                          const float* h, const Workspace& ws);
+                          const float* h, const Workspace& ws, const RowNorm* norm = nullptr);
+bool router_fuses_norm(int n, int e);
 cudaError_t launch_route_topk(const LaunchCfg& c, const Workspace& ws);
 cudaError_t launch_sort(const LaunchCfg& c, const Workspace& ws);
 cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace& ws, bool quant,
-                            bool f32);
+                            bool f32, const RowNorm* norm = nullptr);
 cudaError_t launch_experts(const LaunchCfg& c, const DevTiles& gate_up, const DevTiles& down,
                            const DevTiles& sh_gate_up, const DevTiles& sh_down, const Workspace& ws);
 // What the combine sums for token t: for each of its k slots j with ids[t*k+j] >= 0, in
@@ -225,13 +237,22 @@ struct PeerLayout {
     size_t rows, returned, tags, counts, bytes;   // byte offsets: [W][cap][e] f32 received rows,
                                                    // [W][cap][e] f32 returned sums, [W][cap][2k] i32
                                                    // tags, [W] i32 counts; the block's size
+    size_t flags;                                  // [W] u32 barrier epochs, word r written by rank r;
+                                                   // then (64 words on) this rank's own two counters:
+                                                   // barriers signalled, barriers waited for
 };
+constexpr int kPeerFlagCounters = 64;              // word offset of the two counters after `flags`
 cudaError_t launch_ep_peer_scatter(const LaunchCfg& c, const float* h, const Workspace& ws, int world,
                                    int me, int n_local, int32_t* slot, int32_t* counts,
                                    int32_t* rank_ids, int32_t* rank_pos, const PeerTable& peers,
                                    const PeerLayout& lay);
 cudaError_t launch_ep_peer_localize(const LaunchCfg& c, const uint8_t* block, const PeerLayout& lay,
                                     int first, const Workspace& ws);
+// the two halves of a stream-ordered barrier over the ranks' blocks (ep.cu)
+cudaError_t launch_ep_peer_signal(cudaStream_t stream, uint8_t* block, int me, int world,
+                                  const PeerTable& peers, const PeerLayout& lay);
+cudaError_t launch_ep_peer_wait(cudaStream_t stream, uint8_t* block, int world, const PeerLayout& lay,
+                                unsigned long long limit_ns, int32_t* status);
 // the combine over an owner's receive regions, each row's sum stored into the return
 // buffer of the rank it came from (rowops.cu)
 cudaError_t launch_combine_to_peers(const LaunchCfg& c, const CombineSrc& src, const uint8_t* block, int me,
@@ -254,6 +275,22 @@ cudaError_t launch_experts_prefill(const LaunchCfg& c, const DevTiles& gate_up, 
                                    const Workspace& ws);
 
 void count_launch(int n = 1);
+
+// Makes a device current for the duration of an entry point and puts the caller's
+// back afterwards (a caller with several GPUs in one process need not switch).
+struct DeviceScope {
+    int prev = -1;
+    bool switched = false;
+    explicit DeviceScope(int device) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != device)
+            switched = cudaSetDevice(device) == cudaSuccess;
+    }
+    ~DeviceScope() {
+        if (switched) cudaSetDevice(prev);
+    }
+    DeviceScope(const DeviceScope&) = delete;
+    DeviceScope& operator=(const DeviceScope&) = delete;
+};
 
 // what the routing step needs to know about a layer (filled by api.cu)
 struct RouteView {

@@ -240,4 +240,77 @@ cudaError_t launch_ep_peer_localize(const LaunchCfg& c, const uint8_t* block, co
     return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------
+// A stream-ordered barrier over the ranks' blocks, in two halves.  Barrier number e
+// (every rank runs the same sequence of barriers, so the numbers agree without being
+// exchanged): a rank SIGNALS by storing e into word [its rank] of every rank's flag
+// array - a peer store like the rows' - and WAITS until every word of its own array
+// has reached e.  Kernels earlier in the signalling stream have completed, so their
+// peer stores are in place before the flag is; the waiting side reads the flags with
+// acquire loads from its own memory.  The wait is bounded by a time limit, after which
+// the kernel records BIVMOE_ERR_TIMEOUT in the layer's status word and returns: a rank
+// that never arrives costs its peers the limit, not the GPU.  The barrier numbers live
+// in device memory (the two counters behind the flags), so a captured graph replays
+// the barrier with fresh numbers.
+__device__ __forceinline__ unsigned long long ep_now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__global__ void ep_peer_signal_kernel(uint8_t* block, PeerTable peers, PeerLayout lay, int me, int world) {
+    __shared__ uint32_t s_epoch;
+    uint32_t* ctr = (uint32_t*)(block + lay.flags) + kPeerFlagCounters;
+    if (threadIdx.x == 0) {
+        s_epoch = ctr[0] + 1;   // only this rank's own kernels touch the counters, in stream order
+        ctr[0] = s_epoch;
+    }
+    __syncwarp();
+    __threadfence_system();
+    if ((int)threadIdx.x < world) {
+        uint32_t* flag = (uint32_t*)(peers.base[threadIdx.x] + lay.flags) + me;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(s_epoch) : "memory");
+    }
+}
+
+__global__ void ep_peer_wait_kernel(uint8_t* block, PeerLayout lay, int world, unsigned long long limit_ns,
+                                    int32_t* status) {
+    uint32_t* flags = (uint32_t*)(block + lay.flags);
+    uint32_t* ctr = flags + kPeerFlagCounters;
+    const uint32_t epoch = ctr[1] + 1;
+    bool late = false;
+    if ((int)threadIdx.x < world) {
+        const unsigned long long t0 = ep_now_ns();
+        while (true) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
+            if ((int32_t)(v - epoch) >= 0) break;
+            if (ep_now_ns() - t0 > limit_ns) { late = true; break; }
+            __nanosleep(200);
+        }
+    }
+    late = __any_sync(0xffffffffu, late);
+    if (threadIdx.x == 0) {
+        ctr[1] = epoch;   // the barrier is spent either way: the sequence stays in step
+        if (late) atomicExch(status, BIVMOE_ERR_TIMEOUT);
+    }
+    __threadfence_system();
+}
+
+cudaError_t launch_ep_peer_signal(cudaStream_t stream, uint8_t* block, int me, int world,
+                                  const PeerTable& peers, const PeerLayout& lay) {
+    if (world > 32) return cudaErrorInvalidValue;
+    ep_peer_signal_kernel<<<1, 32, 0, stream>>>(block, peers, lay, me, world);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ep_peer_wait(cudaStream_t stream, uint8_t* block, int world, const PeerLayout& lay,
+                                unsigned long long limit_ns, int32_t* status) {
+    if (world > 32) return cudaErrorInvalidValue;
+    ep_peer_wait_kernel<<<1, 32, 0, stream>>>(block, lay, world, limit_ns, status);
+    count_launch();
+    return cudaGetLastError();
+}
+
 }  // namespace bivmoe

@@ -34,8 +34,9 @@ extern "C" int bivmoe_route_noalloc(bivmoe_layer* layer, const float* h_dev, int
         layer_route_view(layer, nullptr, text);
         return code;
     };
-    if (!h_dev || !ids_dev || !weights_dev) return fail(BIVMOE_ERR_ARGUMENT, "null device pointer");
     if (n < 0) return fail(BIVMOE_ERR_ARGUMENT, "negative token count");
+    if (n == 0) return BIVMOE_OK;   // no rows (their pointers may be null): nothing to do
+    if (!h_dev || !ids_dev || !weights_dev) return fail(BIVMOE_ERR_ARGUMENT, "null device pointer");
     if ((int64_t)n * (v.n_expert + 1) > (int64_t)ROUTE_SCRATCH_FLOATS) {
         snprintf(msg, sizeof msg,
                  "bivmoe_route_noalloc: %d tokens x %d logits exceed the built-in scratch of %d "
@@ -44,10 +45,13 @@ extern "C" int bivmoe_route_noalloc(bivmoe_layer* layer, const float* h_dev, int
         return fail(BIVMOE_ERR_ARGUMENT, msg);
     }
     if (v.device < 0 || v.device >= kMaxDevices) return fail(BIVMOE_ERR_ARGUMENT, "device ordinal");
-    if (n == 0) return BIVMOE_OK;
-    cudaError_t ce = cudaSetDevice(v.device);
-    if (ce == cudaSuccess && !g_route_scratch_addr[v.device]) {
-        // set-up, once per device, with that device current
+    // the layer's device is current inside the call only; the caller's comes back on return
+    DeviceScope on_device(v.device);
+    cudaError_t ce = cudaSuccess;
+    if (!g_route_scratch_addr[v.device]) {
+        // set-up, once per device, with that device current.  Two host threads that make
+        // their first call on one device together both look the address up and store the
+        // same value: harmless, so the cache needs no lock.
         float* p = nullptr;
         ce = cudaGetSymbolAddress((void**)&p, g_route_scratch);
         if (ce == cudaSuccess) g_route_scratch_addr[v.device] = p;

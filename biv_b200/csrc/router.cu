@@ -30,7 +30,8 @@ __device__ __forceinline__ uint32_t rt_smem_u32(const void* p) {
 // round trip instead of one per step of the dot.
 __global__ void __launch_bounds__(RT_THREADS, 1)
 router_logits_kernel(const float* __restrict__ W, const float* __restrict__ h,
-                     float* __restrict__ logits, int n, int e, int n_rows, int* status) {
+                     float* __restrict__ logits, int n, int e, int n_rows, int* status,
+                     const float* __restrict__ norm_w, float norm_eps, float* __restrict__ row_scale) {
     extern __shared__ __align__(128) uint8_t rt_smem[];
     uint64_t* bar = (uint64_t*)rt_smem;
     float* s_w = (float*)(rt_smem + 128);              // [RT_BROWS][e]
@@ -75,6 +76,27 @@ router_logits_kernel(const float* __restrict__ W, const float* __restrict__ h,
     if (!ok) {   // bounded wait gave up: every thread waits on the same barrier
         if (threadIdx.x == 0) atomicExch(status, BIVMOE_ERR_TIMEOUT);
         return;
+    }
+    if (norm_w) {
+        // The rows are the residual x: the layer's input is rms_norm(x) (ops.rs:136-149),
+        // h = x * (scale * w) with scale = 1 / sqrt(dot(x, x) / e + eps), the dot in the
+        // lane order of the reference's AVX2 kernel.  Normalised in place in shared
+        // memory, so the normed rows never travel through HBM; the block of the first
+        // router rows publishes the scales for the kernels that read x after this one.
+        for (int tr = warp; tr < RT_BTOKS; tr += RT_THREADS / 32) {
+            float* xr = s_x + (size_t)tr * e;
+            float ss = 0.0f;
+            for (int i = lane; i < e; i += 32) ss = fmaf(xr[i], xr[i], ss);
+            ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, 8));
+            ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, 16));
+            ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, 4));
+            ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, 2));
+            ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, 1));
+            const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)e), norm_eps)));
+            for (int i = lane; i < e; i += 32) xr[i] = __fmul_rn(xr[i], __fmul_rn(scale, norm_w[i]));
+            if (lane == 0 && blockIdx.x == 0 && bt0 + tr < n) row_scale[bt0 + tr] = scale;
+        }
+        __syncthreads();
     }
     const int r0 = (warp & 1) * RT_ROWS, t0 = (warp >> 1) * RT_TOKS;   // inside the block
     float acc[RT_ROWS][RT_TOKS] = {};
@@ -207,10 +229,19 @@ router_logits_tiled_kernel(const float* __restrict__ W, const float* __restrict_
 
 constexpr int RL_MIN_TOKENS = 256;   // from here on the tiled kernel is the faster one
 
+// whether the kernel that stages whole rows serves this call: few tokens, and 8 router
+// rows + 16 token rows fit in shared memory (n_embd <= 2304)
+static bool router_stages_rows(int n, int e) {
+    return n < RL_MIN_TOKENS && 128 + (RT_BROWS + RT_BTOKS) * (size_t)e * 4 <= 227 * 1024;
+}
+bool router_fuses_norm(int n, int e) { return router_stages_rows(n, e); }
+
 cudaError_t launch_router(const LaunchCfg& c, const float* router_dev, const float* h,
-                          const Workspace& ws) {
+                          const Workspace& ws, const RowNorm* norm) {
     int n_rows = c.n_expert + 1;
-    if (c.n >= RL_MIN_TOKENS && c.e % RL_KC == 0) {
+    if (!router_stages_rows(c.n, c.e)) {
+        // many tokens, or rows too wide to stage whole: K travels in chunks of 128 values
+        if (c.e % RL_KC || norm) return cudaErrorInvalidValue;
         static std::atomic<uint64_t> attr_set{0};
         if (cudaError_t err = ensure_dynamic_smem(router_logits_tiled_kernel, RL_SMEM, attr_set)) return err;
         dim3 grid((n_rows + RL_BROWS - 1) / RL_BROWS, (c.n + RL_BTOKS - 1) / RL_BTOKS);
@@ -220,12 +251,12 @@ cudaError_t launch_router(const LaunchCfg& c, const float* router_dev, const flo
         return cudaGetLastError();
     }
     const int smem = 128 + (RT_BROWS + RT_BTOKS) * c.e * 4;
-    if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
     static std::atomic<uint64_t> attr_set{0};
     if (cudaError_t err = ensure_dynamic_smem(router_logits_kernel, 227 * 1024, attr_set)) return err;
     dim3 grid((n_rows + RT_BROWS - 1) / RT_BROWS, (c.n + RT_BTOKS - 1) / RT_BTOKS);
     router_logits_kernel<<<grid, RT_THREADS, smem, c.stream>>>(router_dev, h, ws.logits, c.n, c.e,
-                                                               n_rows, ws.status);
+                                                               n_rows, ws.status, norm ? norm->w : nullptr,
+                                                               norm ? norm->eps : 0.0f, ws.row_scale);
     count_launch();
     return cudaGetLastError();
 }
@@ -234,7 +265,15 @@ cudaError_t launch_router(const LaunchCfg& c, const float* router_dev, const flo
 // One warp per token: softmax in the reference's order (max, exp, sequential
 // sum, multiply by 1/sum), the k best by (probability descending, expert id
 // ascending), weights p / max(sum of the k in rank order, 2^-14).
+// The order of the probabilities is f32::total_cmp's, as in the reference's sort
+// (model.rs:263): a total order, so a row with NaN or Inf activations - whose
+// probabilities are all NaN - still selects k distinct, valid experts (the first k,
+// all keys being equal) and only that token's weights and output are NaN.
 constexpr int TK_WARPS = 4, TK_MAX_EXPERTS = 1024, TK_MAX_K = 32;
+
+// total_cmp's key: the bits with the magnitude inverted for negative values, compared
+// as signed integers; the mapping is its own inverse
+__device__ __forceinline__ int tk_total_key(int bits) { return bits ^ (int)(((uint32_t)(bits >> 31)) >> 1); }
 
 __global__ void __launch_bounds__(TK_WARPS * 32)
 route_topk_kernel(const float* __restrict__ logits, int32_t* __restrict__ ids,
@@ -246,7 +285,7 @@ route_topk_kernel(const float* __restrict__ logits, int32_t* __restrict__ ids,
     float* p = tk_smem + (size_t)warp * n_expert;
     const float* l = logits + (size_t)t * (n_expert + 1);
     float mx = -INFINITY;
-    for (int i = lane; i < n_expert; i += 32) mx = fmaxf(mx, l[i]);
+    for (int i = lane; i < n_expert; i += 32) mx = fmaxf(mx, l[i]);   // f32::max: a NaN is passed over
 #pragma unroll
     for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     for (int i = lane; i < n_expert; i += 32) p[i] = expf(__fsub_rn(l[i], mx));
@@ -265,32 +304,35 @@ route_topk_kernel(const float* __restrict__ logits, int32_t* __restrict__ ids,
     }
     sum = __shfl_sync(0xffffffffu, sum, 0);
     const float inv = __fdiv_rn(1.0f, sum);
-    for (int i = lane; i < n_expert; i += 32) p[i] = __fmul_rn(p[i], inv);
+    int* key = (int*)p;   // the probabilities are replaced by their keys
+    for (int i = lane; i < n_expert; i += 32) key[i] = tk_total_key(__float_as_int(__fmul_rn(p[i], inv)));
     __syncwarp();
     float sel_p = 0.0f;   // lane j keeps the j-th selection
     int sel_id = 0;
+    uint32_t taken = 0;   // bit m: this lane's entry lane + 32 m is selected already
+    constexpr int NONE = 0x7fffffff;
     for (int j = 0; j < k; j++) {
-        float bp = -1.0f;
-        int bi = 0x7fffffff;
-        for (int i = lane; i < n_expert; i += 32) {
-            float v = p[i];
-            if (v > bp) { bp = v; bi = i; }   // ascending i: the lower id wins ties
+        int bk = 0, bi = NONE;
+        for (int i = lane, m = 0; i < n_expert; i += 32, m++) {
+            if ((taken >> m) & 1u) continue;
+            const int kv = key[i];
+            if (bi == NONE || kv > bk) { bk = kv; bi = i; }   // ascending i: the lower id wins ties
         }
 #pragma unroll
         for (int o = 16; o; o >>= 1) {
-            float op = __shfl_xor_sync(0xffffffffu, bp, o);
-            int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (op > bp || (op == bp && oi < bi)) { bp = op; bi = oi; }
+            const int ok = __shfl_xor_sync(0xffffffffu, bk, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != NONE && (bi == NONE || ok > bk || (ok == bk && oi < bi))) { bk = ok; bi = oi; }
         }
-        if (lane == j) { sel_p = bp; sel_id = bi; }
-        if (lane == 0) p[bi] = -2.0f;         // taken
-        __syncwarp();
+        // k <= n_expert, so some lane always had a candidate and bi is a valid id
+        if (lane == j) { sel_p = __int_as_float(tk_total_key(bk)); sel_id = bi; }
+        if (bi < n_expert && (bi & 31) == lane) taken |= 1u << (bi >> 5);
     }
     float tot = 0.0f;
     for (int j = 0; j < k; j++) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, sel_p, j));
-    tot = fmaxf(tot, 1.0f / 16384.0f);
+    tot = fmaxf(tot, 1.0f / 16384.0f);   // f32::max: a NaN sum gives the floor
     if (lane < k) {
-        ids[(size_t)t * k + lane] = sel_id;
+        ids[(size_t)t * k + lane] = min(sel_id, n_expert - 1);
         weights[(size_t)t * k + lane] = __fdiv_rn(sel_p, tot);
     }
 }

@@ -40,12 +40,15 @@ __device__ __forceinline__ void dispatch_positions(const Workspace& ws, int t, i
 // into two 16-byte units by shuffles, so a position costs two 16-byte stores
 // instead of 32 single bytes.
 __global__ void __launch_bounds__(DP_THREADS)
-dispatch_q8_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int has_shared) {
+dispatch_q8_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int has_shared,
+                   const float* __restrict__ norm_w) {
     __shared__ int s_pos[DP_MAX_K + 1], s_big[DP_MAX_K + 1];
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int R = ws.act_rows;
     dispatch_positions(ws, t, n, k, 0, has_shared, 0, s_pos, s_big);
     const float* x = h + (size_t)t * e;
+    // with norm_w the rows are the residual and h = x * (scale * w), rms_norm on the fly
+    const float nscale = norm_w ? ws.row_scale[t] : 1.0f;
     constexpr int NW = DP_THREADS / 32, U = 4;   // U loads in flight per lane
     // blockIdx.y halves the row between two blocks
     for (int b0 = blockIdx.y * NW * U + warp; b0 < e / 32; b0 += gridDim.y * NW * U) {
@@ -54,6 +57,7 @@ dispatch_q8_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int 
         for (int u = 0; u < U; u++) {
             const int b = b0 + u * NW;
             vv[u] = b < e / 32 ? x[32 * b + lane] : 0.0f;
+            if (norm_w && b < e / 32) vv[u] = __fmul_rn(vv[u], __fmul_rn(nscale, norm_w[32 * b + lane]));
         }
 #pragma unroll
         for (int u = 0; u < U; u++) {
@@ -93,14 +97,22 @@ dispatch_q8_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int 
 // of each bf16 term per position of a group the tcgen05 kernel will take.
 __global__ void __launch_bounds__(DP_THREADS)
 dispatch_f32_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int has_shared,
-                    int prefill_min) {
+                    int prefill_min, const float* __restrict__ norm_w) {
     __shared__ int s_pos[DP_MAX_K + 1], s_big[DP_MAX_K + 1];
     const int t = blockIdx.x;
     const int R = ws.act_rows;
     dispatch_positions(ws, t, n, k, 0, has_shared, ws.act_b ? prefill_min : 0, s_pos, s_big);
     const float* x = h + (size_t)t * e;
+    const float nscale = norm_w ? ws.row_scale[t] : 1.0f;
     for (int i0 = threadIdx.x * 8; i0 < e; i0 += DP_THREADS * 8) {
-        const float4 a = *(const float4*)(x + i0), b = *(const float4*)(x + i0 + 4);
+        float4 a = *(const float4*)(x + i0), b = *(const float4*)(x + i0 + 4);
+        if (norm_w) {   // rms_norm on the fly: h = x * (scale * w)
+            const float4 wa = *(const float4*)(norm_w + i0), wb = *(const float4*)(norm_w + i0 + 4);
+            a.x = __fmul_rn(a.x, __fmul_rn(nscale, wa.x)); a.y = __fmul_rn(a.y, __fmul_rn(nscale, wa.y));
+            a.z = __fmul_rn(a.z, __fmul_rn(nscale, wa.z)); a.w = __fmul_rn(a.w, __fmul_rn(nscale, wa.w));
+            b.x = __fmul_rn(b.x, __fmul_rn(nscale, wb.x)); b.y = __fmul_rn(b.y, __fmul_rn(nscale, wb.y));
+            b.z = __fmul_rn(b.z, __fmul_rn(nscale, wb.z)); b.w = __fmul_rn(b.w, __fmul_rn(nscale, wb.w));
+        }
         const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
         uint32_t hi[4], lo[4];
 #pragma unroll
@@ -201,10 +213,12 @@ dispatch_pos_f32_kernel(const float* __restrict__ h, Workspace ws, int n, int k,
 }
 
 cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace& ws, bool quant,
-                            bool f32) {
+                            bool f32, const RowNorm* norm) {
     if (c.k > DP_MAX_K || c.e % 256) return cudaErrorInvalidValue;
+    if (norm && c.n >= DP_MIN_TOKENS) return cudaErrorInvalidValue;   // the by-position kernel reads normed rows
+    const float* nw = norm ? norm->w : nullptr;
     if (quant) {
-        dispatch_q8_kernel<<<dim3(c.n, 2), DP_THREADS, 0, c.stream>>>(h, ws, c.n, c.k, c.e, c.has_shared);
+        dispatch_q8_kernel<<<dim3(c.n, 2), DP_THREADS, 0, c.stream>>>(h, ws, c.n, c.k, c.e, c.has_shared, nw);
         count_launch();
     }
     if (f32 && c.n >= DP_MIN_TOKENS) {
@@ -216,7 +230,7 @@ cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace&
         count_launch();
     } else if (f32) {
         dispatch_f32_kernel<<<c.n, DP_THREADS, 0, c.stream>>>(h, ws, c.n, c.k, c.e, c.has_shared,
-                                                             c.prefill_min);
+                                                             c.prefill_min, nw);
         count_launch();
     }
     return cudaGetLastError();

@@ -13,7 +13,10 @@
  * names the reference interface it stands in for.
  *
  * Conventions: every function returns a status (0 = ok); nothing aborts,
- * throws across the boundary or traps the device.  A layer handle is not
+ * throws across the boundary or traps the device.  Calls that only enqueue work
+ * on a stream return before it runs: what the device finds out later (a bounded
+ * wait that gave up) is reported by `bivmoe_status`, which waits for the stream
+ * (`bivmoe_host_wait` for the host-buffer calls).  A layer handle is not
  * thread-safe; distinct handles may be driven from distinct host threads.
  * Host pointers passed to `bivmoe_create` stay owned by the caller and may be
  * freed after it returns (the engine's GGUF mmap, src/lib.rs:74-84).
@@ -42,7 +45,8 @@ enum {
     BIVMOE_ERR_UNSUPPORTED = 2, /* a ggml type or shape without a kernel: Error::NoKernel */
     BIVMOE_ERR_OOM = 3,         /* device allocation failed: Error::OutOfMemory{bytes} */
     BIVMOE_ERR_CUDA = 4,        /* a CUDA runtime call failed: Error::Backend */
-    BIVMOE_ERR_NCCL = 5,        /* a collective failed or NCCL is not loadable: Error::Backend */
+    BIVMOE_ERR_NCCL = 5,        /* reserved: the library calls no collective (the exchanges are the
+                                   caller's, or the library's own peer stores and barrier) */
     BIVMOE_ERR_TIMEOUT = 6,     /* a bounded device-side wait gave up: Error::Backend */
 };
 
@@ -121,6 +125,14 @@ BIVMOE_API int bivmoe_dense_create(int32_t device, int32_t n_embd, int32_t n_ff,
  * of model.rs:790.  Asynchronous on `stream` (a cudaStream_t); no host sync. */
 BIVMOE_API int bivmoe_forward(bivmoe_layer* layer, const float* h_dev, float* out_dev, int32_t n,
                    int32_t accumulate, void* stream);
+
+/* Waits for `stream` and reports what the layer's kernels recorded on the device since
+ * the last report: BIVMOE_ERR_TIMEOUT when a bounded device-side wait (a copy that never
+ * landed, a peer that never reached a barrier) gave up, in which case the outputs of the
+ * passes since then are not to be used; BIVMOE_OK otherwise.  The flag is cleared by the
+ * report.  For any layer, sharded or not.  Stands in for the `Result` a Metal command
+ * buffer's completion yields (engine/src/metal/mod.rs:1535-1541, which panics instead). */
+BIVMOE_API int bivmoe_status(bivmoe_layer* layer, void* stream);
 
 /* The same call for an engine that keeps activations on the host (the CPU
  * backend's calling convention, `fn moe(&self, m, h: &[f32], n) -> Vec<f32>`,
@@ -256,8 +268,8 @@ BIVMOE_API int bivmoe_route_noalloc(bivmoe_layer* layer, const float* h_dev, int
  * asynchronous on `stream`; the caller orders them against its exchanges.
  * `max_tokens` bounds n (a rank's own rows), `max_recv_rows` bounds m (W *
  * max_tokens is always enough).  bivmoe_ep_status synchronises the stream and
- * reports device-side failures (a bounded wait that gave up).  With W = 1
- * bivmoe_ep_create is bivmoe_create and bivmoe_forward applies. */
+ * is bivmoe_status for a sharded layer.  With W = 1 bivmoe_ep_create is bivmoe_create
+ * and bivmoe_forward applies. */
 BIVMOE_API int bivmoe_ep_create(const bivmoe_desc* desc, int32_t ep_rank, int32_t ep_world,
                                 int32_t max_recv_rows, bivmoe_layer** out);
 BIVMOE_API int bivmoe_ep_route(bivmoe_layer* layer, const float* h_dev, int32_t n,
@@ -279,14 +291,16 @@ BIVMOE_API int bivmoe_ep_status(bivmoe_layer* layer, void* stream);
  * into region [home rank] of its owner's receive buffer; steps 3-4 one call whose last
  * kernel writes each partial sum into region [owner] of the home rank's return
  * buffer; a region's unused rows count as rows without experts.  No size depends on
- * another rank's counts, so the host never waits.  The caller's part is two barriers:
+ * another rank's counts, so the host never waits.  Two barriers order the stores against
+ * their readers - the library's own (bivmoe_ep_peer_barrier, below) or any stream-ordered
+ * barrier of the caller's communicator:
  *
  *   setup   bivmoe_ep_peer_info on every rank, the W results gathered to every rank (any
  *           transport), bivmoe_ep_peer_attach.  Ranks may be processes (the block is
  *           opened through its CUDA IPC handle) or threads of one process (the pointer
  *           is used as it is, peer access enabled between distinct devices).
  *   pass    bivmoe_ep_peer_dispatch(h, n)                    home: route, stores to owners
- *           barrier A (stream-ordered, e.g. a one-element all-reduce)
+ *           barrier A (bivmoe_ep_peer_barrier, or e.g. a one-element all-reduce)
  *           bivmoe_ep_shared(h)            [may run beside the next call on another stream]
  *           bivmoe_ep_peer_experts()                         owner: experts, stores to homes
  *           barrier B
@@ -312,6 +326,22 @@ BIVMOE_API int bivmoe_ep_peer_experts(bivmoe_layer* layer, void* stream);
 BIVMOE_API int bivmoe_ep_peer_combine(bivmoe_layer* layer, float* out_dev, int32_t n, int32_t accumulate,
                                       void* stream);
 
+/* The barrier of the peer-store pass, inside the library: no communicator, no host step.
+ * Every rank runs the same sequence of barriers.  `signal` stores this rank's next barrier
+ * number into a word of every rank's block (after the stream's earlier stores);
+ * `wait` holds the stream until every rank's number for this barrier is in this rank's
+ * own block, or until the wait limit (2 s unless bivmoe_ep_peer_wait_limit says otherwise)
+ * has passed - then the kernel records BIVMOE_ERR_TIMEOUT, which bivmoe_status reports,
+ * and the stream goes on.  `barrier` is signal followed by wait.  The ranks must sit on
+ * different GPUs for a wait to run beside the signals it waits for; where ranks share a
+ * GPU (tests), enqueue every rank's signal before any rank's wait.  With these a whole
+ * pass is five calls per rank and nothing else: dispatch, barrier, (shared,) experts,
+ * barrier, combine.  The reference has no counterpart (one device). */
+BIVMOE_API int bivmoe_ep_peer_signal(bivmoe_layer* layer, void* stream);
+BIVMOE_API int bivmoe_ep_peer_wait(bivmoe_layer* layer, void* stream);
+BIVMOE_API int bivmoe_ep_peer_barrier(bivmoe_layer* layer, void* stream);
+BIVMOE_API int bivmoe_ep_peer_wait_limit(bivmoe_layer* layer, uint64_t microseconds);
+
 /* The int8 tensor-pipe peak of the layer's GPU in tera-operations per second (two per
  * multiply-add), measured with back-to-back tcgen05.mma kind::i8 on resident operands
  * (about 10 ms).  A benchmark hook with no reference counterpart: the roofline
@@ -328,6 +358,10 @@ BIVMOE_API int bivmoe_memory(const bivmoe_layer* layer, uint64_t* weight_bytes, 
 
 /* Kernels this library launched since load, for benchmark accounting. */
 BIVMOE_API uint64_t bivmoe_launch_count(void);
+
+/* The size of the device allocation whose failure made the calling thread's last
+ * BIVMOE_ERR_OOM: the `bytes` of `Error::OutOfMemory` (engine/src/error.rs:53-56). */
+BIVMOE_API uint64_t bivmoe_last_oom_bytes(void);
 
 BIVMOE_API const char* bivmoe_last_error(const bivmoe_layer* layer);
 BIVMOE_API const char* bivmoe_global_error(void);

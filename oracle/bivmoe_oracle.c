@@ -806,6 +806,16 @@ ORC_API void orc_softmax(float* x, long n) { /* ops.rs:192-201 */
     for (long i = 0; i < n; i++) x[i] *= inv;
 }
 
+/* f32::total_cmp as the reference's sort uses it (model.rs:263): the bits, with the
+ * magnitude inverted for negative values, compared as signed integers.  A total order:
+ * NaNs sort too (positive ones above +inf), so a row of NaN probabilities still yields
+ * k distinct experts - the first k, every key being equal. */
+static int32_t total_key(float v) {
+    int32_t b;
+    memcpy(&b, &v, 4);
+    return b ^ (int32_t)(((uint32_t)(b >> 31)) >> 1);
+}
+
 /* model.rs:259-268: softmax, the k experts of highest probability with the
  * lowest index first among equals, weights = p / max(sum of the k, 2^-14).
  * `scratch` holds n_expert floats. */
@@ -813,20 +823,21 @@ ORC_API void orc_route(const float* logits, long n_expert, int k, int32_t* ids, 
                        float* scratch) {
     memcpy(scratch, logits, sizeof(float) * (size_t)n_expert);
     orc_softmax(scratch, n_expert);
-    /* selection of the k best by (p desc, id asc): same result as the full sort */
+    /* selection of the k best by (p descending under total_cmp, id ascending): the
+     * first k of the reference's full sort */
     for (int j = 0; j < k; j++) {
         long best = -1;
         for (long e = 0; e < n_expert; e++) {
             int taken = 0;
             for (int i = 0; i < j; i++) taken |= ids[i] == e;
             if (taken) continue;
-            if (best < 0 || scratch[e] > scratch[best]) best = e; /* strict: lower id wins ties */
+            if (best < 0 || total_key(scratch[e]) > total_key(scratch[best])) best = e; /* strict: lower id wins ties */
         }
         ids[j] = (int32_t)best;
     }
     float sum = 0.0f;
     for (int j = 0; j < k; j++) sum += scratch[ids[j]];
-    if (!(sum > 1.0f / 16384.0f)) sum = 1.0f / 16384.0f; /* f32::max */
+    if (!(sum > 1.0f / 16384.0f)) sum = 1.0f / 16384.0f; /* f32::max: a NaN sum gives the floor */
     for (int j = 0; j < k; j++) w[j] = scratch[ids[j]] / sum;
 }
 

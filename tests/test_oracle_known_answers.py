@@ -144,6 +144,30 @@ def test_route_picks_and_weighs():
     assert ids.tolist() == [0] and w.tolist() == [1.0]
 
 
+def test_route_orders_non_finite_rows_like_total_cmp():
+    """`route` sorts with f32::total_cmp (engine/src/model.rs:263), a total order: a row
+    whose probabilities are all NaN (NaN or Inf activations) still yields k distinct, valid
+    experts - the first k, the keys being equal - with NaN weights (`sum.max(2^-14)` passes
+    a NaN sum over, and p / 2^-14 is NaN)."""
+    for bad in (np.nan, np.inf, -np.inf):
+        l = np.linspace(-1, 1, 16).astype(np.float32)
+        l[5] = bad
+        l[9] = -bad if np.isinf(bad) else bad     # +inf and -inf together: inf - inf is NaN
+        ids, w = oracle.route(l, 4)
+        if np.isnan(bad) or np.isinf(bad):
+            assert ids.tolist() == [0, 1, 2, 3] and np.isnan(w).all(), (bad, ids, w)
+    # one +inf alone is an ordinary maximum: p = 1 there (exp(inf - inf) is NaN, though:
+    # the reference's softmax makes every p NaN as well)
+    l = np.linspace(-1, 1, 16).astype(np.float32)
+    l[7] = np.inf
+    ids, w = oracle.route(l, 2)
+    assert ids.tolist() == [0, 1] and np.isnan(w).all()
+    # total_cmp ranks -0.0 below +0.0 and orders finite values as usual
+    p = np.array([0.0, 3.0, -0.0, 3.0, 1.0], dtype=np.float32)
+    ids, _ = oracle.route(p, 5)
+    assert ids.tolist()[:2] == [1, 3]
+
+
 def test_q4_generators_round_trip_through_the_reference_layouts():
     """The build's own Q4_0 / Q4_1 / F16 weight generators against the oracle's statement of
     the reference's dequantisation (engine/src/quant.rs:174-192): a value comes back within
