@@ -139,15 +139,18 @@ def ep_pass_finish(steps, h, out, accumulate: bool, comm, begun):
     return plan
 
 
-def ep_pass_peer(steps, h, out, accumulate: bool, comm):
+def ep_pass_peer(steps, h, out, accumulate: bool, comm, lib_barrier: bool = False):
     """The pass with the library's own exchange kernels (stores into the peers' memory over
     NVLink, ``bivmoe_ep_peer_*``): no packing by destination, no counts on the host, no
-    host wait; ``comm`` supplies the two stream-ordered barriers."""
+    host wait.  The two stream-ordered barriers are ``comm``'s, or with ``lib_barrier`` the
+    library's own (``bivmoe_ep_peer_barrier``: flag words in the ranks' blocks, bounded
+    waits), which makes the pass five library calls and nothing else - no communicator."""
+    barrier = steps.peer_barrier if lib_barrier else (lambda: comm.barrier(h.device))
     steps.peer_dispatch(h)
-    comm.barrier(h.device)          # every rank's rows are where their owners read them
+    barrier()                       # every rank's rows are where their owners read them
     steps.shared(h)                 # beside the owners' work, on the side stream
     steps.peer_experts()
-    comm.barrier(h.device)          # the partial sums are back; the receive buffers are free
+    barrier()                       # the partial sums are back; the receive buffers are free
     steps.peer_combine(out, accumulate)
 
 
@@ -263,6 +266,18 @@ class DeviceSteps:
     def peer_experts(self):
         capi.check(capi.lib().bivmoe_ep_peer_experts(self._h, self._stream()), self._h)
 
+    def peer_signal(self):
+        capi.check(capi.lib().bivmoe_ep_peer_signal(self._h, self._stream()), self._h)
+
+    def peer_wait(self):
+        capi.check(capi.lib().bivmoe_ep_peer_wait(self._h, self._stream()), self._h)
+
+    def peer_barrier(self):
+        capi.check(capi.lib().bivmoe_ep_peer_barrier(self._h, self._stream()), self._h)
+
+    def peer_wait_limit(self, microseconds: int):
+        capi.check(capi.lib().bivmoe_ep_peer_wait_limit(self._h, microseconds), self._h)
+
     def peer_combine(self, out, accumulate: bool):
         import torch
         torch.cuda.current_stream(self.device).wait_stream(self._side)   # the shared expert is done
@@ -275,12 +290,17 @@ class EpMoe:
     process group; every rank passes its own rows."""
 
     def __init__(self, layer: MoeLayer, max_tokens: int, rank: int, world: int, device: int = 0,
-                 comm=None, max_recv_rows: Optional[int] = None, exchange: str = "all_to_all"):
+                 comm=None, max_recv_rows: Optional[int] = None, exchange: str = "all_to_all",
+                 barrier: str = "comm"):
         """``exchange``: "all_to_all" (the communicator's collectives move the rows) or
         "peer" (the library's kernels store them into the peers' memory; the ranks are on
-        the GPUs of one node; all ranks construct the object together)."""
+        the GPUs of one node; all ranks construct the object together).  ``barrier`` (peer
+        form): "comm" - the communicator's stream-ordered barrier - or "lib" - the
+        library's own, for ranks on different GPUs; the communicator is then used at
+        construction only."""
         import torch
-        assert exchange in ("all_to_all", "peer")
+        assert exchange in ("all_to_all", "peer") and barrier in ("comm", "lib")
+        self.lib_barrier = barrier == "lib"
         self.steps = DeviceSteps(layer, max_tokens, rank, world, device, max_recv_rows)
         self.comm = comm or TorchComm()
         self.n_embd = layer.n_embd
@@ -292,7 +312,7 @@ class EpMoe:
 
     def moe_(self, h, out, accumulate: bool = True):
         if self.exchange == "peer" and self.steps.world > 1:
-            ep_pass_peer(self.steps, h, out, accumulate, self.comm)
+            ep_pass_peer(self.steps, h, out, accumulate, self.comm, self.lib_barrier)
         else:
             self.last_plan = ep_pass(self.steps, h, out, accumulate, self.comm)
         return out

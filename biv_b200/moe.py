@@ -144,6 +144,11 @@ class Moe:
     def wait(self):
         capi.check(capi.lib().bivmoe_host_wait(self._h), self._h)
 
+    def status(self):
+        """Waits for the current stream and raises if a kernel of this layer recorded a
+        failure on the device (a bounded wait that gave up) since the last report."""
+        capi.check(capi.lib().bivmoe_status(self._h, self._stream()), self._h)
+
     STAGES = ("router", "topk", "sort", "quantize", "gateup", "down", "combine")
 
     def profile(self, h, out) -> dict:

@@ -188,12 +188,17 @@ def _random_bytes(rng: np.random.Generator, n: int) -> np.ndarray:
 
 
 def random_kquant(rng: np.random.Generator, ty: int, n_rows: int, cols: int,
-                  d_lo: float = 1e-3, d_hi: float = 5e-3) -> np.ndarray:
+                  d_lo: float = 1e-3, d_hi: float = 5e-3, fast: bool = False) -> np.ndarray:
     """Random k-quant rows: uniform quant bits and packed 6-bit (or int8) sub-block
-    scales, f16 ``d`` (and ``dmin``) drawn from U(d_lo, d_hi)."""
+    scales, f16 ``d`` (and ``dmin``) drawn from U(d_lo, d_hi).  ``fast`` draws the bytes
+    with ``rng.integers`` (an order of magnitude quicker than ``rng.bytes``, a different
+    stream of the same distribution)."""
     be, bb = _BLOCK[ty]
     nblk = n_rows * (cols // be)
-    raw = _random_bytes(rng, nblk * bb).reshape(nblk, bb)
+    if fast:
+        raw = rng.integers(0, 256, size=(nblk, bb), dtype=np.uint8)
+    else:
+        raw = _random_bytes(rng, nblk * bb).reshape(nblk, bb)
     d = f32_to_f16_bits(rng.uniform(d_lo, d_hi, nblk).astype(np.float32))
     if ty in (Q4_K, Q5_K):
         dmin = f32_to_f16_bits(rng.uniform(d_lo, d_hi, nblk).astype(np.float32))
@@ -210,11 +215,12 @@ def _stack(ty, cols, rows, n, data) -> ExpertStack:
     return ExpertStack(ty, cols, rows, n, np.ascontiguousarray(data.reshape(-1)))
 
 
-def make_weights(rng, ty: int, n: int, rows: int, cols: int, sigma: float = 0.02) -> ExpertStack:
+def make_weights(rng, ty: int, n: int, rows: int, cols: int, sigma: float = 0.02,
+                 fast: bool = False) -> ExpertStack:
     """``n`` matrices [rows, cols] of type ``ty``: N(0, sigma) values for Q8_0, Q4_0,
     Q4_1, BF16, F16 and F32; random blocks for the k-quants."""
     if ty in (Q4_K, Q5_K, Q6_K):
-        return _stack(ty, cols, rows, n, random_kquant(rng, ty, n * rows, cols))
+        return _stack(ty, cols, rows, n, random_kquant(rng, ty, n * rows, cols, fast=fast))
     rb = row_size(ty, cols)
     out = np.empty((n, rows * rb), dtype=np.uint8)
     for e in range(n):      # one expert at a time keeps the f32 temporary small
@@ -236,7 +242,7 @@ def make_weights(rng, ty: int, n: int, rows: int, cols: int, sigma: float = 0.02
 
 def make_layer(rng, *, n_embd=2048, n_expert=256, k=8, ff=512, ff_sh=512,
                gate_ty=Q8_0, up_ty=None, down_ty=None, router_bias=None,
-               router_dist="normal") -> MoeLayer:
+               router_dist="normal", fast=False) -> MoeLayer:
     up_ty = gate_ty if up_ty is None else up_ty
     down_ty = gate_ty if down_ty is None else down_ty
     if router_dist == "uniform":   # same standard deviation as N(0, 0.02)
@@ -248,13 +254,13 @@ def make_layer(rng, *, n_embd=2048, n_expert=256, k=8, ff=512, ff_sh=512,
         router[:, 0] = np.asarray(router_bias, dtype=np.float32)
     layer = MoeLayer(
         n_embd, n_expert, k, ff, ff_sh, router,
-        gate=make_weights(rng, gate_ty, n_expert, ff, n_embd),
-        up=make_weights(rng, up_ty, n_expert, ff, n_embd),
-        down=make_weights(rng, down_ty, n_expert, n_embd, ff))
+        gate=make_weights(rng, gate_ty, n_expert, ff, n_embd, fast=fast),
+        up=make_weights(rng, up_ty, n_expert, ff, n_embd, fast=fast),
+        down=make_weights(rng, down_ty, n_expert, n_embd, ff, fast=fast))
     if ff_sh:
-        layer.sh_gate = make_weights(rng, gate_ty, 1, ff_sh, n_embd)
-        layer.sh_up = make_weights(rng, up_ty, 1, ff_sh, n_embd)
-        layer.sh_down = make_weights(rng, down_ty, 1, n_embd, ff_sh)
+        layer.sh_gate = make_weights(rng, gate_ty, 1, ff_sh, n_embd, fast=fast)
+        layer.sh_up = make_weights(rng, up_ty, 1, ff_sh, n_embd, fast=fast)
+        layer.sh_down = make_weights(rng, down_ty, 1, n_embd, ff_sh, fast=fast)
         layer.sh_gate_inp = rng.standard_normal(n_embd, dtype=np.float32) * np.float32(0.02)
     return layer
 
@@ -314,6 +320,26 @@ def mtp_stack(n_seq=32, n_tok=5, n_layers=40, seed=3, **shape) -> Workload:
     x0 = rng.standard_normal((n_seq * n_tok, e), dtype=np.float32)
     return Workload("mtp_stack", seed, layers, x0,
                     norm_w=[np.ones(e, dtype=np.float32) for _ in range(n_layers)])
+
+
+def mtp_stack_layer(l: int, seed=3, **shape):
+    """Layer ``l`` of the streamed stack (``mtp_stack_streamed``): ``(MoeLayer, norm_w)``
+    from the layer's own stream ``default_rng([seed, l])``."""
+    rng = np.random.default_rng([seed, l])
+    layer = make_layer(rng, gate_ty=Q5_K, down_ty=Q6_K, fast=True, **shape)
+    return layer, np.ones(layer.n_embd, dtype=np.float32)
+
+
+def mtp_stack_streamed(n_seq=32, n_tok=5, n_layers=40, seed=3, **shape):
+    """Configuration 4 one layer at a time, for hosts that should not hold 40 layers of
+    random weights (0.6 GB each) at once: returns ``(x0, eps, layers)`` where ``layers``
+    yields ``(MoeLayer, norm_w)``.  Layer ``l`` comes from its own stream
+    ``default_rng([seed, l])`` (``mtp_stack_layer``; layers can be built in any order, or
+    on several host threads) and the rows from ``default_rng([seed, 1 << 20])``; the values
+    differ from ``mtp_stack``'s, the distributions do not."""
+    e = shape.get("n_embd", 2048)
+    x0 = np.random.default_rng([seed, 1 << 20]).standard_normal((n_seq * n_tok, e), dtype=np.float32)
+    return x0, 1e-6, (mtp_stack_layer(l, seed, **shape) for l in range(n_layers))
 
 
 def ep_bf16(n=16384, seed=4, **shape) -> Workload:

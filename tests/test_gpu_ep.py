@@ -238,6 +238,94 @@ def test_steps_reject_a_plain_layer_and_bad_sizes():
         st.close()
 
 
+def test_a_whole_pass_through_the_c_abi_alone_with_the_library_barrier():
+    """Two ranks as two layer objects on one GPU, driven from one host thread through
+    ctypes only - no torch.distributed, no communicator: peer info gathered by hand, then
+    per pass dispatch, barrier, shared, experts, barrier, combine.  The ranks share a GPU,
+    so every rank's signal is enqueued before any rank's wait (a waiting kernel must never
+    depend on a launch that may not be running beside it)."""
+    import torch
+    from biv_b200.ep import DeviceSteps
+    wl = _small("decode_q4k", 24)
+    layer, h = wl.layers[0], np.ascontiguousarray(wl.h)
+    world, n_per = 2, 12
+    ranks = [DeviceSteps(layer, n_per, r, world, 0) for r in range(world)]
+    try:
+        infos = [st.peer_info() for st in ranks]
+        for st in ranks:
+            st.peer_attach(infos)
+            st.peer_wait_limit(200_000)     # 0.2 s: ample on one GPU, and it bounds the test
+        hs = [torch.from_numpy(h[r * n_per:(r + 1) * n_per]).cuda() for r in range(world)]
+        outs = [torch.empty_like(x) for x in hs]
+        for _ in range(3):                  # thrice: the regions and the barrier numbers move on
+            for st, x in zip(ranks, hs):
+                st.peer_dispatch(x)
+            for st in ranks:
+                st.peer_signal()
+            for st in ranks:
+                st.peer_wait()
+            for st, x in zip(ranks, hs):
+                st.shared(x)
+                st.peer_experts()
+            for st in ranks:
+                st.peer_signal()
+            for st in ranks:
+                st.peer_wait()
+            for st, o in zip(ranks, outs):
+                st.peer_combine(o, False)
+        for st in ranks:
+            st.status()                     # no wait gave up
+        got = np.concatenate([o.cpu().numpy() for o in outs])
+    finally:
+        for st in ranks:
+            st.close()
+    want = np.concatenate([_single_gpu(layer, np.ascontiguousarray(h[r * n_per:(r + 1) * n_per]))
+                           for r in range(world)])
+    np.testing.assert_allclose(got, want, rtol=0, atol=1e-6 * float(np.abs(want).max()))
+    assert rel_err(got, oracle.moe_forward(layer, h)) < TOL
+
+
+def test_a_rank_that_never_arrives_costs_its_peers_a_timeout_status_not_the_gpu():
+    """The barrier's wait is bounded: when a rank never signals, the waiting kernel gives up
+    after the limit (5 ms here), records BIVMOE_ERR_TIMEOUT, and the stream goes on;
+    bivmoe_status reports it once and the layer stays usable.  No fault, no hang: the flag
+    the kernel polls is simply never written."""
+    import time
+    import torch
+    from biv_b200 import capi
+    from biv_b200.ep import DeviceSteps
+    wl = _small("parity_q8_0", 8)
+    layer = wl.layers[0]
+    ranks = [DeviceSteps(layer, 4, r, 2, 0) for r in range(2)]
+    try:
+        infos = [st.peer_info() for st in ranks]
+        for st in ranks:
+            st.peer_attach(infos)
+            st.peer_wait_limit(5_000)
+        ranks[0].peer_signal()              # rank 1 never does
+        t0 = time.perf_counter()
+        ranks[0].peer_wait()
+        with pytest.raises(capi.BivMoeError) as ei:
+            ranks[0].status()
+        assert ei.value.code == capi.ERR_TIMEOUT
+        assert time.perf_counter() - t0 < 2.0
+        ranks[0].status()                   # reported once, then clear
+        # the late rank arrives: both are in step again (each has one barrier behind it)
+        ranks[1].peer_signal()
+        ranks[1].peer_wait()
+        ranks[1].status()
+        for st in ranks:
+            st.peer_signal()
+        for st in ranks:
+            st.peer_wait()
+        for st in ranks:
+            st.status()
+        torch.cuda.synchronize()
+    finally:
+        for st in ranks:
+            st.close()
+
+
 def _nccl_worker(rank, world, port, cfg, n, tmp):
     import torch
     import torch.distributed as dist
@@ -262,6 +350,15 @@ def _nccl_worker(rank, world, port, cfg, n, tmp):
         assert torch.equal(outp, out)
         dist.barrier()      # nobody unmaps a block a peer may still write to
         mp_.close()
+        # and with the library's own barrier in place of the communicator's: the pass is
+        # five library calls per rank, the ranks meet through flag words in their blocks
+        ml = EpMoe(layer, n_per, rank, world, rank, exchange="peer", barrier="lib")
+        for _ in range(3):
+            outl = ml.moe(hd)
+        ml.status()
+        assert torch.equal(outl, out)
+        dist.barrier()
+        ml.close()
         np.save(os.path.join(tmp, f"out{rank}.npy"), out.cpu().numpy())
         # the same rows as two micro-batches in flight, each with its own layer object and stream
         half = n_per // 2

@@ -15,6 +15,23 @@ from helpers import FLOAT_TYPES, loose_err, rel_err, routing_mismatches
 pytestmark = pytest.mark.gpu
 TOL = 1e-3        # the gate
 FLIP_TOL = 1e-2   # tokens touched by a re-quantisation flip (see run_case)
+# The share of int8 values of the re-quantised SwiGLU rows that may differ from the
+# oracle's (each by one step): ten times the rate observed on a B200 over the cases of
+# this file (see the figures log_stats records).
+FLIP_RATE = 2e-4
+
+
+def log_stats(case, **figures):
+    """Appends the observed flip counts and errors of a case to gpurun_out/parity_stats.jsonl
+    (when that folder exists) and prints them: the figures the tolerances above are set by."""
+    import json
+    import os
+    line = json.dumps({"case": case, **figures})
+    print("parity stats:", line)
+    d = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
+    if os.path.isdir(d):
+        with open(os.path.join(d, "parity_stats.jsonl"), "a") as f:
+            f.write(line + "\n")
 
 
 def run_case(wl, max_tokens=None, check_dots=True, make=None):
@@ -90,9 +107,14 @@ def run_case(wl, max_tokens=None, check_dots=True, make=None):
             assert rel_err(mid, tap["mid"]) < TOL
             pair_out = m.tap(capi.TAP_PAIR_OUT)
             flipped = np.zeros(n * k, bool)
+            flip_elems = 0
             if tap["mid_q"] is not None:
                 mq, _, _ = oracle.q8_quantize(mid)
-                flipped = (mq != tap["mid_q"]).any(axis=1)
+                differ = mq != tap["mid_q"]
+                flipped = differ.any(axis=1)
+                flip_elems = int(differ.sum())
+                assert np.abs(mq.astype(np.int32) - tap["mid_q"].astype(np.int32)).max(initial=0) <= 1
+                assert differ.mean() < FLIP_RATE, differ.mean()
                 assert flipped.mean() < 0.02, flipped.mean()
                 for p in np.nonzero(flipped)[0][:16]:
                     e = int(flat[p])
@@ -115,6 +137,11 @@ def run_case(wl, max_tokens=None, check_dots=True, make=None):
             floor_ref = ref     # the rms floor is taken over the whole output
             err_all = np.abs(got.astype(np.float64) - ref) / np.maximum(
                 np.abs(ref), np.sqrt(np.mean(floor_ref.astype(np.float64) ** 2)))
+            log_stats(wl.name, n=n, types=[layer.gate.ty, layer.down.ty], pairs=n * k,
+                      flipped_int8=flip_elems, flipped_pairs=int(flipped.sum()),
+                      flipped_shared_rows=int(sh_flipped.sum()), flipped_tokens=int(tok_flipped.sum()),
+                      worst_unflipped_token=float(err_all[~tok_flipped].max(initial=0.0)),
+                      worst_flipped_token=float(err_all[tok_flipped].max(initial=0.0)))
             assert err_all[~tok_flipped].max(initial=0.0) < TOL, err_all[~tok_flipped].max()
             assert err_all.max() < FLIP_TOL, (err_all.max(), loose_err(got, ref))
         else:   # tokens whose routing was tie-broken differently are excused
@@ -300,44 +327,58 @@ def test_config3_prefill_q8_0_full_shape():
     assert np.isfinite(got).all()
 
 
-def test_config4_stack_full_shape_eight_layers():
+def test_config4_stack_full_shape_all_forty_layers():
     # The MTP-verify shape (32 sequences x 5 tokens, gate/up Q5_K, down Q6_K, rms_norm per
-    # layer, residual carried) at the model's sizes; 8 of the 40 layers, which bounds the
-    # host memory the random weights take (0.6 GB per layer).  The residual reaches ~1e6
-    # (uniform k-quant fields), and a stack is chaotic: a 1e-3 difference in one layer's
-    # output moves the next layer's logits enough to change a top-8 choice somewhere.  The
-    # reference's own scalar and AVX2 kernels diverge the same way.  So every layer of
-    # the stack is checked on the oracle's input to that layer (norm, layer, residual
-    # add through the stack call), and the free-running stack on its first layers.
+    # layer, residual carried) at the model's sizes, all 40 layers, one layer at a time
+    # (generate, upload, check, free: 0.6 GB of random weights per layer).  The residual
+    # reaches ~1e6 (uniform k-quant fields), and a stack is chaotic: a 1e-3 difference in
+    # one layer's output moves the next layer's logits enough to change a top-8 choice
+    # somewhere.  The reference's own scalar and AVX2 kernels diverge the same way.  So
+    # every layer of the stack is checked on the oracle's input to that layer (norm, layer,
+    # residual add through the stack call, the norm fused into the router kernel), and the
+    # free-running stack on its first two layers.
     import torch
     from biv_b200.moe import Moe, MoeStack
-    wl = W.mtp_stack(n_layers=8)
+    x0, eps, gen = W.mtp_stack_streamed(n_layers=40)
     level, thr = oracle.host_level(), oracle.max_threads()
-    xs = [wl.h]
-    for l, nw in zip(wl.layers, wl.norm_w):
-        xs.append(oracle.moe_stack([l], [nw], wl.eps, xs[-1], level=level, threads=thr))
-    assert all(np.isfinite(x).all() for x in xs)
-    layers = [Moe(l, wl.n) for l in wl.layers]
+    x_ref = x0
+    first_two, x_two = [], None
+    worst_median, worst_row, least_ids = 0.0, 0.0, 1.0
     try:
-        for m, nw in zip(layers, wl.norm_w):
-            m.set_post_norm(nw, wl.eps)
-        for i, m in enumerate(layers):
-            x = torch.from_numpy(xs[i]).cuda()
+        for i, (layer, nw) in enumerate(gen):
+            nxt = oracle.moe_stack([layer], [nw], eps, x_ref, level=level, threads=thr)
+            assert np.isfinite(nxt).all(), i
+            m = Moe(layer, x0.shape[0])
+            m.set_post_norm(nw, eps)
+            if i < 2:
+                first_two.append(m)
+            x = torch.from_numpy(x_ref).cuda()
             MoeStack([m]).forward_(x)
             torch.cuda.synchronize()
             got = x.cpu().numpy()
-            ids_ok = (m.tap(capi.TAP_IDS) == oracle_ids(wl.layers[i], xs[i], wl.norm_w[i], wl.eps)).all(axis=1)
-            assert ids_ok.mean() > 0.98
-            assert rel_err(got[ids_ok], xs[i + 1][ids_ok]) < FLIP_TOL, i
-            assert np.median(np.abs(got - xs[i + 1]).max(axis=1) / np.sqrt(np.mean(xs[i + 1].astype(np.float64) ** 2))) < 2e-4
-        x = torch.from_numpy(wl.h).cuda()
-        MoeStack(layers[:2]).forward_(x)
-        torch.cuda.synchronize()
-        got = x.cpu().numpy()
-        close = np.abs(got - xs[2]).max(axis=1) / np.sqrt(np.mean(xs[2].astype(np.float64) ** 2)) < FLIP_TOL
+            ids_ok = (m.tap(capi.TAP_IDS) == oracle_ids(layer, x_ref, nw, eps)).all(axis=1)
+            rms = np.sqrt(np.mean(nxt.astype(np.float64) ** 2))
+            row = np.abs(got - nxt).max(axis=1) / rms
+            least_ids = min(least_ids, float(ids_ok.mean()))
+            worst_median, worst_row = max(worst_median, float(np.median(row))), max(worst_row, float(row[ids_ok].max()))
+            assert ids_ok.mean() > 0.98, i
+            assert rel_err(got[ids_ok], nxt[ids_ok]) < FLIP_TOL, i
+            assert np.median(row) < 2e-4, i
+            if i == 1:      # the free-running stack over the first two layers
+                x = torch.from_numpy(x0).cuda()
+                MoeStack(first_two).forward_(x)
+                torch.cuda.synchronize()
+                x_two = (x.cpu().numpy(), nxt)
+            if i >= 2:
+                m.close()
+            x_ref = nxt
+        got2, want2 = x_two
+        close = np.abs(got2 - want2).max(axis=1) / np.sqrt(np.mean(want2.astype(np.float64) ** 2)) < FLIP_TOL
         assert close.mean() > 0.9
+        log_stats("mtp_stack_40_layers", layers=40, least_rows_with_equal_ids=least_ids,
+                  worst_median_row_err=worst_median, worst_row_err=worst_row)
     finally:
-        for m in layers:
+        for m in first_two:
             m.close()
 
 
@@ -354,28 +395,30 @@ def test_config5_bf16_4096_tokens_against_the_oracle():
     run_case(wl)
 
 
-def test_config5_bf16_full_size_kernel_families_agree(monkeypatch):
-    # 16 384 tokens: too slow for the CPU oracle inside a test, so the check is a
-    # property - the tcgen05 path and the warp-MMA path (tensor-core kernels disabled)
-    # are independent statements of the same products and must agree
+def test_config5_bf16_full_size_sampled_rows_against_the_oracle():
+    # 16 384 tokens, the configuration's real size (every group ~512 tokens: the tcgen05
+    # kind::f16 kernel in tiles of 128).  The layer is token-wise - a row's output depends
+    # on that row alone - so the oracle on 512 sampled rows is the reference for those rows
+    # of the full pass: ids exact (up to the tie rule), outputs inside the gate.
     import torch
     from biv_b200.moe import Moe
     wl = W.ep_bf16()
-    h = torch.from_numpy(wl.h).cuda()
+    rows = np.sort(np.random.default_rng(5).choice(wl.n, 512, replace=False))
+    ref, tap = oracle.moe_forward(wl.layer, wl.h[rows], level=oracle.host_level(),
+                                  threads=oracle.max_threads(), taps=True)
     m = Moe(wl.layer, wl.n)
     try:
-        a = m.moe(h).cpu().numpy()
+        got = m.moe(torch.from_numpy(wl.h).cuda()).cpu().numpy()
         ids = m.tap(capi.TAP_IDS)
     finally:
         m.close()
-    monkeypatch.setenv("BIVMOE_PREFILL_MIN", "0")
-    m = Moe(wl.layer, wl.n)
-    try:
-        b = m.moe(h).cpu().numpy()
-        assert np.array_equal(ids, m.tap(capi.TAP_IDS))
-    finally:
-        m.close()
-    assert np.isfinite(a).all() and rel_err(a, b) < 1e-4
+    assert np.isfinite(got).all()
+    assert not routing_mismatches(ids[rows], tap["ids"], tap["logits"])
+    same = (ids[rows] == tap["ids"]).all(axis=1)
+    assert same.mean() > 0.99
+    err = rel_err(got[rows][same], ref[same])
+    log_stats("ep_bf16_16384_sampled", rows=int(same.sum()), rel_err=err)
+    assert err < TOL, err
     assert np.bincount(ids.reshape(-1), minlength=256).min() > 300   # balanced routing: all large groups
 
 
@@ -481,3 +524,63 @@ def test_int8_peak_probe_is_plausible():
         assert 1000.0 < tops < 6000.0, tops
     finally:
         m.close()
+
+
+def test_a_row_of_nan_or_inf_costs_only_its_own_output():
+    # model.rs:263 sorts with total_cmp: a row with NaN or Inf activations selects the first
+    # k experts with NaN weights, and every other row is untouched (the oracle states this;
+    # tests/test_oracle_known_answers.py pins it)
+    import torch
+    from biv_b200.moe import Moe
+    for cfg in ("decode_q4k", "ep_bf16"):
+        wl = W.CONFIGS[cfg](n=21, **W.SMALL)
+        h = wl.h.copy()
+        h[3, 7] = np.nan
+        h[11, 0] = np.inf
+        h[12, 5] = -np.inf
+        bad = np.array([3, 11, 12])
+        good = np.setdiff1d(np.arange(wl.n), bad)
+        ref, tap = oracle.moe_forward(wl.layer, h, taps=True)
+        m = Moe(wl.layer, wl.n)
+        try:
+            got = m.moe(torch.from_numpy(h).cuda()).cpu().numpy()
+            ids = m.tap(capi.TAP_IDS)
+            k = wl.layer.n_expert_used
+            assert (ids >= 0).all() and (ids < wl.layer.n_expert).all()
+            assert all(len(set(r.tolist())) == k for r in ids)            # distinct, valid ids
+            assert np.array_equal(ids[bad], tap["ids"][bad])              # the first k, as the oracle
+            assert np.array_equal(ids[bad], np.tile(np.arange(k), (3, 1)))
+            assert np.isnan(m.tap(capi.TAP_WEIGHTS)[bad]).all()
+            assert not np.isfinite(got[bad]).all(axis=1).any()            # their outputs are lost
+            assert np.isfinite(got[good]).all()
+            assert not routing_mismatches(ids[good], tap["ids"][good], tap["logits"][good])
+            assert rel_err(got[good], ref[good]) < FLIP_TOL
+        finally:
+            m.close()
+
+
+def test_rows_wider_than_the_row_staging_router_kernel():
+    # n_embd = 4096: 8 router rows + 16 token rows no longer fit in shared memory, so few
+    # tokens also take the router kernel that moves K in chunks; same logits bit for bit
+    run_case(W.parity_q8_0(n=5, **dict(W.SMALL, n_embd=4096)), check_dots=False)
+    run_case(W.decode_q4k(n=33, **dict(W.SMALL, n_embd=2560)), check_dots=False)
+
+
+def test_stack_with_many_rows_takes_the_separate_norm_kernel():
+    # from 256 rows on the norm is a kernel of its own (below it is fused into the router)
+    import torch
+    from biv_b200.moe import Moe, MoeStack
+    wl = W.mtp_stack(n_seq=60, n_tok=5, n_layers=2, **W.SMALL)
+    ref = oracle.moe_stack(wl.layers, wl.norm_w, wl.eps, wl.h, level=oracle.host_level())
+    layers = [Moe(l, wl.n) for l in wl.layers]
+    try:
+        for m, nw in zip(layers, wl.norm_w):
+            m.set_post_norm(nw, wl.eps)
+        x = torch.from_numpy(wl.h).cuda()
+        MoeStack(layers).forward_(x)
+        torch.cuda.synchronize()
+        assert rel_err(x.cpu().numpy(), ref) < FLIP_TOL
+        layers[0].status()          # nothing gave up on the device
+    finally:
+        for m in layers:
+            m.close()
