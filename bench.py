@@ -324,8 +324,9 @@ def measure_layer(wl, args, local, copies=1, in_flight=1, parity_rows=256, with_
     sync()
     experts_hit = int((ms_[0].tap(capi.TAP_COUNTS) > 0).sum())
     l0 = launch_count()
-    ms_loop, loops = timed_loops(alone, args.steps, streams[0], sync)
+    ms_loop, loops = timed_loops(alone, args.steps, streams[0], sync, min_ms=0.0 if args.quick else MIN_TIMED_MS)
     launches = (launch_count() - l0) // len(loops)
+    ms_[0].status()      # no bounded wait gave up on the device
     res.update(ms_per_step=ms_loop / args.steps, loops=len(loops), launches=launches,
                experts_hit=experts_hit, warmup=warm,
                spread=[min(loops) / args.steps, max(loops) / args.steps])
@@ -513,6 +514,8 @@ def measure_stack(args, local, budget_s):
     ms_loop, loops = timed_loops(run, steps, stream, sync)
     launches = (launch_count() - l0) // len(loops)
     ms = ms_loop / steps
+    for m in layers:
+        m.status()      # no bounded wait gave up on the device
     hits = [int((m.tap(capi.TAP_COUNTS) > 0).sum()) for m in layers]
     # parity of the first layer (norm fused into the router, layer, residual add)
     one = xd0.clone()

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libbivmoe.so")
+# BIVMOE_LIB names another build of the library (a development aid for comparing builds)
+LIB_PATH = os.environ.get("BIVMOE_LIB") or os.path.join(_HERE, "libbivmoe.so")
 
 OK, ERR_ARGUMENT, ERR_UNSUPPORTED, ERR_OOM, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT = range(7)
 STATUS_NAMES = {1: "argument", 2: "unsupported (NoKernel)", 3: "out of memory", 4: "cuda",

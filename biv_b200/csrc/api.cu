@@ -821,15 +821,16 @@ int bivmoe_status(bivmoe_layer* L, void* stream) {
     std::string* errp = &L->error;
     cudaStream_t s = (cudaStream_t)stream;
     const bool ep = L->ep_world > 1;
-    int32_t st[2] = {0, 0};
-    CU(cudaMemcpyAsync(&st[0], L->ws.status, 4, cudaMemcpyDeviceToHost, s));
-    if (ep) CU(cudaMemcpyAsync(&st[1], L->ws_owner.status, 4, cudaMemcpyDeviceToHost, s));
+    int32_t st[2][4] = {};
+    CU(cudaMemcpyAsync(st[0], L->ws.status, 16, cudaMemcpyDeviceToHost, s));
+    if (ep) CU(cudaMemcpyAsync(st[1], L->ws_owner.status, 16, cudaMemcpyDeviceToHost, s));
     CU(cudaStreamSynchronize(s));
-    if (st[0] || st[1]) {
+    if (st[0][0] || st[1][0]) {
         cudaMemsetAsync(L->ws.status, 0, 16, s);
         if (ep) cudaMemsetAsync(L->ws_owner.status, 0, 16, s);
-        const int code = st[0] ? st[0] : st[1];
-        return set_err(errp, code, "a device-side bounded wait gave up (status %d)", code);
+        const int which = st[0][0] ? 0 : 1;
+        return set_err(errp, st[which][0], "a device-side bounded wait gave up (status %d, wait site %d)",
+                       st[which][0], st[which][2]);
     }
     return BIVMOE_OK;
 }

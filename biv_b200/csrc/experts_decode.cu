@@ -26,11 +26,11 @@
 #include "common.cuh"
 #include "formats.cuh"
 #include "tcgen05.cuh"
+#include "launch.cuh"
 
 namespace bivmoe {
 
 constexpr int EX_TT = 8;                       // tokens per tile
-constexpr int EX_THREADS = 128;                // four warps
 constexpr uint32_t EX_WAIT_LIMIT = 1u << 16;   // bounded mbarrier wait: tries that may sleep wait_hint_ns each
 
 enum { MODE_GATEUP = 0, MODE_DOWN = 1 };
@@ -190,7 +190,7 @@ template <int TY> struct Fmt;
 
 // ---- Q8_0 (quant.rs:599-607): term = d_w * d_x * sum(q_w * q_x) ------------
 template <> struct Fmt<BIVMOE_Q8_0> {
-    static constexpr int ELEMS = 256, SL = 272, MINB = 2;   // 2 x 37.7 KB stages per block
+    static constexpr int ELEMS = 256, SL = 272, MINB = 2;   // consumer groups per block: 2 x 2 stages of 37.7 KB
     static constexpr bool F32ACT = false;
     using Side = NoSide;
     __device__ static void compute(const uint32_t (&rowp)[2][2], Side, uint32_t act,
@@ -573,6 +573,20 @@ template <> struct Fmt<BIVMOE_F16> : FmtFloat<BIVMOE_F16> {};
 template <> struct Fmt<BIVMOE_F32> : FmtFloat<BIVMOE_F32> {};
 
 // ---------------------------------------------------------------------------
+// The kernel.  One block per SM: G consumer groups of four warps and one producer
+// warp.  A group works on its own items - a tile of up to 8 tokens times one chunk
+// (gate+up) or two chunks (down) - and owns a two-slot ring of stages (one K-slice of a
+// chunk's 128 rows plus the tile's activation record) that lane g of the producer warp
+// keeps full: the lane claims the group's next item from the counter the sort kernel
+// resets, and issues its stages as slots come free.  A consumer warp waits for a slot,
+// computes its 32 rows of the stage, and hands the slot back with one mbarrier arrive:
+// the consumer warps never meet per stage and carry no pipeline state - everything a
+// stage needs to know (tile, chunk, whether it opens or closes an accumulation) comes in
+// a small descriptor the producer writes beside it.  The groups of a block share nothing
+// but the producer warp, so one group's epilogue overlaps the others' products.
+// Every wait is bounded; a wait that gives up records BIVMOE_ERR_TIMEOUT (and which wait
+// it was) in the status words and raises a block-wide flag on which every role leaves its
+// loop (the producer first waits, bounded again, for its copies still in flight).
 template <int TY>
 __host__ __device__ constexpr int act_stage_bytes() {
     return Fmt<TY>::F32ACT ? EX_TT * Fmt<TY>::ELEMS * 4 : kActCopyBytes;
@@ -581,289 +595,293 @@ template <int TY>
 __host__ __device__ constexpr int stage_bytes() {
     return kChunkRows * Fmt<TY>::SL + act_stage_bytes<TY>();
 }
-constexpr int EX_SMEM_HEAD = 64 + EX_TT * 64 * 4;   // barriers, counter slots; the SwiGLU staging
+constexpr int EX_SLOTS = 2;               // ring slots per group
+constexpr int EX_HEAD = 1024;             // barriers, abort flag, stage descriptors
+constexpr int EX_SMEM_MAX = 227 * 1024;
 template <int TY>
 __host__ __device__ constexpr int smem_bytes() {
-    return EX_SMEM_HEAD + 2 * stage_bytes<TY>();
+    constexpr int G = Fmt<TY>::MINB;
+    return EX_HEAD + G * EX_TT * 64 * 4 + G * EX_SLOTS * stage_bytes<TY>();
 }
 
-struct Item {           // a decoded work item (block-uniform): a token tile x a run of chunks
-    int valid;
+struct StageDesc {      // what the producer tells a group about a stage
+    int pos0, tc;       // the tile: first position, tokens
+    int chunk, slice;   // the weights: chunk of the expert's matrix, K-slice
+    int expert;         // expert id (n_expert: the shared expert)
+    int rows;           // rows of the expert's matrix (down: the stride of the output rows)
+    int flags;          // SD_*
+    int pad;
+};
+enum { SD_FIRST = 1, SD_LAST = 2, SD_END = 4 };
+// which bounded wait gave up (status word 2, for the error text)
+enum { SITE_PRODUCER_SLOT = 1, SITE_CONSUMER_STAGE = 2, SITE_END_MARKER = 3 };
+
+struct Item {           // a decoded work item: a token tile x a run of chunks
     int shared;         // the shared expert's group
     int expert;
-    int chunk0;         // first chunk; the item's chunks are consecutive in memory
+    int chunk0;         // first chunk
+    int nch;            // chunks of the item present in this matrix
     int nsl;            // K-slices per chunk
-    int nst;            // stages of the item: chunks * nsl (0: nothing to do for this group)
     int pos0;           // first position of the tile
     int tc;             // tokens in the tile
-    const uint8_t* src; // stage 0; stage s is s * 128 * SL further
+    int rows;
+    const uint8_t* src; // K-slice 0 of chunk0; slice s of chunk chunk0 + j is (j * nsl + s) * 128 * SL further
 };
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void group_sync(int grp) {   // the 128 threads of one consumer group
+    asm volatile("bar.sync %0, 128;" ::"r"(grp + 1) : "memory");
+}
 template <int TY, int MODE>
-__global__ void __launch_bounds__(EX_THREADS, Fmt<TY>::MINB)
+__global__ void __launch_bounds__(32 * (4 * Fmt<TY>::MINB + 1), 1)
 experts_kernel(const ExpertArgs A) {
     using F = Fmt<TY>;
     using Side = typename F::Side;
+    constexpr int G = F::MINB;
     constexpr int SB = stage_bytes<TY>();
     constexpr uint32_t W_BYTES = kChunkRows * F::SL, ACT_BYTES = act_stage_bytes<TY>();
     constexpr int CH = MODE == MODE_GATEUP ? 64 : 128;   // output rows per chunk
+    pdl_launch_dependents();
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t* mbar = (uint64_t*)smem;          // [2]
-    int* s_item = (int*)(smem + 16);           // [2]
-    float* s_mid = (float*)(smem + 64);        // [EX_TT][64]
-    uint8_t* ring = smem + EX_SMEM_HEAD;
-    const uint32_t ring_a = smem_u32(ring);
+    uint64_t* full = (uint64_t*)smem;                 // [G][2] a stage has landed
+    uint64_t* empty = full + G * EX_SLOTS;            // [G][2] its four warps are done with it
+    int* s_abort = (int*)(smem + 256);
+    StageDesc* s_desc = (StageDesc*)(smem + 512);     // [G][2]
+    float* s_mid_all = (float*)(smem + EX_HEAD);      // [G][EX_TT][64] SwiGLU staging
+    uint8_t* ring = (uint8_t*)(s_mid_all + G * EX_TT * 64);   // [G][2][SB]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, c = lane & 3;
+    const uint32_t hint = A.wait_hint_ns;
 
     if (tid == 0) {
-        mbar_init(&mbar[0], 1);
-        mbar_init(&mbar[1], 1);
+        for (int i = 0; i < G * EX_SLOTS; i++) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 4);
+        }
+        *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    pdl_wait();   // the tile lists and the activation records are the previous kernels'
 
-    const int tiles_all = A.n_tiles[0], tiles_sh = A.n_tiles[1];
-    const int tile_lo = A.tiles_mode == 1 ? tiles_sh : 0;
-    const int tile_hi = A.tiles_mode == 2 ? tiles_sh : tiles_all;
-    // an item takes EX_CG consecutive chunks (gate+up: 1, down: 4), i.e. 8 stages at
-    // the qwen35moe shapes, so that claiming the next item a few stages before the end
-    // of the current one hides the claim
-    constexpr int CG = MODE == MODE_GATEUP ? 1 : 4;
-    const int groups_of_chunks = (A.chunks + CG - 1) / CG;
-    const int total = (tile_hi - tile_lo) * groups_of_chunks;
-    int n_fetch = 0;
-
-    // decodes the item whose counter value thread 0 left in s_item (whole block)
-    auto fetch = [&]() -> Item {
-        Item it;
-        const int idx = s_item[n_fetch & 1];
-        n_fetch++;
-        it.valid = idx < total;
-        if (!it.valid) return it;
-        const int tile = tile_lo + idx / groups_of_chunks;
-        it.chunk0 = (idx % groups_of_chunks) * CG;
-        const int4 td = A.tile_desc[tile];   // one load: no chain of dependent lookups
-        it.expert = td.x;
-        it.shared = it.expert == A.n_expert;
-        it.pos0 = td.y;
-        it.tc = td.z;
-        const DevTiles& m = it.shared ? A.sh : A.w;
-        it.nsl = m.nslices;
-        it.nst = max(0, min(CG, m.chunks - it.chunk0)) * m.nslices;
-        it.src = m.stage(it.shared ? 0 : it.expert, min(it.chunk0, max(m.chunks - 1, 0)), 0);
-        return it;
-    };
-    // issues stage `s` of an item into ring slot `slot` (one thread)
-    auto issue = [&](const Item& it, int s, int slot) {
-        uint8_t* dst = ring + (size_t)slot * SB;
-        fence_proxy_async();   // the slot was last read through the generic proxy
-        mbar_expect_tx(&mbar[slot], W_BYTES + ACT_BYTES);
-        bulk_g2s(dst, it.src + (size_t)s * W_BYTES, W_BYTES, &mbar[slot]);
-        uint8_t* adst = dst + W_BYTES;
-        const int sl = s % it.nsl;   // the K-slice of this stage
-        if (F::F32ACT) {
-            const size_t row = (size_t)sl * A.act_rows + it.pos0;
-            bulk_g2s(adst, A.x_f32 + row * F::ELEMS, EX_TT * F::ELEMS * 4, &mbar[slot]);
-        } else {   // the tile's Q8 record of this K-slice (pos0 is a multiple of 8)
-            bulk_g2s(adst, A.x_t + ((size_t)sl * (A.act_rows / 8) + it.pos0 / 8) * kActTileBytes,
-                     kActCopyBytes, &mbar[slot]);
+    // bounded wait that also gives up when another role has
+    auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+        for (uint32_t i = 0; i < EX_WAIT_LIMIT; i++) {
+            if (mbar_try_wait(bar, parity, hint)) return true;
+            if ((i & 31) == 31 && *(volatile int*)s_abort) return false;
         }
+        return false;
     };
+    auto give_up = [&](int site) {
+        if (atomicExch(A.status, BIVMOE_ERR_TIMEOUT) == 0) atomicExch(A.status + 2, site);
+        atomicExch(s_abort, 1);
+    };
+
+    if (warp == 4 * G) {
+        // ------------------------------------------------------------ producer warp
+        // lane g feeds group g; the lanes share nothing and go their own ways
+        if (lane >= G) return;
+        const int tiles_all = A.n_tiles[0], tiles_sh = A.n_tiles[1];
+        const int tile_lo = A.tiles_mode == 1 ? tiles_sh : 0;
+        const int tile_hi = A.tiles_mode == 2 ? tiles_sh : tiles_all;
+        // an item is a tile times one chunk: 8 stages (gate+up), 2 stages (down) at the qwen35moe shapes
+        const int total = (tile_hi - tile_lo) * A.chunks;
+        const int units = total;
+        uint32_t issued = 0;      // stages this lane has given its group
+        bool dead = false;
+        // the first items need no counter (group g of block b starts with item b * G + g);
+        // later claims follow the grid
+        int idx = (int)blockIdx.x * G + lane;
+        while (idx < units && !dead) {
+            Item it;
+            const int tile = tile_lo + idx / A.chunks;
+            it.chunk0 = idx % A.chunks;
+            const int4 td = A.tile_desc[tile];
+            it.expert = td.x;
+            it.shared = it.expert == A.n_expert;
+            it.pos0 = td.y;
+            it.tc = td.z;
+            const DevTiles& m = it.shared ? A.sh : A.w;
+            it.nsl = m.nslices;
+            it.nch = it.chunk0 < m.chunks ? 1 : 0;
+            it.rows = m.rows;
+            it.src = m.stage(it.shared ? 0 : it.expert, min(it.chunk0, max(m.chunks - 1, 0)), 0);
+            const int s0 = 0, s1 = it.nch ? it.nsl : 0;
+            for (int slice = s0; slice < s1 && !dead; slice++) {
+                const int bi = lane * EX_SLOTS + (int)(issued & 1);
+                if (!wait(&empty[bi], ((issued >> 1) & 1) ^ 1)) {
+                    give_up(SITE_PRODUCER_SLOT);
+                    dead = true;
+                    break;
+                }
+                StageDesc d;
+                d.pos0 = it.pos0; d.tc = it.tc; d.chunk = it.chunk0; d.slice = slice;
+                d.expert = it.shared ? A.n_expert : it.expert; d.rows = it.rows;
+                d.flags = (slice == s0 ? SD_FIRST : 0) | (slice == s1 - 1 ? SD_LAST : 0);
+                d.pad = 0;
+                s_desc[bi] = d;
+                uint8_t* dst = ring + (size_t)bi * SB;
+                fence_proxy_async();   // the slot was last read through the generic proxy
+                mbar_expect_tx(&full[bi], W_BYTES + ACT_BYTES);
+                bulk_g2s(dst, it.src + (size_t)slice * W_BYTES, W_BYTES, &full[bi]);
+                uint8_t* adst = dst + W_BYTES;
+                if (F::F32ACT) {
+                    const size_t row = (size_t)slice * A.act_rows + it.pos0;
+                    bulk_g2s(adst, A.x_f32 + row * F::ELEMS, EX_TT * F::ELEMS * 4, &full[bi]);
+                } else {   // the tile's Q8 record of this K-slice (pos0 is a multiple of 8)
+                    bulk_g2s(adst, A.x_t + ((size_t)slice * (A.act_rows / 8) + it.pos0 / 8) * kActTileBytes,
+                             kActCopyBytes, &full[bi]);
+                }
+                issued++;
+            }
+            if (dead || *(volatile int*)s_abort) break;
+            idx = (int)(gridDim.x * G + atomicAdd(A.work_ctr, 1u));
+        }
+        dead = dead || *(volatile int*)s_abort != 0;
+        if (!dead) {   // the end marker: a stage without data
+            const int bi = lane * EX_SLOTS + (int)(issued & 1);
+            if (wait(&empty[bi], ((issued >> 1) & 1) ^ 1)) {
+                StageDesc d{};
+                d.flags = SD_END;
+                s_desc[bi] = d;
+                mbar_arrive(&full[bi]);
+            } else {
+                give_up(SITE_END_MARKER);
+                dead = true;
+            }
+        }
+        if (dead) {    // leave no copy in flight behind: the last two stages this lane issued
+            for (uint32_t q = issued > 2 ? issued - 2 : 0; q < issued; q++)
+                mbar_wait_bounded(&full[lane * EX_SLOTS + (q & 1)], (q >> 1) & 1, hint);
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumer groups
+    const int grp = warp >> 2, wig = warp & 3;
+    const int g = lane >> 2, c = lane & 3;
+    const uint32_t ring_a = smem_u32(ring);
+    float* s_mid = s_mid_all + grp * EX_TT * 64;
     // the first chunk row of this warp's two 16-row MMA tiles
     int row_of[2];
     if (MODE == MODE_GATEUP) {   // warp w: gate rows 16w..16w+15 and the same up rows (64 further)
-        row_of[0] = 16 * warp;
-        row_of[1] = 64 + 16 * warp;
+        row_of[0] = 16 * wig;
+        row_of[1] = 64 + 16 * wig;
     } else {                     // warp w: down rows 32w..32w+31
-        row_of[0] = 32 * warp;
-        row_of[1] = 32 * warp + 16;
+        row_of[0] = 32 * wig;
+        row_of[1] = 32 * wig + 16;
     }
-    auto side_of = [&](const Item& it, int s) -> Side {
-        if constexpr (TY == BIVMOE_Q6_K) {
-            const DevTiles& m = it.shared ? A.sh : A.w;
-            const size_t base = ((size_t)(it.shared ? 0 : it.expert) * m.chunks + it.chunk0 + s / it.nsl) * kChunkRows;
-            Side v;
+    float acc[8];   // MMA path: [mt][i] = acc[4 * mt + i], i = 2 * r + tt: row g + 8r, token 2c + tt;
+                    // float path: token t of this lane's row
 #pragma unroll
-            for (int mt = 0; mt < 2; mt++)
+    for (int i = 0; i < 8; i++) acc[i] = 0.0f;
+    for (uint32_t q = 0;; q++) {
+        const int bi = grp * EX_SLOTS + (int)(q & 1);
+        if (!wait(&full[bi], (q >> 1) & 1)) {
+            give_up(SITE_CONSUMER_STAGE);
+            return;
+        }
+        const StageDesc d = s_desc[bi];
+        if (d.flags & SD_END) return;
+        if (d.flags & SD_FIRST) {
 #pragma unroll
-                for (int r = 0; r < 2; r++)
-                    v.d[mt][r] = __half2float(__ushort_as_half(
-                        m.side[(base + row_of[mt] + g + 8 * r) * m.nslices + s % it.nsl]));
-            return v;
+            for (int i = 0; i < 8; i++) acc[i] = 0.0f;
+        }
+        const bool shared = d.expert == A.n_expert;
+        const uint32_t sta = ring_a + (uint32_t)bi * SB;
+        if constexpr (F::F32ACT) {
+            // a lane per weight row: GATEUP lanes 0-15 gate rows, 16-31 up rows
+            const uint8_t* st = ring + (size_t)bi * SB;
+            const uint8_t* wrow;
+            if (MODE == MODE_GATEUP) wrow = st + (row_of[lane >> 4] + (lane & 15)) * 16;
+            else wrow = st + (32 * wig + lane) * 16;
+            F::compute_f32(wrow, (const float*)(st + W_BYTES), d.tc, acc);
         } else {
-            return Side{};
-        }
-    };
-
-    // the first item needs no counter: block b starts with item b, later claims follow the grid
-    if (tid == 0) s_item[0] = (int)blockIdx.x;
-    __syncthreads();
-    Item cur = fetch();
-    if (!cur.valid) return;
-    Item nxt;
-    nxt.valid = 0;
-    nxt.nst = 0;
-    // The stages of successive items form one stream; stream stage q lives in
-    // slot q & 1.  `issued` runs at most two ahead of `consumed`; the producer
-    // cursor (p_in_next, p_stage) names the next stage to issue.  The next item
-    // is claimed EX_LEAD stages before the current one ends: early enough to hide
-    // the claim, late enough that blocks do not hoard items they will not start soon.
-    constexpr int EX_LEAD = 4;
-    int issued = 0, consumed = 0, p_in_next = 0, p_stage = 0;
-    int nxt_claimed = 0, pf = 0;
-    Side side0{}, side1{};
-    auto pump = [&]() {
-        while (issued < consumed + 2) {
-            if (!p_in_next && p_stage >= cur.nst) {
-                p_in_next = 1;
-                p_stage = 0;
-            }
-            if (p_in_next && (!nxt.valid || p_stage >= nxt.nst)) break;
-            const Item& it = p_in_next ? nxt : cur;
-            const int slot = issued & 1;
-            const Side sv = side_of(it, p_stage);
-            if (slot) side1 = sv; else side0 = sv;
-            if (tid == 0) issue(it, p_stage, slot);
-            p_stage++;
-            issued++;
-        }
-    };
-    pump();
-
-    while (true) {
-        float acc[2][4] = {};
-        float accf[EX_TT];
-#pragma unroll
-        for (int t = 0; t < EX_TT; t++) accf[t] = 0.0f;
-        if (cur.nst == 0 && !nxt_claimed) {   // nothing to do for this group: claim the next right away
-            if (tid == 0) s_item[n_fetch & 1] = (int)(gridDim.x + atomicAdd(A.work_ctr, 1u));
-            __syncthreads();
-            nxt = fetch();
-            nxt_claimed = 1;
-            pump();
-        }
-        int ks = 0, chunk = cur.chunk0;   // the stage's K-slice inside its chunk, and the chunk
-        for (int s = 0; s < cur.nst; s++) {
-            const bool claim = !nxt_claimed && cur.nst - s <= EX_LEAD;
-            if (claim && tid == 0) pf = (int)(gridDim.x + atomicAdd(A.work_ctr, 1u));
-            const int slot = consumed & 1;
-            if (!mbar_wait_bounded(&mbar[slot], (consumed >> 1) & 1, A.wait_hint_ns)) {
-                // every thread waits on the same barrier, so all give up together: flag
-                // it, give the other slot's copies the same bounded wait, leave
-                if (tid == 0) atomicExch(A.status, BIVMOE_ERR_TIMEOUT);
-                if (issued > consumed + 1)
-                    mbar_wait_bounded(&mbar[slot ^ 1], ((consumed + 1) >> 1) & 1, A.wait_hint_ns);
-                return;
-            }
-            const uint8_t* st = ring + (size_t)slot * SB;
-            const uint8_t* act = st + W_BYTES;
-            if constexpr (F::F32ACT) {
-                // a lane per weight row: GATEUP lanes 0-15 gate rows, 16-31 up rows
-                const uint8_t* wrow;
-                if (MODE == MODE_GATEUP) wrow = st + (row_of[lane >> 4] + (lane & 15)) * 16;
-                else wrow = st + (32 * warp + lane) * 16;
-                F::compute_f32(wrow, (const float*)act, cur.tc, accf);
-            } else {
-                uint32_t rowp[2][2];
-                const uint32_t sta = ring_a + (uint32_t)slot * SB;
+            Side side{};
+            if constexpr (TY == BIVMOE_Q6_K) {
+                const DevTiles& m = shared ? A.sh : A.w;
+                const size_t base = ((size_t)(shared ? 0 : d.expert) * m.chunks + d.chunk) * kChunkRows;
 #pragma unroll
                 for (int mt = 0; mt < 2; mt++)
 #pragma unroll
                     for (int r = 0; r < 2; r++)
-                        rowp[mt][r] = sta + (row_of[mt] + g + 8 * r) * 16;
-                F::compute(rowp, slot ? side1 : side0, sta + W_BYTES, acc, g, c);
+                        side.d[mt][r] = __half2float(__ushort_as_half(
+                            m.side[(base + row_of[mt] + g + 8 * r) * m.nslices + d.slice]));
             }
-            if (claim && tid == 0) s_item[n_fetch & 1] = pf;
-            __syncthreads();   // every warp is done with the slot; the claimed value is visible
-            consumed++;
-            if (claim) {
-                nxt = fetch();
-                nxt_claimed = 1;
-            }
-            pump();
-            if (++ks < cur.nsl) continue;
-            // ---- epilogue of the chunk that just ended
-            const int rows = (cur.shared ? A.sh : A.w).rows;
-            if (MODE == MODE_GATEUP) {
-                // SwiGLU into the staging tile [token][64 rows of the chunk]
-                if constexpr (F::F32ACT) {
-#pragma unroll
-                    for (int t = 0; t < EX_TT; t++) {
-                        const float u = __shfl_down_sync(0xffffffffu, accf[t], 16);
-                        if (lane < 16) {
-                            const float gt = accf[t];
-                            s_mid[t * 64 + 16 * warp + lane] = (gt * __fdiv_rn(1.0f, 1.0f + expf(-gt))) * u;
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        // ops.rs:160-167: silu(x) = x * (1 / (1 + exp(-x)))
-                        const float gt = acc[0][i], u = acc[1][i];
-                        s_mid[(2 * c + (i & 1)) * 64 + 16 * warp + g + 8 * (i >> 1)] =
-                            (gt * __fdiv_rn(1.0f, 1.0f + expf(-gt))) * u;
-                    }
-                }
-                __syncthreads();
-                // rows of mid: f32 (slice-major by 64) and, for quantised down types, the
-                // Q8Act of each 32-row block (quant.rs:368-394); one warp per (token, block)
-                for (int p = warp; p < 2 * cur.tc; p += EX_THREADS / 32) {
-                    const int t = p >> 1, blk = p & 1;
-                    const float v = s_mid[t * 64 + 32 * blk + lane];
-                    const int r = chunk * CH + 32 * blk + lane;
-                    const size_t pos = cur.pos0 + t;
-                    A.out[((size_t)(r / 64) * A.act_rows + pos) * 64 + r % 64] = v;
-                    if (A.out_t) {
-                        float dd, ss;
-                        const int q = q8_quantize_lane(v, dd, ss);
-                        uint8_t* rec = A.out_t + ((size_t)(r / 256) * (A.act_rows / 8) + pos / 8) * kActTileBytes;
-                        rec[act_q_off((int)(pos % 8), r % 256)] = (uint8_t)(int8_t)q;
-                        if (lane < 4) {
-                            float shi, slo;
-                            split_tf32(ss, &shi, &slo);
-                            const float val = lane == 0 ? dd : lane == 1 ? shi : lane == 2 ? slo : ss;
-                            *(float*)(rec + kActOffDx + 256 * lane + (((r % 256) / 32) * 8 + pos % 8) * 4) = val;
-                        }
-                    }
-                }
-                // s_mid is rewritten after the next chunk's stages, which have barriers
-            } else {
-                if constexpr (F::F32ACT) {
-#pragma unroll
-                    for (int t = 0; t < EX_TT; t++)
-                        if (t < cur.tc)
-                            A.out[(size_t)(cur.pos0 + t) * rows + chunk * CH + 32 * warp + lane] = accf[t];
-                } else {
-#pragma unroll
-                    for (int mt = 0; mt < 2; mt++)
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            const int t = 2 * c + (i & 1);
-                            if (t < cur.tc)
-                                A.out[(size_t)(cur.pos0 + t) * rows + chunk * CH + 32 * warp + 16 * mt +
-                                      g + 8 * (i >> 1)] = acc[mt][i];
-                        }
-                }
-            }
+            uint32_t rowp[2][2];
 #pragma unroll
             for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) acc[mt][i] = 0.0f;
-#pragma unroll
-            for (int t = 0; t < EX_TT; t++) accf[t] = 0.0f;
-            ks = 0;
-            chunk++;
+                for (int r = 0; r < 2; r++) rowp[mt][r] = sta + (row_of[mt] + g + 8 * r) * 16;
+            F::compute(rowp, side, sta + W_BYTES, *(float(*)[2][4])acc, g, c);
         }
-        if (!nxt.valid) break;
-        // the stream may already run inside `nxt`: it becomes the current item
-        cur = nxt;
-        nxt.valid = 0;
-        nxt.nst = 0;
-        nxt_claimed = 0;
-        if (p_in_next) p_in_next = 0;
-        else p_stage = 0;
-        pump();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[bi]);   // this warp is done with the slot
+        if (!(d.flags & SD_LAST)) continue;
+
+        // ---- the chunk is complete
+        if (MODE == MODE_GATEUP) {
+            // SwiGLU into the staging tile [token][64 rows of the chunk]
+            if constexpr (F::F32ACT) {
+#pragma unroll
+                for (int t = 0; t < EX_TT; t++) {
+                    const float u = __shfl_down_sync(0xffffffffu, acc[t], 16);
+                    if (lane < 16) {
+                        const float gt = acc[t];
+                        s_mid[t * 64 + 16 * wig + lane] = (gt * __fdiv_rn(1.0f, 1.0f + expf(-gt))) * u;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    // ops.rs:160-167: silu(x) = x * (1 / (1 + exp(-x)))
+                    const float gt = acc[i], u = acc[4 + i];
+                    s_mid[(2 * c + (i & 1)) * 64 + 16 * wig + g + 8 * (i >> 1)] =
+                        (gt * __fdiv_rn(1.0f, 1.0f + expf(-gt))) * u;
+                }
+            }
+            group_sync(grp);
+            // rows of mid: f32 (slice-major by 64) and, for quantised down types, the
+            // Q8Act of each 32-row block (quant.rs:368-394); one warp per (token, block)
+            for (int p = wig; p < 2 * d.tc; p += 4) {
+                const int t = p >> 1, blk = p & 1;
+                const float v = s_mid[t * 64 + 32 * blk + lane];
+                const int r = d.chunk * CH + 32 * blk + lane;
+                const size_t pos = d.pos0 + t;
+                A.out[((size_t)(r / 64) * A.act_rows + pos) * 64 + r % 64] = v;
+                if (A.out_t) {
+                    float dd, ss;
+                    const int qv = q8_quantize_lane(v, dd, ss);
+                    uint8_t* rec = A.out_t + ((size_t)(r / 256) * (A.act_rows / 8) + pos / 8) * kActTileBytes;
+                    rec[act_q_off((int)(pos % 8), r % 256)] = (uint8_t)(int8_t)qv;
+                    if (lane < 4) {
+                        float shi, slo;
+                        split_tf32(ss, &shi, &slo);
+                        const float val = lane == 0 ? dd : lane == 1 ? shi : lane == 2 ? slo : ss;
+                        *(float*)(rec + kActOffDx + 256 * lane + (((r % 256) / 32) * 8 + pos % 8) * 4) = val;
+                    }
+                }
+            }
+            group_sync(grp);   // the staging tile is free for the group's next chunk
+        } else {
+            if constexpr (F::F32ACT) {
+#pragma unroll
+                for (int t = 0; t < EX_TT; t++)
+                    if (t < d.tc)
+                        A.out[(size_t)(d.pos0 + t) * d.rows + d.chunk * CH + 32 * wig + lane] = acc[t];
+            } else {
+#pragma unroll
+                for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int t = 2 * c + (i & 1);
+                        if (t < d.tc)
+                            A.out[(size_t)(d.pos0 + t) * d.rows + d.chunk * CH + 32 * wig + 16 * mt + g +
+                                  8 * (i >> 1)] = acc[4 * mt + i];
+                    }
+            }
+        }
     }
 }
 
@@ -883,12 +901,13 @@ template <int TY, int MODE>
 static cudaError_t launch_one(const LaunchCfg& c, ExpertArgs A) {
     A.chunks = std::max(A.w.chunks, A.sh.chunks);
     constexpr int smem = smem_bytes<TY>();
-    static_assert(smem * Fmt<TY>::MINB <= 227 * 1024, "the blocks of one SM must fit in shared memory");
+    static_assert(smem <= EX_SMEM_MAX, "the block must fit in shared memory");
     static std::atomic<uint64_t> attr_set{0};
     if (cudaError_t e = ensure_dynamic_smem(experts_kernel<TY, MODE>, smem, attr_set)) return e;
-    experts_kernel<TY, MODE><<<c.sm_count * Fmt<TY>::MINB, EX_THREADS, smem, c.stream>>>(A);
+    constexpr int threads = 32 * (4 * Fmt<TY>::MINB + 1);
+    cudaError_t e = launch_after(c.stream, experts_kernel<TY, MODE>, dim3(c.sm_count), dim3(threads), smem, A);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 template <int MODE>

@@ -39,6 +39,7 @@
 #include "common.cuh"
 #include "formats.cuh"
 #include "tcgen05.cuh"
+#include "launch.cuh"
 
 namespace bivmoe {
 
@@ -87,6 +88,7 @@ struct PfItem {
 template <int MODE>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 experts_prefill_kernel(const PrefillArgs A) {
+    pdl_launch_dependents();
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* full = (uint64_t*)smem;            // [2] copies landed
     uint64_t* empty = full + 2;                  // [2] stage free: MMAs done + the epilogue warps
@@ -125,6 +127,7 @@ experts_prefill_kernel(const PrefillArgs A) {
     __syncthreads();
     pf_fence_after();
     const uint32_t tmem = *s_tmem;
+    pdl_wait();   // the tile lists and the activation records are the previous kernels'
 
     const int tiles_all = A.n_ptiles[0], tiles_sh = A.n_ptiles[1];
     const int tile_lo = A.tiles_mode == 1 ? tiles_sh : 0;
@@ -343,9 +346,8 @@ static cudaError_t launch_prefill_one(const LaunchCfg& c, PrefillArgs A) {
     A.chunks = std::max(A.w.chunks, A.sh.chunks);
     static std::atomic<uint64_t> attr_set{0};
     if (cudaError_t e = ensure_dynamic_smem(experts_prefill_kernel<MODE>, (int)PF_SMEM, attr_set)) return e;
-    experts_prefill_kernel<MODE><<<c.sm_count, PF_THREADS, PF_SMEM, c.stream>>>(A);
     count_launch();
-    return cudaGetLastError();
+    return launch_after(c.stream, experts_prefill_kernel<MODE>, dim3(c.sm_count), dim3(PF_THREADS), PF_SMEM, A);
 }
 
 // gate+up then down for the groups the sort put on the prefill tile list

@@ -35,6 +35,7 @@
 
 #include "common.cuh"
 #include "tcgen05.cuh"
+#include "launch.cuh"
 
 namespace bivmoe {
 
@@ -83,6 +84,7 @@ struct BfItem {
 template <int MODE>
 __global__ void __launch_bounds__(BF_THREADS, 1)
 experts_prefill_bf16_kernel(const Bf16Args A) {
+    pdl_launch_dependents();
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* full = (uint64_t*)smem;            // [3] copies landed
     uint64_t* empty = full + 4;                  // [3] stage free: its MMAs are done
@@ -121,6 +123,7 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
     __syncthreads();
     pf_fence_after();
     const uint32_t tmem = *s_tmem;
+    pdl_wait();   // the tile lists and the activation records are the previous kernels'
 
     const int tiles_all = A.n_ptiles[0], tiles_sh = A.n_ptiles[1];
     const int tile_lo = A.tiles_mode == 1 ? tiles_sh : 0;
@@ -305,9 +308,8 @@ static cudaError_t launch_bf16_one(const LaunchCfg& c, Bf16Args A) {
     A.chunks = std::max(A.w.chunks, A.sh.chunks);
     static std::atomic<uint64_t> attr_set{0};
     if (cudaError_t e = ensure_dynamic_smem(experts_prefill_bf16_kernel<MODE>, (int)BF_SMEM, attr_set)) return e;
-    experts_prefill_bf16_kernel<MODE><<<c.sm_count, BF_THREADS, BF_SMEM, c.stream>>>(A);
     count_launch();
-    return cudaGetLastError();
+    return launch_after(c.stream, experts_prefill_bf16_kernel<MODE>, dim3(c.sm_count), dim3(BF_THREADS), BF_SMEM, A);
 }
 
 // gate+up then down for the groups the sort put on the prefill tile list

@@ -4,6 +4,7 @@
 // engine/src/quant.rs:1177-1206 (the AVX2 f32 dot whose summation order the
 // logits kernel reproduces bit for bit).
 #include "common.cuh"
+#include "launch.cuh"
 
 namespace bivmoe {
 
@@ -32,6 +33,7 @@ __global__ void __launch_bounds__(RT_THREADS, 1)
 router_logits_kernel(const float* __restrict__ W, const float* __restrict__ h,
                      float* __restrict__ logits, int n, int e, int n_rows, int* status,
                      const float* __restrict__ norm_w, float norm_eps, float* __restrict__ row_scale) {
+    pdl_enter();
     extern __shared__ __align__(128) uint8_t rt_smem[];
     uint64_t* bar = (uint64_t*)rt_smem;
     float* s_w = (float*)(rt_smem + 128);              // [RT_BROWS][e]
@@ -156,6 +158,7 @@ __device__ __forceinline__ void rl_reduce_step(float (&acc)[RL_ROWS * RL_TOKS], 
 __global__ void __launch_bounds__(RT_THREADS, 1)
 router_logits_tiled_kernel(const float* __restrict__ W, const float* __restrict__ h,
                            float* __restrict__ logits, int n, int e, int n_rows) {
+    pdl_enter();
     extern __shared__ __align__(128) uint8_t rt_smem[];
     float* ring = (float*)(rt_smem + 128);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -245,20 +248,18 @@ cudaError_t launch_router(const LaunchCfg& c, const float* router_dev, const flo
         static std::atomic<uint64_t> attr_set{0};
         if (cudaError_t err = ensure_dynamic_smem(router_logits_tiled_kernel, RL_SMEM, attr_set)) return err;
         dim3 grid((n_rows + RL_BROWS - 1) / RL_BROWS, (c.n + RL_BTOKS - 1) / RL_BTOKS);
-        router_logits_tiled_kernel<<<grid, RT_THREADS, RL_SMEM, c.stream>>>(router_dev, h, ws.logits, c.n,
-                                                                           c.e, n_rows);
         count_launch();
-        return cudaGetLastError();
+        return launch_after(c.stream, router_logits_tiled_kernel, grid, dim3(RT_THREADS), RL_SMEM, router_dev, h,
+                            ws.logits, c.n, c.e, n_rows);
     }
     const int smem = 128 + (RT_BROWS + RT_BTOKS) * c.e * 4;
     static std::atomic<uint64_t> attr_set{0};
     if (cudaError_t err = ensure_dynamic_smem(router_logits_kernel, 227 * 1024, attr_set)) return err;
     dim3 grid((n_rows + RT_BROWS - 1) / RT_BROWS, (c.n + RT_BTOKS - 1) / RT_BTOKS);
-    router_logits_kernel<<<grid, RT_THREADS, smem, c.stream>>>(router_dev, h, ws.logits, c.n, c.e,
-                                                               n_rows, ws.status, norm ? norm->w : nullptr,
-                                                               norm ? norm->eps : 0.0f, ws.row_scale);
     count_launch();
-    return cudaGetLastError();
+    return launch_after(c.stream, router_logits_kernel, grid, dim3(RT_THREADS), smem, router_dev, h, ws.logits, c.n,
+                        c.e, n_rows, ws.status, norm ? norm->w : (const float*)nullptr,
+                        norm ? norm->eps : 0.0f, ws.row_scale);
 }
 
 // ---------------------------------------------------------------------------
@@ -278,6 +279,7 @@ __device__ __forceinline__ int tk_total_key(int bits) { return bits ^ (int)(((ui
 __global__ void __launch_bounds__(TK_WARPS * 32)
 route_topk_kernel(const float* __restrict__ logits, int32_t* __restrict__ ids,
                   float* __restrict__ weights, int n, int n_expert, int k) {
+    pdl_enter();
     extern __shared__ float tk_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x * TK_WARPS + warp;
@@ -340,10 +342,9 @@ route_topk_kernel(const float* __restrict__ logits, int32_t* __restrict__ ids,
 cudaError_t launch_route_topk(const LaunchCfg& c, const Workspace& ws) {
     if (c.n_expert > TK_MAX_EXPERTS || c.k > TK_MAX_K) return cudaErrorInvalidValue;
     size_t smem = (size_t)TK_WARPS * c.n_expert * sizeof(float);
-    route_topk_kernel<<<(c.n + TK_WARPS - 1) / TK_WARPS, TK_WARPS * 32, smem, c.stream>>>(
-        ws.logits, ws.ids, ws.weights, c.n, c.n_expert, c.k);
     count_launch();
-    return cudaGetLastError();
+    return launch_after(c.stream, route_topk_kernel, dim3((c.n + TK_WARPS - 1) / TK_WARPS), dim3(TK_WARPS * 32),
+                        smem, (const float*)ws.logits, ws.ids, ws.weights, c.n, c.n_expert, c.k);
 }
 
 // ---------------------------------------------------------------------------
@@ -536,6 +537,7 @@ __device__ void sort_scatter(const Workspace& ws, const uint16_t* s_ids, const u
 __global__ void __launch_bounds__(SORT_THREADS)
 sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int prefill_min, int ptile,
             int phase) {
+    pdl_enter();
     extern __shared__ uint8_t sort_smem[];
     uint16_t* s_ids = (uint16_t*)sort_smem;
     int* s_cnt = (int*)(sort_smem + (((size_t)SORT_TOKENS * k * 2 + 15) & ~(size_t)15));
@@ -575,16 +577,18 @@ cudaError_t launch_sort(const LaunchCfg& c, const Workspace& ws) {
                   (size_t)c.n_expert * (SORT_TOKENS / 32) * 4;   // <= 16 + 4 + 32 KiB
     static std::atomic<uint64_t> attr_set{0};
     if (cudaError_t err = ensure_dynamic_smem(sort_kernel, 64 * 1024, attr_set)) return err;
+    auto phase = [&](int blocks, int ph) {
+        return launch_after(c.stream, sort_kernel, dim3(blocks), dim3(SORT_THREADS), smem, ws, c.n, c.k, c.n_expert,
+                            c.has_shared, c.prefill_min, c.prefill_tile, ph);
+    };
     if (nblk == 1) {
-        sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, c.prefill_tile, 0);
         count_launch();
-    } else {
-        sort_kernel<<<nblk, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, c.prefill_tile, 1);
-        sort_kernel<<<1, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, c.prefill_tile, 2);
-        sort_kernel<<<nblk, SORT_THREADS, smem, c.stream>>>(ws, c.n, c.k, c.n_expert, c.has_shared, c.prefill_min, c.prefill_tile, 3);
-        count_launch(3);
+        return phase(1, 0);
     }
-    return cudaGetLastError();
+    count_launch(3);
+    if (cudaError_t err = phase(nblk, 1)) return err;
+    if (cudaError_t err = phase(1, 2)) return err;
+    return phase(nblk, 3);
 }
 
 }  // namespace bivmoe

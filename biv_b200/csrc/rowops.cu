@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "formats.cuh"
+#include "launch.cuh"
 
 namespace bivmoe {
 
@@ -43,6 +44,7 @@ __global__ void __launch_bounds__(DP_THREADS)
 dispatch_q8_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int has_shared,
                    const float* __restrict__ norm_w) {
     __shared__ int s_pos[DP_MAX_K + 1], s_big[DP_MAX_K + 1];
+    pdl_enter();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int R = ws.act_rows;
     dispatch_positions(ws, t, n, k, 0, has_shared, 0, s_pos, s_big);
@@ -99,6 +101,7 @@ __global__ void __launch_bounds__(DP_THREADS)
 dispatch_f32_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int has_shared,
                     int prefill_min, const float* __restrict__ norm_w) {
     __shared__ int s_pos[DP_MAX_K + 1], s_big[DP_MAX_K + 1];
+    pdl_enter();
     const int t = blockIdx.x;
     const int R = ws.act_rows;
     dispatch_positions(ws, t, n, k, 0, has_shared, ws.act_b ? prefill_min : 0, s_pos, s_big);
@@ -177,6 +180,7 @@ __global__ void __launch_bounds__(DP_THREADS)
 dispatch_pos_f32_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int n_expert,
                         int has_shared, int prefill_min) {
     __shared__ int s_tok[8], s_big;
+    pdl_enter();
     const int pos0 = blockIdx.x * 8;
     if (!dispatch_tile(ws, pos0, n, k, n_expert, has_shared, ws.act_b ? prefill_min : 0, s_tok, &s_big))
         return;
@@ -218,19 +222,23 @@ cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace&
     if (norm && c.n >= DP_MIN_TOKENS) return cudaErrorInvalidValue;   // the by-position kernel reads normed rows
     const float* nw = norm ? norm->w : nullptr;
     if (quant) {
-        dispatch_q8_kernel<<<dim3(c.n, 2), DP_THREADS, 0, c.stream>>>(h, ws, c.n, c.k, c.e, c.has_shared, nw);
+        if (cudaError_t err = launch_after(c.stream, dispatch_q8_kernel, dim3(c.n, 2), dim3(DP_THREADS), 0, h, ws,
+                                           c.n, c.k, c.e, c.has_shared, nw))
+            return err;
         count_launch();
     }
     if (f32 && c.n >= DP_MIN_TOKENS) {
         // an upper bound of the tiles in use; blocks past the last group return at once
         const int shared_tiles = c.has_shared ? (c.n + 7) / 8 : 0;
         const int tiles = c.k == 0 ? shared_tiles : shared_tiles + (c.n * c.k) / 8 + c.n_expert;
-        dispatch_pos_f32_kernel<<<tiles, DP_THREADS, 0, c.stream>>>(h, ws, c.n, max(c.k, 1), c.e, c.n_expert,
-                                                                    c.has_shared, c.prefill_min);
+        if (cudaError_t err = launch_after(c.stream, dispatch_pos_f32_kernel, dim3(tiles), dim3(DP_THREADS), 0, h, ws,
+                                           c.n, max(c.k, 1), c.e, c.n_expert, c.has_shared, c.prefill_min))
+            return err;
         count_launch();
     } else if (f32) {
-        dispatch_f32_kernel<<<c.n, DP_THREADS, 0, c.stream>>>(h, ws, c.n, c.k, c.e, c.has_shared,
-                                                             c.prefill_min, nw);
+        if (cudaError_t err = launch_after(c.stream, dispatch_f32_kernel, dim3(c.n), dim3(DP_THREADS), 0, h, ws, c.n,
+                                           c.k, c.e, c.has_shared, c.prefill_min, nw))
+            return err;
         count_launch();
     }
     return cudaGetLastError();
@@ -242,6 +250,7 @@ cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace&
 __global__ void __launch_bounds__(128)
 rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
                 float* __restrict__ out, int n, int e) {
+    pdl_enter();
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= n) return;
@@ -261,9 +270,8 @@ rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float 
 
 cudaError_t launch_rms_norm(const LaunchCfg& c, const float* x, const float* w, float eps,
                             float* out) {
-    rms_norm_kernel<<<(c.n + 3) / 4, 128, 0, c.stream>>>(x, w, eps, out, c.n, c.e);
     count_launch();
-    return cudaGetLastError();
+    return launch_after(c.stream, rms_norm_kernel, dim3((c.n + 3) / 4), dim3(128), 0, x, w, eps, out, c.n, c.e);
 }
 
 // ---------------------------------------------------------------------------
@@ -295,6 +303,7 @@ combine_kernel(const int32_t* __restrict__ ids, const float* __restrict__ weight
     __shared__ float s_w[CB_MAX_K];
     __shared__ float s_gate;
     __shared__ int s_valid;
+    pdl_enter();
     const int t = blockIdx.x;
     if (PEER && t % pd.lay.cap >= pd.counts[t / pd.lay.cap]) return;   // the whole block
     if (threadIdx.x == 0) s_valid = 0;
@@ -349,12 +358,10 @@ combine_kernel(const int32_t* __restrict__ ids, const float* __restrict__ weight
 cudaError_t launch_combine(const LaunchCfg& c, const CombineSrc& src, float* out, int accumulate) {
     if (c.k > CB_MAX_K || c.e % 4) return cudaErrorInvalidValue;
     dim3 grid(c.n, (c.e / 4 + CB_THREADS - 1) / CB_THREADS);
-    combine_kernel<false><<<grid, CB_THREADS, 0, c.stream>>>(src.ids, src.weights, src.routed_rows,
-                                                             src.routed_pos, src.shared_rows, src.logits, out,
-                                                             c.n, c.k, c.e, c.n_expert, c.has_shared,
-                                                             accumulate, PeerDest{});
     count_launch();
-    return cudaGetLastError();
+    return launch_after(c.stream, combine_kernel<false>, grid, dim3(CB_THREADS), 0, src.ids, src.weights,
+                        src.routed_rows, src.routed_pos, src.shared_rows, src.logits, out, c.n, c.k, c.e,
+                        c.n_expert, c.has_shared, accumulate, PeerDest{});
 }
 
 cudaError_t launch_combine_to_peers(const LaunchCfg& c, const CombineSrc& src, const uint8_t* block, int me,
@@ -362,11 +369,10 @@ cudaError_t launch_combine_to_peers(const LaunchCfg& c, const CombineSrc& src, c
     if (c.k > CB_MAX_K || c.e % 4) return cudaErrorInvalidValue;
     dim3 grid(c.n, (c.e / 4 + CB_THREADS - 1) / CB_THREADS);
     const PeerDest pd{peers, lay, (const int32_t*)(block + lay.counts), me};
-    combine_kernel<true><<<grid, CB_THREADS, 0, c.stream>>>(src.ids, src.weights, src.routed_rows,
-                                                            src.routed_pos, src.shared_rows, src.logits, nullptr,
-                                                            c.n, c.k, c.e, c.n_expert, c.has_shared, 0, pd);
     count_launch();
-    return cudaGetLastError();
+    return launch_after(c.stream, combine_kernel<true>, grid, dim3(CB_THREADS), 0, src.ids, src.weights,
+                        src.routed_rows, src.routed_pos, src.shared_rows, src.logits, (float*)nullptr, c.n, c.k,
+                        c.e, c.n_expert, c.has_shared, 0, pd);
 }
 
 // ---------------------------------------------------------------------------

@@ -184,6 +184,15 @@ def test_other_weight_types(gate_ty, down_ty, n):
     run_case(W.typed_layer(gate_ty, down_ty, n=n, **W.SMALL))
 
 
+@pytest.mark.parametrize("gate_ty,down_ty", [(W.Q5_K, W.Q6_K), (W.Q6_K, W.Q5_K), (W.Q8_0, W.Q4_K),
+                                             (W.BF16, W.F32), (W.F32, W.F16)])
+def test_every_decode_kernel_at_the_model_shape(gate_ty, down_ty):
+    # hidden 2048 and ff 512 as in the model (8 K-slices per gate+up chunk, 2 per down
+    # chunk), fewer experts: every weight type's decode kernel in both products, with the
+    # consumer-group counts and ring sizes the type gets at these sizes
+    run_case(W.typed_layer(gate_ty, down_ty, n=40, n_expert=16, k=4))
+
+
 def test_q4_0_and_q4_1_at_the_model_shape():
     run_case(W.typed_layer(W.Q4_0, W.Q4_1, n=64, n_expert=32))
 
