@@ -80,6 +80,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, ui
         : "memory");
     return ok != 0;
 }
+// One look, without blocking: has the phase of parity `parity` completed?
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Waits for a phase with an iteration limit; false when it gave up.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
     for (uint32_t i = 0; i < EX_WAIT_LIMIT; i++)
@@ -577,13 +589,20 @@ template <> struct Fmt<BIVMOE_F32> : FmtFloat<BIVMOE_F32> {};
 // warp.  A group works on its own items - a tile of up to 8 tokens times one chunk
 // (gate+up) or two chunks (down) - and owns a two-slot ring of stages (one K-slice of a
 // chunk's 128 rows plus the tile's activation record) that lane g of the producer warp
-// keeps full: the lane claims the group's next item from the counter the sort kernel
-// resets, and issues its stages as slots come free.  A consumer warp waits for a slot,
+// keeps full: the lane takes the group's next item from the block's own list - item i of
+// a launch belongs to block i mod gridDim.x, so every SM gets the same number of (equal)
+// items give or take one, and the groups of a block share its list through a counter in
+// shared memory - and issues its stages as slots come free.  (Claiming from one global
+// counter instead left the SMs unevenly loaded at the end: measured 33 k to 69 k active
+// cycles per SM, because an SM's groups share its issue slots and an SM that happened to
+// claim four late items took twice as long over them as one that claimed two.)  A consumer warp waits for a slot,
 // computes its 32 rows of the stage, and hands the slot back with one mbarrier arrive:
 // the consumer warps never meet per stage and carry no pipeline state - everything a
 // stage needs to know (tile, chunk, whether it opens or closes an accumulation) comes in
 // a small descriptor the producer writes beside it.  The groups of a block share nothing
 // but the producer warp, so one group's epilogue overlaps the others' products.
+// The producer lanes never block: they stay together and poll their groups' slots in turn,
+// so no lane's wait holds up the lanes of the other groups.
 // Every wait is bounded; a wait that gives up records BIVMOE_ERR_TIMEOUT (and which wait
 // it was) in the status words and raises a block-wide flag on which every role leaves its
 // loop (the producer first waits, bounded again, for its copies still in flight).
@@ -648,6 +667,7 @@ experts_kernel(const ExpertArgs A) {
     uint64_t* full = (uint64_t*)smem;                 // [G][2] a stage has landed
     uint64_t* empty = full + G * EX_SLOTS;            // [G][2] its four warps are done with it
     int* s_abort = (int*)(smem + 256);
+    int* s_next = (int*)(smem + 260);                 // the block's next unclaimed item (index in its list)
     StageDesc* s_desc = (StageDesc*)(smem + 512);     // [G][2]
     float* s_mid_all = (float*)(smem + EX_HEAD);      // [G][EX_TT][64] SwiGLU staging
     uint8_t* ring = (uint8_t*)(s_mid_all + G * EX_TT * 64);   // [G][2][SB]
@@ -660,6 +680,7 @@ experts_kernel(const ExpertArgs A) {
             mbar_init(&empty[i], 4);
         }
         *s_abort = 0;
+        *s_next = G;   // the first G items of the list are the groups' first items
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -680,78 +701,98 @@ experts_kernel(const ExpertArgs A) {
 
     if (warp == 4 * G) {
         // ------------------------------------------------------------ producer warp
-        // lane g feeds group g; the lanes share nothing and go their own ways
+        // lane g feeds group g
         if (lane >= G) return;
         const int tiles_all = A.n_tiles[0], tiles_sh = A.n_tiles[1];
         const int tile_lo = A.tiles_mode == 1 ? tiles_sh : 0;
         const int tile_hi = A.tiles_mode == 2 ? tiles_sh : tiles_all;
         // an item is a tile times one chunk: 8 stages (gate+up), 2 stages (down) at the qwen35moe shapes
-        const int total = (tile_hi - tile_lo) * A.chunks;
-        const int units = total;
+        const int units = (tile_hi - tile_lo) * A.chunks;
+        // The lanes stay together: every turn of the loop each lane looks once (without
+        // blocking) whether its group has a free slot and, if so, issues its next stage, so
+        // no group waits for another lane's wait to end.  A turn without progress in any
+        // lane sleeps 64 ns; 2^20 such turns in a row (about 70 ms) end the kernel.
+        constexpr uint32_t LANES = (1u << G) - 1u;
         uint32_t issued = 0;      // stages this lane has given its group
-        bool dead = false;
-        // the first items need no counter (group g of block b starts with item b * G + g);
-        // later claims follow the grid
-        int idx = (int)blockIdx.x * G + lane;
-        while (idx < units && !dead) {
-            Item it;
-            const int tile = tile_lo + idx / A.chunks;
-            it.chunk0 = idx % A.chunks;
-            const int4 td = A.tile_desc[tile];
-            it.expert = td.x;
-            it.shared = it.expert == A.n_expert;
-            it.pos0 = td.y;
-            it.tc = td.z;
-            const DevTiles& m = it.shared ? A.sh : A.w;
-            it.nsl = m.nslices;
-            it.nch = it.chunk0 < m.chunks ? 1 : 0;
-            it.rows = m.rows;
-            it.src = m.stage(it.shared ? 0 : it.expert, min(it.chunk0, max(m.chunks - 1, 0)), 0);
-            const int s0 = 0, s1 = it.nch ? it.nsl : 0;
-            for (int slice = s0; slice < s1 && !dead; slice++) {
+        Item it;
+        it.nsl = 0;
+        int slice = 0, s1 = 0;    // next K-slice of the lane's item, and its end
+        int first = 1, ending = 0, done = 0;
+        uint32_t idle = 0;
+        while (true) {
+            int progressed = 0;
+            if (!done && !ending && slice >= s1) {
+                // the block's list: items blockIdx.x, blockIdx.x + gridDim.x, ...; group g
+                // starts with entry g, later entries go to whichever group is ready first
+                const int entry = first ? lane : atomicAdd(s_next, 1);
+                first = 0;
+                const int idx = (int)blockIdx.x + entry * (int)gridDim.x;
+                if (idx >= units) {
+                    ending = 1;
+                } else {
+                    const int tile = tile_lo + idx / A.chunks;
+                    it.chunk0 = idx % A.chunks;
+                    const int4 td = A.tile_desc[tile];
+                    it.expert = td.x;
+                    it.shared = it.expert == A.n_expert;
+                    it.pos0 = td.y;
+                    it.tc = td.z;
+                    const DevTiles& m = it.shared ? A.sh : A.w;
+                    it.nsl = m.nslices;
+                    it.nch = it.chunk0 < m.chunks ? 1 : 0;
+                    it.rows = m.rows;
+                    it.src = m.stage(it.shared ? 0 : it.expert, min(it.chunk0, max(m.chunks - 1, 0)), 0);
+                    slice = 0;
+                    s1 = it.nch ? it.nsl : 0;
+                }
+                progressed = 1;
+            }
+            if (!done && (ending || slice < s1)) {
                 const int bi = lane * EX_SLOTS + (int)(issued & 1);
-                if (!wait(&empty[bi], ((issued >> 1) & 1) ^ 1)) {
-                    give_up(SITE_PRODUCER_SLOT);
-                    dead = true;
-                    break;
+                if (mbar_test_wait(&empty[bi], ((issued >> 1) & 1) ^ 1)) {
+                    if (ending) {   // the end marker: a stage without data
+                        StageDesc d{};
+                        d.flags = SD_END;
+                        s_desc[bi] = d;
+                        mbar_arrive(&full[bi]);
+                        done = 1;
+                    } else {
+                        StageDesc d;
+                        d.pos0 = it.pos0; d.tc = it.tc; d.chunk = it.chunk0; d.slice = slice;
+                        d.expert = it.shared ? A.n_expert : it.expert; d.rows = it.rows;
+                        d.flags = (slice == 0 ? SD_FIRST : 0) | (slice == s1 - 1 ? SD_LAST : 0);
+                        d.pad = 0;
+                        s_desc[bi] = d;
+                        uint8_t* dst = ring + (size_t)bi * SB;
+                        fence_proxy_async();   // the slot was last read through the generic proxy
+                        mbar_expect_tx(&full[bi], W_BYTES + ACT_BYTES);
+                        bulk_g2s(dst, it.src + (size_t)slice * W_BYTES, W_BYTES, &full[bi]);
+                        uint8_t* adst = dst + W_BYTES;
+                        if (F::F32ACT) {
+                            const size_t row = (size_t)slice * A.act_rows + it.pos0;
+                            bulk_g2s(adst, A.x_f32 + row * F::ELEMS, EX_TT * F::ELEMS * 4, &full[bi]);
+                        } else {   // the tile's Q8 record of this K-slice (pos0 is a multiple of 8)
+                            bulk_g2s(adst, A.x_t + ((size_t)slice * (A.act_rows / 8) + it.pos0 / 8) * kActTileBytes,
+                                     kActCopyBytes, &full[bi]);
+                        }
+                        issued++;
+                        slice++;
+                    }
+                    progressed = 1;
                 }
-                StageDesc d;
-                d.pos0 = it.pos0; d.tc = it.tc; d.chunk = it.chunk0; d.slice = slice;
-                d.expert = it.shared ? A.n_expert : it.expert; d.rows = it.rows;
-                d.flags = (slice == s0 ? SD_FIRST : 0) | (slice == s1 - 1 ? SD_LAST : 0);
-                d.pad = 0;
-                s_desc[bi] = d;
-                uint8_t* dst = ring + (size_t)bi * SB;
-                fence_proxy_async();   // the slot was last read through the generic proxy
-                mbar_expect_tx(&full[bi], W_BYTES + ACT_BYTES);
-                bulk_g2s(dst, it.src + (size_t)slice * W_BYTES, W_BYTES, &full[bi]);
-                uint8_t* adst = dst + W_BYTES;
-                if (F::F32ACT) {
-                    const size_t row = (size_t)slice * A.act_rows + it.pos0;
-                    bulk_g2s(adst, A.x_f32 + row * F::ELEMS, EX_TT * F::ELEMS * 4, &full[bi]);
-                } else {   // the tile's Q8 record of this K-slice (pos0 is a multiple of 8)
-                    bulk_g2s(adst, A.x_t + ((size_t)slice * (A.act_rows / 8) + it.pos0 / 8) * kActTileBytes,
-                             kActCopyBytes, &full[bi]);
-                }
-                issued++;
             }
-            if (dead || *(volatile int*)s_abort) break;
-            idx = (int)(gridDim.x * G + atomicAdd(A.work_ctr, 1u));
-        }
-        dead = dead || *(volatile int*)s_abort != 0;
-        if (!dead) {   // the end marker: a stage without data
-            const int bi = lane * EX_SLOTS + (int)(issued & 1);
-            if (wait(&empty[bi], ((issued >> 1) & 1) ^ 1)) {
-                StageDesc d{};
-                d.flags = SD_END;
-                s_desc[bi] = d;
-                mbar_arrive(&full[bi]);
+            if (__all_sync(LANES, done)) break;
+            if (*(volatile int*)s_abort) break;
+            if (__any_sync(LANES, progressed)) {
+                idle = 0;
+            } else if (++idle > (1u << 20)) {
+                if (lane == 0) give_up(SITE_PRODUCER_SLOT);
+                break;
             } else {
-                give_up(SITE_END_MARKER);
-                dead = true;
+                __nanosleep(64);
             }
         }
-        if (dead) {    // leave no copy in flight behind: the last two stages this lane issued
+        if (!done) {   // leave no copy in flight behind: the last two stages this lane issued
             for (uint32_t q = issued > 2 ? issued - 2 : 0; q < issued; q++)
                 mbar_wait_bounded(&full[lane * EX_SLOTS + (q & 1)], (q >> 1) & 1, hint);
         }
