@@ -128,6 +128,21 @@ class OraclePeerSteps(OracleSteps):
                 out = self.experts(mine["rows"][src, :c], mine["tags"][src, :c], c)
                 self.blocks[src]["returned"][self.rank, :c] = out   # region [me] of the home's block
 
+    def peer_barrier(self, limit_s=20.0):
+        """The library's barrier restated on the shared-memory blocks: barrier number e
+        (every rank counts its own barriers, the numbers are never exchanged) is signalled
+        by storing e into word [my rank] of every rank's flag array, and waited for by
+        polling this rank's own array until every word has reached e - with a time limit."""
+        import time
+        self.epoch = getattr(self, "epoch", 0) + 1
+        for d in range(self.world):
+            self.blocks[d]["flags"][self.rank] = self.epoch
+        t0 = time.monotonic()
+        mine = self.blocks[self.rank]["flags"]
+        while int(mine.min()) < self.epoch:
+            assert time.monotonic() - t0 < limit_s, "a rank never reached the barrier"
+            time.sleep(0.0005)
+
     def peer_combine(self, out, accumulate):
         ret = self.blocks[self.rank]["returned"]
         packed = torch.cat([ret[d, :int(self.base[d + 1] - self.base[d])] for d in range(self.world)])
@@ -140,7 +155,7 @@ class GlooComm(TorchComm):
         dist.barrier()
 
 
-def _peer_worker(rank, world, port, cfg, rows_per_rank, cap, blocks):
+def _peer_worker(rank, world, port, cfg, rows_per_rank, cap, blocks, lib_barrier=False):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -152,16 +167,18 @@ def _peer_worker(rank, world, port, cfg, rows_per_rank, cap, blocks):
         h = np.ascontiguousarray(w.h[lo:lo + rows_per_rank[rank]])
         steps = OraclePeerSteps(layer, rank, world, blocks, cap)
         out = torch.zeros((h.shape[0], layer.n_embd), dtype=torch.float32)
-        for _ in range(2):      # twice: the regions are reused, the second barrier frees them
-            ep_pass_peer(steps, torch.from_numpy(h), out, False, GlooComm())
+        for _ in range(3):      # several times: the regions are reused, the second barrier frees them
+            ep_pass_peer(steps, torch.from_numpy(h), out, False, GlooComm(), lib_barrier=lib_barrier)
         want = oracle.moe_forward(layer, h)
         np.testing.assert_allclose(out.numpy(), want, rtol=0, atol=4e-7 * float(np.abs(want).max()))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("cfg,rows_per_rank", [("parity_q8_0", (12, 12)), ("ep_bf16", (9, 3))])
-def test_two_gloo_ranks_exchange_through_each_others_blocks(cfg, rows_per_rank):
+@pytest.mark.parametrize("cfg,rows_per_rank,lib_barrier", [("parity_q8_0", (12, 12), False),
+                                                          ("ep_bf16", (9, 3), False),
+                                                          ("decode_q4k", (5, 11), True)])
+def test_two_gloo_ranks_exchange_through_each_others_blocks(cfg, rows_per_rank, lib_barrier):
     import torch.multiprocessing as mp
     world, cap = 2, 16      # regions larger than any rank's rows: the rest is padding
     layer = getattr(wl, cfg)(n=4, **wl.SMALL).layers[0]
@@ -169,9 +186,10 @@ def test_two_gloo_ranks_exchange_through_each_others_blocks(cfg, rows_per_rank):
     blocks = [{"rows": torch.zeros((world, cap, e)).share_memory_(),
                "returned": torch.zeros((world, cap, e)).share_memory_(),
                "tags": torch.zeros((world, cap, 2 * k), dtype=torch.int32).share_memory_(),
-               "counts": torch.zeros((world,), dtype=torch.int32).share_memory_()} for _ in range(world)]
-    mp.spawn(_peer_worker, args=(world, _free_port(), cfg, rows_per_rank, cap, blocks), nprocs=world,
-             join=True)
+               "counts": torch.zeros((world,), dtype=torch.int32).share_memory_(),
+               "flags": torch.zeros((world,), dtype=torch.int32).share_memory_()} for _ in range(world)]
+    mp.spawn(_peer_worker, args=(world, _free_port(), cfg, rows_per_rank, cap, blocks, lib_barrier),
+             nprocs=world, join=True)
 
 
 def _worker(rank, world, port, cfg, n_per_rank):
