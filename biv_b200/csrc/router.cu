@@ -5,6 +5,7 @@
 // logits kernel reproduces bit for bit).
 #include "common.cuh"
 #include "launch.cuh"
+#include "tcgen05.cuh"
 
 namespace bivmoe {
 
@@ -133,7 +134,8 @@ router_logits_kernel(const float* __restrict__ W, const float* __restrict__ h,
 // tokens, a warp 8 rows x 16 tokens (128 accumulators per lane, so 24 shared-
 // memory loads feed 128 multiply-adds), over K in chunks of 128 values that a
 // three-stage ring of 16-byte asynchronous copies keeps in flight (a chunk of
-// one row is 512 bytes: too small for bulk copies to pay).  The per-lane order of the
+// one row is 512 bytes: too small for bulk copies to pay).  The multiply-adds are issued
+// two tokens at a time (fma.rn.f32x2; measured 0.64 -> 0.56 ms at 16 384 tokens).  The per-lane order of the
 // multiply-adds and the order of the final lane sums are those of the small
 // kernel above, so the logits are the same bits.
 constexpr int RL_ROWS = 8, RL_TOKS = 16;              // register tile of one warp
@@ -184,9 +186,11 @@ router_logits_tiled_kernel(const float* __restrict__ W, const float* __restrict_
         else asm volatile("cp.async.commit_group;" ::: "memory");
     }
     const int r0 = (warp & 1) * RL_ROWS, t0 = (warp >> 1) * RL_TOKS;   // inside the block
-    float acc[RL_ROWS * RL_TOKS];
+    // two tokens per multiply-add (fma.rn.f32x2: each half rounds as the scalar form does,
+    // so the logits keep their bits): acc2[r][j] = tokens 2j, 2j+1 of row r
+    f32x2 acc2[RL_ROWS * RL_TOKS / 2];
 #pragma unroll
-    for (int i = 0; i < RL_ROWS * RL_TOKS; i++) acc[i] = 0.0f;
+    for (int i = 0; i < RL_ROWS * RL_TOKS / 2; i++) acc2[i] = 0ull;
     for (int c = 0; c < nchunk; c++) {
         // chunk c has landed (one younger group may still be in flight); after the barrier
         // everyone is also done with chunk c - 1, whose stage chunk c + RL_STAGES - 1 reuses
@@ -200,17 +204,26 @@ router_logits_tiled_kernel(const float* __restrict__ W, const float* __restrict_
 #pragma unroll
         for (int kk = 0; kk < RL_KC / 32; kk++) {
             const int i = kk * 32 + lane;
-            float w[RL_ROWS], x[RL_TOKS];
+            float w[RL_ROWS];
+            f32x2 x2[RL_TOKS / 2];
 #pragma unroll
             for (int r = 0; r < RL_ROWS; r++) w[r] = sw[r * RL_KC + i];
 #pragma unroll
-            for (int t = 0; t < RL_TOKS; t++) x[t] = sx[t * RL_KC + i];
+            for (int t = 0; t < RL_TOKS / 2; t++) x2[t] = pk(sx[(2 * t) * RL_KC + i], sx[(2 * t + 1) * RL_KC + i]);
 #pragma unroll
-            for (int r = 0; r < RL_ROWS; r++)
+            for (int r = 0; r < RL_ROWS; r++) {
+                const f32x2 w2 = pk(w[r], w[r]);
 #pragma unroll
-                for (int t = 0; t < RL_TOKS; t++)
-                    acc[r * RL_TOKS + t] = fmaf(w[r], x[t], acc[r * RL_TOKS + t]);
+                for (int t = 0; t < RL_TOKS / 2; t++)
+                    acc2[r * (RL_TOKS / 2) + t] = fma2(w2, x2[t], acc2[r * (RL_TOKS / 2) + t]);
+            }
         }
+    }
+    float acc[RL_ROWS * RL_TOKS];
+#pragma unroll
+    for (int i = 0; i < RL_ROWS * RL_TOKS / 2; i++) {
+        acc[2 * i] = lo_of(acc2[i]);
+        acc[2 * i + 1] = hi_of(acc2[i]);
     }
     // Lane sums in the order 8, 16, 4, 2, 1.  Each step halves the values a lane
     // carries: a lane keeps the half chosen by its bit of the step and gives the
