@@ -54,6 +54,9 @@ struct Arena {   // carves 256-byte aligned pieces out of one allocation
 
 using namespace bivmoe;
 
+// bivmoe_forward_host: rows per section and the most sections of one call
+constexpr int kHostSectionRows = 2048, kHostSectionsDefault = 4, kHostSectionsMax = 8;
+
 struct bivmoe_layer {
     int device = 0, sm_count = 0;
     int e = 0, n_expert = 0, k = 0, ff = 0, ff_sh = 0, max_tokens = 0;
@@ -66,9 +69,13 @@ struct bivmoe_layer {
     size_t ws_bytes = 0, weight_bytes = 0;
     Workspace ws{};
     cudaStream_t own_stream = nullptr;   // bivmoe_forward_host
+    // a host-buffer call over many rows runs in sections: the copy-in of the next section
+    // and the copy-out of the last one (streams of their own) overlap the section at work
+    cudaStream_t in_stream = nullptr, out_stream = nullptr;
+    cudaEvent_t host_ev[2 * kHostSectionsMax + 2] = {};
     float* host_in = nullptr;            // device staging of forward_host
     float* host_out = nullptr;
-    int last_n = 0;
+    int last_n = 0, host_last_n = 0;
     // the launch sequence of the last forward call, replayed as a CUDA graph while the
     // call's arguments stay the same (an engine passes the same scratch buffers each pass)
     struct {
@@ -276,6 +283,10 @@ void bivmoe_destroy(bivmoe_layer* L) {
     for (void* p : L->ipc_opened) cudaIpcCloseMemHandle(p);
     for (void* p : L->allocs) cudaFree(p);
     if (L->own_stream) cudaStreamDestroy(L->own_stream);
+    if (L->in_stream) cudaStreamDestroy(L->in_stream);
+    if (L->out_stream) cudaStreamDestroy(L->out_stream);
+    for (cudaEvent_t ev : L->host_ev)
+        if (ev) cudaEventDestroy(ev);
     delete L;
 }
 
@@ -364,11 +375,17 @@ static int create_impl(const bivmoe_desc* d, int ep_rank, int ep_world, int max_
                                    (size_t)L->e * 4, cudaMemcpyHostToDevice)) != cudaSuccess)
         return cu_fail(ce, "shared gate upload");
     // groups of at least this many tokens run on the tcgen05 kernels, where they exist
-    // for the layer's types (shared expert of the same types, or none)
+    // for the layer's types (shared expert of the same types, or none).  Q8_0: the
+    // warp-MMA kernels win below about 96 rows (0.25 / 0.41 ms against 0.29 / 0.44 ms per
+    // pass of 512 / 1024 tokens).  BF16: the tcgen05 kernel sizes its MMA to the tile's rows
+    // and reads the weights once per group, the float kernel once per 8 rows on the CUDA
+    // cores: every group that needs more than one 8-row tile goes to the tensor core
+    // (0.60 / 0.55 / 0.65 ms against 1.75 / 3.16 / 5.83 ms per pass of 512 / 1024 / 2048
+    // tokens).
     if (prefill_supported(L->gate_up.ty, L->down.ty) &&
         (!shared || (L->sh_gate_up.ty == L->gate_up.ty && L->sh_down.ty == L->down.ty))) {
         const char* env = getenv("BIVMOE_PREFILL_MIN");
-        L->prefill_min = env ? atoi(env) : 96;
+        L->prefill_min = env ? atoi(env) : L->gate_up.ty == BIVMOE_BF16 ? 9 : 96;
         L->prefill_tile = L->gate_up.ty == BIVMOE_BF16 ? kPrefillTileBf16 : kPrefillTile;
     }
     Arena probe;
@@ -866,11 +883,60 @@ static bool page_locked(const void* p) {
     return a.type == cudaMemoryTypeHost;
 }
 
-// copy in, the layer, copy out, status out - enqueued on the layer's own stream
+// How many sections a host-buffer call of n rows runs in.  The layer is row-wise, so a
+// section's result does not depend on the rows of the others; a section should still be
+// large enough for the tensor-core kernels' 128-row tiles to fill (rows per expert =
+// section * k / n_expert).  BIVMOE_HOST_SECTIONS overrides the rule (1 = no overlap).
+static int host_sections(const bivmoe_layer* L, int n) {
+    static const int forced = [] {
+        const char* v = getenv("BIVMOE_HOST_SECTIONS");
+        return v ? atoi(v) : 0;
+    }();
+    int c = forced > 0 ? forced : std::min(n / kHostSectionRows, kHostSectionsDefault);
+    c = std::min(c, kHostSectionsMax);
+    c = std::min(c, n / 8);
+    return std::max(c, 1);
+}
+
+// copy in, the layer, copy out, status out - enqueued on the layer's own stream; with
+// more than one section the copies run on two more streams, forked from and joined to it
+// by events (so that the whole can be captured from the layer's stream)
 static int forward_host_enqueue(bivmoe_layer* L, const float* h_host, float* out_host, int n) {
     std::string* errp = &L->error;
     const size_t bytes = (size_t)n * L->e * 4;
     cudaStream_t s = L->own_stream;
+    const int sections = host_sections(L, n);
+    if (sections > 1) {
+        cudaStream_t si = L->in_stream, so = L->out_stream;
+        cudaEvent_t* ev = L->host_ev;
+        cudaEvent_t fork = ev[2 * kHostSectionsMax], join = ev[2 * kHostSectionsMax + 1];
+        const int per = ((n + sections - 1) / sections + 7) / 8 * 8;
+        CU(cudaEventRecord(fork, s));
+        CU(cudaStreamWaitEvent(si, fork, 0));
+        CU(cudaStreamWaitEvent(so, fork, 0));
+        for (int c = 0, t0 = 0; t0 < n; c++, t0 += per) {
+            const size_t off = (size_t)t0 * L->e, nb = (size_t)std::min(per, n - t0) * L->e * 4;
+            CU(cudaMemcpyAsync(L->host_in + off, h_host + off, nb, cudaMemcpyHostToDevice, si));
+            CU(cudaEventRecord(ev[2 * c], si));
+        }
+        int last = 0;
+        for (int c = 0, t0 = 0; t0 < n; c++, t0 += per) {
+            const size_t off = (size_t)t0 * L->e;
+            last = std::min(per, n - t0);
+            CU(cudaStreamWaitEvent(s, ev[2 * c], 0));
+            if (int rc = forward_impl(L, L->host_in + off, L->host_out + off, last, 0, s)) return rc;
+            CU(cudaEventRecord(ev[2 * c + 1], s));
+            CU(cudaStreamWaitEvent(so, ev[2 * c + 1], 0));
+            CU(cudaMemcpyAsync(out_host + off, L->host_out + off, (size_t)last * L->e * 4,
+                               cudaMemcpyDeviceToHost, so));
+        }
+        CU(cudaEventRecord(join, so));
+        CU(cudaStreamWaitEvent(s, join, 0));
+        CU(cudaMemcpyAsync(L->status_host, L->ws.status, 16, cudaMemcpyDeviceToHost, s));
+        L->host_last_n = last;   // what the workspace holds afterwards: the last section
+        return BIVMOE_OK;
+    }
+    L->host_last_n = n;
     CU(cudaMemcpyAsync(L->host_in, h_host, bytes, cudaMemcpyHostToDevice, s));
     int rc = forward_graphed(L, L->host_in, L->host_out, n, 0, s);   // plain launches under a capture
     if (rc) return rc;
@@ -898,6 +964,9 @@ int bivmoe_forward_host_async(bivmoe_layer* L, const float* h_host, float* out_h
         L->allocs.push_back(L->host_out);
         L->ws_bytes += 2 * bytes;
         CU(cudaHostAlloc((void**)&L->status_host, 16, cudaHostAllocDefault));
+        CU(cudaStreamCreateWithFlags(&L->in_stream, cudaStreamNonBlocking));
+        CU(cudaStreamCreateWithFlags(&L->out_stream, cudaStreamNonBlocking));
+        for (cudaEvent_t& ev : L->host_ev) CU(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
     }
     cudaStream_t s = L->own_stream;
     auto& G = L->host_graph;
@@ -935,7 +1004,7 @@ int bivmoe_forward_host_async(bivmoe_layer* L, const float* h_host, float* out_h
         int rc = forward_host_enqueue(L, h_host, out_host, n);
         if (rc) return rc;
     }
-    L->last_n = n;
+    L->last_n = L->host_last_n;
     return BIVMOE_OK;
 }
 

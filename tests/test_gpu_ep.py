@@ -138,7 +138,11 @@ def test_ranks_as_threads_match_the_single_gpu_layer(cfg, world, n):
     n_per = n // world
     want = np.concatenate([_single_gpu(layer, np.ascontiguousarray(h[r * n_per:(r + 1) * n_per]))
                            for r in range(world)])
-    np.testing.assert_allclose(got, want, rtol=0, atol=1e-6 * float(np.abs(want).max()))
+    # (BF16: an owner's groups gather the rows of every rank and can pass the 9 rows from
+    # which the tensor-core kernel - f32 rows as two bf16 terms, 2^-17 of a value - takes
+    # over from the float kernel that the rank alone would use)
+    atol = (3e-5 if cfg == "ep_bf16" else 1e-6) * float(np.abs(want).max())
+    np.testing.assert_allclose(got, want, rtol=0, atol=atol)
     ref = oracle.moe_forward(layer, h)
     assert rel_err(got, ref) < TOL
     # a token's row goes once to every rank that owns one of its experts

@@ -456,6 +456,30 @@ def test_host_call_with_page_locked_buffers_replays_one_graph():
         m.close()
 
 
+def test_host_call_over_many_rows_runs_in_sections_with_the_same_result():
+    # from 4096 rows on the host-buffer call copies and computes in sections (the next
+    # section's copy-in and the last one's copy-out overlap the section at work); rows
+    # are independent, so the result is the device call's, bit for bit - also when the
+    # last section is ragged, and when the whole is replayed as one graph
+    import torch
+    from biv_b200.moe import Moe
+    for make, n in ((W.decode_q4k, 4100), (W.prefill_q8_0, 6151), (W.ep_bf16, 8200)):
+        wl = make(n=n, **W.SMALL)
+        m = Moe(wl.layer, wl.n)
+        try:
+            want = m.moe(torch.from_numpy(wl.h).cuda()).cpu().numpy()
+            assert np.array_equal(m.moe_host(wl.h), want)            # pageable buffers
+            h_pin = torch.from_numpy(wl.h).pin_memory()
+            out_pin = torch.empty_like(h_pin).pin_memory()
+            for _ in range(3):
+                out_pin.zero_()
+                m.moe_host(h_pin, out_pin)
+                assert np.array_equal(out_pin.numpy(), want)
+            m.status()
+        finally:
+            m.close()
+
+
 def test_edges_empty_input_every_expert_and_the_expert_limit():
     import torch
     from biv_b200.moe import Moe
