@@ -159,7 +159,7 @@ static void layout_one(bivmoe_layer* L, Arena& a, Workspace& w, size_t N, size_t
     w.act_t = a.take<uint8_t>(qact ? (e / 256) * (R / 8) * kActTileBytes : 0);
     w.act_f = a.take<float>(fact ? R * e : 0);
     const bool brec = L->prefill_min > 0 && L->gate_up.ty == BIVMOE_BF16;   // bf16 hi/lo records
-    w.act_b = a.take<uint8_t>(brec ? (e / 64) * (R / 8) * kActBRec : 0);
+    w.tok_b = a.take<uint8_t>(brec ? N * (e / 64) * kTokBRec : 0);
     w.mid_b = a.take<uint8_t>(brec ? (mid / 64) * (R / 8) * kActBRec : 0);
     w.mid = a.take<float>(R * mid);
     w.mid_t = a.take<uint8_t>(qmid ? (mid / 256) * (R / 8) * kActTileBytes : 0);

@@ -107,6 +107,9 @@ struct DevTiles {          // the tiles of one product (gate+up, or down) of a s
 //     hi    [8 units][8 tokens][8 bf16]   the canonical K-major operand layout
 //     lo    the same, 1024 bytes further
 constexpr int kActBRec = 2048, kActBLo = 1024;
+// the same two terms of one token and K-slice before they are gathered into records:
+// hi[64] then lo[64]
+constexpr int kTokBRec = 256, kTokBLo = 128;
 // byte offset inside a record of element i (0..63) of token tk (0..7), hi term
 __host__ __device__ inline int act_b_off(int tk, int i) { return ((i >> 3) * 8 + tk) * 16 + (i & 7) * 2; }
 constexpr int kActOffDx = 2048, kActOffSHi = kActOffDx + 256, kActOffSLo = kActOffSHi + 256,
@@ -151,7 +154,7 @@ struct Workspace {
     int act_rows;        // R: positions
     uint8_t* act_t;      // Q8 records of h, [n_embd/256][R/8] tiles (quantised gate/up types)
     float* act_f;        // f32 rows of h by position, slice-major (float-activation types)
-    uint8_t* act_b;      // bf16 hi/lo records of h, [n_embd/64][R/8] (BF16 layers with the tcgen05 kernels)
+    uint8_t* tok_b;      // bf16 hi/lo terms of h by token, [N][n_embd/64][kTokBRec] (BF16 layers with the tcgen05 kernels)
     uint8_t* mid_b;      // the same of silu(gate)*up, [ff/64][R/8]
     float* mid;          // silu(gate)*up by position, slice-major f32 [ff/64][R][64]
     uint8_t* mid_t;      // its Q8 records, [ff/256][R/8] tiles (quantised down types)

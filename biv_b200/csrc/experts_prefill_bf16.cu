@@ -18,8 +18,13 @@
 // a tile of 128 tokens of one group times TWO chunks of 128 weight rows (a chunk:
 // 64 gate rows with their 64 up rows, or 128 down rows).  A pipeline stage is one
 // K-slice of 64 values: 128 rows x 128 bytes of weights per chunk and the tile's
-// 16 activation records (hi and lo), all already in the tensor core's canonical
-// K-major layout (common.cuh), so a stage is three bulk copies.  The kernel is
+// 16 activation records (hi and lo), all in the tensor core's canonical K-major
+// layout (common.cuh).  The weights and, for the down product, the records of mid
+// (written in that layout by the gate+up epilogue) arrive by bulk copies.  For the
+// gate+up product four more warps gather the tile's rows by token from the
+// token-ordered bf16 terms (rowops.cu, split_rows_kernel) with 16-byte asynchronous
+// copies that complete on the stage's barrier: a row is split once and never
+// written per position.  The kernel is
 // bound by what an SM can pull from L2, and the activation records are two
 // thirds of a one-chunk stage: sharing them between two chunks cuts the bytes per
 // multiply-add by a third.  Per stage the MMA thread issues, per chunk, 2 terms x
@@ -40,10 +45,12 @@
 namespace bivmoe {
 
 constexpr int BF_NT = kPrefillTileBf16;                         // tokens per tile = MMA N
-constexpr int BF_EPI_WARPS = 4;
-constexpr int BF_THREADS = 32 * (1 + BF_EPI_WARPS);
+constexpr int BF_EPI_WARPS = 4, BF_GATHER_WARPS = 4;
+constexpr int BF_THREADS = 32 * (1 + BF_EPI_WARPS);                      // the down product
+constexpr int BF_THREADS_GATHER = BF_THREADS + 32 * BF_GATHER_WARPS;     // gate+up
 constexpr uint32_t BF_W_BYTES = kChunkRows * 128;               // 16384: one K-slice of a chunk
 constexpr uint32_t BF_X_BYTES = (BF_NT / 8) * kActBRec;         // 32768
+constexpr uint32_t BF_X_TERM = BF_NT * 128;                     // gathered rows: the lo tile follows the hi tile
 constexpr int BF_MC = 2;                                        // chunks per item
 constexpr uint32_t BF_STAGE = BF_MC * BF_W_BYTES + BF_X_BYTES;  // 65536
 constexpr int BF_NSTAGE = 3;
@@ -57,7 +64,10 @@ enum { BF_GATEUP = 0, BF_DOWN = 1 };
 
 struct Bf16Args {
     DevTiles w, sh;
-    const uint8_t* x_b;    // bf16 hi/lo records of the inputs by position, [K/64][R/8]
+    const uint8_t* x_b;    // DOWN: bf16 hi/lo records of mid by position, [K/64][R/8]
+    const uint8_t* tok_b;  // GATEUP: bf16 hi/lo terms of the rows by token, [N][K/64][kTokBRec]
+    const int32_t* order;  // GATEUP: order[pos] / k is the token at a routed group's position
+    int k;
     int act_rows;          // R
     float* out;            // GATEUP: mid f32 slice-major; DOWN: pair_out [R][rows]
     uint8_t* out_b;        // GATEUP: bf16 hi/lo records of mid
@@ -81,8 +91,17 @@ struct BfItem {
     size_t wstep;          // further, the next chunk wstep further
 };
 
+__device__ __forceinline__ void bf_cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// one arrival on `bar` once this thread's copies so far have landed (counted in the
+// barrier's expected arrivals)
+__device__ __forceinline__ void bf_cp_async_arrive(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(pf_smem(bar)) : "memory");
+}
+
 template <int MODE>
-__global__ void __launch_bounds__(BF_THREADS, 1)
+__global__ void __launch_bounds__(MODE == 0 ? BF_THREADS_GATHER : BF_THREADS, 1)
 experts_prefill_bf16_kernel(const Bf16Args A) {
     pdl_launch_dependents();
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -100,7 +119,8 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
 
     if (tid == 0) {
         for (int i = 0; i < BF_NSTAGE; i++) {
-            pf_bar_init(&full[i], 1);
+            // the copy thread's arrival with the bulk copies' bytes + every gathering thread
+            pf_bar_init(&full[i], MODE == BF_GATEUP ? 1 + 32 * BF_GATHER_WARPS : 1);
             pf_bar_init(&empty[i], 1);
         }
         for (int i = 0; i < 2; i++) {
@@ -164,14 +184,15 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
                 const uint32_t slot = q % BF_NSTAGE;
                 if (!pf_bar_wait(&empty[slot], ((q / BF_NSTAGE) & 1) ^ 1)) { give_up(); dead = true; break; }
                 uint8_t* dst = stages + slot * BF_STAGE;
-                const uint32_t x_bytes = (uint32_t)(it.n_mma / 8) * kActBRec;
+                const uint32_t x_bytes = MODE == BF_GATEUP ? 0u : (uint32_t)(it.n_mma / 8) * kActBRec;
                 pf_bar_expect_tx(&full[slot], it.nch * BF_W_BYTES + x_bytes);
                 for (int ch = 0; ch < it.nch; ch++)
                     pf_bulk_g2s(dst + ch * BF_W_BYTES, it.wsrc + ch * it.wstep + (size_t)s * BF_W_BYTES,
                                 BF_W_BYTES, &full[slot]);
-                pf_bulk_g2s(dst + BF_MC * BF_W_BYTES,
-                            A.x_b + ((size_t)s * (A.act_rows / 8) + it.pos0 / 8) * kActBRec, x_bytes,
-                            &full[slot]);
+                if (MODE == BF_DOWN)
+                    pf_bulk_g2s(dst + BF_MC * BF_W_BYTES,
+                                A.x_b + ((size_t)s * (A.act_rows / 8) + it.pos0 / 8) * kActBRec, x_bytes,
+                                &full[slot]);
             }
         }
     } else if (warp == 0 && lane == 1) {
@@ -188,6 +209,8 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
             for (int s = 0; s < it.nst && !dead; s++, q++) {
                 const uint32_t slot = q % BF_NSTAGE;
                 if (!pf_bar_wait(&full[slot], (q / BF_NSTAGE) & 1)) { give_up(); dead = true; break; }
+                if (MODE == BF_GATEUP)   // the gathered rows were written by ordinary asynchronous copies
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 pf_fence_after();
                 const uint32_t wa = pf_smem(stages + slot * BF_STAGE);
                 const uint32_t xa = wa + BF_MC * BF_W_BYTES;
@@ -199,16 +222,61 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
                             // A: the chunk's rows, units 2ks and 2ks+1 (16 bf16 of K): 8-row groups
                             //    128 B apart, the two units 2048 B apart.  B: the tokens' hi or lo
                             //    term, the same units of each record: 8-token groups one record
-                            //    apart, the two units 128 B apart.
+                            //    apart, the two units 128 B apart (down); the gathered rows of
+                            //    gate+up are swizzled tiles, a K-step 32 B further in the row.
                             const uint64_t ad = pf_desc(wa + ch * BF_W_BYTES + 2 * ks * (kChunkRows * 16),
                                                         kChunkRows * 16, 128);
-                            const uint64_t bd = pf_desc(xa + term * kActBLo + 2 * ks * 128, 128, kActBRec);
+                            const uint64_t bd = MODE == BF_GATEUP
+                                                    ? pf_desc_sw128(xa + term * BF_X_TERM + ks * 32)
+                                                    : pf_desc(xa + term * kActBLo + 2 * ks * 128, 128, kActBRec);
                             pf_mma_bf16(tmem + buf * BF_TBUF + ch * BF_NT, ad, bd, idesc, (s | term | ks) != 0);
                         }
                 pf_commit(&empty[slot]);   // the stage's operands are no longer read
             }
             if (!dead) pf_commit(&tfull[buf]);
             item++;
+        }
+    } else if (MODE == BF_GATEUP && warp > BF_EPI_WARPS) {
+        // ---------------- gathering warps: the tile's rows, by token, into the stage.
+        // The gathered operand uses the 128-byte swizzle (tcgen05.cuh): one tile of 128 rows
+        // x 128 bytes per term.  Warp w owns rows 32w .. 32w+31; eight lanes copy the eight
+        // 16-byte pieces of one row and term, so a warp-wide copy reads 128 contiguous
+        // bytes of each of four token rows (whole 128-byte requests: 16-byte pieces from
+        // eight different rows per request measured half the speed, bound by the L2 tag
+        // rate) and writes 512 contiguous bytes of shared memory, the pieces of a row
+        // permuted by the swizzle.
+        const int gw = warp - (1 + BF_EPI_WARPS), r4 = lane >> 3, pc = lane & 7;
+        const size_t tok_stride = (size_t)max(A.w.nslices, A.sh.nslices) * kTokBRec;
+        uint32_t q = 0;
+        bool dead = false;
+        for (int idx = blockIdx.x; idx < total && !dead && !*(volatile int*)s_abort; idx += gridDim.x) {
+            const BfItem it = decode(idx);
+            if (it.nst == 0) continue;
+            const uint8_t* src[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int j = 32 * gw + 4 * i + r4;      // row of the tile
+                src[i] = nullptr;
+                if (j < it.tc) {
+                    const int tok = it.shared ? it.pos0 + j : A.order[it.pos0 + j] / A.k;
+                    src[i] = A.tok_b + (size_t)tok * tok_stride + pc * 16;
+                }
+            }
+            for (int s = 0; s < it.nst && !dead; s++, q++) {
+                const uint32_t slot = q % BF_NSTAGE;
+                if (!pf_bar_wait(&empty[slot], ((q / BF_NSTAGE) & 1) ^ 1)) { give_up(); dead = true; break; }
+                const uint32_t xa = pf_smem(stages + slot * BF_STAGE + BF_MC * BF_W_BYTES) + (uint32_t)(32 * gw) * 128;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    if (!src[i]) continue;
+                    const int r = 4 * i + r4;            // row within the warp's 32; r % 8 = row of its atom
+                    const uint32_t dp = xa + (uint32_t)r * 128 + (uint32_t)((pc ^ (r & 7)) * 16);
+                    const uint8_t* sp = src[i] + (size_t)s * kTokBRec;
+                    bf_cp_async16(dp, sp);                               // hi
+                    bf_cp_async16(dp + BF_X_TERM, sp + kTokBLo);         // lo
+                }
+                bf_cp_async_arrive(&full[slot]);
+            }
         }
     } else if (warp > 0) {
         // ---------------- epilogue warps: once per item
@@ -309,7 +377,8 @@ static cudaError_t launch_bf16_one(const LaunchCfg& c, Bf16Args A) {
     static std::atomic<uint64_t> attr_set{0};
     if (cudaError_t e = ensure_dynamic_smem(experts_prefill_bf16_kernel<MODE>, (int)BF_SMEM, attr_set)) return e;
     count_launch();
-    return launch_after(c.stream, experts_prefill_bf16_kernel<MODE>, dim3(c.sm_count), dim3(BF_THREADS), BF_SMEM, A);
+    return launch_after(c.stream, experts_prefill_bf16_kernel<MODE>, dim3(c.sm_count),
+                        dim3(MODE == BF_GATEUP ? BF_THREADS_GATHER : BF_THREADS), BF_SMEM, A);
 }
 
 // gate+up then down for the groups the sort put on the prefill tile list
@@ -325,7 +394,8 @@ cudaError_t launch_experts_prefill_bf16(const LaunchCfg& c, const DevTiles& gate
     A.tiles_mode = c.only_shared ? 2 : 0;
     Bf16Args G = A;
     G.w = gate_up; G.sh = sh_gate_up;
-    G.x_b = ws.act_b; G.out = ws.mid; G.out_b = ws.mid_b;
+    G.tok_b = ws.tok_b; G.order = ws.order; G.k = std::max(c.k, 1);
+    G.out = ws.mid; G.out_b = ws.mid_b;
     cudaError_t err = launch_bf16_one<BF_GATEUP>(c, G);
     if (err != cudaSuccess) return err;
     Bf16Args D = A;

@@ -95,8 +95,9 @@ dispatch_q8_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int 
 }
 
 // Float rows (BF16 weights).  A thread owns 8 consecutive values: two float4 stores
-// per position of a decode-sized group (slice-major f32 rows), or one 16-byte unit
-// of each bf16 term per position of a group the tcgen05 kernel will take.
+// per position of a decode-sized group (slice-major f32 rows).  Positions of groups the
+// tcgen05 kernel takes get nothing: that kernel gathers its rows by token from the
+// bf16 terms split_rows_kernel writes.
 __global__ void __launch_bounds__(DP_THREADS)
 dispatch_f32_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int has_shared,
                     int prefill_min, const float* __restrict__ norm_w) {
@@ -104,12 +105,49 @@ dispatch_f32_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int
     pdl_enter();
     const int t = blockIdx.x;
     const int R = ws.act_rows;
-    dispatch_positions(ws, t, n, k, 0, has_shared, ws.act_b ? prefill_min : 0, s_pos, s_big);
+    dispatch_positions(ws, t, n, k, 0, has_shared, ws.tok_b ? prefill_min : 0, s_pos, s_big);
     const float* x = h + (size_t)t * e;
     const float nscale = norm_w ? ws.row_scale[t] : 1.0f;
     for (int i0 = threadIdx.x * 8; i0 < e; i0 += DP_THREADS * 8) {
         float4 a = *(const float4*)(x + i0), b = *(const float4*)(x + i0 + 4);
         if (norm_w) {   // rms_norm on the fly: h = x * (scale * w)
+            const float4 wa = *(const float4*)(norm_w + i0), wb = *(const float4*)(norm_w + i0 + 4);
+            a.x = __fmul_rn(a.x, __fmul_rn(nscale, wa.x)); a.y = __fmul_rn(a.y, __fmul_rn(nscale, wa.y));
+            a.z = __fmul_rn(a.z, __fmul_rn(nscale, wa.z)); a.w = __fmul_rn(a.w, __fmul_rn(nscale, wa.w));
+            b.x = __fmul_rn(b.x, __fmul_rn(nscale, wb.x)); b.y = __fmul_rn(b.y, __fmul_rn(nscale, wb.y));
+            b.z = __fmul_rn(b.z, __fmul_rn(nscale, wb.z)); b.w = __fmul_rn(b.w, __fmul_rn(nscale, wb.w));
+        }
+        const int sl = i0 / 64, off = i0 % 64;
+        for (int j = 0; j <= k; j++) {
+            const int pos = s_pos[j];
+            if (pos < 0 || s_big[j]) continue;
+            float* dst = ws.act_f + ((size_t)sl * R + pos) * 64 + off;
+            *(float4*)dst = a;
+            *(float4*)(dst + 4) = b;
+        }
+    }
+}
+
+// The rows as two bf16 terms, x = hi + lo, by token: [token][K / 64][hi 64 | lo 64], 256
+// bytes per token and K-slice.  The tcgen05 kernel gathers a tile's rows from here in
+// 16-byte units (experts_prefill_bf16.cu), so a row is split once, not once per position
+// it occupies.  A row no group wants (an expert-parallel receive slot that is empty) is
+// skipped.
+__global__ void __launch_bounds__(DP_THREADS)
+split_rows_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int has_shared,
+                  const float* __restrict__ norm_w) {
+    pdl_enter();
+    const int t = blockIdx.x;
+    if (!has_shared) {
+        bool any = false;
+        for (int j = 0; j < k; j++) any |= ws.ids[(size_t)t * k + j] >= 0;
+        if (!any) return;
+    }
+    const float* x = h + (size_t)t * e;
+    const float nscale = norm_w ? ws.row_scale[t] : 1.0f;
+    for (int i0 = threadIdx.x * 8; i0 < e; i0 += DP_THREADS * 8) {
+        float4 a = *(const float4*)(x + i0), b = *(const float4*)(x + i0 + 4);
+        if (norm_w) {
             const float4 wa = *(const float4*)(norm_w + i0), wb = *(const float4*)(norm_w + i0 + 4);
             a.x = __fmul_rn(a.x, __fmul_rn(nscale, wa.x)); a.y = __fmul_rn(a.y, __fmul_rn(nscale, wa.y));
             a.z = __fmul_rn(a.z, __fmul_rn(nscale, wa.z)); a.w = __fmul_rn(a.w, __fmul_rn(nscale, wa.w));
@@ -126,29 +164,17 @@ dispatch_f32_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int
             hi[p] = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
             lo[p] = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
         }
-        const int sl = i0 / 64, off = i0 % 64;
-        for (int j = 0; j <= k; j++) {
-            const int pos = s_pos[j];
-            if (pos < 0) continue;
-            if (s_big[j]) {
-                uint8_t* rec = ws.act_b + ((size_t)sl * (R / 8) + pos / 8) * kActBRec + act_b_off(pos % 8, off);
-                *(uint4*)rec = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *(uint4*)(rec + kActBLo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-            } else {
-                float* dst = ws.act_f + ((size_t)sl * R + pos) * 64 + off;
-                *(float4*)dst = a;
-                *(float4*)(dst + 4) = b;
-            }
-        }
+        uint8_t* rec = ws.tok_b + ((size_t)t * (e / 64) + i0 / 64) * kTokBRec + (i0 % 64) * 2;
+        *(uint4*)rec = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *(uint4*)(rec + kTokBLo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
 }
 
-// Float rows by position, for many tokens: one block per tile of 8 positions.  It
-// finds the tile's group, reads the 8 source rows (a row is read once per position
-// it occupies, mostly from L2) and writes whole records, so that the pieces of a
-// record - which interleave 8 tokens - are written together, 512 contiguous bytes
-// per warp.  (For quantised rows the same arrangement measured slower than the
-// by-token kernel: it quantises a row once per position.)
+// Float rows by position, for many tokens: one block per tile of 8 positions of a
+// decode-sized group.  It finds the tile's group, reads the 8 source rows and writes
+// them slice-major; tiles of groups the tcgen05 kernel takes return at once.  (For
+// quantised rows the same arrangement measured slower than the by-token kernel: it
+// quantises a row once per position.)
 constexpr int DP_MIN_TOKENS = 256;   // from here on the by-position kernel is the faster one
 
 __device__ __forceinline__ bool dispatch_tile(const Workspace& ws, int pos0, int n, int k, int n_expert,
@@ -182,37 +208,21 @@ dispatch_pos_f32_kernel(const float* __restrict__ h, Workspace ws, int n, int k,
     __shared__ int s_tok[8], s_big;
     pdl_enter();
     const int pos0 = blockIdx.x * 8;
-    if (!dispatch_tile(ws, pos0, n, k, n_expert, has_shared, ws.act_b ? prefill_min : 0, s_tok, &s_big))
+    if (!dispatch_tile(ws, pos0, n, k, n_expert, has_shared, ws.tok_b ? prefill_min : 0, s_tok, &s_big))
         return;
-    // thread (tk, u): 8 consecutive values of token tk; the 8 threads of a unit write
-    // 128 contiguous bytes of a record, a warp 512
+    if (s_big) return;
+    // thread (tk, u): 8 consecutive values of token tk
     const int tk = threadIdx.x & 7, u0 = threadIdx.x >> 3;
-    const int tok = s_tok[tk], big = s_big;
+    const int tok = s_tok[tk];
     if (tok < 0) return;
     const int R = ws.act_rows;
     const float* x = h + (size_t)tok * e;
     for (int i0 = u0 * 8; i0 < e; i0 += (DP_THREADS / 8) * 8) {
         const float4 a = *(const float4*)(x + i0), b = *(const float4*)(x + i0 + 4);
         const int sl = i0 / 64, off = i0 % 64;
-        if (big) {
-            const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-            uint32_t hi[4], lo[4];
-#pragma unroll
-            for (int p = 0; p < 4; p++) {
-                const __nv_bfloat16 h0 = __float2bfloat16_rn(v[2 * p]), h1 = __float2bfloat16_rn(v[2 * p + 1]);
-                const __nv_bfloat16 l0 = __float2bfloat16_rn(v[2 * p] - __bfloat162float(h0));
-                const __nv_bfloat16 l1 = __float2bfloat16_rn(v[2 * p + 1] - __bfloat162float(h1));
-                hi[p] = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
-                lo[p] = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
-            }
-            uint8_t* rec = ws.act_b + ((size_t)sl * (R / 8) + pos0 / 8) * kActBRec + act_b_off(tk, off);
-            *(uint4*)rec = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-            *(uint4*)(rec + kActBLo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        } else {
-            float* dst = ws.act_f + ((size_t)sl * R + pos0 + tk) * 64 + off;
-            *(float4*)dst = a;
-            *(float4*)(dst + 4) = b;
-        }
+        float* dst = ws.act_f + ((size_t)sl * R + pos0 + tk) * 64 + off;
+        *(float4*)dst = a;
+        *(float4*)(dst + 4) = b;
     }
 }
 
@@ -224,6 +234,12 @@ cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace&
     if (quant) {
         if (cudaError_t err = launch_after(c.stream, dispatch_q8_kernel, dim3(c.n, 2), dim3(DP_THREADS), 0, h, ws,
                                            c.n, c.k, c.e, c.has_shared, nw))
+            return err;
+        count_launch();
+    }
+    if (f32 && ws.tok_b && c.prefill_min > 0) {
+        if (cudaError_t err = launch_after(c.stream, split_rows_kernel, dim3(c.n), dim3(DP_THREADS), 0, h, ws, c.n,
+                                           c.k, c.e, c.has_shared, nw))
             return err;
         count_launch();
     }

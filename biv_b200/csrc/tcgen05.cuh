@@ -51,6 +51,14 @@ __device__ __forceinline__ uint64_t pf_desc(uint32_t smem_addr, uint32_t lbo, ui
     return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) |
            ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
 }
+// The same for the 128-byte swizzle, K-major: a row is 128 contiguous bytes (64 bf16),
+// 8 rows make a 1024-byte atom (1024-byte aligned), and the 16-byte piece c of row r of
+// an atom sits at piece position c ^ r.  `sbo` = 1024 from one 8-row group to the next;
+// a K step of 16 bf16 advances the start address by 32 bytes.
+__device__ __forceinline__ uint64_t pf_desc_sw128(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
 // kind::i8 instruction descriptor: s32 accumulator, signed 8-bit A and B, both K-major
 __device__ __forceinline__ uint32_t pf_idesc(int m, int n) {
     return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
