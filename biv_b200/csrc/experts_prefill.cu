@@ -5,10 +5,11 @@
 // engine/src/model.rs:1119-1126, over the Q8_0 dot, engine/src/quant.rs:599-607),
 // for experts whose token list is long (model.rs:875-889).
 //
-// Design.  One block per SM, seventeen warps: one warp whose lane 0 issues the
-// copies and whose lane 1 issues the MMAs, and sixteen epilogue warps (four per
-// tensor-memory lane quadrant, 32 token columns each: a thread's accumulators and
-// one drained block fit in the 96 registers that 544 threads leave each, and four
+// Design.  One block per SM, eighteen warps: a warp whose lane 0 issues the copies,
+// a warp whose lane 0 issues the MMAs (two lanes of one warp take turns: the MMA
+// lane then runs only when the copy lane's waits let the warp switch paths), and
+// sixteen epilogue warps (four per tensor-memory lane quadrant, 32 token columns
+// each: a thread's accumulators and one drained block fit in 96 registers, and four
 // warps per scheduler hide the tensor-memory load latency better than three).  A
 // work item is a tile of 128 tokens of one group times a chunk of 128 weight rows
 // (64 gate rows with their 64 up rows, or 128 down rows).  The device layouts of common.cuh are already the tensor core's
@@ -47,7 +48,8 @@ constexpr int PF_NT = kPrefillTile;                  // tokens per tile = MMA N
 constexpr int PF_EPI_WARPS = 16;                     // four per tensor-memory lane quadrant
 constexpr int PF_COLS = PF_NT / (PF_EPI_WARPS / 4);  // token columns per epilogue thread
 static_assert(PF_COLS == 32, "an epilogue thread drains one 32-column load per block dot");
-constexpr int PF_THREADS = 32 * (1 + PF_EPI_WARPS);  // warp 0: lane 0 copies, lane 1 issues MMAs
+constexpr int PF_MMA_WARP = 1 + PF_EPI_WARPS;        // the MMA thread's own warp
+constexpr int PF_THREADS = 32 * (2 + PF_EPI_WARPS);  // warp 0: lane 0 copies; the last warp: lane 0 issues MMAs
 constexpr int PF_SL = 272;                           // Q8_0: bytes per row per K-slice
 constexpr uint32_t PF_W_BYTES = kChunkRows * PF_SL;                // 34816
 constexpr uint32_t PF_X_BYTES = (PF_NT / 8) * kActTileBytes;       // 49152
@@ -155,7 +157,7 @@ experts_prefill_kernel(const PrefillArgs A) {
         atomicExch(s_abort, 1);
     };
 
-    if (warp == 0 && lane != 1) {
+    if (warp == 0) {
         // ---------------- copy thread: two bulk copies per stage
         if (lane == 0) {
             uint32_t q = 0;
@@ -175,9 +177,11 @@ experts_prefill_kernel(const PrefillArgs A) {
                 }
             }
         }
-    } else if (warp == 0) {
-        // ---------------- MMA thread: one MMA per 32-column block
-        {
+    } else if (warp == PF_MMA_WARP) {
+        // ---------------- MMA thread: one MMA per 32-column block.  In a warp of its own:
+        // as a second lane of the copy thread's warp it ran only when that lane's waits
+        // let the warp switch paths.
+        if (lane == 0) {
             uint32_t q = 0, kb = 0;
             bool dead = false;
             for (int idx = blockIdx.x; idx < total && !dead && !*(volatile int*)s_abort; idx += gridDim.x) {

@@ -13,8 +13,8 @@
 // accumulate in tensor memory.  That doubles the MMA count and keeps the result
 // within a few f32 roundings of the reference's, far inside the layer tolerance.
 //
-// Design.  One block per SM, five warps: warp 0 lane 0 issues the copies, lane 1
-// the MMAs; four epilogue warps own the 128 tensor-memory lanes.  A work item is
+// Design.  One block per SM: one thread of warp 0 issues the copies, one thread of a
+// warp of its own the MMAs; four epilogue warps own the 128 tensor-memory lanes.  A work item is
 // a tile of 128 tokens of one group times TWO chunks of 128 weight rows (a chunk:
 // 64 gate rows with their 64 up rows, or 128 down rows).  A pipeline stage is one
 // K-slice of 64 values: 128 rows x 128 bytes of weights per chunk and the tile's
@@ -46,7 +46,8 @@ namespace bivmoe {
 
 constexpr int BF_NT = kPrefillTileBf16;                         // tokens per tile = MMA N
 constexpr int BF_EPI_WARPS = 4, BF_GATHER_WARPS = 4;
-constexpr int BF_THREADS = 32 * (1 + BF_EPI_WARPS);                      // the down product
+constexpr int BF_MMA_WARP = 1 + BF_EPI_WARPS;                            // a warp of its own (see the kernel)
+constexpr int BF_THREADS = 32 * (2 + BF_EPI_WARPS);                      // the down product
 constexpr int BF_THREADS_GATHER = BF_THREADS + 32 * BF_GATHER_WARPS;     // gate+up
 constexpr uint32_t BF_W_BYTES = kChunkRows * 128;               // 16384: one K-slice of a chunk
 constexpr uint32_t BF_X_BYTES = (BF_NT / 8) * kActBRec;         // 32768
@@ -195,8 +196,10 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
                                 &full[slot]);
             }
         }
-    } else if (warp == 0 && lane == 1) {
-        // ---------------- MMA thread: 2 terms x 4 K-steps per stage
+    } else if (warp == BF_MMA_WARP && lane == 0) {
+        // ---------------- MMA thread: 2 terms x 4 K-steps per stage.  In a warp of its own:
+        // as a second lane of the copy thread's warp it ran only when that lane's waits
+        // let the warp switch paths, and the tensor pipe idled in between.
         uint32_t q = 0, item = 0;
         bool dead = false;
         for (int idx = blockIdx.x; idx < total && !dead && !*(volatile int*)s_abort; idx += gridDim.x) {
@@ -236,7 +239,7 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
             if (!dead) pf_commit(&tfull[buf]);
             item++;
         }
-    } else if (MODE == BF_GATEUP && warp > BF_EPI_WARPS) {
+    } else if (MODE == BF_GATEUP && warp > BF_MMA_WARP) {
         // ---------------- gathering warps: the tile's rows, by token, into the stage.
         // The gathered operand uses the 128-byte swizzle (tcgen05.cuh): one tile of 128 rows
         // x 128 bytes per term.  Warp w owns rows 32w .. 32w+31; eight lanes copy the eight
@@ -245,7 +248,7 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
         // eight different rows per request measured half the speed, bound by the L2 tag
         // rate) and writes 512 contiguous bytes of shared memory, the pieces of a row
         // permuted by the swizzle.
-        const int gw = warp - (1 + BF_EPI_WARPS), r4 = lane >> 3, pc = lane & 7;
+        const int gw = warp - (1 + BF_MMA_WARP), r4 = lane >> 3, pc = lane & 7;
         const size_t tok_stride = (size_t)max(A.w.nslices, A.sh.nslices) * kTokBRec;
         uint32_t q = 0;
         bool dead = false;
@@ -278,7 +281,7 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
                 bf_cp_async_arrive(&full[slot]);
             }
         }
-    } else if (warp > 0) {
+    } else if (warp > 0 && warp <= BF_EPI_WARPS) {
         // ---------------- epilogue warps: once per item
         const int quad = warp & 3;               // the tensor-memory lanes this warp may read
         const int row = 32 * quad + lane;        // chunk row = tensor-memory lane

@@ -23,7 +23,24 @@ __device__ __forceinline__ void pf_bar_expect_tx(uint64_t* bar, uint32_t bytes) 
                  : "memory");
 }
 // bounded wait for the phase of parity `parity`; false when it gave up
+#ifndef PF_WAIT_HINT_NS
+#define PF_WAIT_HINT_NS 20000
+#endif
 __device__ __forceinline__ bool pf_bar_wait(uint64_t* bar, uint32_t parity) {
+#ifdef PF_WAIT_SPIN
+    for (uint32_t i = 0; i < (PF_WAIT_TRIES << 8); i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(pf_smem(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+#else
     for (uint32_t i = 0; i < PF_WAIT_TRIES; i++) {
         uint32_t ok;
         asm volatile(
@@ -31,11 +48,12 @@ __device__ __forceinline__ bool pf_bar_wait(uint64_t* bar, uint32_t parity) {
             "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok)
-            : "r"(pf_smem(bar)), "r"(parity), "r"(20000u)
+            : "r"(pf_smem(bar)), "r"(parity), "r"((uint32_t)PF_WAIT_HINT_NS)
             : "memory");
         if (ok) return true;
     }
     return false;
+#endif
 }
 __device__ __forceinline__ void pf_bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile(
