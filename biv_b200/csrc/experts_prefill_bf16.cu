@@ -45,7 +45,8 @@
 namespace bivmoe {
 
 constexpr int BF_NT = kPrefillTileBf16;                         // tokens per tile = MMA N
-constexpr int BF_EPI_WARPS = 4, BF_GATHER_WARPS = 4;
+constexpr int BF_CG = 4;                                        // epilogue warps per tensor-memory lane quadrant
+constexpr int BF_EPI_WARPS = 4 * BF_CG, BF_GATHER_WARPS = 4;
 constexpr int BF_MMA_WARP = 1 + BF_EPI_WARPS;                            // a warp of its own (see the kernel)
 constexpr int BF_THREADS = 32 * (2 + BF_EPI_WARPS);                      // the down product
 constexpr int BF_THREADS_GATHER = BF_THREADS + 32 * BF_GATHER_WARPS;     // gate+up
@@ -56,8 +57,8 @@ constexpr int BF_MC = 2;                                        // chunks per it
 constexpr uint32_t BF_STAGE = BF_MC * BF_W_BYTES + BF_X_BYTES;  // 65536
 constexpr int BF_NSTAGE = 3;
 constexpr uint32_t BF_HEAD = 1024;
-constexpr uint32_t BF_XCHG = 64 * 32 * 4;                       // SwiGLU exchange of 32 tokens
-constexpr uint32_t BF_SMEM = BF_HEAD + BF_NSTAGE * BF_STAGE + BF_XCHG;   // 205824
+constexpr uint32_t BF_XCHG = BF_CG * 64 * 16 * 4;               // SwiGLU exchange: 16 tokens per column group
+constexpr uint32_t BF_SMEM = BF_HEAD + BF_NSTAGE * BF_STAGE + BF_XCHG;   // 214016
 constexpr uint32_t BF_TMEM_COLS = 512;                          // two buffers of 2 x 128 columns
 constexpr uint32_t BF_TBUF = BF_MC * BF_NT;                     // columns of one buffer
 
@@ -110,11 +111,11 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
     uint64_t* empty = full + 4;                  // [3] stage free: its MMAs are done
     uint64_t* tfull = full + 8;                  // [2] an item's products are in tensor memory
     uint64_t* tempty = full + 10;                // [2] drained by the epilogue warps
-    uint64_t* xbar = full + 12;                  // [1] meeting point of the epilogue warps
+    uint64_t* xbar = full + 12;                  // [BF_CG] meeting points of the epilogue warps of a column group
     uint32_t* s_tmem = (uint32_t*)(smem + 256);
     int* s_abort = (int*)(smem + 260);
     uint8_t* stages = smem + BF_HEAD;
-    float* s_xchg = (float*)(smem + BF_HEAD + BF_NSTAGE * BF_STAGE);   // [32 tokens][64 rows]
+    float* s_xchg = (float*)(smem + BF_HEAD + BF_NSTAGE * BF_STAGE);   // [BF_CG][16 tokens][64 rows]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int CH = MODE == BF_GATEUP ? 64 : 128;   // output rows per chunk
 
@@ -128,7 +129,7 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
             pf_bar_init(&tfull[i], 1);
             pf_bar_init(&tempty[i], BF_EPI_WARPS);
         }
-        pf_bar_init(xbar, BF_EPI_WARPS);
+        for (int i = 0; i < BF_CG; i++) pf_bar_init(&xbar[i], 4);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -282,15 +283,22 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
             }
         }
     } else if (warp > 0 && warp <= BF_EPI_WARPS) {
-        // ---------------- epilogue warps: once per item
+        // ---------------- epilogue warps: once per item.  Warp (quad, cg) reads the 32
+        // tensor-memory lanes of its quadrant and, of each chunk's four 32-token column
+        // pieces, the pieces cg, cg + BF_CG, ...: with one warp per quadrant each scheduler
+        // had a single epilogue warp and nothing to hide its latencies behind, and the
+        // epilogue, not the tensor pipe, set the kernel's time.
         const int quad = warp & 3;               // the tensor-memory lanes this warp may read
+        const int cg = (warp - 1) >> 2;
         const int row = 32 * quad + lane;        // chunk row = tensor-memory lane
         const uint32_t tlane = tmem + ((uint32_t)(32 * quad) << 16);
+        float* xch = s_xchg + cg * (16 * 64);    // [16 tokens][64 rows] of this column group
+        uint64_t* xb = xbar + cg;
         uint32_t item = 0, xphase = 0;
-        auto meet = [&]() -> bool {   // the epilogue warps meet (bounded): false when the wait gave up
+        auto meet = [&]() -> bool {   // the four warps of a column group meet (bounded)
             __syncwarp();
-            if (lane == 0) pf_bar_arrive(xbar);
-            const bool ok = pf_bar_wait(xbar, xphase);
+            if (lane == 0) pf_bar_arrive(xb);
+            const bool ok = pf_bar_wait(xb, xphase);
             xphase ^= 1;
             return ok;
         };
@@ -302,57 +310,65 @@ experts_prefill_bf16_kernel(const Bf16Args A) {
             if (!pf_bar_wait(&tfull[buf], (item >> 1) & 1)) { ok = false; break; }
             pf_fence_after();
             const int rows = MODE == BF_DOWN ? (it.shared ? A.sh : A.w).rows : 0;
-            const int ncol = it.nch * (BF_NT / 32);   // 32-column pieces: chunk cc / 4, tokens 32 * (cc % 4)
 #pragma unroll 1
-            for (int cc = 0; cc < ncol && ok; cc++) {
-                const int c = cc % (BF_NT / 32), chunk = it.chunk + cc / (BF_NT / 32);
-                int v[32];
-                pf_tmem_ld32(tlane + buf * BF_TBUF + cc * 32, v);
-                pf_tmem_wait_ld();
-                if (cc == ncol - 1) {           // the buffer is in registers: hand it back
-                    pf_fence_before();
-                    __syncwarp();
-                    if (lane == 0) pf_bar_arrive(&tempty[buf]);
-                }
-                const int tok0 = c * 32;
-                if (tok0 >= it.tc) continue;     // uniform; the loads above still ran for the hand-back
-                if (MODE == BF_GATEUP) {
-                    // Thread `row` of quadrants 0-1 holds gate row `row`, its partner in
-                    // quadrants 2-3 the up row of the same output.  Each finishes half of
-                    // the 32 tokens: the gate thread hands over tokens 16..31, the up thread
-                    // tokens 0..15.
-                    const int half = quad >> 1;
-                    const int orow = row & 63;
-#pragma unroll
-                    for (int i = 0; i < 16; i++)
-                        s_xchg[(half ? i : 16 + i) * 64 + orow] = __int_as_float(v[half ? i : 16 + i]);
-                    if (!meet()) { ok = false; break; }
-                    const int r = chunk * CH + orow;      // row of mid
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        const int tl = 16 * half + i, tok = tok0 + tl;
-                        if (tok >= it.tc) break;          // uniform across the warp
-                        const float other = s_xchg[tl * 64 + orow];
-                        const float gt = half ? other : __int_as_float(v[i]);
-                        const float u = half ? __int_as_float(v[16 + i]) : other;
-                        // ops.rs:160-167: silu(x) = x * (1 / (1 + exp(-x)))
-                        const float y = (gt * __fdiv_rn(1.0f, 1.0f + expf(-gt))) * u;
-                        const size_t pos = (size_t)it.pos0 + tok;
-                        A.out[((size_t)(r / 64) * A.act_rows + pos) * 64 + r % 64] = y;
-                        const __nv_bfloat16 hi = __float2bfloat16_rn(y);
-                        const __nv_bfloat16 lo = __float2bfloat16_rn(y - __bfloat162float(hi));
-                        uint8_t* rec = A.out_b + ((size_t)(r / 64) * (A.act_rows / 8) + pos / 8) * kActBRec +
-                                       act_b_off((int)(pos % 8), r % 64);
-                        *(__nv_bfloat16*)rec = hi;
-                        *(__nv_bfloat16*)(rec + kActBLo) = lo;
+            for (int ch = 0; ch < it.nch && ok; ch++) {
+#pragma unroll 1
+                for (int c = cg; c < BF_NT / 32 && ok; c += BF_CG) {
+                    const int chunk = it.chunk + ch;
+                    int v[32];
+                    pf_tmem_ld32(tlane + buf * BF_TBUF + ch * BF_NT + c * 32, v);
+                    pf_tmem_wait_ld();
+                    if (ch == it.nch - 1 && c + BF_CG >= BF_NT / 32) {   // this warp's last piece is in registers
+                        pf_fence_before();
+                        __syncwarp();
+                        if (lane == 0) pf_bar_arrive(&tempty[buf]);
                     }
-                    if (!meet()) { ok = false; break; }   // the exchange tile is free again
-                } else {
+                    const int tok0 = c * 32;
+                    if (tok0 >= it.tc) continue;     // uniform; the loads above still ran for the hand-back
+                    if (MODE == BF_GATEUP) {
+                        // Thread `row` of quadrants 0-1 holds gate row `row`, its partner in
+                        // quadrants 2-3 the up row of the same output.  The gate thread finishes
+                        // tokens 0..15 of the piece, the up thread tokens 16..31, in two rounds
+                        // of 8: each hands the other the 8 values it needs through the tile.
+                        const int half = quad >> 1;
+                        const int orow = row & 63;
+                        const int r = chunk * CH + orow;      // row of mid
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const int tok = tok0 + i;
-                        if (tok >= it.tc) break;
-                        A.out[((size_t)it.pos0 + tok) * rows + chunk * CH + row] = __int_as_float(v[i]);
+                        for (int rd = 0; rd < 2 && ok; rd++) {
+#pragma unroll
+                            for (int i = 0; i < 8; i++)
+                                xch[(half ? i : 8 + i) * 64 + orow] =
+                                    __int_as_float(half ? v[8 * rd + i] : v[16 + 8 * rd + i]);
+                            if (!meet()) { ok = false; break; }
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                const int tl = 16 * half + 8 * rd + i, tok = tok0 + tl;
+                                if (tok >= it.tc) break;          // uniform across the warp
+                                const float other = xch[(half ? 8 + i : i) * 64 + orow];
+                                const float gt = half ? other : __int_as_float(v[8 * rd + i]);
+                                const float u = half ? __int_as_float(v[16 + 8 * rd + i]) : other;
+                                // ops.rs:160-167: silu(x) = x * (1 / (1 + exp(-x))); the hardware's
+                                // approximate exp2 and reciprocal (about 2^-21 relative) - the
+                                // bf16 terms of the operands are ten times coarser
+                                const float y = (gt * __fdividef(1.0f, 1.0f + __expf(-gt))) * u;
+                                const size_t pos = (size_t)it.pos0 + tok;
+                                A.out[((size_t)(r / 64) * A.act_rows + pos) * 64 + r % 64] = y;
+                                const __nv_bfloat16 hi = __float2bfloat16_rn(y);
+                                const __nv_bfloat16 lo = __float2bfloat16_rn(y - __bfloat162float(hi));
+                                uint8_t* rec = A.out_b + ((size_t)(r / 64) * (A.act_rows / 8) + pos / 8) * kActBRec +
+                                               act_b_off((int)(pos % 8), r % 64);
+                                *(__nv_bfloat16*)rec = hi;
+                                *(__nv_bfloat16*)(rec + kActBLo) = lo;
+                            }
+                            if (!meet()) { ok = false; break; }   // the exchange tile is free again
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            const int tok = tok0 + i;
+                            if (tok >= it.tc) break;
+                            A.out[((size_t)it.pos0 + tok) * rows + chunk * CH + row] = __int_as_float(v[i]);
+                        }
                     }
                 }
             }
