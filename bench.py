@@ -434,7 +434,7 @@ def tensor_roofline(layer, n, r, int8):
     t_roof = max(lbytes / (hbm_peak * 1e9), ops / (peak * 1e12))
     return {"bound": "tensor",
             "kernel": "experts_prefill_kernel (tcgen05 kind::i8)" if int8
-            else "experts_prefill_bf16_kernel (tcgen05 kind::f16)",
+            else "experts_prefill_bf16_gateup_kernel + experts_prefill_bf16_down_kernel (tcgen05 kind::f16)",
             "achieved": ops / t_exp / 1e12, "peak": peak,
             "peak_kind": "int8 tensor pipe measured in this run (back-to-back tcgen05.mma kind::i8, "
                          "bivmoe_int8_peak)" if int8 else f"of {kind}",
