@@ -170,59 +170,34 @@ split_rows_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e
     }
 }
 
-// Float rows by position, for many tokens: one block per tile of 8 positions of a
-// decode-sized group.  It finds the tile's group, reads the 8 source rows and writes
-// them slice-major; tiles of groups the tcgen05 kernel takes return at once.  (For
-// quantised rows the same arrangement measured slower than the by-token kernel: it
-// quantises a row once per position.)
+// Float rows by position, for many tokens: a block per tile of 8 positions of a
+// decode-sized group, taken from the sort's tile list (groups the tcgen05 kernel takes
+// have no tiles there).  It reads the tile's 8 source rows and writes them slice-major.
+// (For quantised rows the same arrangement measured slower than the by-token kernel:
+// it quantises a row once per position.)
 constexpr int DP_MIN_TOKENS = 256;   // from here on the by-position kernel is the faster one
 
-__device__ __forceinline__ bool dispatch_tile(const Workspace& ws, int pos0, int n, int k, int n_expert,
-                                              int has_shared, int prefill_min, int* s_tok, int* s_big) {
-    if (pos0 >= ws.offsets[n_expert]) return false;   // past the last group (uniform: whole block)
-    if (threadIdx.x < 8) {
-        const int p = pos0 + threadIdx.x;
-        int start, count, tok = -1;
-        if (has_shared && pos0 < (n + 7) / 8 * 8) {
-            start = 0; count = n;
-            if (p < n) tok = p;
-        } else {
-            int lo = 0, hi = n_expert;   // the last expert whose first position is <= pos0
-            while (hi - lo > 1) {
-                const int mid = (lo + hi) >> 1;
-                if (ws.offsets[mid] <= pos0) lo = mid; else hi = mid;
-            }
-            start = ws.offsets[lo]; count = ws.counts[lo];
-            if (p - start < count) tok = ws.order[p] / k;
-        }
-        s_tok[threadIdx.x] = tok;
-        if (threadIdx.x == 0) *s_big = prefill_min > 0 && count >= prefill_min;
-    }
-    __syncthreads();
-    return true;
-}
-
 __global__ void __launch_bounds__(DP_THREADS)
-dispatch_pos_f32_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int n_expert,
-                        int has_shared, int prefill_min) {
-    __shared__ int s_tok[8], s_big;
+dispatch_pos_f32_kernel(const float* __restrict__ h, Workspace ws, int k, int e, int n_expert,
+                        int only_shared) {
     pdl_enter();
-    const int pos0 = blockIdx.x * 8;
-    if (!dispatch_tile(ws, pos0, n, k, n_expert, has_shared, ws.tok_b ? prefill_min : 0, s_tok, &s_big))
-        return;
-    if (s_big) return;
+    const int n_tiles = ws.n_tiles[only_shared ? 1 : 0];   // the shared group's tiles come first
     // thread (tk, u): 8 consecutive values of token tk
     const int tk = threadIdx.x & 7, u0 = threadIdx.x >> 3;
-    const int tok = s_tok[tk];
-    if (tok < 0) return;
     const int R = ws.act_rows;
-    const float* x = h + (size_t)tok * e;
-    for (int i0 = u0 * 8; i0 < e; i0 += (DP_THREADS / 8) * 8) {
-        const float4 a = *(const float4*)(x + i0), b = *(const float4*)(x + i0 + 4);
-        const int sl = i0 / 64, off = i0 % 64;
-        float* dst = ws.act_f + ((size_t)sl * R + pos0 + tk) * 64 + off;
-        *(float4*)dst = a;
-        *(float4*)(dst + 4) = b;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int4 td = ws.tile_desc[tile];   // {expert (n_expert: shared), first position, tokens, 0}
+        if (tk >= td.z) continue;
+        const int pos = td.y + tk;
+        const int tok = td.x == n_expert ? pos : ws.order[pos] / k;
+        const float* x = h + (size_t)tok * e;
+        for (int i0 = u0 * 8; i0 < e; i0 += (DP_THREADS / 8) * 8) {
+            const float4 a = *(const float4*)(x + i0), b = *(const float4*)(x + i0 + 4);
+            const int sl = i0 / 64, off = i0 % 64;
+            float* dst = ws.act_f + ((size_t)sl * R + pos) * 64 + off;
+            *(float4*)dst = a;
+            *(float4*)(dst + 4) = b;
+        }
     }
 }
 
@@ -244,11 +219,12 @@ cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace&
         count_launch();
     }
     if (f32 && c.n >= DP_MIN_TOKENS) {
-        // an upper bound of the tiles in use; blocks past the last group return at once
+        // the tiles in use are known on the device only: blocks stride over the list
         const int shared_tiles = c.has_shared ? (c.n + 7) / 8 : 0;
         const int tiles = c.k == 0 ? shared_tiles : shared_tiles + (c.n * c.k) / 8 + c.n_expert;
-        if (cudaError_t err = launch_after(c.stream, dispatch_pos_f32_kernel, dim3(tiles), dim3(DP_THREADS), 0, h, ws,
-                                           c.n, max(c.k, 1), c.e, c.n_expert, c.has_shared, c.prefill_min))
+        if (cudaError_t err = launch_after(c.stream, dispatch_pos_f32_kernel, dim3(min(tiles, 16 * c.sm_count)),
+                                           dim3(DP_THREADS), 0, h, ws, max(c.k, 1), c.e, c.n_expert,
+                                           c.only_shared || c.k == 0 ? 1 : 0))
             return err;
         count_launch();
     } else if (f32) {

@@ -147,8 +147,9 @@ def ep_pass_peer(steps, h, out, accumulate: bool, comm, lib_barrier: bool = Fals
     waits), which makes the pass five library calls and nothing else - no communicator."""
     barrier = steps.peer_barrier if lib_barrier else (lambda: comm.barrier(h.device))
     steps.peer_dispatch(h)
+    steps.shared(h)                 # on the side stream: needs only h, so it also runs while
+                                    # this rank waits for the slowest rank's rows
     barrier()                       # every rank's rows are where their owners read them
-    steps.shared(h)                 # beside the owners' work, on the side stream
     steps.peer_experts()
     barrier()                       # the partial sums are back; the receive buffers are free
     steps.peer_combine(out, accumulate)
