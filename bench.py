@@ -377,7 +377,7 @@ def measure_layer(wl, args, local, copies=1, in_flight=1, parity_rows=256, with_
                       "h2d_bytes_per_step": n * layer.n_embd * 4, "d2h_bytes_per_step": n * layer.n_embd * 4,
                       "call": "bivmoe_forward_host on page-locked buffers, one pass at a time: every step "
                               "copies its rows in and its result out (from 4096 rows on the call works in "
-                              "up to four sections whose copies overlap the section at work)"}
+                              "sections whose copies overlap the section at work)"}
         if in_flight > 1 and copies % in_flight == 0:
             hp = [h_pin] + [torch.from_numpy(wl.h).pin_memory() for _ in range(in_flight - 1)]
             op = [out_pin] + [torch.empty_like(h_pin).pin_memory() for _ in range(in_flight - 1)]

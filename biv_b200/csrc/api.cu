@@ -72,7 +72,7 @@ struct bivmoe_layer {
     // a host-buffer call over many rows runs in sections: the copy-in of the next section
     // and the copy-out of the last one (streams of their own) overlap the section at work
     cudaStream_t in_stream = nullptr, out_stream = nullptr;
-    cudaEvent_t host_ev[2 * kHostSectionsMax + 2] = {};
+    cudaEvent_t host_ev[2 * (kHostSectionsMax + 1) + 2] = {};
     float* host_in = nullptr;            // device staging of forward_host
     float* host_out = nullptr;
     int last_n = 0, host_last_n = 0;
@@ -909,20 +909,40 @@ static int forward_host_enqueue(bivmoe_layer* L, const float* h_host, float* out
     if (sections > 1) {
         cudaStream_t si = L->in_stream, so = L->out_stream;
         cudaEvent_t* ev = L->host_ev;
-        cudaEvent_t fork = ev[2 * kHostSectionsMax], join = ev[2 * kHostSectionsMax + 1];
-        const int per = ((n + sections - 1) / sections + 7) / 8 * 8;
+        cudaEvent_t fork = ev[2 * (kHostSectionsMax + 1)], join = ev[2 * (kHostSectionsMax + 1) + 1];
+        // Section boundaries.  With three sections or more the first and the last are half
+        // as long as the others (one more section in all): what cannot overlap anything is
+        // the first section's copy-in and the last one's copy-out.
+        int bound[kHostSectionsMax + 2];
+        int nsec = 0;
+        {
+            const int per = ((n + sections - 1) / sections + 7) / 8 * 8;
+            const int edge = sections >= 3 ? (per / 2 + 7) / 8 * 8 : per;
+            bound[0] = 0;
+            for (int t0 = edge; t0 < n; t0 += (n - t0 > per + edge / 2 ? per : n - t0)) bound[++nsec] = t0;
+            bound[++nsec] = n;
+            if (sections >= 3 && nsec >= 3 && bound[nsec] - bound[nsec - 1] > edge) {
+                // the tail came out long: cut it so that the last section is an edge
+                const int cut = (bound[nsec] - edge) / 8 * 8;
+                if (cut > bound[nsec - 1] && nsec < kHostSectionsMax + 1) {
+                    bound[nsec + 1] = bound[nsec];
+                    bound[nsec] = cut;
+                    nsec++;
+                }
+            }
+        }
         CU(cudaEventRecord(fork, s));
         CU(cudaStreamWaitEvent(si, fork, 0));
         CU(cudaStreamWaitEvent(so, fork, 0));
-        for (int c = 0, t0 = 0; t0 < n; c++, t0 += per) {
-            const size_t off = (size_t)t0 * L->e, nb = (size_t)std::min(per, n - t0) * L->e * 4;
+        for (int c = 0; c < nsec; c++) {
+            const size_t off = (size_t)bound[c] * L->e, nb = (size_t)(bound[c + 1] - bound[c]) * L->e * 4;
             CU(cudaMemcpyAsync(L->host_in + off, h_host + off, nb, cudaMemcpyHostToDevice, si));
             CU(cudaEventRecord(ev[2 * c], si));
         }
         int last = 0;
-        for (int c = 0, t0 = 0; t0 < n; c++, t0 += per) {
-            const size_t off = (size_t)t0 * L->e;
-            last = std::min(per, n - t0);
+        for (int c = 0; c < nsec; c++) {
+            const size_t off = (size_t)bound[c] * L->e;
+            last = bound[c + 1] - bound[c];
             CU(cudaStreamWaitEvent(s, ev[2 * c], 0));
             if (int rc = forward_impl(L, L->host_in + off, L->host_out + off, last, 0, s)) return rc;
             CU(cudaEventRecord(ev[2 * c + 1], s));

@@ -138,10 +138,12 @@ BIVMOE_API int bivmoe_status(bivmoe_layer* layer, void* stream);
  * backend's calling convention, `fn moe(&self, m, h: &[f32], n) -> Vec<f32>`,
  * model.rs:861): copies h in, runs the layer, copies the delta out and
  * waits for it.  Pinned host buffers make the copies asynchronous.  From 4096 rows on
- * the call works in up to four sections of at least 2048 rows: the copy-in of the next
- * section and the copy-out of the last one run on streams of their own beside the
- * section at work (rows are independent, so the result is the same; the taps then
- * describe the last section).  BIVMOE_HOST_SECTIONS=1 in the environment keeps one. */
+ * the call works in sections of at least 2048 rows (up to five; from three on the first
+ * and the last are half as long as the others, their copies being the ones nothing
+ * overlaps): the copy-in of the next section and the copy-out of the last one run on
+ * streams of their own beside the section at work (rows are independent, so the result
+ * is the same; the taps then describe the last section).  BIVMOE_HOST_SECTIONS=1 in the
+ * environment keeps one. */
 BIVMOE_API int bivmoe_forward_host(bivmoe_layer* layer, const float* h_host, float* out_host, int32_t n);
 
 /* The same in two halves, for a host that keeps several passes in flight (layers
