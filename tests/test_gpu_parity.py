@@ -599,6 +599,34 @@ def test_rows_wider_than_the_row_staging_router_kernel():
     run_case(W.decode_q4k(n=33, **dict(W.SMALL, n_embd=2560)), check_dots=False)
 
 
+def test_bf16_stack_with_the_norm_applied_while_the_rows_are_split():
+    # BF16 layers in a stack: with fewer than 256 rows the router kernel publishes the rms_norm
+    # scales and the rows are normed while they are split into bf16 terms for the tensor-core
+    # kernels (groups of 9 rows or more: 60 rows x 4 of 16 experts = 15 per expert); with more
+    # rows the norm is a kernel of its own
+    import torch
+    from biv_b200.moe import Moe, MoeStack
+    for n_seq in (12, 64):
+        rng = np.random.default_rng(11)
+        lays = [W.make_layer(rng, gate_ty=W.BF16, router_dist="uniform", **W.SMALL) for _ in range(2)]
+        e = lays[0].n_embd
+        x0 = rng.standard_normal((n_seq * 5, e), dtype=np.float32)
+        norm_w = [(1.0 + 0.1 * rng.standard_normal(e)).astype(np.float32) for _ in lays]
+        ref = oracle.moe_stack(lays, norm_w, 1e-6, x0, level=oracle.host_level())
+        layers = [Moe(l, x0.shape[0]) for l in lays]
+        try:
+            for m, nw in zip(layers, norm_w):
+                m.set_post_norm(nw, 1e-6)
+            x = torch.from_numpy(x0).cuda()
+            MoeStack(layers).forward_(x)
+            torch.cuda.synchronize()
+            assert rel_err(x.cpu().numpy(), ref) < TOL
+            layers[0].status()
+        finally:
+            for m in layers:
+                m.close()
+
+
 def test_stack_with_many_rows_takes_the_separate_norm_kernel():
     # from 256 rows on the norm is a kernel of its own (below it is fused into the router)
     import torch
