@@ -16,7 +16,7 @@ namespace bivmoe {
 // quantised weight types the row is quantised once, Q8Act::quantize_into
 // (quant.rs:368-394) - the reference quantises it again for every expert it is
 // routed to (model.rs:876-884), with the same result, the quantiser being a
-// function of the row alone.  One block per token, one warp per 32-value block.
+// function of the row alone.  One block per token.
 constexpr int DP_THREADS = 256, DP_MAX_K = 32;
 
 // s_pos[j]: the position of pair j (j < k) and, as entry k, the token's position in the
@@ -37,59 +37,69 @@ __device__ __forceinline__ void dispatch_positions(const Workspace& ws, int t, i
     __syncthreads();
 }
 
-// Quantised rows.  One warp per 32-value block; the block's 32 int8 are gathered
-// into two 16-byte units by shuffles, so a position costs two 16-byte stores
-// instead of 32 single bytes.
+// Quantised rows.  A thread owns 8 consecutive values, four threads a 32-value block:
+// the block's amax and sum(q) take two shuffle steps, two neighbouring threads make one
+// 16-byte unit of int8, and one thread of the four stores the block's scales.  (One lane
+// per value - a warp per block, five shuffle steps per reduction - cost eight times the
+// instructions and took 0.18 ms for 4096 rows.)  The quantiser's arithmetic is
+// q8_quantize_lane's: max and the integer sum do not depend on the order.
 __global__ void __launch_bounds__(DP_THREADS)
 dispatch_q8_kernel(const float* __restrict__ h, Workspace ws, int n, int k, int e, int has_shared,
                    const float* __restrict__ norm_w) {
     __shared__ int s_pos[DP_MAX_K + 1], s_big[DP_MAX_K + 1];
     pdl_enter();
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x, lane = threadIdx.x & 31;
     const int R = ws.act_rows;
     dispatch_positions(ws, t, n, k, 0, has_shared, 0, s_pos, s_big);
     const float* x = h + (size_t)t * e;
     // with norm_w the rows are the residual and h = x * (scale * w), rms_norm on the fly
     const float nscale = norm_w ? ws.row_scale[t] : 1.0f;
-    constexpr int NW = DP_THREADS / 32, U = 4;   // U loads in flight per lane
-    // blockIdx.y halves the row between two blocks
-    for (int b0 = blockIdx.y * NW * U + warp; b0 < e / 32; b0 += gridDim.y * NW * U) {
-        float vv[U];
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int b = b0 + u * NW;
-            vv[u] = b < e / 32 ? x[32 * b + lane] : 0.0f;
-            if (norm_w && b < e / 32) vv[u] = __fmul_rn(vv[u], __fmul_rn(nscale, norm_w[32 * b + lane]));
+    for (int i0 = threadIdx.x * 8; i0 < e; i0 += DP_THREADS * 8) {   // e % 256 == 0: whole warps
+        float4 a = *(const float4*)(x + i0), b = *(const float4*)(x + i0 + 4);
+        if (norm_w) {
+            const float4 wa = *(const float4*)(norm_w + i0), wb = *(const float4*)(norm_w + i0 + 4);
+            a.x = __fmul_rn(a.x, __fmul_rn(nscale, wa.x)); a.y = __fmul_rn(a.y, __fmul_rn(nscale, wa.y));
+            a.z = __fmul_rn(a.z, __fmul_rn(nscale, wa.z)); a.w = __fmul_rn(a.w, __fmul_rn(nscale, wa.w));
+            b.x = __fmul_rn(b.x, __fmul_rn(nscale, wb.x)); b.y = __fmul_rn(b.y, __fmul_rn(nscale, wb.y));
+            b.z = __fmul_rn(b.z, __fmul_rn(nscale, wb.z)); b.w = __fmul_rn(b.w, __fmul_rn(nscale, wb.w));
         }
+        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        // quant.rs:380-393: d = amax/127, id = 1/d (0 when d is 0), q = round(v*id) with
+        // halves away from zero, s = d * (float)sum
+        float amax = fabsf(v[0]);
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int b = b0 + u * NW;
-            if (b >= e / 32) break;
-            float dd, ss;
-            const int q = q8_quantize_lane(vv[u], dd, ss);
-            const int sl = b / 8, bb = b % 8;
-            float shi, slo;
-            split_tf32(ss, &shi, &slo);
-            // bytes of lanes l..l+3 in one word (lanes with l % 4 == 0), then four words
-            uint32_t w = (uint32_t)q & 0xffu;
-            w |= __shfl_down_sync(0xffffffffu, w, 1) << 8;
-            w |= __shfl_down_sync(0xffffffffu, w, 2) << 16;
-            uint4 unit;
-            unit.x = w;
-            unit.y = __shfl_down_sync(0xffffffffu, w, 4);
-            unit.z = __shfl_down_sync(0xffffffffu, w, 8);
-            unit.w = __shfl_down_sync(0xffffffffu, w, 12);
-            for (int j = 0; j <= k; j++) {
-                const int pos = s_pos[j];
-                if (pos < 0) continue;
-                uint8_t* rec = ws.act_t + ((size_t)sl * (R / 8) + pos / 8) * kActTileBytes;
-                if ((lane & 15) == 0)   // elements 32*bb + lane .. + 15: unit 2*bb + lane/16
-                    *(uint4*)(rec + act_q_off(pos % 8, 32 * bb + lane)) = unit;
-                if (lane < 4) {
-                    const float val = lane == 0 ? dd : lane == 1 ? shi : lane == 2 ? slo : ss;
-                    *(float*)(rec + kActOffDx + 256 * lane + (bb * 8 + pos % 8) * 4) = val;
-                }
-            }
+        for (int j = 1; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const float dd = __fdiv_rn(amax, 127.0f);
+        const float id = dd != 0.0f ? __fdiv_rn(1.0f, dd) : 0.0f;
+        int sum = 0;
+        uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int q = (int)roundf(__fmul_rn(v[j], id));
+            sum += q;
+            if (j < 4) w0 |= ((uint32_t)q & 0xffu) << (8 * j);
+            else w1 |= ((uint32_t)q & 0xffu) << (8 * (j - 4));
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const float ss = __fmul_rn(dd, (float)sum);
+        // the neighbour's 8 bytes: an even thread holds the low half of a 16-byte unit
+        const uint32_t p0 = __shfl_down_sync(0xffffffffu, w0, 1), p1 = __shfl_down_sync(0xffffffffu, w1, 1);
+        const uint4 unit = make_uint4(w0, w1, p0, p1);
+        float shi, slo;
+        split_tf32(ss, &shi, &slo);
+        const int sl = i0 / 256, el = i0 % 256;      // K-slice, element within it
+        const int bb = el / 32;                       // block of the slice
+        const int which = lane & 3;                   // of the block's four threads: d, s_hi, s_lo, s
+        const float val = which == 0 ? dd : which == 1 ? shi : which == 2 ? slo : ss;
+        for (int j = 0; j <= k; j++) {
+            const int pos = s_pos[j];
+            if (pos < 0) continue;
+            uint8_t* rec = ws.act_t + ((size_t)sl * (R / 8) + pos / 8) * kActTileBytes;
+            if (!(lane & 1)) *(uint4*)(rec + act_q_off(pos % 8, el)) = unit;
+            *(float*)(rec + kActOffDx + 256 * which + (bb * 8 + pos % 8) * 4) = val;
         }
     }
 }
@@ -207,7 +217,7 @@ cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace&
     if (norm && c.n >= DP_MIN_TOKENS) return cudaErrorInvalidValue;   // the by-position kernel reads normed rows
     const float* nw = norm ? norm->w : nullptr;
     if (quant) {
-        if (cudaError_t err = launch_after(c.stream, dispatch_q8_kernel, dim3(c.n, 2), dim3(DP_THREADS), 0, h, ws,
+        if (cudaError_t err = launch_after(c.stream, dispatch_q8_kernel, dim3(c.n), dim3(DP_THREADS), 0, h, ws,
                                            c.n, c.k, c.e, c.has_shared, nw))
             return err;
         count_launch();
