@@ -166,19 +166,27 @@ router_logits_tiled_kernel(const float* __restrict__ W, const float* __restrict_
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int br0 = blockIdx.x * RL_BROWS, bt0 = blockIdx.y * RL_BTOKS;
     const int nchunk = e / RL_KC;
-    // every thread copies ten 16-byte pieces of chunk c into stage `c % RL_STAGES`
+    // every thread copies ten 16-byte pieces of chunk c into stage `c % RL_STAGES`: piece j of
+    // the thread lies in row `warp + 8j` of the stage (rows 0-15 router rows, 16-79 token
+    // rows), 16-byte column `lane`; the rows' addresses are worked out once (rows past the
+    // end repeat the last one)
+    constexpr int RL_PIECES = (RL_BROWS + RL_BTOKS) * (RL_KC / 4) / RT_THREADS;   // 10
+    static_assert(RL_KC / 4 == 32 && RT_THREADS == 256, "a warp copies one row of a chunk");
+    const float* rowp[RL_PIECES];
+#pragma unroll
+    for (int j = 0; j < RL_PIECES; j++) {
+        const int r = warp + 8 * j;
+        rowp[j] = (r < RL_BROWS ? W + (size_t)min(br0 + r, n_rows - 1) * e
+                                : h + (size_t)min(bt0 + r - RL_BROWS, n - 1) * e) + lane * 4;
+    }
+    const uint32_t ring_u32 = rt_smem_u32(ring) + (uint32_t)(warp * RL_KC + lane * 4) * 4;
     auto fill = [&](int c) {
-        float* st = ring + (size_t)(c % RL_STAGES) * RL_STAGE_FLOATS;
-        for (int p = threadIdx.x; p < (RL_BROWS + RL_BTOKS) * (RL_KC / 4); p += RT_THREADS) {
-            const int r = p / (RL_KC / 4), q4 = p % (RL_KC / 4);   // rows past the end repeat the last one
-            const float* src = (r < RL_BROWS ? W + (size_t)min(br0 + r, n_rows - 1) * e
-                                             : h + (size_t)min(bt0 + r - RL_BROWS, n - 1) * e) +
-                               (size_t)c * RL_KC + q4 * 4;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
-                             rt_smem_u32(st + (size_t)r * RL_KC + q4 * 4)),
-                         "l"(src)
+        const uint32_t st = ring_u32 + (uint32_t)(c % RL_STAGES) * (RL_STAGE_FLOATS * 4);
+#pragma unroll
+        for (int j = 0; j < RL_PIECES; j++)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(st + j * 8 * RL_KC * 4),
+                         "l"(rowp[j] + (size_t)c * RL_KC)
                          : "memory");
-        }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     for (int c = 0; c < RL_STAGES - 1; c++) {
