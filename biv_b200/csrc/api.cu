@@ -1241,10 +1241,19 @@ int bivmoe_int8_peak(bivmoe_layer* L, double* tops) {
 
 int bivmoe_numerics(const bivmoe_layer* L, char* buf, size_t len) {
     if (!L || !buf || !len) return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "null layer or buffer");
+    // which expert kernels this layer's types get: groups of at most 8 rows (and every group
+    // of types without a tcgen05 kernel) take the warp-level kernels
+    const bool f32act = type_uses_f32_act(L->gate_up.ty);
+    const char* small = f32act ? "f32-fma" : "mma.sync-s8-block-dots";
+    char big[96] = "";
+    if (L->prefill_min > 0)
+        snprintf(big, sizeof big, "+tcgen05-%s-from-%d-rows", L->gate_up.ty == BIVMOE_BF16 ? "f16-two-bf16-terms" : "i8-block-dots",
+                 L->prefill_min);
     snprintf(buf, len,
-             "kind=cuda device=%s sms=%d repack=v%d experts=mma.sync-s8-block-dots/bulk-copy-ring/tiled-weights "
+             "kind=cuda device=%s sms=%d repack=v%d experts=%s/bulk-copy-ring/tiled-weights%s "
              "router=f32-avx2-order combine=ordered-fma types=%d/%d/%d",
-             L->device_name.c_str(), L->sm_count, kRepackVersion, L->gate_up.ty, L->gate_up.ty, L->down.ty);
+             L->device_name.c_str(), L->sm_count, kRepackVersion, small, big, L->gate_up.ty, L->gate_up.ty,
+             L->down.ty);
     return BIVMOE_OK;
 }
 
