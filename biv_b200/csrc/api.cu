@@ -94,6 +94,15 @@ struct bivmoe_layer {
         float* out = nullptr;
         int n = -1, seen = 0;
     } host_graph;
+    // bivmoe_forward_stack, kept by the stack's first layer: the launches of all layers as
+    // one graph, replayed while the same layers, rows and stream come back
+    struct {
+        cudaGraphExec_t exec = nullptr;
+        std::vector<bivmoe_layer*> layers;
+        float* x = nullptr;
+        int n = -1, seen = 0;
+        cudaStream_t stream = nullptr;
+    } stack_graph;
     int32_t* status_host = nullptr;   // page-locked copy of the device status words
     int prefill_min = 0;   // set at create when the tcgen05 kernels support the layer's types
     int prefill_tile = kPrefillTile;
@@ -279,6 +288,7 @@ void bivmoe_destroy(bivmoe_layer* L) {
     DeviceScope on_device(L->device);
     if (L->graph.exec) cudaGraphExecDestroy(L->graph.exec);
     if (L->host_graph.exec) cudaGraphExecDestroy(L->host_graph.exec);
+    if (L->stack_graph.exec) cudaGraphExecDestroy(L->stack_graph.exec);
     if (L->status_host) cudaFreeHost(L->status_host);
     for (void* p : L->ipc_opened) cudaIpcCloseMemHandle(p);
     for (void* p : L->allocs) cudaFree(p);
@@ -1048,10 +1058,33 @@ int bivmoe_forward_host(bivmoe_layer* L, const float* h_host, float* out_host, i
     return n > 0 ? bivmoe_host_wait(L) : BIVMOE_OK;
 }
 
+// the launches of every layer of the stack, in order, on `stream`
+static int stack_enqueue(bivmoe_layer* const* layers, int n_layers, float* x_dev, int n, cudaStream_t stream) {
+    for (int l = 0; l < n_layers; l++) {
+        bivmoe_layer* L = layers[l];
+        std::string* errp = &L->error;
+        DeviceScope on_device(L->device);
+        LaunchCfg c{stream, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh, L->has_shared ? 1 : 0, L->sm_count};
+        int rc;
+        if (router_fuses_norm(n, L->e)) {
+            // the router kernel normalises the rows it stages and publishes the scales; the
+            // dispatch kernel applies them on the fly: the normed rows never reach HBM
+            const RowNorm norm{L->post_norm, L->norm_eps, L->ws.row_scale};
+            rc = forward_impl(L, x_dev, x_dev, n, 1, stream, nullptr, &norm);
+        } else {
+            CU(launch_rms_norm(c, x_dev, L->post_norm, L->norm_eps, L->ws.h_norm));
+            rc = forward_impl(L, L->ws.h_norm, x_dev, n, 1, stream);
+        }
+        if (rc) return rc;
+    }
+    return BIVMOE_OK;
+}
+
 int bivmoe_forward_stack(bivmoe_layer* const* layers, int32_t n_layers, float* x_dev, int32_t n,
                          void* stream) {
     if (!layers || n_layers <= 0 || !layers[0])
         return set_err(nullptr, BIVMOE_ERR_ARGUMENT, "no layers");
+    bool one_device = true;
     for (int l = 0; l < n_layers; l++) {
         bivmoe_layer* L = layers[l];
         std::string* errp = L ? &L->error : nullptr;
@@ -1059,22 +1092,49 @@ int bivmoe_forward_stack(bivmoe_layer* const* layers, int32_t n_layers, float* x
             return set_err(errp, BIVMOE_ERR_ARGUMENT, "layer %d has no post_norm weights", l);
         if (n < 0 || n > L->max_tokens)
             return set_err(errp, BIVMOE_ERR_ARGUMENT, "n = %d outside 0..max_tokens", n);
-        if (n == 0) continue;
-        DeviceScope on_device(L->device);
-        LaunchCfg c{(cudaStream_t)stream, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh,
-                    L->has_shared ? 1 : 0, L->sm_count};
-        int rc;
-        if (router_fuses_norm(n, L->e)) {
-            // the router kernel normalises the rows it stages and publishes the scales; the
-            // dispatch kernel applies them on the fly: the normed rows never reach HBM
-            const RowNorm norm{L->post_norm, L->norm_eps, L->ws.row_scale};
-            rc = forward_impl(L, x_dev, x_dev, n, 1, (cudaStream_t)stream, nullptr, &norm);
-        } else {
-            CU(launch_rms_norm(c, x_dev, L->post_norm, L->norm_eps, L->ws.h_norm));
-            rc = forward_impl(L, L->ws.h_norm, x_dev, n, 1, (cudaStream_t)stream);
-        }
-        if (rc) return rc;
+        one_device = one_device && L->device == layers[0]->device;
     }
+    if (n == 0) return BIVMOE_OK;
+    // The same stack over the same rows again (an engine's decode loop): the launches of all
+    // layers - 7 each - are replayed as one graph from the second identical call on.
+    bivmoe_layer* L0 = layers[0];
+    std::string* errp = &L0->error;
+    cudaStream_t s = (cudaStream_t)stream;
+    auto& G = L0->stack_graph;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    const bool can_graph = L0->use_graph && one_device && s != nullptr && s != cudaStreamLegacy &&
+                           cudaStreamIsCapturing(s, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone;
+    if (!can_graph) return stack_enqueue(layers, n_layers, x_dev, n, s);
+    DeviceScope on_device(L0->device);
+    const bool same = G.x == x_dev && G.n == n && G.stream == s && (int)G.layers.size() == n_layers &&
+                      std::equal(G.layers.begin(), G.layers.end(), layers);
+    if (same && G.exec) {
+        CU(cudaGraphLaunch(G.exec, s));
+        count_launch(L0->launches_per_forward * n_layers);
+        for (int l = 0; l < n_layers; l++) layers[l]->last_n = n;
+        return BIVMOE_OK;
+    }
+    if (!same) {
+        if (G.exec) { cudaGraphExecDestroy(G.exec); G.exec = nullptr; }
+        G.layers.assign(layers, layers + n_layers);
+        G.x = x_dev; G.n = n; G.stream = s; G.seen = 0;
+    }
+    if (++G.seen < 2) return stack_enqueue(layers, n_layers, x_dev, n, s);   // the first call also sets kernel attributes
+    cudaGraph_t graph = nullptr;
+    const uint64_t before = bivmoe_launch_count();
+    CU(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    const int rc = stack_enqueue(layers, n_layers, x_dev, n, s);
+    cudaError_t ce = cudaStreamEndCapture(s, &graph);
+    L0->launches_per_forward = (int)((bivmoe_launch_count() - before) / n_layers);
+    if (!rc && ce == cudaSuccess && graph) ce = cudaGraphInstantiate(&G.exec, graph, 0);
+    if (graph) cudaGraphDestroy(graph);
+    if (rc || ce != cudaSuccess) {
+        G.exec = nullptr;
+        L0->use_graph = false;   // plain launches from here on
+        cudaGetLastError();
+        return rc ? rc : stack_enqueue(layers, n_layers, x_dev, n, s);
+    }
+    CU(cudaGraphLaunch(G.exec, s));
     return BIVMOE_OK;
 }
 

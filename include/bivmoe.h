@@ -171,7 +171,9 @@ BIVMOE_API int bivmoe_set_post_norm(bivmoe_layer* layer, const float* w, float e
 
 /* A run of layers with the residual carried on the device, FFN half of
  * `Model::layer` only (model.rs:788-790): per layer h = rms_norm(x, post_norm),
- * x += moe(h).  `x_dev` [n][n_embd] is updated in place. */
+ * x += moe(h).  `x_dev` [n][n_embd] is updated in place.  Like `bivmoe_forward`, the
+ * call replays its launches - of all layers - as one CUDA graph from the second call with
+ * the same layers, buffer, n and (non-default) stream on. */
 BIVMOE_API int bivmoe_forward_stack(bivmoe_layer* const* layers, int32_t n_layers, float* x_dev, int32_t n,
                          void* stream);
 

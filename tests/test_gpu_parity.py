@@ -251,6 +251,18 @@ def test_stack_matches_oracle():
         MoeStack(layers).forward_(x)
         torch.cuda.synchronize()
         assert rel_err(x.cpu().numpy(), ref) < TOL
+        # the same stack over the same buffer again, on a stream of its own: from the second
+        # identical call on the launches of all layers are one graph replay
+        x0 = torch.from_numpy(wl.h).cuda()
+        stack, st = MoeStack(layers), torch.cuda.Stream()
+        st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(st):
+            for _ in range(4):
+                x.copy_(x0)
+                stack.forward_(x)
+                st.synchronize()
+                assert rel_err(x.cpu().numpy(), ref) < TOL
+        layers[0].status()
     finally:
         for m in layers:
             m.close()
