@@ -230,6 +230,13 @@ def test_no_shared_expert_and_max_tokens_larger_than_n():
     run_case(wl, max_tokens=64)
 
 
+def test_bf16_tensor_core_groups_without_a_shared_expert():
+    # rows gathered by token for routed groups only: no shared group whose positions are
+    # the tokens themselves; a hidden size of 8 K-slices, ragged tiles (300 rows over 8 experts)
+    run_case(W.ep_bf16(n=300, n_embd=512, n_expert=8, k=2, ff=512, ff_sh=0))
+    run_case(W.ep_bf16(n=40, n_embd=512, n_expert=8, k=2, ff=256, ff_sh=0), max_tokens=64)
+
+
 def test_config1_parity_q8_0_full_shape():
     run_case(W.parity_q8_0())
 
