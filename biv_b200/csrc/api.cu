@@ -592,13 +592,13 @@ int bivmoe_ep_route(bivmoe_layer* L, const float* h_dev, int32_t n, float* send_
         return BIVMOE_OK;
     }
     LaunchCfg c{s, n, L->k, L->e, L->n_expert, L->ff, L->ff_sh, L->has_shared ? 1 : 0, L->sm_count};
-    // the sort serves the shared expert's group, which is computed here; its size
-    // decides its kernel
+    // the lists of the shared expert's group, which is computed here; its size decides
+    // its kernel (the routed pairs are sorted by the ranks that own their experts)
     c.prefill_min = L->prefill_min;
     c.prefill_tile = L->prefill_tile;
     CU(launch_router(c, L->router, h_dev, L->ws));
     CU(launch_route_topk(c, L->ws));
-    if (L->has_shared) CU(launch_sort(c, L->ws));
+    if (L->has_shared) CU(launch_shared_lists(c, L->ws));
     CU(launch_ep_gather(c, h_dev, L->ws, L->ep_world, L->n_local, L->ep_slot, L->ep_counts,
                         L->ep_rank_ids, L->ep_rank_pos, send_rows_dev, send_tags_dev, send_counts_dev));
     return BIVMOE_OK;
@@ -774,7 +774,7 @@ int bivmoe_ep_peer_dispatch(bivmoe_layer* L, const float* h_dev, int32_t n, void
     if (n > 0) {
         CU(launch_router(c, L->router, h_dev, L->ws));
         CU(launch_route_topk(c, L->ws));
-        if (L->has_shared) CU(launch_sort(c, L->ws));
+        if (L->has_shared) CU(launch_shared_lists(c, L->ws));
     }
     CU(launch_ep_peer_scatter(c, h_dev, L->ws, L->ep_world, L->ep_rank, L->n_local, L->ep_slot, L->ep_counts,
                               L->ep_rank_ids, L->ep_rank_pos, L->peers, L->peer_lay));

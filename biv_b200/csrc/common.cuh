@@ -207,6 +207,7 @@ cudaError_t launch_router(const LaunchCfg& c, const float* router_dev /*[n_exper
 bool router_fuses_norm(int n, int e);
 cudaError_t launch_route_topk(const LaunchCfg& c, const Workspace& ws);
 cudaError_t launch_sort(const LaunchCfg& c, const Workspace& ws);
+cudaError_t launch_shared_lists(const LaunchCfg& c, const Workspace& ws);
 cudaError_t launch_dispatch(const LaunchCfg& c, const float* h, const Workspace& ws, bool quant,
                             bool f32, const RowNorm* norm = nullptr);
 cudaError_t launch_experts(const LaunchCfg& c, const DevTiles& gate_up, const DevTiles& down,

@@ -592,6 +592,42 @@ sort_kernel(Workspace ws, int n, int k, int n_expert, int has_shared, int prefil
     }
 }
 
+// The lists of the shared expert's group alone (its positions are the tokens, in order):
+// what sort_kernel writes for that group, for a rank of an expert-parallel layer, whose
+// routed pairs are sorted where their experts live.
+__global__ void __launch_bounds__(SORT_THREADS)
+shared_lists_kernel(Workspace ws, int n, int n_expert, int prefill_min, int ptile) {
+    pdl_enter();
+    const bool big_sh = prefill_min > 0 && n >= prefill_min;
+    const int p_sh = (n + SORT_TILE - 1) / SORT_TILE * SORT_TILE;
+    const int t_sh = big_sh ? 0 : p_sh / SORT_TILE;
+    const int pt_sh = big_sh ? (n + ptile - 1) / ptile : 0;
+    for (int j = threadIdx.x; j < t_sh; j += blockDim.x)
+        ws.tile_desc[j] = make_int4(n_expert, j * SORT_TILE, min(SORT_TILE, n - j * SORT_TILE), 0);
+    for (int j = threadIdx.x; j < pt_sh; j += blockDim.x) {
+        ws.ptile_group[j] = 0;
+        ws.ptile_t0[j] = j * ptile;
+    }
+    if (threadIdx.x == 0) {
+        ws.grp_expert[0] = n_expert;
+        ws.grp_start[0] = 0;
+        ws.grp_count[0] = n;
+        ws.offsets[n_expert] = p_sh;
+        *ws.n_groups = 1;
+        ws.n_tiles[0] = t_sh;
+        ws.n_tiles[1] = t_sh;
+        ws.n_ptiles[0] = pt_sh;
+        ws.n_ptiles[1] = pt_sh;
+        for (int i = 0; i < 8; i++) ws.work_ctr[i] = 0;
+    }
+}
+
+cudaError_t launch_shared_lists(const LaunchCfg& c, const Workspace& ws) {
+    count_launch();
+    return launch_after(c.stream, shared_lists_kernel, dim3(1), dim3(SORT_THREADS), 0, ws, c.n, c.n_expert,
+                        c.prefill_min, c.prefill_tile);
+}
+
 cudaError_t launch_sort(const LaunchCfg& c, const Workspace& ws) {
     const int nblk = (c.n + SORT_TOKENS - 1) / SORT_TOKENS;
     size_t smem = (((size_t)SORT_TOKENS * c.k * 2 + 15) & ~(size_t)15) + (size_t)c.n_expert * 4 +
