@@ -1225,9 +1225,38 @@ int bivmoe_tap(bivmoe_layer* L, int32_t which, void* dst, size_t bytes) {
             std::vector<int32_t> pos(P);
             CU(cudaMemcpy(tmp.data(), w.mid, tmp.size() * 4, cudaMemcpyDeviceToHost));
             CU(cudaMemcpy(pos.data(), w.pos_of, P * 4, cudaMemcpyDeviceToHost));
-            for (size_t p = 0; p < P; p++)
-                for (size_t sl = 0; sl < ffw / 64; sl++)
-                    memcpy((float*)dst + p * ffw + sl * 64, tmp.data() + (sl * R + pos[p]) * 64, 256);
+            // pairs of groups the BF16 tensor-core kernels took have no f32 mid row: theirs is
+            // the sum of the two bf16 terms the down product reads (mid to 2^-17)
+            std::vector<uint8_t> terms;
+            std::vector<int32_t> ids, cnt;
+            const bool has_terms = w.mid_b && L->prefill_min > 0;
+            if (has_terms) {
+                terms.resize((mid / 64) * (R / 8) * (size_t)kActBRec);
+                ids.resize(P);
+                cnt.resize(ne);
+                CU(cudaMemcpy(terms.data(), w.mid_b, terms.size(), cudaMemcpyDeviceToHost));
+                CU(cudaMemcpy(ids.data(), w.ids, P * 4, cudaMemcpyDeviceToHost));
+                CU(cudaMemcpy(cnt.data(), w.counts, ne * 4, cudaMemcpyDeviceToHost));
+            }
+            auto bf = [](uint16_t v) { uint32_t u = (uint32_t)v << 16; float f; memcpy(&f, &u, 4); return f; };
+            for (size_t p = 0; p < P; p++) {
+                float* o = (float*)dst + p * ffw;
+                if (pos[p] < 0) { memset(o, 0, ffw * 4); continue; }
+                const bool big = has_terms && ids[p] >= 0 && cnt[ids[p]] >= L->prefill_min;
+                for (size_t sl = 0; sl < ffw / 64; sl++) {
+                    if (!big) {
+                        memcpy(o + sl * 64, tmp.data() + (sl * R + pos[p]) * 64, 256);
+                        continue;
+                    }
+                    const uint8_t* rec = terms.data() + (sl * (R / 8) + pos[p] / 8) * (size_t)kActBRec;
+                    for (int i = 0; i < 64; i++) {
+                        uint16_t hi, lo;
+                        memcpy(&hi, rec + act_b_off(pos[p] % 8, i), 2);
+                        memcpy(&lo, rec + kActBLo + act_b_off(pos[p] % 8, i), 2);
+                        o[sl * 64 + i] = bf(hi) + bf(lo);
+                    }
+                }
+            }
             return BIVMOE_OK;
         }
         case BIVMOE_TAP_PAIR_OUT: {

@@ -74,7 +74,7 @@ struct Bf16Args {
     const int32_t* order;  // GATEUP: order[pos] / k is the token at a routed group's position
     int k;
     int act_rows;          // R
-    float* out;            // GATEUP: mid f32 slice-major; DOWN: pair_out [R][rows]
+    float* out;            // DOWN: pair_out [R][rows]
     uint8_t* out_b;        // GATEUP: bf16 hi/lo records of mid
     const int32_t* grp_expert;
     const int32_t* grp_start;
@@ -506,9 +506,8 @@ experts_prefill_bf16_gateup_kernel(const Bf16Args A) {
                     y[i] = (gt * __fdividef(1.0f, 1.0f + __expf(-gt))) * __int_as_float(u[i]);
                 }
                 const int chunk = it.chunk + ch;   // rows 64 chunk + 16cg .. of mid: K-slice `chunk` of the down product
-                float4* dst = (float4*)(A.out + ((size_t)chunk * A.act_rows + pos) * 64 + 16 * cg);
-#pragma unroll
-                for (int i = 0; i < 4; i++) dst[i] = make_float4(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]);
+                // (no f32 copy of mid for these groups: the down product reads the two terms,
+                //  and the tap of mid adds them up)
                 uint8_t* rec = A.out_b + ((size_t)chunk * (A.act_rows / 8) + pos / 8) * kActBRec +
                                act_b_off((int)(pos % 8), 16 * cg);
 #pragma unroll
