@@ -22,8 +22,9 @@ FLIP_RATE = 2e-4
 
 
 def log_stats(case, **figures):
-    """Appends the observed flip counts and errors of a case to gpurun_out/parity_stats.jsonl
-    (when that folder exists) and prints them: the figures the tolerances above are set by."""
+    """Prints the observed flip counts and errors of a case and appends them to
+    parity_stats.jsonl in the run's output folder (when that folder exists): the figures the
+    tolerances above are set by."""
     import json
     import os
     line = json.dumps({"case": case, **figures})
